@@ -1,0 +1,47 @@
+// Host-compiled harness around the device SAM routines (sam_core.cuh), used
+// only by the CPU test-suite to check the kernel's index arithmetic against
+// the oracle without a GPU.  It is not part of the shipped library.
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "../../ullis_b200/csrc/sam_core.cuh"
+
+using namespace ullis::sam;
+
+template <typename Ix>
+static int run_batch(int algo, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw, size_t n_streams,
+                     uint32_t T, uint32_t* out, unsigned long long* visits, unsigned long long* chain) {
+    const size_t wps = (T + 31) / 32;
+    const size_t bytes = algo == 0 ? EagerLayout<Ix>(T).total : EulerLayout<Ix>(T).total;
+    std::vector<uint8_t> scratch(bytes + 64);
+    uint8_t* base = scratch.data();
+    base += (64 - reinterpret_cast<uintptr_t>(base) % 64) % 64;
+    Counters cnt{0, 0};
+    for (size_t s = 0; s < n_streams; ++s) {
+        std::memset(base, 0xA5, bytes);  // the routines must not rely on zeroed scratch
+        if (algo == 0)
+            run_eager<Ix>(base, qw + s * wps, kw + s * wps, vw + s * wps, out + s * wps, T, &cnt);
+        else
+            run_euler<Ix>(base, qw + s * wps, kw + s * wps, vw + s * wps, out + s * wps, T, &cnt);
+    }
+    if (visits) *visits = cnt.node_visits;
+    if (chain) *chain = cnt.chain_steps;
+    return 0;
+}
+
+extern "C" int sam_host_batch(int algo, int ix_bits, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw,
+                              size_t n_streams, uint32_t T, uint32_t* out, unsigned long long* visits,
+                              unsigned long long* chain) {
+    if (ix_bits == 16) {
+        if (node_capacity(T) > 0xFFFFu) return 1;
+        return run_batch<uint16_t>(algo, qw, kw, vw, n_streams, T, out, visits, chain);
+    }
+    return run_batch<uint32_t>(algo, qw, kw, vw, n_streams, T, out, visits, chain);
+}
+
+extern "C" size_t sam_host_scratch_bytes(int algo, int ix_bits, uint32_t T) {
+    if (ix_bits == 16) return algo == 0 ? EagerLayout<uint16_t>(T).total : EulerLayout<uint16_t>(T).total;
+    return algo == 0 ? EagerLayout<uint32_t>(T).total : EulerLayout<uint32_t>(T).total;
+}

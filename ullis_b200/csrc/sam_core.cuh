@@ -1,0 +1,339 @@
+// 1-bit ROSA suffix-automaton match for ONE (sequence, channel) stream.
+//
+// Semantics: idx[t] for t = 0..T-1 equals T successive calls of the
+// reference's RosaSam::push(q[t], k[t], v[t]) (src/rosa.rs:100-176), i.e.
+// rosa_qkv_ref (src/rosa.rs:180-193).  Two implementations live here:
+//
+//  * run_eager  - statement-by-statement form of push(), including the loop
+//    that stamps `last = i` along the whole suffix-link chain of the newest
+//    state (src/rosa.rs:168-173).  That loop is O(chain length) per step and
+//    O(T^2) per stream on constant / periodic bit streams.
+//
+//  * run_euler  - same results in O(T log T) regardless of the input:
+//      pass 1  builds the automaton and tracks the query state exactly as
+//              push() does, but never touches `last`; it records the state
+//              v_t each query would read `last` from, and the state j_i that
+//              step i creates.  (v_t does not depend on any `last` value:
+//              every non-root state is stamped in the step that creates it,
+//              so the reference's `last < 0` skip only ever removes the root.)
+//      tour    `last[v]` at query time t is the largest i < t whose new state
+//              j_i lies in the suffix-link subtree of v.  The link tree only
+//              grows by new leaves and by clones subdividing an edge, so
+//              ancestor relations between existing states never change and
+//              the FINAL tree can be used for every t.  A preorder walk gives
+//              each state the half-open rank range [lo, hi) of the stamped
+//              (non-clone, non-root) states below it.
+//      pass 2  replays time: a max segment tree over ranks holds i+1 for
+//              every j_i with i < t; the query is a range max over [lo, hi)
+//              of v_t, the answer indexes the v history.
+//
+// The code is plain C++ over caller-provided memory so that the same source
+// runs inside the CUDA kernels and in a host-compiled test harness.
+#pragma once
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define SAM_HD __host__ __device__ __forceinline__
+#else
+#define SAM_HD inline
+#endif
+
+namespace ullis {
+namespace sam {
+
+template <typename Ix>
+struct Nil;
+template <>
+struct Nil<uint16_t> {
+    static constexpr uint32_t value = 0xFFFFu;
+};
+template <>
+struct Nil<uint32_t> {
+    static constexpr uint32_t value = 0xFFFFFFFFu;
+};
+
+// One automaton state; a visit is a single 4*sizeof(Ix)-byte access.
+template <typename Ix>
+struct alignas(4 * sizeof(Ix)) Node {
+    Ix t0, t1, fail, maxlen;
+};
+
+SAM_HD uint32_t node_capacity(uint32_t T) { return 2u * T + 2u; }
+SAM_HD uint32_t pow2_at_least(uint32_t n) {
+    uint32_t p = 1;
+    while (p < n) p <<= 1;
+    return p;
+}
+SAM_HD size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Byte layout of one stream's scratch block for run_euler.
+template <typename Ix>
+struct EulerLayout {
+    size_t nodes, vq, jid, head, next, lo, hi, clone_bits, total;
+    SAM_HD explicit EulerLayout(uint32_t T) {
+        const size_t cap = node_capacity(T);
+        size_t off = 0;
+        nodes = off; off = align_up(off + cap * sizeof(Node<Ix>), 16);
+        vq = off;    off = align_up(off + (size_t)T * sizeof(Ix), 16);
+        jid = off;   off = align_up(off + (size_t)T * sizeof(Ix), 16);
+        // head/next are dead once the tour is done; the segment tree (2*L
+        // entries, L = pow2 >= T, so at most 4T <= 2*cap) reuses their space.
+        head = off;  off = align_up(off + cap * sizeof(Ix), 16);
+        next = off;  off = align_up(off + cap * sizeof(Ix), 16);
+        lo = off;    off = align_up(off + cap * sizeof(Ix), 16);
+        hi = off;    off = align_up(off + cap * sizeof(Ix), 16);
+        clone_bits = off; off = align_up(off + ((cap + 31) / 32) * 4, 16);
+        total = align_up(off, 128);
+    }
+};
+
+// Byte layout of one stream's scratch block for run_eager.
+template <typename Ix>
+struct EagerLayout {
+    size_t nodes, last, total;
+    SAM_HD explicit EagerLayout(uint32_t T) {
+        const size_t cap = node_capacity(T);
+        size_t off = 0;
+        nodes = off; off = align_up(off + cap * sizeof(Node<Ix>), 16);
+        last = off;  off = align_up(off + cap * sizeof(Ix), 16);
+        total = align_up(off, 128);
+    }
+};
+
+SAM_HD uint32_t stream_bit(const uint32_t* words, uint32_t t) { return (words[t >> 5] >> (t & 31)) & 1u; }
+
+// Work counters (optional instrumentation; pass nullptr to skip).
+struct Counters {
+    unsigned long long node_visits;   // automaton state reads in pass 1 / eager
+    unsigned long long chain_steps;   // eager: iterations of the last-stamping loop
+};
+
+// ------------------------------------------------------------------ shared step
+//
+// Query + extend of one time step, without any `last` bookkeeping.
+// Returns the state the reference would read `last` from (NIL if none), and
+// reports the state created for this step through *j_out / the clone through
+// *b_out (NIL when no clone was made).
+template <typename Ix>
+struct Walker {
+    static constexpr uint32_t NIL = Nil<Ix>::value;
+    Node<Ix>* N;
+    uint32_t u, g, w;
+    int32_t h;
+    uint32_t gmax;  // maxlen of g
+
+    SAM_HD void init(Node<Ix>* nodes) {
+        N = nodes;
+        Node<Ix> root;
+        root.t0 = (Ix)NIL; root.t1 = (Ix)NIL; root.fail = (Ix)NIL; root.maxlen = 0;
+        N[0] = root;
+        u = 1; g = 0; w = 0; h = 0; gmax = 0;
+    }
+
+    // src/rosa.rs:104-128 (query half of push)
+    SAM_HD uint32_t query(uint32_t qb, unsigned long long* visits) {
+        uint32_t p = w;
+        int32_t x = h;
+        uint32_t c = NIL;
+        while (p != NIL) {
+            Node<Ix> n = N[p];
+            if (visits) ++*visits;
+            c = qb ? n.t1 : n.t0;
+            if (c != NIL) break;
+            if (x > (int32_t)n.maxlen) x = (int32_t)n.maxlen;
+            p = n.fail;
+        }
+        uint32_t v;
+        if (p == NIL) {
+            p = 0; x = 0; v = NIL;
+        } else {
+            p = c; x += 1;
+            v = p;
+            Node<Ix> nv = N[v];
+            if (visits) ++*visits;
+            while (nv.fail != NIL) {
+                Node<Ix> nf = N[nv.fail];
+                if (visits) ++*visits;
+                if ((int32_t)nf.maxlen >= x) { v = nv.fail; nv = nf; } else break;
+            }
+            if (nv.maxlen == 0) v = NIL;  // only the root has maxlen 0; its fail is NIL
+        }
+        w = p; h = x;
+        return v;
+    }
+
+    // src/rosa.rs:139-167 (extend half of push). The new state's `last`
+    // handling is left to the caller.
+    SAM_HD void extend(uint32_t kb, uint32_t* j_out, uint32_t* b_out, uint32_t* d_out,
+                       unsigned long long* visits) {
+        const uint32_t j = u++;
+        Node<Ix> nj;
+        nj.t0 = (Ix)NIL; nj.t1 = (Ix)NIL; nj.fail = 0; nj.maxlen = (Ix)(gmax + 1);
+        uint32_t p = g, d = NIL, b = NIL;
+        Node<Ix> n;
+        n.t0 = n.t1 = n.fail = (Ix)NIL; n.maxlen = 0;
+        while (p != NIL) {
+            n = N[p];
+            if (visits) ++*visits;
+            d = kb ? n.t1 : n.t0;
+            if (d != NIL) break;
+            if (kb) N[p].t1 = (Ix)j; else N[p].t0 = (Ix)j;
+            p = n.fail;
+        }
+        if (p == NIL) {
+            nj.fail = 0;
+            d = NIL;
+        } else {
+            Node<Ix> nd = N[d];
+            if (visits) ++*visits;
+            if ((uint32_t)n.maxlen + 1u == (uint32_t)nd.maxlen) {
+                nj.fail = (Ix)d;
+                d = NIL;  // no clone
+            } else {
+                b = u++;
+                Node<Ix> nb = nd;            // the clone copies every field of d
+                nb.maxlen = (Ix)(n.maxlen + 1u);
+                N[b] = nb;
+                N[d].fail = (Ix)b;
+                nj.fail = (Ix)b;
+                while (p != NIL) {
+                    Node<Ix> n2 = N[p];
+                    if (visits) ++*visits;
+                    if ((kb ? n2.t1 : n2.t0) != d) break;
+                    if (kb) N[p].t1 = (Ix)b; else N[p].t0 = (Ix)b;
+                    p = n2.fail;
+                }
+            }
+        }
+        N[j] = nj;
+        g = j;
+        gmax = gmax + 1;
+        *j_out = j; *b_out = b; *d_out = d;
+    }
+};
+
+// ------------------------------------------------------------------ eager
+
+// scratch: EagerLayout<Ix>(T).total bytes.  qw/kw/vw: this stream's bits, bit t
+// at word t/32, bit t%32.  out: idx bits in the same layout (whole words are
+// written, tail bits zero).
+template <typename Ix>
+SAM_HD void run_eager(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw,
+                      uint32_t* out, uint32_t T, Counters* cnt) {
+    constexpr uint32_t NIL = Nil<Ix>::value;
+    EagerLayout<Ix> L(T);
+    Node<Ix>* N = reinterpret_cast<Node<Ix>*>(scratch + L.nodes);
+    Ix* last = reinterpret_cast<Ix*>(scratch + L.last);  // stores last+1, 0 = never
+    Walker<Ix> wk;
+    wk.init(N);
+    last[0] = 0;
+    uint32_t acc = 0;
+    unsigned long long* visits = cnt ? &cnt->node_visits : nullptr;
+    for (uint32_t i = 0; i < T; ++i) {
+        const uint32_t qb = stream_bit(qw, i), kb = stream_bit(kw, i);
+        const uint32_t v = wk.query(qb, visits);
+        uint32_t bit = 0;
+        if (v != NIL) {
+            const uint32_t pos = last[v];  // == last + 1 >= 1 for any non-root state
+            bit = stream_bit(vw, pos);
+        }
+        acc |= bit << (i & 31);
+        if ((i & 31) == 31 || i + 1 == T) { out[i >> 5] = acc; acc = 0; }
+        uint32_t j, b, d;
+        wk.extend(kb, &j, &b, &d, visits);
+        if (b != NIL) last[b] = last[d];
+        last[j] = 0;
+        // src/rosa.rs:168-173: stamp the whole suffix-link chain of j
+        uint32_t c = j;
+        while (c != NIL && (uint32_t)last[c] < i + 1u) {
+            last[c] = (Ix)(i + 1u);
+            c = N[c].fail;
+            if (cnt) ++cnt->chain_steps;
+        }
+    }
+}
+
+// ------------------------------------------------------------------ euler
+
+template <typename Ix>
+SAM_HD void run_euler(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw,
+                      uint32_t* out, uint32_t T, Counters* cnt) {
+    constexpr uint32_t NIL = Nil<Ix>::value;
+    EulerLayout<Ix> L(T);
+    Node<Ix>* N = reinterpret_cast<Node<Ix>*>(scratch + L.nodes);
+    Ix* vq = reinterpret_cast<Ix*>(scratch + L.vq);
+    Ix* jid = reinterpret_cast<Ix*>(scratch + L.jid);
+    Ix* head = reinterpret_cast<Ix*>(scratch + L.head);
+    Ix* next = reinterpret_cast<Ix*>(scratch + L.next);
+    Ix* lo = reinterpret_cast<Ix*>(scratch + L.lo);
+    Ix* hi = reinterpret_cast<Ix*>(scratch + L.hi);
+    uint32_t* clone_bits = reinterpret_cast<uint32_t*>(scratch + L.clone_bits);
+    unsigned long long* visits = cnt ? &cnt->node_visits : nullptr;
+
+    // ---- pass 1: automaton + query states
+    const uint32_t cap = node_capacity(T);
+    for (uint32_t wd = 0; wd < (cap + 31) / 32; ++wd) clone_bits[wd] = 0;
+    Walker<Ix> wk;
+    wk.init(N);
+    for (uint32_t i = 0; i < T; ++i) {
+        const uint32_t qb = stream_bit(qw, i), kb = stream_bit(kw, i);
+        vq[i] = (Ix)wk.query(qb, visits);
+        uint32_t j, b, d;
+        wk.extend(kb, &j, &b, &d, visits);
+        jid[i] = (Ix)j;
+        if (b != NIL) clone_bits[b >> 5] |= 1u << (b & 31);
+    }
+    const uint32_t n = wk.u;
+
+    // ---- tour: children lists, then preorder ranks of the stamped states
+    for (uint32_t v = 0; v < n; ++v) head[v] = (Ix)NIL;
+    for (uint32_t v = 1; v < n; ++v) {
+        const uint32_t f = N[v].fail;
+        next[v] = head[f];
+        head[f] = (Ix)v;
+    }
+    {
+        uint32_t r = 0, v = 0;
+        bool entering = true;
+        for (;;) {
+            if (entering) {
+                lo[v] = (Ix)r;
+                if (v != 0 && !((clone_bits[v >> 5] >> (v & 31)) & 1u)) ++r;
+                const uint32_t c = head[v];
+                if (c != NIL) { v = c; continue; }
+                entering = false;
+            }
+            hi[v] = (Ix)r;
+            if (v == 0) break;
+            const uint32_t s = next[v];
+            if (s != NIL) { v = s; entering = true; } else { v = N[v].fail; }
+        }
+    }
+
+    // ---- pass 2: replay time over a max segment tree keyed by rank
+    const uint32_t Lp = pow2_at_least(T);
+    Ix* seg = head;  // reuse (head/next are contiguous and large enough)
+    for (uint32_t k = 0; k < 2 * Lp; ++k) seg[k] = 0;
+    uint32_t acc = 0;
+    for (uint32_t t = 0; t < T; ++t) {
+        const uint32_t v = vq[t];
+        uint32_t bit = 0;
+        if (v != NIL) {
+            uint32_t l = (uint32_t)lo[v] + Lp, r = (uint32_t)hi[v] + Lp, m = 0;
+            while (l < r) {
+                if (l & 1u) { const uint32_t s = seg[l++]; m = s > m ? s : m; }
+                if (r & 1u) { const uint32_t s = seg[--r]; m = s > m ? s : m; }
+                l >>= 1; r >>= 1;
+            }
+            // m = last + 1 >= 1: every state that exists at time t has a stamped
+            // descendant (itself, or the state whose creation cloned it).
+            bit = m ? stream_bit(vw, m) : 0u;
+        }
+        acc |= bit << (t & 31);
+        if ((t & 31) == 31 || t + 1 == T) { out[t >> 5] = acc; acc = 0; }
+        for (uint32_t p = (uint32_t)lo[jid[t]] + Lp; p >= 1; p >>= 1) seg[p] = (Ix)(t + 1u);
+    }
+}
+
+}  // namespace sam
+}  // namespace ullis
