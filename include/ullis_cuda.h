@@ -1,0 +1,224 @@
+/*
+ * ullis_cuda.h - C ABI of the B200 (sm_100a) `cuda` backend for the Heron
+ * forward + next-token cross-entropy path of Ullis.
+ *
+ * This is the drop-in boundary beside the reference's Metal backend: the
+ * entry points are what a `src/cuda.rs` sitting next to `src/metal.rs` binds
+ * over FFI.  Conventions shared by every function:
+ *
+ *  - plain pointers and sizes only; FP16 parameters cross as raw IEEE
+ *    binary16 bit patterns (`uint16_t`), packed +/-1 weights as `uint32_t`
+ *    words in the checkpoint's order (row-major [out,in], bit (o*in+i) of an
+ *    LSB-first word stream, 1 => +1, 0 => -1; reference src/model.rs:146-148,
+ *    2267-2268);
+ *  - op-level calls take HOST pointers for inputs and caller-allocated HOST
+ *    outputs, are synchronous, and mirror the `MetalRuntime` method of the
+ *    same name (reference src/metal.rs, cited per function);
+ *  - every call returns an `int32_t` status (0 = ok); the message of the last
+ *    failure is available from ullis_cuda_last_error();
+ *  - a runtime handle is bound to one device and one host thread at a time;
+ *  - there is no CPU fallback: without a CUDA device runtime creation fails.
+ */
+#ifndef ULLIS_CUDA_H
+#define ULLIS_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define ULLIS_CUDA_API __attribute__((visibility("default")))
+#else
+#define ULLIS_CUDA_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ullis_cuda_runtime ullis_cuda_runtime;
+typedef struct ullis_cuda_model ullis_cuda_model;
+
+enum {
+    ULLIS_CUDA_OK = 0,
+    ULLIS_CUDA_ERR_SHAPE = 1,        /* dimension / length mismatch (reference: bail!("... mismatch")) */
+    ULLIS_CUDA_ERR_CHECKPOINT = 2,   /* unparsable, v1, or shape-inconsistent checkpoint */
+    ULLIS_CUDA_ERR_CUDA = 3,         /* CUDA runtime error (reference: command buffer error, src/metal.rs:736-738) */
+    ULLIS_CUDA_ERR_DEVICE_CHECK = 4, /* a kernel's own bounds / progress check failed */
+    ULLIS_CUDA_ERR_NCCL = 5,
+    ULLIS_CUDA_ERR_TIMEOUT = 6,
+    ULLIS_CUDA_ERR_ARG = 7,          /* null handle / pointer, unknown option */
+    ULLIS_CUDA_ERR_TOKEN = 8,        /* token or target id >= vocabulary (src/model.rs:2662-2664) */
+    ULLIS_CUDA_ERR_NOMEM = 9
+};
+
+/* Arithmetic mode of the linears / LayerNorm.
+ * FAST  : tensor-core (tcgen05) GEMMs, warp-shuffle LayerNorm; results within
+ *         the stated tolerances of the reference CPU backend.
+ * EXACT : f32 accumulation in the reference's summation order on CUDA cores;
+ *         every +,-,*,/,sqrt result is bit-identical to the reference CPU
+ *         backend (validation mode, much slower). */
+enum { ULLIS_CUDA_MODE_FAST = 0, ULLIS_CUDA_MODE_EXACT = 1 };
+
+/* Suffix-automaton schedule. Both give identical idx.
+ * EULER : O(T log T) per stream for any input (default).
+ * EAGER : the reference's per-step chain stamping, O(T^2) on constant streams. */
+enum { ULLIS_CUDA_SAM_EULER = 0, ULLIS_CUDA_SAM_EAGER = 1 };
+
+/* Which per-layer intermediate ullis_cuda_model_tap returns (all row-major
+ * [B*T, C] unless noted; f32 = float, u8 = one byte per element). */
+enum {
+    ULLIS_CUDA_TAP_BLOCK_IN = 0,   /* f32 residual stream entering the layer (after ln0 on layer 0) */
+    ULLIS_CUDA_TAP_LN3_OUT = 1,    /* f32 */
+    ULLIS_CUDA_TAP_Q_BITS = 2,     /* u8 0/1 */
+    ULLIS_CUDA_TAP_K_BITS = 3,     /* u8 0/1 */
+    ULLIS_CUDA_TAP_V_BITS = 4,     /* u8 0/1 */
+    ULLIS_CUDA_TAP_IDX = 5,        /* u8 0/1 */
+    ULLIS_CUDA_TAP_AFTER_ROSA = 6, /* f32 residual stream after the ROSA branch */
+    ULLIS_CUDA_TAP_BLOCK_OUT = 7,  /* f32 residual stream leaving the layer */
+    ULLIS_CUDA_TAP_HIDDEN = 8      /* f32 ln_out output (layer argument ignored) */
+};
+
+/* ---------------------------------------------------------------- lifecycle
+ * Replaces MetalRuntime::new (src/metal.rs:466) and the `--backend` runtime
+ * construction in train() (src/main.rs:650-678). */
+ULLIS_CUDA_API int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out);
+ULLIS_CUDA_API void ullis_cuda_runtime_destroy(ullis_cuda_runtime* rt);
+/* Message of the last failed call on `rt` (or of the last failed
+ * ullis_cuda_runtime_create when rt is NULL). Never NULL. */
+ULLIS_CUDA_API const char* ullis_cuda_last_error(const ullis_cuda_runtime* rt);
+ULLIS_CUDA_API int32_t ullis_cuda_runtime_set_mode(ullis_cuda_runtime* rt, int32_t mode);
+ULLIS_CUDA_API int32_t ullis_cuda_runtime_set_sam(ullis_cuda_runtime* rt, int32_t sam_algo);
+/* MetalRuntime::synchronize (src/metal.rs:598). */
+ULLIS_CUDA_API int32_t ullis_cuda_runtime_synchronize(ullis_cuda_runtime* rt);
+/* The CUDA stream (cudaStream_t) every kernel of this runtime is launched on. */
+ULLIS_CUDA_API void* ullis_cuda_runtime_stream(ullis_cuda_runtime* rt);
+/* Number of this library's kernels launched through `rt` so far. */
+ULLIS_CUDA_API uint64_t ullis_cuda_runtime_launch_count(const ullis_cuda_runtime* rt);
+/* Compute capability check: 1 when the device is sm_100 class. */
+ULLIS_CUDA_API int32_t ullis_cuda_runtime_is_sm100(const ullis_cuda_runtime* rt);
+
+/* -------------------------------------------------------------------- model
+ * Device-resident whole-model path.  `bytes` is a v2 checkpoint.safetensors
+ * exactly as ModelCheckpoint::to_safetensors_bytes writes it
+ * (src/model.rs:3426-3468); loading follows from_safetensors_bytes /
+ * validate_checkpoint_shapes / heron_from_checkpoint (src/model.rs:3470-3553,
+ * 4402-4456, 4258-4309): format_version must be 2, a missing head bias loads
+ * as zeros, train-carry tensors are ignored. */
+ULLIS_CUDA_API int32_t ullis_cuda_model_load_safetensors(ullis_cuda_runtime* rt, const uint8_t* bytes, size_t len,
+                                          ullis_cuda_model** out);
+ULLIS_CUDA_API void ullis_cuda_model_destroy(ullis_cuda_model* model);
+/* d_model, n_layers, vocab_size, context_len, batch_size, dim_ffn (resolved). */
+ULLIS_CUDA_API int32_t ullis_cuda_model_dims(const ullis_cuda_model* model, size_t dims[6]);
+
+/* Forward + next-token CE: UllisHeron::hidden (src/model.rs:2644-2683) followed
+ * by the CE forward of apply_head_ce (src/model.rs:3205-3228, 3253-3257) with
+ * the valid-row rule of causal_ce_row_valid (src/model.rs:27-39), horizon 1.
+ * tokens, labels: [batch*time] host; ignore_id = UINT32_MAX supervises every
+ * in-range target.  Outputs (each nullable): mean_loss = loss_sum / n_valid
+ * (0 when n_valid is 0), loss_sum, n_valid, row_loss [batch*time] (0 on
+ * invalid rows).  Rejects batch > config.batch_size, time > context_len and
+ * ids >= vocab like the reference. */
+ULLIS_CUDA_API int32_t ullis_cuda_model_forward_ce(ullis_cuda_model* model, const uint32_t* tokens, const uint32_t* labels,
+                                    uint32_t ignore_id, size_t batch, size_t time, float* mean_loss,
+                                    double* loss_sum, uint64_t* n_valid, float* row_loss);
+/* The same step split for device-resident timing: copy ids in, enqueue every
+ * kernel on the runtime stream without synchronising, read the result. */
+ULLIS_CUDA_API int32_t ullis_cuda_model_upload_tokens(ullis_cuda_model* model, const uint32_t* tokens, const uint32_t* labels,
+                                       size_t batch, size_t time);
+ULLIS_CUDA_API int32_t ullis_cuda_model_enqueue_forward_ce(ullis_cuda_model* model, uint32_t ignore_id, size_t batch,
+                                            size_t time);
+ULLIS_CUDA_API int32_t ullis_cuda_model_read_loss(ullis_cuda_model* model, float* mean_loss, double* loss_sum,
+                                   uint64_t* n_valid, float* row_loss, size_t rows);
+
+/* UllisHeron::logits (src/model.rs:2685-2688): logits [batch*time*vocab] host. */
+ULLIS_CUDA_API int32_t ullis_cuda_model_logits(ullis_cuda_model* model, const uint32_t* tokens, size_t batch, size_t time,
+                                float* logits);
+/* UllisHeron::hidden (src/model.rs:2644-2683): hidden [batch*time*d_model] host. */
+ULLIS_CUDA_API int32_t ullis_cuda_model_hidden(ullis_cuda_model* model, const uint32_t* tokens, size_t batch, size_t time,
+                                float* hidden);
+/* Keep per-layer intermediates of the next forward (costs memory; for parity
+ * tests) and read one of them back. `bytes` must equal the tap's size. */
+ULLIS_CUDA_API int32_t ullis_cuda_model_set_taps(ullis_cuda_model* model, int32_t enabled);
+ULLIS_CUDA_API int32_t ullis_cuda_model_tap(ullis_cuda_model* model, int32_t layer, int32_t which, void* out, size_t bytes);
+/* Milliseconds of the last enqueue_forward_ce spent in each phase, measured
+ * with CUDA events when profiling is enabled (same phase idea as the
+ * reference's TrainStepProfile, src/model.rs:101-124):
+ * [embed_ln, qkv, sam, o, cmix, head_ce]. */
+ULLIS_CUDA_API int32_t ullis_cuda_model_set_profile(ullis_cuda_model* model, int32_t enabled);
+ULLIS_CUDA_API int32_t ullis_cuda_model_phase_ms(ullis_cuda_model* model, float ms[6]);
+
+/* ------------------------------------------------------------------ op level
+ * Host pointers in, caller-allocated host buffers out; one synchronous call
+ * each, like the MetalRuntime methods they mirror. */
+
+/* MetalRuntime::layer_norm (src/metal.rs:1590); LayerNorm::forward
+ * (src/model.rs:259-276), eps 1e-5. weight/bias are FP16 bits. */
+ULLIS_CUDA_API int32_t ullis_cuda_layer_norm(ullis_cuda_runtime* rt, const float* x, const uint16_t* weight,
+                              const uint16_t* bias, float* y, size_t rows, size_t channels);
+/* MetalRuntime::time_shift_delta (src/metal.rs:1103); src/model.rs:186-212. */
+ULLIS_CUDA_API int32_t ullis_cuda_time_shift_delta(ullis_cuda_runtime* rt, const float* x, float* xx, size_t rows, size_t time,
+                                    size_t channels);
+/* MetalRuntime::binary_linear (src/metal.rs:1705); PackedBinaryLinear::forward
+ * (src/model.rs:724-742). bias nullable. y [rows*out]. */
+ULLIS_CUDA_API int32_t ullis_cuda_binary_linear(ullis_cuda_runtime* rt, const float* x, const uint32_t* bits,
+                                 const uint16_t* scale, const uint16_t* bias, float* y, size_t rows,
+                                 size_t in_features, size_t out_features);
+/* MetalRuntime::fp16_linear (src/metal.rs:2790); Fp16Linear::forward
+ * (src/model.rs:419-436). weight FP16 bits [out*in]. */
+ULLIS_CUDA_API int32_t ullis_cuda_fp16_linear(ullis_cuda_runtime* rt, const float* x, const uint16_t* weight, float* y,
+                               size_t rows, size_t in_features, size_t out_features);
+/* MetalRuntime::sign_pack_bits (src/metal.rs:1142); bit = x > 0, 32 per word
+ * LSB-first (src/rosa.rs:372-374, 400-411). bits [(n+31)/32]. */
+ULLIS_CUDA_API int32_t ullis_cuda_sign_pack_bits(ullis_cuda_runtime* rt, const float* x, uint32_t* bits, size_t n);
+/* MetalRuntime::cmix_relu2 (src/metal.rs:1542): max(v,0)^2. */
+ULLIS_CUDA_API int32_t ullis_cuda_cmix_relu2(ullis_cuda_runtime* rt, const float* x, float* y, size_t n);
+/* MetalRuntime::residual_add (src/metal.rs:1078): out = residual + update. */
+ULLIS_CUDA_API int32_t ullis_cuda_residual_add(ullis_cuda_runtime* rt, const float* residual, const float* update, float* out,
+                                size_t n);
+/* MetalRuntime::rosa_qkv_1bit_fwd (src/metal.rs:1168); rosa_qkv_batch_packed +
+ * rosa_qkv_out_batched (src/rosa.rs:459-481, 585-609).  q/k/v_bits: packed
+ * planes over the flat [B,T,C] index; e: FP16 bits [C]; idx u8 [B,T,C]
+ * (nullable), out f32 [B,T,C] = (2*idx-1)*e (nullable). */
+ULLIS_CUDA_API int32_t ullis_cuda_rosa_qkv_1bit_fwd(ullis_cuda_runtime* rt, const uint32_t* q_bits, const uint32_t* k_bits,
+                                     const uint32_t* v_bits, const uint16_t* e, uint8_t* idx, float* out,
+                                     size_t batch, size_t time, size_t channels);
+/* MetalRuntime::rosa_block_forward (src/metal.rs:1334); RwkvRosaQkv1Bit::forward
+ * (src/model.rs:1284-1318).  x f32 [B*T*C]; mixes/e FP16 [C]; each linear is
+ * {bits [C*C/32], scale [C], bias [C]}.  Outputs (nullable): q/k/v planes
+ * packed over [B,T,C], idx u8, y = (2*idx-1)*e f32, out f32 (after O). */
+ULLIS_CUDA_API int32_t ullis_cuda_rosa_block_forward(ullis_cuda_runtime* rt, const float* x, const uint16_t* mix_q,
+                                      const uint16_t* mix_k, const uint16_t* mix_v, const uint32_t* q_bits,
+                                      const uint16_t* q_scale, const uint16_t* q_bias, const uint32_t* k_bits,
+                                      const uint16_t* k_scale, const uint16_t* k_bias, const uint32_t* v_bits,
+                                      const uint16_t* v_scale, const uint16_t* v_bias, const uint16_t* e,
+                                      const uint32_t* o_bits, const uint16_t* o_scale, const uint16_t* o_bias,
+                                      size_t batch, size_t time, size_t channels, uint32_t* q_plane,
+                                      uint32_t* k_plane, uint32_t* v_plane, uint8_t* idx, float* y, float* out);
+/* MetalRuntime::cmix_block_forward (src/metal.rs:1891); RwkvCMixX070::forward
+ * (src/model.rs:987-1001). value FP16 [d_model*dim_ffn] (out=d_model). */
+ULLIS_CUDA_API int32_t ullis_cuda_cmix_block_forward(ullis_cuda_runtime* rt, const float* x, const uint16_t* mix,
+                                      const uint32_t* key_bits, const uint16_t* key_scale,
+                                      const uint16_t* value, size_t batch, size_t time, size_t d_model,
+                                      size_t dim_ffn, float* out);
+/* MetalRuntime::streamed_cross_entropy_fp16 (src/metal.rs:2921), forward part,
+ * with the head bias the CPU model applies (src/model.rs:737, 4244); CE as in
+ * apply_head_ce (src/model.rs:3205-3228, 3253-3257).  Logits never reach
+ * host or (in FAST mode) device memory.  row_loss [rows] nullable. */
+ULLIS_CUDA_API int32_t ullis_cuda_streamed_ce(ullis_cuda_runtime* rt, const float* hidden, const uint32_t* bits,
+                               const uint16_t* scale, const uint16_t* bias, const uint32_t* labels,
+                               uint32_t ignore_id, size_t rows, size_t time, size_t channels, size_t vocab,
+                               float* row_loss, float* mean_loss, uint64_t* n_valid);
+
+/* ------------------------------------------------------------ data parallel
+ * Sequences are independent; ranks own disjoint blocks of sequences and only
+ * {loss_sum, n_valid} is summed across ranks (NCCL all-reduce, 16 bytes).
+ * No counterpart in the reference (single process, single device). */
+ULLIS_CUDA_API int32_t ullis_cuda_dp_unique_id(uint8_t id[128]);
+ULLIS_CUDA_API int32_t ullis_cuda_dp_init(ullis_cuda_runtime* rt, int32_t rank, int32_t world, const uint8_t id[128]);
+ULLIS_CUDA_API int32_t ullis_cuda_dp_allreduce_loss(ullis_cuda_runtime* rt, double* loss_sum, uint64_t* n_valid);
+ULLIS_CUDA_API int32_t ullis_cuda_dp_finalize(ullis_cuda_runtime* rt);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ULLIS_CUDA_H */

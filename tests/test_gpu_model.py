@@ -1,0 +1,154 @@
+"""Whole-model parity of the device-resident Heron forward + CE against the
+CPU oracle on the same seeded checkpoint and tokens.
+
+EXACT mode: every tap (LayerNorm output, Q/K/V sign bits, idx, residual
+stream) and the logits are bit-identical; mean CE within 1e-3 absolute (exp /
+ln are evaluated by different math libraries).
+FAST mode: per-layer residual stream and logits within 1e-2 relative, mean CE
+within 1e-3 absolute; ROSA bits are compared where both paths see the same
+input (tests/test_gpu_ops.py::test_rosa_block_forward) and their end-to-end
+mismatch rate is bounded here."""
+import numpy as np
+import pytest
+
+from ullis_b200 import cuda, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(got, ref):
+    return float(np.linalg.norm(got.astype(np.float64) - ref) / max(np.linalg.norm(ref.astype(np.float64)), 1e-30))
+
+
+@pytest.fixture(scope="module", params=[("tiny", 2, 64, False), ("tiny", 3, 50, True), ("small", 1, 512, False),
+                                        ("small", 2, 200, True)],
+                ids=["tiny-literal", "tiny-gain1-ragged", "config0-literal", "small-gain1-b2"])
+def case(request, oracle):
+    name, B, T, gain = request.param
+    data = synth.heron_checkpoint(name, batch_size=max(B, 2), ln_gain_one=gain)
+    m = oracle.HeronOracle(data)
+    tokens = synth.uniform_tokens(11, B * T, m.vocab) if name == "small" and not gain else \
+        synth.zipf_tokens(11, B * T, m.vocab)
+    labels = tokens.copy()
+    labels[3] = 0  # one ignored target (pad id 0)
+    taps = {}
+    mean, n_valid, row_loss, logits = m.forward_ce(tokens, labels, 0, B, T, taps=taps, want_logits=True)
+    return dict(data=data, B=B, T=T, tokens=tokens, labels=labels, taps=taps, mean=mean, n_valid=n_valid,
+                row_loss=row_loss, logits=logits, layers=m.layers, d=m.d, vocab=m.vocab)
+
+
+def run_cuda(cuda_rt, case, mode, sam=cuda.SAM_EULER):
+    cuda_rt.set_mode(mode)
+    cuda_rt.set_sam(sam)
+    try:
+        m = cuda.CudaHeron(cuda_rt, case["data"])
+        m.set_taps(True)
+        res = m.forward_ce(case["tokens"], case["labels"], 0, case["B"], case["T"], want_row_loss=True)
+        rows = case["B"] * case["T"]
+        taps = {}
+        for l in range(case["layers"]):
+            for name in ("block_in", "ln3_out", "q_bits", "k_bits", "v_bits", "idx", "after_rosa", "block_out"):
+                taps[f"{l}.{name}"] = m.tap(l, name, rows)
+        taps["hidden"] = m.tap(0, "hidden", rows)
+        logits = m.logits(case["tokens"], case["B"], case["T"])
+        hidden = m.hidden(case["tokens"], case["B"], case["T"])
+        m.close()
+        return res, taps, logits, hidden
+    finally:
+        cuda_rt.set_mode(cuda.MODE_FAST)
+        cuda_rt.set_sam(cuda.SAM_EULER)
+
+
+@pytest.mark.parametrize("sam", [cuda.SAM_EULER, cuda.SAM_EAGER], ids=["euler", "eager"])
+def test_exact_mode_is_bit_identical(cuda_rt, case, sam):
+    (mean, loss_sum, n_valid, row_loss), taps, logits, hidden = run_cuda(cuda_rt, case, cuda.MODE_EXACT, sam)
+    ref = case["taps"]
+    for l in range(case["layers"]):
+        for name in ("block_in", "ln3_out", "q_bits", "k_bits", "v_bits", "idx", "after_rosa", "block_out"):
+            assert np.array_equal(taps[f"{l}.{name}"], ref[f"{l}.{name}"]), (l, name)
+    assert np.array_equal(taps["hidden"], ref["hidden"]) and np.array_equal(hidden, ref["hidden"])
+    assert np.array_equal(logits, case["logits"])
+    assert n_valid == case["n_valid"]
+    assert abs(mean - case["mean"]) <= 1e-3
+    assert np.abs(row_loss - case["row_loss"]).max() <= 1e-4
+    assert abs(loss_sum - float(case["row_loss"].astype(np.float64).sum())) <= 1e-3 * max(1, n_valid) * 1e-1
+
+
+def test_fast_mode_within_tolerance(cuda_rt, case):
+    (mean, loss_sum, n_valid, row_loss), taps, logits, hidden = run_cuda(cuda_rt, case, cuda.MODE_FAST)
+    ref = case["taps"]
+    mism = 0
+    total = 0
+    for l in range(case["layers"]):
+        assert rel_err(taps[f"{l}.block_out"], ref[f"{l}.block_out"]) <= 1e-2, l   # activations: 1e-2 relative
+        for name in ("q_bits", "k_bits", "v_bits", "idx"):
+            mism += int((taps[f"{l}.{name}"] != ref[f"{l}.{name}"]).sum())
+            total += taps[f"{l}.{name}"].size
+    assert mism / total <= 2e-3, f"ROSA bit mismatch rate {mism / total:.2e}"
+    assert rel_err(logits, case["logits"]) <= 1e-2                                     # logits: 1e-2 relative
+    assert n_valid == case["n_valid"]
+    assert abs(mean - case["mean"]) <= 1e-3                                            # mean CE: 1e-3 absolute
+
+
+def test_model_error_paths(cuda_rt):
+    data = synth.heron_checkpoint("tiny", batch_size=2)
+    m = cuda.CudaHeron(cuda_rt, data)
+    tok = np.zeros(3 * 64, np.uint32)
+    with pytest.raises(cuda.UllisCudaError) as e:      # batch > config.batch_size
+        m.forward_ce(tok, tok, cuda.CE_NO_IGNORE, 3, 64)
+    assert e.value.code == cuda.ERR_SHAPE
+    with pytest.raises(cuda.UllisCudaError) as e:      # time > context_len
+        m.forward_ce(np.zeros(65, np.uint32), np.zeros(65, np.uint32), cuda.CE_NO_IGNORE, 1, 65)
+    assert e.value.code == cuda.ERR_SHAPE
+    bad = np.zeros(64, np.uint32)
+    bad[9] = 512
+    with pytest.raises(cuda.UllisCudaError) as e:      # token id >= vocab
+        m.forward_ce(bad, np.zeros(64, np.uint32), cuda.CE_NO_IGNORE, 1, 64)
+    assert e.value.code == cuda.ERR_TOKEN and "exceeds vocabulary" in e.value.message
+    with pytest.raises(cuda.UllisCudaError) as e:      # target id >= vocab
+        m.forward_ce(np.zeros(64, np.uint32), bad, cuda.CE_NO_IGNORE, 1, 64)
+    assert e.value.code == cuda.ERR_TOKEN
+    mean, s, n = m.forward_ce(np.zeros(64, np.uint32), np.zeros(64, np.uint32), 0, 1, 64)  # everything ignored
+    assert n == 0 and mean == 0.0
+    mean, s, n = m.forward_ce(np.ones(2, np.uint32), np.ones(2, np.uint32), cuda.CE_NO_IGNORE, 2, 1)  # T=1
+    assert n == 0
+    m.close()
+    from ullis_b200 import checkpoint as ckpt
+    cfg = synth.train_config(64, 2, 512, 64, 1, 128)
+    t = synth.heron_tensors(cfg)
+    for blob, needle in [(ckpt.to_safetensors_bytes(t, cfg, format_version=1), "unloadable"), (b"\x01\x02\x03", "header"),
+                         (data[:1000], "header")]:
+        with pytest.raises(cuda.UllisCudaError) as e:
+            cuda.CudaHeron(cuda_rt, blob)
+        assert e.value.code == cuda.ERR_CHECKPOINT and needle in e.value.message
+    short = dict(t)
+    short["blocks.1.rosa.e"] = short["blocks.1.rosa.e"][:-1]
+    with pytest.raises(cuda.UllisCudaError) as e:
+        cuda.CudaHeron(cuda_rt, ckpt.to_safetensors_bytes(short, cfg))
+    assert e.value.code == cuda.ERR_CHECKPOINT and "length mismatch" in e.value.message
+
+
+def test_head_without_bias_loads_as_zero_bias(cuda_rt, oracle):  # src/model.rs:4773-4784
+    data = synth.heron_checkpoint("tiny", head_bias=False)
+    tokens = synth.uniform_tokens(3, 64, 512)
+    ref = oracle.HeronOracle(data).logits(tokens, 1, 64)
+    cuda_rt.set_mode(cuda.MODE_EXACT)
+    try:
+        m = cuda.CudaHeron(cuda_rt, data)
+        assert np.array_equal(m.logits(tokens, 1, 64), ref)
+        m.close()
+    finally:
+        cuda_rt.set_mode(cuda.MODE_FAST)
+
+
+def test_split_enqueue_api_and_phase_profile(cuda_rt, case):
+    m = cuda.CudaHeron(cuda_rt, case["data"])
+    m.set_profile(True)
+    m.upload_tokens(case["tokens"], case["labels"], case["B"], case["T"])
+    before = cuda_rt.launch_count
+    m.enqueue_forward_ce(0, case["B"], case["T"])
+    mean, s, n = m.read_loss()
+    assert cuda_rt.launch_count > before and n == case["n_valid"] and abs(mean - case["mean"]) <= 1e-3
+    ms = m.phase_ms()
+    assert ms["sam"] > 0 and ms["qkv"] > 0 and ms["head_ce"] > 0
+    m.close()

@@ -1,0 +1,82 @@
+"""ROSA 1-bit suffix-automaton kernel against the oracle: idx must be
+bit-exact for every stream, for both schedules, at ragged sizes, on worst-case
+(constant / periodic) streams and at the benchmark's context lengths."""
+import numpy as np
+import pytest
+
+from conftest import pack_plane
+from ullis_b200 import cuda, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def f16(x):
+    return np.asarray(x, np.float32).astype(np.float16).view(np.uint16)
+
+
+def run_both(cuda_rt, oracle, q, k, v, B, T, C, algos=(cuda.SAM_EULER, cuda.SAM_EAGER)):
+    e = f16(np.linspace(0.01, 0.5, C))
+    ref = oracle.rosa_qkv_batch_packed(q, k, v, B, T, C)
+    for algo in algos:
+        cuda_rt.set_sam(algo)
+        idx, out = cuda_rt.rosa_qkv_1bit_fwd(q, k, v, e, B, T, C)
+        assert np.array_equal(idx, ref), f"algo {algo}"
+        assert np.array_equal(out, oracle.rosa_qkv_out_batched(ref, e, B, T, C))
+    cuda_rt.set_sam(cuda.SAM_EULER)
+
+
+@pytest.mark.parametrize("B,T,C", [(1, 1, 1), (1, 5, 3), (3, 31, 5), (2, 33, 32), (1, 64, 70), (2, 100, 33), (1, 1000, 9)])
+def test_ragged_sizes_random_bits(cuda_rt, oracle, B, T, C):
+    rng = np.random.default_rng(B * 10000 + T * 10 + C)
+    q, k, v = (pack_plane(rng.integers(0, 2, B * T * C, dtype=np.uint8)) for _ in range(3))
+    run_both(cuda_rt, oracle, q, k, v, B, T, C)
+
+
+def test_exhaustive_t4_as_one_batch(cuda_rt, oracle):
+    T = 4
+    n = 1 << (3 * T)  # every (q,k,v) triple of 4-bit streams, one stream per channel
+    a = np.arange(n)
+    bits = lambda s: ((a[None, :] >> (s * T + np.arange(T)[:, None])) & 1).astype(np.uint8).reshape(-1)  # [T, n]
+    run_both(cuda_rt, oracle, pack_plane(bits(0)), pack_plane(bits(1)), pack_plane(bits(2)), 1, T, n)
+
+
+@pytest.mark.parametrize("kind", ["const", "biased", "periodic_clean", "qk_same"])
+def test_worst_case_streams(cuda_rt, oracle, kind):
+    B, T, C = 1, 2048, 32
+    rng = np.random.default_rng(len(kind))
+    if kind == "const":
+        q = np.repeat(rng.integers(0, 2, (1, C), dtype=np.uint8), T, 0)
+        k = np.repeat(rng.integers(0, 2, (1, C), dtype=np.uint8), T, 0)
+    elif kind == "biased":
+        pr = rng.choice([0.001, 0.01, 0.99, 0.999], (1, C))
+        q, k = (rng.random((T, C)) < pr).astype(np.uint8), (rng.random((T, C)) < pr).astype(np.uint8)
+    elif kind == "periodic_clean":
+        P = rng.integers(2, 64, C)
+        base = rng.integers(0, 2, (64, C), dtype=np.uint8)
+        q = np.take_along_axis(base, np.arange(T)[:, None] % P[None, :], 0)
+        k = q.copy()
+    else:
+        q = rng.integers(0, 2, (T, C), dtype=np.uint8)
+        k = q.copy()
+    v = rng.integers(0, 2, (T, C), dtype=np.uint8)
+    run_both(cuda_rt, oracle, pack_plane(q), pack_plane(k), pack_plane(v), B, T, C)
+
+
+def test_model_context_length_batch(cuda_rt, oracle):
+    B, T, C = 2, 2048, 256
+    q, k, v = synth.rosa_bits_iid(21, B, T, C)
+    run_both(cuda_rt, oracle, q, k, v, B, T, C)
+
+
+def test_standalone_benchmark_context_length(cuda_rt, oracle):
+    B, T, C = 1, 8192, 64  # context of the standalone ROSA configuration, fewer streams
+    q, k, v = synth.rosa_bits_iid(22, B, T, C)
+    run_both(cuda_rt, oracle, q, k, v, B, T, C, algos=(cuda.SAM_EULER,))
+    q, k, v = synth.rosa_bits_periodic(23, B, T, C)
+    run_both(cuda_rt, oracle, q, k, v, B, T, C)
+
+
+def test_context_beyond_16_bit_state_ids(cuda_rt, oracle):
+    B, T, C = 1, 32768, 4  # MAX_CONTEXT_LEN: needs the 32-bit state-id kernels
+    q, k, v = synth.rosa_bits_iid(24, B, T, C)
+    run_both(cuda_rt, oracle, q, k, v, B, T, C, algos=(cuda.SAM_EULER,))

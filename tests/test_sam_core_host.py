@@ -1,0 +1,64 @@
+"""The device suffix-automaton routines (ullis_b200/csrc/sam_core.cuh), compiled
+for the host, against the oracle: exhaustively for short streams and on long
+random, constant, biased and periodic streams, for both schedules and both
+state-id widths."""
+import numpy as np
+import pytest
+
+from conftest import pack_streams
+
+ALGOS = {"eager": 0, "euler": 1}
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 4, 5])
+def test_exhaustive_short_streams(oracle, sam_host, T):
+    n = 1 << (3 * T)
+    a = np.arange(n, dtype=np.uint32)
+    m = (1 << T) - 1
+    q, k, v = a & m, (a >> T) & m, (a >> (2 * T)) & m
+    ref = oracle.rosa_qkv_streams(q, k, v, n, T)
+    for algo in ALGOS.values():
+        for ix in (16, 32):
+            assert np.array_equal(sam_host(algo, ix, q, k, v, n, T), ref)
+
+
+def _streams(kind, n, T, rng):
+    if kind == "iid":
+        return [rng.integers(0, 2, (n, T), dtype=np.uint8) for _ in range(3)]
+    if kind == "const":
+        return [np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1),
+                np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1), rng.integers(0, 2, (n, T), dtype=np.uint8)]
+    if kind == "biased":
+        pr = rng.choice([0.001, 0.01, 0.99, 0.999], (n, 1))
+        return [(rng.random((n, T)) < pr).astype(np.uint8), (rng.random((n, T)) < pr).astype(np.uint8),
+                rng.integers(0, 2, (n, T), dtype=np.uint8)]
+    if kind in ("periodic", "periodic_clean"):
+        P = rng.integers(2, 64, n)
+        base = rng.integers(0, 2, (n, 64), dtype=np.uint8)
+        b = np.take_along_axis(base, np.arange(T)[None, :] % P[:, None], 1)
+        fl = 0.0 if kind == "periodic_clean" else 0.05
+        return [(b ^ (rng.random((n, T)) < fl)).astype(np.uint8), (b ^ (rng.random((n, T)) < fl)).astype(np.uint8),
+                rng.integers(0, 2, (n, T), dtype=np.uint8)]
+    if kind == "qk_same":
+        q = rng.integers(0, 2, (n, T), dtype=np.uint8)
+        return [q, q.copy(), rng.integers(0, 2, (n, T), dtype=np.uint8)]
+    raise ValueError(kind)
+
+
+@pytest.mark.parametrize("kind,T,n", [("iid", 97, 200), ("iid", 2048, 24), ("const", 1024, 16), ("biased", 2048, 16),
+                                      ("periodic", 1500, 16), ("periodic_clean", 2048, 8), ("qk_same", 777, 32)])
+def test_long_streams(oracle, sam_host, kind, T, n):
+    rng = np.random.default_rng(hash((kind, T)) & 0xFFFF)
+    q, k, v = (pack_streams(b) for b in _streams(kind, n, T, rng))
+    ref = oracle.rosa_qkv_streams(q, k, v, n, T)
+    for algo in ALGOS.values():
+        assert np.array_equal(sam_host(algo, 16, q, k, v, n, T), ref), (kind, algo)
+    assert np.array_equal(sam_host(1, 32, q, k, v, n, T), ref)
+
+
+def test_wide_state_ids_beyond_16_bits(oracle, sam_host):
+    T, n = 33000, 2  # 2T+2 > 65535: the 32-bit state-id instantiation is required
+    rng = np.random.default_rng(5)
+    q, k, v = (pack_streams(b) for b in _streams("iid", n, T, rng))
+    ref = oracle.rosa_qkv_streams(q, k, v, n, T)
+    assert np.array_equal(sam_host(1, 32, q, k, v, n, T), ref)

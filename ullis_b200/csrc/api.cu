@@ -1,0 +1,590 @@
+// extern "C" surface declared in include/ullis_cuda.h: runtime lifecycle,
+// the device-resident model entry points and the op-level calls that mirror
+// the reference's MetalRuntime methods.  No C++ exception leaves this file.
+#include <algorithm>
+#include <cstring>
+#include <exception>
+#include <new>
+
+#include "kernels.hpp"
+#include "linear_tc.hpp"
+#include "model.hpp"
+
+using namespace ullis;
+
+namespace {
+
+std::string g_create_error;  // last failure of a call that had no runtime to blame
+
+template <typename F>
+int32_t guard(ullis_cuda_runtime* rt, F&& body) {
+    if (!rt) {
+        g_create_error = "runtime handle is null";
+        return ULLIS_CUDA_ERR_ARG;
+    }
+    try {
+        rt->bind();
+        body();
+        return ULLIS_CUDA_OK;
+    } catch (const Error& e) {
+        rt->last_error = e.msg;
+        return e.code;
+    } catch (const std::bad_alloc&) {
+        rt->last_error = "host allocation failed";
+        return ULLIS_CUDA_ERR_NOMEM;
+    } catch (const std::exception& e) {
+        rt->last_error = e.what();
+        return ULLIS_CUDA_ERR_ARG;
+    }
+}
+
+template <typename F>
+int32_t guard_model(ullis_cuda_model* m, F&& body) {
+    if (!m) {
+        g_create_error = "model handle is null";
+        return ULLIS_CUDA_ERR_ARG;
+    }
+    return guard(m->rt, body);
+}
+
+void need_ptr(const void* p, const char* name) {
+    if (!p) fail(ULLIS_CUDA_ERR_ARG, std::string(name) + " is null");
+}
+
+size_t mul_or_fail(size_t a, size_t b, const char* what) {
+    if (b != 0 && a > SIZE_MAX / b) fail(ULLIS_CUDA_ERR_SHAPE, std::string(what) + " shape overflow");
+    return a * b;
+}
+
+template <typename T>
+T* stage(ullis_cuda_runtime* rt, int slot, const T* host, size_t count) {
+    T* dev = rt->pool[slot].as<T>(count ? count : 1);
+    rt->h2d(dev, host, count * sizeof(T));
+    return dev;
+}
+
+void packed_linear_dev(ullis_cuda_runtime* rt, const float* x, const uint32_t* bits, const uint16_t* scale,
+                       const uint16_t* bias, float* y, size_t rows, size_t K, size_t N) {
+    if (rt->mode == ULLIS_CUDA_MODE_EXACT || !tc::binary_linear(rt, x, bits, scale, bias, y, rows, K, N))
+        k::binary_linear_exact(rt, x, bits, scale, bias, y, rows, K, N, false);
+}
+
+void dense_linear_dev(ullis_cuda_runtime* rt, const float* x, const uint16_t* w, float* y, size_t rows, size_t K,
+                      size_t N) {
+    if (rt->mode == ULLIS_CUDA_MODE_EXACT || !tc::fp16_linear(rt, x, w, y, rows, K, N))
+        k::fp16_linear_exact(rt, x, w, y, rows, K, N, false);
+}
+
+}  // namespace
+
+void ullis_cuda_runtime::launched(const char* what) {
+    ++launches;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) fail(ULLIS_CUDA_ERR_CUDA, std::string("launch of ") + what + ": " + cudaGetErrorString(e));
+}
+
+void ullis_cuda_runtime::check_status() {
+    d2h(host_status, dev_status, 16);
+    sync();
+    const uint32_t code = host_status[0];
+    if (code == ULLIS_DEV_OK) return;
+    if (code == ULLIS_DEV_BAD_TOKEN)
+        fail(ULLIS_CUDA_ERR_TOKEN, "token id exceeds vocabulary (row " + std::to_string(host_status[1]) + ")");
+    if (code == ULLIS_DEV_WAIT_TIMEOUT)
+        fail(ULLIS_CUDA_ERR_TIMEOUT, "a kernel gave up waiting (site " + std::to_string(host_status[1]) + ")");
+    fail(ULLIS_CUDA_ERR_DEVICE_CHECK, "device-side check failed, code " + std::to_string(code) + " detail " +
+                                          std::to_string(host_status[1]));
+}
+
+extern "C" {
+
+int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
+    if (!out) {
+        g_create_error = "out is null";
+        return ULLIS_CUDA_ERR_ARG;
+    }
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        g_create_error = std::string("--backend cuda requires a CUDA device: ") +
+                         (e != cudaSuccess ? cudaGetErrorString(e) : "no device found");
+        return ULLIS_CUDA_ERR_CUDA;
+    }
+    if (device < 0 || device >= count) {
+        g_create_error = "device index out of range";
+        return ULLIS_CUDA_ERR_ARG;
+    }
+    ullis_cuda_runtime* rt = new (std::nothrow) ullis_cuda_runtime();
+    if (!rt) {
+        g_create_error = "host allocation failed";
+        return ULLIS_CUDA_ERR_NOMEM;
+    }
+    rt->device = device;
+    try {
+        rt->bind();
+        cudaDeviceProp prop;
+        ULLIS_CUDA_CHECK(cudaGetDeviceProperties(&prop, device));
+        rt->sm_count = prop.multiProcessorCount;
+        rt->cc_major = prop.major;
+        rt->cc_minor = prop.minor;
+        ULLIS_CUDA_CHECK(cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking));
+        ULLIS_CUDA_CHECK(cudaMalloc(&rt->dev_status, 16));
+        ULLIS_CUDA_CHECK(cudaMallocHost(&rt->host_status, 16));
+        rt->clear_status();
+        rt->sync();
+    } catch (const Error& err) {
+        g_create_error = err.msg;
+        ullis_cuda_runtime_destroy(rt);
+        return err.code;
+    }
+    *out = rt;
+    return ULLIS_CUDA_OK;
+}
+
+void ullis_cuda_runtime_destroy(ullis_cuda_runtime* rt) {
+    if (!rt) return;
+    cudaSetDevice(rt->device);
+    ullis_cuda_dp_finalize(rt);
+    if (rt->stream) {
+        cudaStreamSynchronize(rt->stream);
+        cudaStreamDestroy(rt->stream);
+    }
+    if (rt->dev_status) cudaFree(rt->dev_status);
+    if (rt->host_status) cudaFreeHost(rt->host_status);
+    delete rt;
+}
+
+const char* ullis_cuda_last_error(const ullis_cuda_runtime* rt) {
+    return rt ? rt->last_error.c_str() : g_create_error.c_str();
+}
+
+int32_t ullis_cuda_runtime_set_mode(ullis_cuda_runtime* rt, int32_t mode) {
+    return guard(rt, [&] {
+        if (mode != ULLIS_CUDA_MODE_FAST && mode != ULLIS_CUDA_MODE_EXACT) fail(ULLIS_CUDA_ERR_ARG, "unknown mode");
+        rt->mode = mode;
+    });
+}
+
+int32_t ullis_cuda_runtime_set_sam(ullis_cuda_runtime* rt, int32_t sam_algo) {
+    return guard(rt, [&] {
+        if (sam_algo != ULLIS_CUDA_SAM_EULER && sam_algo != ULLIS_CUDA_SAM_EAGER)
+            fail(ULLIS_CUDA_ERR_ARG, "unknown suffix-automaton schedule");
+        rt->sam_algo = sam_algo;
+    });
+}
+
+int32_t ullis_cuda_runtime_synchronize(ullis_cuda_runtime* rt) {
+    return guard(rt, [&] { rt->sync(); });
+}
+
+void* ullis_cuda_runtime_stream(ullis_cuda_runtime* rt) { return rt ? (void*)rt->stream : nullptr; }
+
+uint64_t ullis_cuda_runtime_launch_count(const ullis_cuda_runtime* rt) { return rt ? rt->launches : 0; }
+
+int32_t ullis_cuda_runtime_is_sm100(const ullis_cuda_runtime* rt) { return rt && rt->cc_major == 10 ? 1 : 0; }
+
+// ------------------------------------------------------------------ model
+
+int32_t ullis_cuda_model_load_safetensors(ullis_cuda_runtime* rt, const uint8_t* bytes, size_t len,
+                                          ullis_cuda_model** out) {
+    return guard(rt, [&] {
+        need_ptr(out, "out");
+        *out = nullptr;
+        need_ptr(bytes, "bytes");
+        ullis_cuda_model* m = new ullis_cuda_model();
+        m->rt = rt;
+        try {
+            m->load(bytes, len);
+        } catch (...) {
+            delete m;
+            throw;
+        }
+        *out = m;
+    });
+}
+
+void ullis_cuda_model_destroy(ullis_cuda_model* model) {
+    if (!model) return;
+    cudaSetDevice(model->rt->device);
+    cudaStreamSynchronize(model->rt->stream);
+    delete model;
+}
+
+int32_t ullis_cuda_model_dims(const ullis_cuda_model* model, size_t dims[6]) {
+    if (!model || !dims) return ULLIS_CUDA_ERR_ARG;
+    dims[0] = model->d;
+    dims[1] = model->layers;
+    dims[2] = model->vocab;
+    dims[3] = model->context_len;
+    dims[4] = model->batch_size;
+    dims[5] = model->ffn;
+    return ULLIS_CUDA_OK;
+}
+
+int32_t ullis_cuda_model_forward_ce(ullis_cuda_model* model, const uint32_t* tokens, const uint32_t* labels,
+                                    uint32_t ignore_id, size_t batch, size_t time, float* mean_loss,
+                                    double* loss_sum, uint64_t* n_valid, float* row_loss) {
+    return guard_model(model, [&] {
+        need_ptr(labels, "labels");
+        model->upload_tokens(tokens, labels, batch, time);
+        model->enqueue_forward_ce(ignore_id, batch, time);
+        model->read_loss(mean_loss, loss_sum, n_valid, row_loss, batch * time);
+    });
+}
+
+int32_t ullis_cuda_model_upload_tokens(ullis_cuda_model* model, const uint32_t* tokens, const uint32_t* labels,
+                                       size_t batch, size_t time) {
+    return guard_model(model, [&] { model->upload_tokens(tokens, labels, batch, time); });
+}
+
+int32_t ullis_cuda_model_enqueue_forward_ce(ullis_cuda_model* model, uint32_t ignore_id, size_t batch,
+                                            size_t time) {
+    return guard_model(model, [&] { model->enqueue_forward_ce(ignore_id, batch, time); });
+}
+
+int32_t ullis_cuda_model_read_loss(ullis_cuda_model* model, float* mean_loss, double* loss_sum,
+                                   uint64_t* n_valid, float* row_loss, size_t rows) {
+    return guard_model(model, [&] { model->read_loss(mean_loss, loss_sum, n_valid, row_loss, rows); });
+}
+
+int32_t ullis_cuda_model_logits(ullis_cuda_model* model, const uint32_t* tokens, size_t batch, size_t time,
+                                float* logits) {
+    return guard_model(model, [&] {
+        need_ptr(logits, "logits");
+        model->upload_tokens(tokens, nullptr, batch, time);
+        model->enqueue_logits(batch, time, logits);
+    });
+}
+
+int32_t ullis_cuda_model_hidden(ullis_cuda_model* model, const uint32_t* tokens, size_t batch, size_t time,
+                                float* hidden) {
+    return guard_model(model, [&] {
+        need_ptr(hidden, "hidden");
+        model->upload_tokens(tokens, nullptr, batch, time);
+        model->enqueue_hidden(batch, time);
+        model->rt->d2h(hidden, model->a.get(), batch * time * model->d * 4);
+        model->rt->check_status();
+    });
+}
+
+int32_t ullis_cuda_model_set_taps(ullis_cuda_model* model, int32_t enabled) {
+    return guard_model(model, [&] {
+        model->taps_enabled = enabled != 0;
+        if (!enabled) {
+            model->tap_bufs.clear();
+            model->tap_rows = 0;
+        }
+    });
+}
+
+int32_t ullis_cuda_model_tap(ullis_cuda_model* model, int32_t layer, int32_t which, void* out, size_t bytes) {
+    return guard_model(model, [&] {
+        need_ptr(out, "out");
+        model->tap(layer, which, out, bytes);
+    });
+}
+
+int32_t ullis_cuda_model_set_profile(ullis_cuda_model* model, int32_t enabled) {
+    return guard_model(model, [&] {
+        model->profile = enabled != 0;
+        model->spans_used = 0;
+    });
+}
+
+int32_t ullis_cuda_model_phase_ms(ullis_cuda_model* model, float ms[6]) {
+    return guard_model(model, [&] {
+        need_ptr(ms, "ms");
+        model->phase_ms(ms);
+    });
+}
+
+// ---------------------------------------------------------------- op level
+
+int32_t ullis_cuda_layer_norm(ullis_cuda_runtime* rt, const float* x, const uint16_t* weight,
+                              const uint16_t* bias, float* y, size_t rows, size_t channels) {
+    return guard(rt, [&] {
+        if (channels == 0) fail(ULLIS_CUDA_ERR_SHAPE, "LayerNorm input shape mismatch");
+        const size_t n = mul_or_fail(rows, channels, "LayerNorm");
+        if (n == 0) return;
+        need_ptr(x, "x"); need_ptr(weight, "weight"); need_ptr(bias, "bias"); need_ptr(y, "y");
+        float* dx = stage(rt, 0, x, n);
+        uint16_t* dw = stage(rt, 1, weight, channels);
+        uint16_t* db = stage(rt, 2, bias, channels);
+        float* dy = rt->pool[3].as<float>(n);
+        k::layer_norm(rt, dx, dw, db, dy, rows, channels, rt->mode == ULLIS_CUDA_MODE_EXACT);
+        rt->d2h(y, dy, n * 4);
+        rt->sync();
+    });
+}
+
+int32_t ullis_cuda_time_shift_delta(ullis_cuda_runtime* rt, const float* x, float* xx, size_t rows, size_t time,
+                                    size_t channels) {
+    return guard(rt, [&] {
+        if (time == 0 || channels == 0 || rows % time != 0) fail(ULLIS_CUDA_ERR_SHAPE, "time-shift input shape mismatch");
+        const size_t n = mul_or_fail(rows, channels, "time-shift");
+        if (n == 0) return;
+        need_ptr(x, "x"); need_ptr(xx, "xx");
+        float* dx = stage(rt, 0, x, n);
+        float* dy = rt->pool[1].as<float>(n);
+        k::time_shift_delta(rt, dx, dy, rows, time, channels);
+        rt->d2h(xx, dy, n * 4);
+        rt->sync();
+    });
+}
+
+int32_t ullis_cuda_binary_linear(ullis_cuda_runtime* rt, const float* x, const uint32_t* bits,
+                                 const uint16_t* scale, const uint16_t* bias, float* y, size_t rows,
+                                 size_t in_features, size_t out_features) {
+    return guard(rt, [&] {
+        if (in_features == 0 || out_features == 0) fail(ULLIS_CUDA_ERR_SHAPE, "packed linear input shape mismatch");
+        const size_t nx = mul_or_fail(rows, in_features, "packed linear");
+        const size_t ny = mul_or_fail(rows, out_features, "packed linear");
+        const size_t words = (mul_or_fail(in_features, out_features, "packed linear") + 31) / 32;
+        if (rows == 0) return;
+        need_ptr(x, "x"); need_ptr(bits, "bits"); need_ptr(scale, "scale"); need_ptr(y, "y");
+        float* dx = stage(rt, 0, x, nx);
+        uint32_t* dbits = stage(rt, 1, bits, words);
+        uint16_t* ds = stage(rt, 2, scale, out_features);
+        uint16_t* db = bias ? stage(rt, 3, bias, out_features) : nullptr;
+        float* dy = rt->pool[4].as<float>(ny);
+        packed_linear_dev(rt, dx, dbits, ds, db, dy, rows, in_features, out_features);
+        rt->d2h(y, dy, ny * 4);
+        rt->sync();
+    });
+}
+
+int32_t ullis_cuda_fp16_linear(ullis_cuda_runtime* rt, const float* x, const uint16_t* weight, float* y,
+                               size_t rows, size_t in_features, size_t out_features) {
+    return guard(rt, [&] {
+        if (in_features == 0 || out_features == 0) fail(ULLIS_CUDA_ERR_SHAPE, "FP16 linear shape mismatch");
+        const size_t nx = mul_or_fail(rows, in_features, "FP16 linear");
+        const size_t ny = mul_or_fail(rows, out_features, "FP16 linear");
+        const size_t nw = mul_or_fail(in_features, out_features, "FP16 linear");
+        if (rows == 0) return;
+        need_ptr(x, "x"); need_ptr(weight, "weight"); need_ptr(y, "y");
+        float* dx = stage(rt, 0, x, nx);
+        uint16_t* dw = stage(rt, 1, weight, nw);
+        float* dy = rt->pool[2].as<float>(ny);
+        dense_linear_dev(rt, dx, dw, dy, rows, in_features, out_features);
+        rt->d2h(y, dy, ny * 4);
+        rt->sync();
+    });
+}
+
+int32_t ullis_cuda_sign_pack_bits(ullis_cuda_runtime* rt, const float* x, uint32_t* bits, size_t n) {
+    return guard(rt, [&] {
+        if (n == 0) return;
+        need_ptr(x, "x"); need_ptr(bits, "bits");
+        float* dx = stage(rt, 0, x, n);
+        uint32_t* dw = rt->pool[1].as<uint32_t>((n + 31) / 32);
+        k::sign_pack_flat(rt, dx, dw, n);
+        rt->d2h(bits, dw, ((n + 31) / 32) * 4);
+        rt->sync();
+    });
+}
+
+int32_t ullis_cuda_cmix_relu2(ullis_cuda_runtime* rt, const float* x, float* y, size_t n) {
+    return guard(rt, [&] {
+        if (n == 0) return;
+        need_ptr(x, "x"); need_ptr(y, "y");
+        float* dx = stage(rt, 0, x, n);
+        float* dy = rt->pool[1].as<float>(n);
+        k::relu2(rt, dx, dy, n);
+        rt->d2h(y, dy, n * 4);
+        rt->sync();
+    });
+}
+
+int32_t ullis_cuda_residual_add(ullis_cuda_runtime* rt, const float* residual, const float* update, float* out,
+                                size_t n) {
+    return guard(rt, [&] {
+        if (n == 0) return;
+        need_ptr(residual, "residual"); need_ptr(update, "update"); need_ptr(out, "out");
+        float* da = stage(rt, 0, residual, n);
+        float* db = stage(rt, 1, update, n);
+        float* dy = rt->pool[2].as<float>(n);
+        k::residual_add(rt, da, db, dy, n);
+        rt->d2h(out, dy, n * 4);
+        rt->sync();
+    });
+}
+
+int32_t ullis_cuda_rosa_qkv_1bit_fwd(ullis_cuda_runtime* rt, const uint32_t* q_bits, const uint32_t* k_bits,
+                                     const uint32_t* v_bits, const uint16_t* e, uint8_t* idx, float* out,
+                                     size_t batch, size_t time, size_t channels) {
+    return guard(rt, [&] {
+        // reference: MetalDispatchShape::new rejects zero dims (src/metal.rs:36-53)
+        if (batch == 0 || time == 0 || channels == 0) fail(ULLIS_CUDA_ERR_SHAPE, "ROSA dispatch dimensions must be non-zero");
+        const size_t n = mul_or_fail(mul_or_fail(batch, time, "ROSA"), channels, "ROSA");
+        need_ptr(q_bits, "q_bits"); need_ptr(k_bits, "k_bits"); need_ptr(v_bits, "v_bits"); need_ptr(e, "e");
+        const size_t words = (n + 31) / 32, wps = (time + 31) / 32, sw = batch * channels * wps;
+        uint32_t* dq = stage(rt, 0, q_bits, words);
+        uint32_t* dk = stage(rt, 1, k_bits, words);
+        uint32_t* dv = stage(rt, 2, v_bits, words);
+        uint16_t* de = stage(rt, 3, e, channels);
+        uint32_t* qs = rt->pool[4].as<uint32_t>(sw);
+        uint32_t* ks = rt->pool[5].as<uint32_t>(sw);
+        uint32_t* vs = rt->pool[6].as<uint32_t>(sw);
+        uint32_t* is = rt->pool[7].as<uint32_t>(sw);
+        k::planes_to_streams(rt, dq, qs, batch, time, channels);
+        k::planes_to_streams(rt, dk, ks, batch, time, channels);
+        k::planes_to_streams(rt, dv, vs, batch, time, channels);
+        rt->clear_status();
+        k::rosa_sam(rt, qs, ks, vs, is, batch * channels, time);
+        uint8_t* didx = idx ? rt->pool[8].as<uint8_t>(n) : nullptr;
+        float* dout = out ? rt->pool[9].as<float>(n) : nullptr;
+        if (idx || out) k::rosa_emit(rt, is, de, didx, dout, batch, time, channels);
+        if (idx) rt->d2h(idx, didx, n);
+        if (out) rt->d2h(out, dout, n * 4);
+        rt->check_status();
+    });
+}
+
+int32_t ullis_cuda_rosa_block_forward(ullis_cuda_runtime* rt, const float* x, const uint16_t* mix_q,
+                                      const uint16_t* mix_k, const uint16_t* mix_v, const uint32_t* q_bits,
+                                      const uint16_t* q_scale, const uint16_t* q_bias, const uint32_t* k_bits,
+                                      const uint16_t* k_scale, const uint16_t* k_bias, const uint32_t* v_bits,
+                                      const uint16_t* v_scale, const uint16_t* v_bias, const uint16_t* e,
+                                      const uint32_t* o_bits, const uint16_t* o_scale, const uint16_t* o_bias,
+                                      size_t batch, size_t time, size_t channels, uint32_t* q_plane,
+                                      uint32_t* k_plane, uint32_t* v_plane, uint8_t* idx, float* y, float* out) {
+    return guard(rt, [&] {
+        if (batch == 0 || time == 0 || channels == 0) fail(ULLIS_CUDA_ERR_SHAPE, "ROSA dispatch dimensions must be non-zero");
+        const size_t rows = mul_or_fail(batch, time, "ROSA block");
+        const size_t n = mul_or_fail(rows, channels, "ROSA block");
+        const size_t d = channels, words = (d * d + 31) / 32, wps = (time + 31) / 32, sw = batch * d * wps;
+        const void* req[] = {x, mix_q, mix_k, mix_v, q_bits, q_scale, q_bias, k_bits, k_scale, k_bias,
+                             v_bits, v_scale, v_bias, e, o_bits, o_scale, o_bias};
+        for (const void* p : req) need_ptr(p, "ROSA block argument");
+        LayerWeights L;
+        float* dx = stage(rt, 0, x, n);
+        L.x_q = stage(rt, 1, mix_q, d);
+        L.x_k = stage(rt, 2, mix_k, d);
+        L.x_v = stage(rt, 3, mix_v, d);
+        L.e = stage(rt, 4, e, d);
+        auto lin = [&](PackedWeights& w, int slot, const uint32_t* b, const uint16_t* s, const uint16_t* bi) {
+            w.out = d; w.in = d;
+            w.bits = stage(rt, slot, b, words);
+            w.scale = stage(rt, slot + 1, s, d);
+            w.bias = stage(rt, slot + 2, bi, d);
+        };
+        lin(L.q, 5, q_bits, q_scale, q_bias);
+        lin(L.k, 8, k_bits, k_scale, k_bias);
+        lin(L.v, 11, v_bits, v_scale, v_bias);
+        lin(L.o, 14, o_bits, o_scale, o_bias);
+        // one allocation for the activations of this call
+        float* work = rt->pool[17].as<float>(n * 5);
+        float *bq = work, *bk = work + n, *bv = work + 2 * n, *w = work + 3 * n, *dout = work + 4 * n;
+        uint32_t* sws = rt->pool[18].as<uint32_t>(sw * 4);
+        uint32_t *qs = sws, *ks = sws + sw, *vs = sws + 2 * sw, *is = sws + 3 * sw;
+        rt->clear_status();
+        const bool exact = rt->mode == ULLIS_CUDA_MODE_EXACT;
+        if (exact || !tc::rosa_qkv_bits(rt, dx, L, qs, ks, vs, batch, time, d)) {
+            k::shift_mix(rt, dx, L.x_q, L.x_k, L.x_v, bq, bk, bv, rows, time, d);
+            k::binary_linear_exact(rt, bq, L.q.bits, L.q.scale, L.q.bias, w, rows, d, d, false);
+            k::sign_pack_streams(rt, w, qs, batch, time, d);
+            k::binary_linear_exact(rt, bk, L.k.bits, L.k.scale, L.k.bias, w, rows, d, d, false);
+            k::sign_pack_streams(rt, w, ks, batch, time, d);
+            k::binary_linear_exact(rt, bv, L.v.bits, L.v.scale, L.v.bias, w, rows, d, d, false);
+            k::sign_pack_streams(rt, w, vs, batch, time, d);
+        }
+        k::rosa_sam(rt, qs, ks, vs, is, batch * d, time);
+        uint8_t* didx = rt->pool[19].as<uint8_t>(n);
+        k::rosa_emit(rt, is, L.e, didx, w, batch, time, d);  // w <- y
+        packed_linear_dev(rt, w, L.o.bits, L.o.scale, L.o.bias, dout, rows, d, d);
+        const size_t plane_words = (n + 31) / 32;
+        uint32_t* dplane = rt->pool[20].as<uint32_t>(plane_words);
+        uint32_t* planes_out[3] = {q_plane, k_plane, v_plane};
+        uint32_t* planes_in[3] = {qs, ks, vs};
+        for (int i = 0; i < 3; ++i) {
+            if (!planes_out[i]) continue;
+            k::streams_to_planes(rt, planes_in[i], dplane, batch, time, d);
+            rt->d2h(planes_out[i], dplane, plane_words * 4);
+            rt->sync();  // dplane is reused
+        }
+        if (idx) rt->d2h(idx, didx, n);
+        if (y) rt->d2h(y, w, n * 4);
+        if (out) rt->d2h(out, dout, n * 4);
+        rt->check_status();
+    });
+}
+
+int32_t ullis_cuda_cmix_block_forward(ullis_cuda_runtime* rt, const float* x, const uint16_t* mix,
+                                      const uint32_t* key_bits, const uint16_t* key_scale,
+                                      const uint16_t* value, size_t batch, size_t time, size_t d_model,
+                                      size_t dim_ffn, float* out) {
+    return guard(rt, [&] {
+        if (batch == 0 || time == 0 || d_model == 0 || dim_ffn == 0) fail(ULLIS_CUDA_ERR_SHAPE, "CMix shape mismatch");
+        const size_t rows = mul_or_fail(batch, time, "CMix");
+        const size_t n = mul_or_fail(rows, d_model, "CMix");
+        const size_t nf = mul_or_fail(rows, dim_ffn, "CMix");
+        const size_t nw = mul_or_fail(d_model, dim_ffn, "CMix");
+        need_ptr(x, "x"); need_ptr(mix, "mix"); need_ptr(key_bits, "key_bits"); need_ptr(key_scale, "key_scale");
+        need_ptr(value, "value"); need_ptr(out, "out");
+        float* dx = stage(rt, 0, x, n);
+        uint16_t* dm = stage(rt, 1, mix, d_model);
+        uint32_t* dkb = stage(rt, 2, key_bits, (nw + 31) / 32);
+        uint16_t* dks = stage(rt, 3, key_scale, dim_ffn);
+        uint16_t* dv = stage(rt, 4, value, nw);
+        float* sh = rt->pool[5].as<float>(n);
+        float* key = rt->pool[6].as<float>(nf);
+        float* dout = rt->pool[7].as<float>(n);
+        k::shift_mix(rt, dx, dm, nullptr, nullptr, sh, nullptr, nullptr, rows, time, d_model);
+        packed_linear_dev(rt, sh, dkb, dks, nullptr, key, rows, d_model, dim_ffn);
+        k::relu2(rt, key, key, nf);
+        dense_linear_dev(rt, key, dv, dout, rows, dim_ffn, d_model);
+        rt->d2h(out, dout, n * 4);
+        rt->sync();
+    });
+}
+
+int32_t ullis_cuda_streamed_ce(ullis_cuda_runtime* rt, const float* hidden, const uint32_t* bits,
+                               const uint16_t* scale, const uint16_t* bias, const uint32_t* labels,
+                               uint32_t ignore_id, size_t rows, size_t time, size_t channels, size_t vocab,
+                               float* row_loss, float* mean_loss, uint64_t* n_valid) {
+    return guard(rt, [&] {
+        // reference: src/metal.rs:2932-2941
+        if (time == 0 || rows % time != 0 || channels == 0 || vocab == 0) fail(ULLIS_CUDA_ERR_SHAPE, "streamed CE shape mismatch");
+        const size_t nh = mul_or_fail(rows, channels, "streamed CE");
+        const size_t words = (mul_or_fail(vocab, channels, "streamed CE") + 31) / 32;
+        if (rows == 0) {
+            if (mean_loss) *mean_loss = 0.0f;
+            if (n_valid) *n_valid = 0;
+            return;
+        }
+        need_ptr(hidden, "hidden"); need_ptr(bits, "bits"); need_ptr(scale, "scale"); need_ptr(labels, "labels");
+        float* dh = stage(rt, 0, hidden, nh);
+        PackedWeights head;
+        head.out = vocab; head.in = channels;
+        head.bits = stage(rt, 1, bits, words);
+        head.scale = stage(rt, 2, scale, vocab);
+        head.bias = bias ? stage(rt, 3, bias, vocab) : nullptr;
+        uint32_t* dl = stage(rt, 4, labels, rows);
+        float* rl = rt->pool[5].as<float>(rows);
+        uint8_t* res = static_cast<uint8_t*>(rt->pool[6].ensure(16));
+        rt->clear_status();
+        if (rt->mode == ULLIS_CUDA_MODE_EXACT ||
+            !tc::head_ce(rt, dh, head, dl, ignore_id, rows, time, channels, vocab, rl)) {
+            const size_t chunk = std::max<size_t>(1, std::min<size_t>(rows, ((size_t)256 << 20) / (vocab * 4)));
+            float* lg = rt->pool[7].as<float>(chunk * vocab);
+            for (size_t r0 = 0; r0 < rows; r0 += chunk) {
+                const size_t nr = std::min(chunk, rows - r0);
+                k::binary_linear_exact(rt, dh + r0 * channels, head.bits, head.scale, head.bias, lg, nr, channels,
+                                       vocab, false);
+                k::ce_rows_from_logits(rt, lg, dl, ignore_id, r0, nr, rows, time, vocab, rl);
+            }
+        }
+        k::ce_reduce(rt, rl, dl, ignore_id, rows, time, reinterpret_cast<double*>(res),
+                     reinterpret_cast<unsigned long long*>(res + 8));
+        struct { double sum; unsigned long long n; } host;
+        rt->d2h(&host, res, 16);
+        if (row_loss) rt->d2h(row_loss, rl, rows * 4);
+        rt->check_status();
+        if (mean_loss) *mean_loss = host.n == 0 ? 0.0f : (float)(host.sum / (double)host.n);
+        if (n_valid) *n_valid = host.n;
+    });
+}
+
+}  // extern "C"

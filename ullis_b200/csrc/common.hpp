@@ -1,0 +1,107 @@
+// Host-side plumbing shared by the CUDA backend: status/exception type, the
+// runtime object behind `ullis_cuda_runtime`, and grow-only device buffers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/ullis_cuda.h"
+
+namespace ullis {
+
+struct Error {
+    int32_t code;
+    std::string msg;
+};
+
+[[noreturn]] inline void fail(int32_t code, const std::string& msg) { throw Error{code, msg}; }
+
+#define ULLIS_CUDA_CHECK(expr)                                                                   \
+    do {                                                                                         \
+        cudaError_t _e = (expr);                                                                 \
+        if (_e != cudaSuccess)                                                                   \
+            ::ullis::fail(ULLIS_CUDA_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
+    } while (0)
+
+// Grow-only device allocation (cudaMalloc'd; freed with the owner).
+class DeviceBuffer {
+   public:
+    DeviceBuffer() = default;
+    DeviceBuffer(const DeviceBuffer&) = delete;
+    DeviceBuffer& operator=(const DeviceBuffer&) = delete;
+    ~DeviceBuffer() { release(); }
+    void release() {
+        if (ptr_) cudaFree(ptr_);
+        ptr_ = nullptr;
+        bytes_ = 0;
+    }
+    void* ensure(size_t bytes) {
+        if (bytes > bytes_) {
+            release();
+            size_t want = (bytes + 255) / 256 * 256;
+            cudaError_t e = cudaMalloc(&ptr_, want);
+            if (e != cudaSuccess) {
+                ptr_ = nullptr;
+                cudaGetLastError();
+                fail(ULLIS_CUDA_ERR_NOMEM, "cudaMalloc of " + std::to_string(want) + " bytes failed: " +
+                                               cudaGetErrorString(e));
+            }
+            bytes_ = want;
+        }
+        return ptr_;
+    }
+    template <typename T>
+    T* as(size_t count) {
+        return static_cast<T*>(ensure(count * sizeof(T)));
+    }
+    void* get() const { return ptr_; }
+    size_t bytes() const { return bytes_; }
+
+   private:
+    void* ptr_ = nullptr;
+    size_t bytes_ = 0;
+};
+
+struct NcclState;  // dp.cpp
+
+}  // namespace ullis
+
+// Device-side status word layout (one per runtime, zeroed before each call
+// that uses it): 0 = ok, otherwise a kernel-specific code; slots 1..3 hold
+// details (e.g. the offending row / stream).
+enum { ULLIS_DEV_OK = 0, ULLIS_DEV_BAD_TOKEN = 1, ULLIS_DEV_SAM_CAPACITY = 2, ULLIS_DEV_SAM_NOMATCH = 3,
+       ULLIS_DEV_WAIT_TIMEOUT = 4 };
+
+struct ullis_cuda_runtime {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    int mode = ULLIS_CUDA_MODE_FAST;
+    int sam_algo = ULLIS_CUDA_SAM_EULER;
+    uint64_t launches = 0;
+    std::string last_error;
+    uint32_t* dev_status = nullptr;     // 4 words, device
+    uint32_t* host_status = nullptr;    // 4 words, pinned
+    ullis::DeviceBuffer pool[24];       // op-level scratch slots
+    ullis::DeviceBuffer sam_scratch;    // suffix-automaton state blocks
+    ullis::NcclState* nccl = nullptr;
+
+    void bind() const { ULLIS_CUDA_CHECK(cudaSetDevice(device)); }
+    void sync() { ULLIS_CUDA_CHECK(cudaStreamSynchronize(stream)); }
+    void h2d(void* dst, const void* src, size_t bytes) {
+        if (bytes) ULLIS_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, stream));
+    }
+    void d2h(void* dst, const void* src, size_t bytes) {
+        if (bytes) ULLIS_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, stream));
+    }
+    void zero(void* dst, size_t bytes) {
+        if (bytes) ULLIS_CUDA_CHECK(cudaMemsetAsync(dst, 0, bytes, stream));
+    }
+    void clear_status() { zero(dev_status, 16); }
+    // Synchronises and throws when a kernel reported a problem.
+    void check_status();
+    void launched(const char* what);  // counts a launch and checks the launch error
+};

@@ -1,0 +1,31 @@
+// Tensor-core (tcgen05 / TMEM) stages of the forward pass.  Each function
+// returns false without launching anything when it does not take the request
+// (validation mode, or a shape outside its tiling), in which case the caller
+// runs the CUDA-core kernels instead; nothing here ever computes on the host.
+#pragma once
+#include "model.hpp"
+
+namespace ullis {
+namespace tc {
+
+// y = bias + scale * (x . sign^T), x f32 [rows,K] on the device.
+bool binary_linear(ullis_cuda_runtime* rt, const float* x, const uint32_t* bits, const uint16_t* scale,
+                   const uint16_t* bias, float* y, size_t rows, size_t in_features, size_t out_features);
+// y = x . W^T, W FP16 [out,in].
+bool fp16_linear(ullis_cuda_runtime* rt, const float* x, const uint16_t* w, float* y, size_t rows,
+                 size_t in_features, size_t out_features);
+// ln3 output -> time-shift mixes -> packed Q,K,V -> stream-major sign bits.
+bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeights& L, uint32_t* q_sw,
+                   uint32_t* k_sw, uint32_t* v_sw, size_t batch, size_t time, size_t d);
+// x += O((2*idx-1)*e)
+bool rosa_out_residual(ullis_cuda_runtime* rt, const uint32_t* idx_sw, const LayerWeights& L, float* x,
+                       size_t batch, size_t time, size_t d);
+// x += value(relu(key(mix(ln2(x))))^2)
+bool cmix_residual(ullis_cuda_runtime* rt, const LayerWeights& L, float* x, size_t batch, size_t time, size_t d,
+                   size_t ffn);
+// row_loss from hidden without materialising logits.
+bool head_ce(ullis_cuda_runtime* rt, const float* hidden, const PackedWeights& head, const uint32_t* labels,
+             uint32_t ignore_id, size_t rows, size_t time, size_t d, size_t vocab, float* row_loss);
+
+}  // namespace tc
+}  // namespace ullis

@@ -1,0 +1,383 @@
+#include "model.hpp"
+
+#include <algorithm>
+#include <cstring>
+
+#include "kernels.hpp"
+#include "linear_tc.hpp"
+#include "safetensors.hpp"
+
+using namespace ullis;
+
+namespace {
+
+constexpr size_t MAX_CONTEXT_LEN = 32768;  // reference src/config.rs:6
+constexpr size_t MIN_VOCAB = 260;          // reference src/tokenizer.rs:34 (4 specials + 256 bytes)
+
+const TensorView& need(const SafeTensors& st, const std::string& name, const char* dtype, size_t elements,
+                       const char* what) {
+    auto it = st.tensors.find(name);
+    if (it == st.tensors.end()) fail(ULLIS_CUDA_ERR_CHECKPOINT, "checkpoint tensor " + name);
+    if (it->second.dtype != dtype)
+        fail(ULLIS_CUDA_ERR_CHECKPOINT, std::string("expected ") + dtype + " tensor, got " + it->second.dtype +
+                                            " (" + name + ")");
+    if (it->second.elements() != elements) fail(ULLIS_CUDA_ERR_CHECKPOINT, std::string(what) + " (" + name + ")");
+    return it->second;
+}
+
+struct ArenaPlan {
+    struct Item { const uint8_t* src; size_t bytes, offset; };
+    std::vector<Item> items;
+    size_t total = 0;
+    size_t add(const uint8_t* src, size_t bytes) {
+        size_t off = total;
+        items.push_back({src, bytes, off});
+        total = (total + bytes + 255) / 256 * 256;
+        return off;
+    }
+};
+
+}  // namespace
+
+ullis_cuda_model::~ullis_cuda_model() {
+    for (auto& s : spans) {
+        cudaEventDestroy(s.start);
+        cudaEventDestroy(s.stop);
+    }
+}
+
+// reference: from_safetensors_bytes (src/model.rs:3470-3553), require_v2
+// (2426-2431), TrainConfig::validate (src/config.rs:151-190, without the
+// host-memory admission, which is the trainer's policy for its own process),
+// validate_checkpoint_shapes (4402-4456), heron_from_checkpoint (4258-4309).
+void ullis_cuda_model::load(const uint8_t* bytes, size_t len) {
+    if (len && bytes[0] == '{')
+        fail(ULLIS_CUDA_ERR_CHECKPOINT, "JSON v2 checkpoints are not supported by the cuda backend; use checkpoint.safetensors");
+    SafeTensors st = parse_safetensors(bytes, len);
+    if (!st.has_metadata) fail(ULLIS_CUDA_ERR_CHECKPOINT, "safetensors checkpoint is missing metadata");
+    uint64_t version = 0;
+    {
+        auto it = st.metadata.find("format_version");
+        if (it != st.metadata.end()) {
+            char* endp = nullptr;
+            version = strtoull(it->second.c_str(), &endp, 10);
+            if (endp == it->second.c_str() || *endp) version = 0;
+        }
+    }
+    if (version != 2)
+        fail(ULLIS_CUDA_ERR_CHECKPOINT,
+             "Hyena checkpoints (v1) are intentionally unloadable after the RWKV-8 cut (got format_version " +
+                 std::to_string(version) + ")");
+    auto cit = st.metadata.find("config");
+    if (cit == st.metadata.end()) fail(ULLIS_CUDA_ERR_CHECKPOINT, "safetensors checkpoint is missing config");
+    Json cfg = parse_json(cit->second.data(), cit->second.size());
+    if (cfg.kind != Json::Object) fail(ULLIS_CUDA_ERR_CHECKPOINT, "parse safetensors checkpoint config");
+    if (const Json* arch = cfg.get("architecture"))
+        if (arch->kind != Json::String || arch->text != "heron")
+            fail(ULLIS_CUDA_ERR_CHECKPOINT, "the cuda backend implements the heron architecture only");
+    bool ok_d, ok_l, ok_v, ok_c, ok_b;
+    d = cfg.u64("d_model", 0, &ok_d);
+    layers = cfg.u64("n_layers", 0, &ok_l);
+    vocab = cfg.u64("vocab_size", 0, &ok_v);
+    context_len = cfg.u64("context_len", 0, &ok_c);
+    batch_size = cfg.u64("batch_size", 0, &ok_b);
+    if (!(ok_d && ok_l && ok_v && ok_c && ok_b)) fail(ULLIS_CUDA_ERR_CHECKPOINT, "parse safetensors checkpoint config");
+    ffn = cfg.u64("dim_ffn", 0);
+    if (ffn == 0) ffn = d * 4;  // src/config.rs:135-141
+    if (d == 0 || layers == 0) fail(ULLIS_CUDA_ERR_CHECKPOINT, "d_model and n_layers must be non-zero");
+    if (vocab < MIN_VOCAB) fail(ULLIS_CUDA_ERR_CHECKPOINT, "vocab_size must be at least " + std::to_string(MIN_VOCAB));
+    if (context_len == 0 || context_len > MAX_CONTEXT_LEN)
+        fail(ULLIS_CUDA_ERR_CHECKPOINT, "context_len must be in 1..=" + std::to_string(MAX_CONTEXT_LEN));
+    if (batch_size == 0) fail(ULLIS_CUDA_ERR_CHECKPOINT, "batch_size must be positive");
+    if (cfg.u64("rosa_bits", 1) != 1) fail(ULLIS_CUDA_ERR_CHECKPOINT, "rosa_bits must be 1 in Ullis 0.10");
+    if (cfg.u64("head_size", 16) != 16) fail(ULLIS_CUDA_ERR_CHECKPOINT, "head_size must be 16");
+    if (d > (1u << 20) || vocab > (1u << 24) || ffn > (1u << 22) || layers > 4096)
+        fail(ULLIS_CUDA_ERR_CHECKPOINT, "model size overflow");
+
+    size_t n_blocks = 0;
+    while (st.tensors.count("blocks." + std::to_string(n_blocks) + ".ln2.weight")) ++n_blocks;
+    if (n_blocks != layers || st.tensors.count("hybrid_blocks.0.ln_a.weight"))
+        fail(ULLIS_CUDA_ERR_CHECKPOINT, "heron checkpoint must store exactly n_layers Heron blocks");
+
+    ArenaPlan plan;
+    struct Fix { const void** slot; size_t offset; };
+    std::vector<Fix> fixes;
+    auto put = [&](const void** slot, const TensorView& v) { fixes.push_back({slot, plan.add(v.data, v.bytes)}); };
+    auto f16 = [&](const void** slot, const std::string& name, size_t n, const char* what) {
+        put(slot, need(st, name, "F16", n, what));
+    };
+    auto ln = [&](LayerNormWeights& w, const std::string& prefix) {
+        f16((const void**)&w.weight, prefix + ".weight", d, "checkpoint LayerNorm shape mismatch");
+        f16((const void**)&w.bias, prefix + ".bias", d, "checkpoint LayerNorm shape mismatch");
+    };
+    // bias: 1 required, 0 forbidden, -1 optional (head: absent loads as zeros)
+    std::vector<uint8_t> zero_bias;
+    auto packed = [&](PackedWeights& w, const std::string& prefix, size_t out, size_t in, int bias) {
+        w.out = out;
+        w.in = in;
+        put((const void**)&w.bits, need(st, prefix + ".bits", "U32", (out * in + 31) / 32,
+                                        "checkpoint packed-linear shape mismatch"));
+        f16((const void**)&w.scale, prefix + ".scale", out, "checkpoint packed-linear shape mismatch");
+        const bool has = st.tensors.count(prefix + ".bias") != 0;
+        if ((bias == 1 && !has) || (bias == 0 && has))
+            fail(ULLIS_CUDA_ERR_CHECKPOINT, "checkpoint packed-linear bias mismatch (" + prefix + ")");
+        if (has) {
+            f16((const void**)&w.bias, prefix + ".bias", out, "checkpoint packed-linear bias mismatch");
+        } else if (bias == -1) {
+            zero_bias.assign(out * 2, 0);
+            fixes.push_back({(const void**)&w.bias, plan.add(zero_bias.data(), zero_bias.size())});
+        }
+    };
+
+    blocks.assign(layers, LayerWeights{});
+    f16((const void**)&embedding, "embedding", vocab * d, "checkpoint embedding shape does not match its configuration");
+    ln(ln_out, "ln_out");
+    packed(head, "head", vocab, d, -1);
+    for (size_t i = 0; i < layers; ++i) {
+        const std::string pre = "blocks." + std::to_string(i);
+        LayerWeights& L = blocks[i];
+        const bool has_ln0 = st.tensors.count(pre + ".ln0.weight") != 0;
+        if (has_ln0 != (i == 0)) fail(ULLIS_CUDA_ERR_CHECKPOINT, "ln0 must be present only on Heron layer 0");
+        if (has_ln0) ln(L.ln0, pre + ".ln0");
+        ln(L.ln2, pre + ".ln2");
+        ln(L.ln3, pre + ".ln3");
+        f16((const void**)&L.x_q, pre + ".rosa.x_q", d, "checkpoint x_q length mismatch");
+        f16((const void**)&L.x_k, pre + ".rosa.x_k", d, "checkpoint x_k length mismatch");
+        f16((const void**)&L.x_v, pre + ".rosa.x_v", d, "checkpoint x_v length mismatch");
+        f16((const void**)&L.e, pre + ".rosa.e", d, "checkpoint e length mismatch");
+        packed(L.q, pre + ".rosa.q", d, d, 1);
+        packed(L.k, pre + ".rosa.k", d, d, 1);
+        packed(L.v, pre + ".rosa.v", d, d, 1);
+        packed(L.o, pre + ".rosa.o", d, d, 1);
+        f16((const void**)&L.ffn_x_k, pre + ".ffn.x_k", d, "checkpoint cmix.x_k length mismatch");
+        packed(L.key, pre + ".ffn.key", ffn, d, 0);
+        f16((const void**)&L.value, pre + ".ffn.value", ffn * d, "checkpoint cmix.value length mismatch");
+    }
+
+    rt->bind();
+    uint8_t* base = static_cast<uint8_t*>(arena.ensure(plan.total ? plan.total : 256));
+    for (const auto& it : plan.items) rt->h2d(base + it.offset, it.src, it.bytes);
+    rt->sync();  // sources (file bytes, zero_bias) may go away after return
+    for (const auto& f : fixes) *f.slot = base + f.offset;
+}
+
+void ullis_cuda_model::check_shape(size_t batch, size_t time) const {
+    // reference src/model.rs:2649-2656
+    if (batch == 0 || batch > batch_size || time == 0 || time > context_len)
+        fail(ULLIS_CUDA_ERR_SHAPE, "token shape or context length is invalid");
+}
+
+void ullis_cuda_model::upload_tokens(const uint32_t* tokens, const uint32_t* lab, size_t batch, size_t time) {
+    check_shape(batch, time);
+    if (!tokens) fail(ULLIS_CUDA_ERR_ARG, "tokens is null");
+    const size_t rows = batch * time;
+    for (size_t r = 0; r < rows; ++r)
+        if (tokens[r] >= vocab) fail(ULLIS_CUDA_ERR_TOKEN, "token id exceeds vocabulary");
+    rt->bind();
+    rt->h2d(ids.as<uint32_t>(rows), tokens, rows * 4);
+    if (lab) rt->h2d(labels.as<uint32_t>(rows), lab, rows * 4);
+    cur_batch = batch;
+    cur_time = time;
+    have_result = false;
+}
+
+void ullis_cuda_model::begin(int phase) {
+    if (!profile) return;
+    if (spans_used == spans.size()) {
+        Span s{phase, nullptr, nullptr};
+        ULLIS_CUDA_CHECK(cudaEventCreate(&s.start));
+        ULLIS_CUDA_CHECK(cudaEventCreate(&s.stop));
+        spans.push_back(s);
+    }
+    spans[spans_used].phase = phase;
+    ULLIS_CUDA_CHECK(cudaEventRecord(spans[spans_used].start, rt->stream));
+}
+
+void ullis_cuda_model::end() {
+    if (!profile) return;
+    ULLIS_CUDA_CHECK(cudaEventRecord(spans[spans_used].stop, rt->stream));
+    ++spans_used;
+}
+
+void ullis_cuda_model::phase_ms(float ms[6]) {
+    for (int i = 0; i < 6; ++i) ms[i] = 0.0f;
+    rt->sync();
+    for (size_t i = 0; i < spans_used; ++i) {
+        float t = 0.0f;
+        ULLIS_CUDA_CHECK(cudaEventElapsedTime(&t, spans[i].start, spans[i].stop));
+        ms[spans[i].phase] += t;
+    }
+}
+
+void ullis_cuda_model::save_tap(int layer, int which, const void* src, size_t bytes) {
+    if (!taps_enabled) return;
+    const size_t slot = which == ULLIS_CUDA_TAP_HIDDEN ? layers * 8 : (size_t)layer * 8 + (size_t)which;
+    void* dst = tap_bufs[slot].ensure(bytes);
+    ULLIS_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, rt->stream));
+}
+
+void ullis_cuda_model::save_tap_bits(int layer, int which, const uint32_t* sw, size_t batch, size_t time) {
+    if (!taps_enabled) return;
+    const size_t slot = (size_t)layer * 8 + (size_t)which;
+    uint8_t* dst = tap_bufs[slot].as<uint8_t>(batch * time * d);
+    k::rosa_emit(rt, sw, nullptr, dst, nullptr, batch, time, d);
+}
+
+void ullis_cuda_model::tap(int layer, int which, void* out, size_t bytes) {
+    if (which < 0 || which > ULLIS_CUDA_TAP_HIDDEN) fail(ULLIS_CUDA_ERR_ARG, "unknown tap");
+    if (which != ULLIS_CUDA_TAP_HIDDEN && (layer < 0 || (size_t)layer >= layers))
+        fail(ULLIS_CUDA_ERR_ARG, "tap layer out of range");
+    if (tap_bufs.empty()) fail(ULLIS_CUDA_ERR_ARG, "taps were not enabled for the last forward");
+    const size_t slot = which == ULLIS_CUDA_TAP_HIDDEN ? layers * 8 : (size_t)layer * 8 + (size_t)which;
+    const bool is_u8 = which >= ULLIS_CUDA_TAP_Q_BITS && which <= ULLIS_CUDA_TAP_IDX;
+    const size_t want = tap_rows * d * (is_u8 ? 1 : 4);
+    if (!tap_bufs[slot].get() || want == 0) fail(ULLIS_CUDA_ERR_ARG, "taps were not enabled for the last forward");
+    if (bytes != want) fail(ULLIS_CUDA_ERR_SHAPE, "tap size mismatch: expected " + std::to_string(want) + " bytes");
+    rt->bind();
+    rt->d2h(out, tap_bufs[slot].get(), bytes);
+    rt->sync();
+}
+
+// UllisHeron::hidden (src/model.rs:2644-2683) with HeronBlock::forward
+// (2224-2241), RwkvRosaQkv1Bit::forward (1284-1318), RwkvCMixX070::forward
+// (987-1001).  The residual stream `x` stays on the device for the whole pass.
+void ullis_cuda_model::enqueue_hidden(size_t batch, size_t time) {
+    check_shape(batch, time);
+    if (batch != cur_batch || time != cur_time) fail(ULLIS_CUDA_ERR_SHAPE, "upload_tokens was not called for this shape");
+    rt->bind();
+    const size_t rows = batch * time, n = rows * d;
+    const bool exact = rt->mode == ULLIS_CUDA_MODE_EXACT;
+    const size_t wps = (time + 31) / 32, sw_words = batch * d * wps;
+    float* X = x.as<float>(n);
+    float* A = a.as<float>(n);
+    float* Bq = b.as<float>(n);
+    float* Bk = c.as<float>(n);
+    float* Bv = dd.as<float>(n);
+    float* W = wide.as<float>(rows * std::max(ffn, d));
+    uint32_t* QS = q_sw.as<uint32_t>(sw_words);
+    uint32_t* KS = k_sw.as<uint32_t>(sw_words);
+    uint32_t* VS = v_sw.as<uint32_t>(sw_words);
+    uint32_t* IS = idx_sw.as<uint32_t>(sw_words);
+    if (taps_enabled) {
+        if (tap_bufs.size() != layers * 8 + 1) tap_bufs = std::vector<DeviceBuffer>(layers * 8 + 1);
+        tap_rows = rows;
+    }
+    spans_used = 0;
+    rt->clear_status();
+
+    begin(PH_EMBED_LN);
+    k::embed(rt, ids.as<uint32_t>(rows), embedding, X, rows, d, vocab);
+    end();
+    for (size_t l = 0; l < layers; ++l) {
+        const LayerWeights& L = blocks[l];
+        begin(PH_EMBED_LN);
+        if (l == 0) {  // ln0 REPLACES x on layer 0 (src/model.rs:2225-2229)
+            k::layer_norm(rt, X, L.ln0.weight, L.ln0.bias, A, rows, d, exact);
+            ULLIS_CUDA_CHECK(cudaMemcpyAsync(X, A, n * 4, cudaMemcpyDeviceToDevice, rt->stream));
+        }
+        save_tap((int)l, ULLIS_CUDA_TAP_BLOCK_IN, X, n * 4);
+        k::layer_norm(rt, X, L.ln3.weight, L.ln3.bias, A, rows, d, exact);
+        save_tap((int)l, ULLIS_CUDA_TAP_LN3_OUT, A, n * 4);
+        end();
+
+        begin(PH_QKV);
+        if (!tc::rosa_qkv_bits(rt, A, L, QS, KS, VS, batch, time, d)) {
+            k::shift_mix(rt, A, L.x_q, L.x_k, L.x_v, Bq, Bk, Bv, rows, time, d);
+            k::binary_linear_exact(rt, Bq, L.q.bits, L.q.scale, L.q.bias, W, rows, d, d, false);
+            k::sign_pack_streams(rt, W, QS, batch, time, d);
+            k::binary_linear_exact(rt, Bk, L.k.bits, L.k.scale, L.k.bias, W, rows, d, d, false);
+            k::sign_pack_streams(rt, W, KS, batch, time, d);
+            k::binary_linear_exact(rt, Bv, L.v.bits, L.v.scale, L.v.bias, W, rows, d, d, false);
+            k::sign_pack_streams(rt, W, VS, batch, time, d);
+        }
+        save_tap_bits((int)l, ULLIS_CUDA_TAP_Q_BITS, QS, batch, time);
+        save_tap_bits((int)l, ULLIS_CUDA_TAP_K_BITS, KS, batch, time);
+        save_tap_bits((int)l, ULLIS_CUDA_TAP_V_BITS, VS, batch, time);
+        end();
+
+        begin(PH_SAM);
+        k::rosa_sam(rt, QS, KS, VS, IS, batch * d, time);
+        save_tap_bits((int)l, ULLIS_CUDA_TAP_IDX, IS, batch, time);
+        end();
+
+        begin(PH_O);
+        if (!tc::rosa_out_residual(rt, IS, L, X, batch, time, d)) {
+            k::rosa_emit(rt, IS, L.e, nullptr, A, batch, time, d);
+            k::binary_linear_exact(rt, A, L.o.bits, L.o.scale, L.o.bias, X, rows, d, d, true);  // x += rosa out
+        }
+        save_tap((int)l, ULLIS_CUDA_TAP_AFTER_ROSA, X, n * 4);
+        end();
+
+        begin(PH_CMIX);
+        if (!tc::cmix_residual(rt, L, X, batch, time, d, ffn)) {
+            k::layer_norm(rt, X, L.ln2.weight, L.ln2.bias, A, rows, d, exact);
+            k::shift_mix(rt, A, L.ffn_x_k, nullptr, nullptr, Bq, nullptr, nullptr, rows, time, d);
+            k::binary_linear_exact(rt, Bq, L.key.bits, L.key.scale, nullptr, W, rows, d, ffn, false);
+            k::relu2(rt, W, W, rows * ffn);
+            k::fp16_linear_exact(rt, W, L.value, X, rows, ffn, d, true);  // x += cmix out
+        }
+        save_tap((int)l, ULLIS_CUDA_TAP_BLOCK_OUT, X, n * 4);
+        end();
+    }
+    begin(PH_HEAD_CE);
+    k::layer_norm(rt, X, ln_out.weight, ln_out.bias, A, rows, d, exact);
+    save_tap(0, ULLIS_CUDA_TAP_HIDDEN, A, n * 4);
+    end();
+}
+
+// CE forward of apply_head_ce (src/model.rs:3205-3228, 3253-3257).
+void ullis_cuda_model::enqueue_forward_ce(uint32_t ignore_id, size_t batch, size_t time) {
+    enqueue_hidden(batch, time);
+    const size_t rows = batch * time;
+    if (!labels.get() || labels.bytes() < rows * 4) fail(ULLIS_CUDA_ERR_ARG, "labels were not uploaded");
+    float* A = a.as<float>(rows * d);
+    float* RL = row_loss.as<float>(rows);
+    uint8_t* res = static_cast<uint8_t*>(result.ensure(16));
+    const uint32_t* lab = labels.as<uint32_t>(rows);
+    begin(PH_HEAD_CE);
+    if (!tc::head_ce(rt, A, head, lab, ignore_id, rows, time, d, vocab, RL)) {
+        const size_t chunk = std::max<size_t>(1, std::min<size_t>(rows, ((size_t)256 << 20) / (vocab * 4)));
+        float* LG = logits.as<float>(chunk * vocab);
+        for (size_t r0 = 0; r0 < rows; r0 += chunk) {
+            const size_t nr = std::min(chunk, rows - r0);
+            k::binary_linear_exact(rt, A + r0 * d, head.bits, head.scale, head.bias, LG, nr, d, vocab, false);
+            k::ce_rows_from_logits(rt, LG, lab, ignore_id, r0, nr, rows, time, vocab, RL);
+        }
+    }
+    k::ce_reduce(rt, RL, lab, ignore_id, rows, time, reinterpret_cast<double*>(res),
+                 reinterpret_cast<unsigned long long*>(res + 8));
+    end();
+    have_result = true;
+}
+
+void ullis_cuda_model::read_loss(float* mean_loss, double* loss_sum, uint64_t* n_valid, float* rl, size_t rows) {
+    if (!have_result) fail(ULLIS_CUDA_ERR_ARG, "no forward_ce result to read");
+    rt->bind();
+    struct { double sum; unsigned long long n; } host;
+    rt->d2h(&host, result.get(), 16);
+    if (rl) {
+        if (rows != cur_batch * cur_time) fail(ULLIS_CUDA_ERR_SHAPE, "row_loss length mismatch");
+        rt->d2h(rl, row_loss.get(), rows * 4);
+    }
+    rt->check_status();  // synchronises
+    if (loss_sum) *loss_sum = host.sum;
+    if (n_valid) *n_valid = host.n;
+    if (mean_loss) *mean_loss = host.n == 0 ? 0.0f : (float)(host.sum / (double)host.n);
+}
+
+// UllisHeron::logits (src/model.rs:2685-2688)
+void ullis_cuda_model::enqueue_logits(size_t batch, size_t time, float* host_logits) {
+    enqueue_hidden(batch, time);
+    const size_t rows = batch * time;
+    float* A = a.as<float>(rows * d);
+    const size_t chunk = std::max<size_t>(1, std::min<size_t>(rows, ((size_t)256 << 20) / (vocab * 4)));
+    float* LG = logits.as<float>(chunk * vocab);
+    for (size_t r0 = 0; r0 < rows; r0 += chunk) {
+        const size_t nr = std::min(chunk, rows - r0);
+        if (!tc::binary_linear(rt, A + r0 * d, head.bits, head.scale, head.bias, LG, nr, d, vocab))
+            k::binary_linear_exact(rt, A + r0 * d, head.bits, head.scale, head.bias, LG, nr, d, vocab, false);
+        rt->d2h(host_logits + r0 * vocab, LG, nr * vocab * 4);
+        rt->sync();  // LG is reused by the next chunk
+    }
+    rt->check_status();
+}

@@ -1,0 +1,94 @@
+// ROSA 1-bit suffix-automaton match on the GPU: one thread per (sequence,
+// channel) stream, automaton state in a per-stream block of global scratch
+// (compact 16-bit state ids whenever 2T+2 <= 65535), bit streams read and idx
+// bits written as stream-major 32-step words.  The per-stream algorithm lives
+// in sam_core.cuh; results equal T pushes of the reference's RosaSam
+// (src/rosa.rs:100-176) for every stream.
+//
+// Streams are processed in waves sized to the scratch budget, so any batch
+// works; all waves are enqueued back to back on the runtime stream.
+#include "kernels.hpp"
+#include "sam_core.cuh"
+
+namespace ullis {
+namespace k {
+
+namespace {
+
+template <typename Ix, int ALGO>
+__global__ void __launch_bounds__(64)
+rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
+                const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ v_sw,
+                uint32_t* __restrict__ idx_sw, size_t streams, uint32_t T, size_t wps) {
+    const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= streams) return;
+    uint8_t* block = scratch + s * scratch_stride;
+    const uint32_t* qw = q_sw + s * wps;
+    const uint32_t* kw = k_sw + s * wps;
+    const uint32_t* vw = v_sw + s * wps;
+    uint32_t* out = idx_sw + s * wps;
+    if (ALGO == ULLIS_CUDA_SAM_EAGER)
+        sam::run_eager<Ix>(block, qw, kw, vw, out, T, nullptr);
+    else
+        sam::run_euler<Ix>(block, qw, kw, vw, out, T, nullptr);
+}
+
+template <typename Ix>
+size_t stride_for(int algo, size_t T) {
+    return algo == ULLIS_CUDA_SAM_EAGER ? sam::EagerLayout<Ix>((uint32_t)T).total
+                                        : sam::EulerLayout<Ix>((uint32_t)T).total;
+}
+
+}  // namespace
+
+size_t rosa_sam_scratch_bytes_per_stream(int algo, size_t time) {
+    const bool narrow = sam::node_capacity((uint32_t)time) <= 0xFFFFu;
+    return narrow ? stride_for<uint16_t>(algo, time) : stride_for<uint32_t>(algo, time);
+}
+
+void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw, const uint32_t* v_sw,
+              uint32_t* idx_sw, size_t streams, size_t time) {
+    if (streams == 0 || time == 0) return;
+    if (time > 0x3FFFFFFFu) fail(ULLIS_CUDA_ERR_SHAPE, "ROSA time does not fit 32-bit state ids");
+    const int algo = rt->sam_algo;
+    const bool narrow = sam::node_capacity((uint32_t)time) <= 0xFFFFu;
+    const size_t stride = rosa_sam_scratch_bytes_per_stream(algo, time);
+    const size_t wps = (time + 31) / 32;
+    // wave size: bounded scratch (default 12 GiB, or what fits in free memory)
+    size_t free_b = 0, total_b = 0;
+    ULLIS_CUDA_CHECK(cudaMemGetInfo(&free_b, &total_b));
+    size_t budget = (size_t)12 << 30;
+    const size_t avail = free_b + rt->sam_scratch.bytes();  // what the scratch buffer could grow to
+    if (avail < budget + ((size_t)2 << 30)) budget = avail > ((size_t)4 << 30) ? avail - ((size_t)2 << 30) : avail / 2;
+    size_t wave = budget / stride;
+    if (wave == 0) fail(ULLIS_CUDA_ERR_NOMEM, "not enough device memory for one suffix-automaton state block");
+    if (wave > streams) wave = streams;
+    uint8_t* scratch = static_cast<uint8_t*>(rt->sam_scratch.ensure(wave * stride));
+    for (size_t s0 = 0; s0 < streams; s0 += wave) {
+        const size_t n = streams - s0 < wave ? streams - s0 : wave;
+        const unsigned grid = (unsigned)((n + 63) / 64);
+        const uint32_t* q = q_sw + s0 * wps;
+        const uint32_t* kk = k_sw + s0 * wps;
+        const uint32_t* v = v_sw + s0 * wps;
+        uint32_t* o = idx_sw + s0 * wps;
+        if (narrow) {
+            if (algo == ULLIS_CUDA_SAM_EAGER)
+                rosa_sam_kernel<uint16_t, ULLIS_CUDA_SAM_EAGER><<<grid, 64, 0, rt->stream>>>(
+                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps);
+            else
+                rosa_sam_kernel<uint16_t, ULLIS_CUDA_SAM_EULER><<<grid, 64, 0, rt->stream>>>(
+                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps);
+        } else {
+            if (algo == ULLIS_CUDA_SAM_EAGER)
+                rosa_sam_kernel<uint32_t, ULLIS_CUDA_SAM_EAGER><<<grid, 64, 0, rt->stream>>>(
+                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps);
+            else
+                rosa_sam_kernel<uint32_t, ULLIS_CUDA_SAM_EULER><<<grid, 64, 0, rt->stream>>>(
+                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps);
+        }
+        rt->launched("rosa_sam");
+    }
+}
+
+}  // namespace k
+}  // namespace ullis

@@ -1,0 +1,379 @@
+"""Host-side mirror of the reference's backend interface for the `cuda`
+backend, over the C ABI of libullis_cuda.so (include/ullis_cuda.h).
+
+`CudaRuntime` plays the role `MetalRuntime` plays in the reference
+(src/metal.rs:452-457): one object per device whose methods take host arrays
+and return host arrays, one synchronous call each, same names and argument
+meaning (`layer_norm`, `binary_linear`, `rosa_qkv_1bit_fwd`,
+`rosa_block_forward`, `cmix_block_forward`, ...).  `CudaHeron` is the
+device-resident whole-model entry point (UllisHeron::hidden / logits and the
+CE forward, src/model.rs:2644-2688, 3205-3228).  Failures raise
+`UllisCudaError` carrying the ABI status code and message, the way the
+reference's methods return `Err(anyhow!(..))`.
+
+There is no CPU fallback: if the shared library is missing, or no CUDA device
+is present, construction fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libullis_cuda.so")
+
+OK, ERR_SHAPE, ERR_CHECKPOINT, ERR_CUDA, ERR_DEVICE_CHECK, ERR_NCCL, ERR_TIMEOUT, ERR_ARG, ERR_TOKEN, ERR_NOMEM = range(10)
+MODE_FAST, MODE_EXACT = 0, 1
+SAM_EULER, SAM_EAGER = 0, 1
+CE_NO_IGNORE = 0xFFFFFFFF  # reference src/model.rs:24
+TAPS = {"block_in": 0, "ln3_out": 1, "q_bits": 2, "k_bits": 3, "v_bits": 4, "idx": 5, "after_rosa": 6,
+        "block_out": 7, "hidden": 8}
+PHASES = ("embed_ln", "qkv", "sam", "o", "cmix", "head_ce")
+
+# every symbol include/ullis_cuda.h declares
+ABI_SYMBOLS = (
+    "ullis_cuda_runtime_create", "ullis_cuda_runtime_destroy", "ullis_cuda_last_error",
+    "ullis_cuda_runtime_set_mode", "ullis_cuda_runtime_set_sam", "ullis_cuda_runtime_synchronize",
+    "ullis_cuda_runtime_stream", "ullis_cuda_runtime_launch_count", "ullis_cuda_runtime_is_sm100",
+    "ullis_cuda_model_load_safetensors", "ullis_cuda_model_destroy", "ullis_cuda_model_dims",
+    "ullis_cuda_model_forward_ce", "ullis_cuda_model_upload_tokens", "ullis_cuda_model_enqueue_forward_ce",
+    "ullis_cuda_model_read_loss", "ullis_cuda_model_logits", "ullis_cuda_model_hidden",
+    "ullis_cuda_model_set_taps", "ullis_cuda_model_tap", "ullis_cuda_model_set_profile",
+    "ullis_cuda_model_phase_ms", "ullis_cuda_layer_norm", "ullis_cuda_time_shift_delta",
+    "ullis_cuda_binary_linear", "ullis_cuda_fp16_linear", "ullis_cuda_sign_pack_bits", "ullis_cuda_cmix_relu2",
+    "ullis_cuda_residual_add", "ullis_cuda_rosa_qkv_1bit_fwd", "ullis_cuda_rosa_block_forward",
+    "ullis_cuda_cmix_block_forward", "ullis_cuda_streamed_ce", "ullis_cuda_dp_unique_id", "ullis_cuda_dp_init",
+    "ullis_cuda_dp_allreduce_loss", "ullis_cuda_dp_finalize",
+)
+
+
+class UllisCudaError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[ullis-cuda {code}] {message}")
+        self.code = code
+        self.message = message
+
+
+_LIB = None
+
+
+def load_library() -> C.CDLL:
+    """Loads libullis_cuda.so (never builds, never falls back)."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise UllisCudaError(ERR_ARG, f"{LIB_PATH} is missing: build it with `python -m ullis_b200.build`")
+        lib = C.CDLL(LIB_PATH)
+        lib.ullis_cuda_last_error.restype = C.c_char_p
+        lib.ullis_cuda_last_error.argtypes = [C.c_void_p]
+        lib.ullis_cuda_runtime_stream.restype = C.c_void_p
+        lib.ullis_cuda_runtime_stream.argtypes = [C.c_void_p]
+        lib.ullis_cuda_runtime_launch_count.restype = C.c_uint64
+        lib.ullis_cuda_runtime_launch_count.argtypes = [C.c_void_p]
+        lib.ullis_cuda_runtime_destroy.restype = None
+        lib.ullis_cuda_runtime_destroy.argtypes = [C.c_void_p]
+        lib.ullis_cuda_model_destroy.restype = None
+        lib.ullis_cuda_model_destroy.argtypes = [C.c_void_p]
+        _LIB = lib
+    return _LIB
+
+
+def _ptr(a):
+    return None if a is None else C.c_void_p(a.ctypes.data)
+
+
+def _arr(a, dtype, name, size=None, allow_none=False):
+    if a is None:
+        if allow_none:
+            return None
+        raise UllisCudaError(ERR_ARG, f"{name} is null")
+    a = np.ascontiguousarray(a, dtype=dtype).reshape(-1)
+    if size is not None and a.size != size:
+        raise UllisCudaError(ERR_SHAPE, f"{name} length mismatch: got {a.size}, expected {size}")
+    return a
+
+
+def _z(n):
+    return C.c_size_t(int(n))
+
+
+class CudaRuntime:
+    """One per device per process, used from one thread (like MetalRuntime)."""
+
+    def __init__(self, device: int = 0):
+        self._lib = load_library()
+        h = C.c_void_p()
+        rc = self._lib.ullis_cuda_runtime_create(C.c_int32(device), C.byref(h))
+        if rc != OK:
+            raise UllisCudaError(rc, self._lib.ullis_cuda_last_error(None).decode())
+        self._h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.ullis_cuda_runtime_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass
+
+    def _check(self, rc: int):
+        if rc != OK:
+            raise UllisCudaError(rc, self._lib.ullis_cuda_last_error(self._h).decode())
+
+    # ---- options / introspection
+    def set_mode(self, mode: int):
+        self._check(self._lib.ullis_cuda_runtime_set_mode(self._h, C.c_int32(mode)))
+
+    def set_sam(self, algo: int):
+        self._check(self._lib.ullis_cuda_runtime_set_sam(self._h, C.c_int32(algo)))
+
+    def synchronize(self):
+        self._check(self._lib.ullis_cuda_runtime_synchronize(self._h))
+
+    @property
+    def stream(self) -> int:
+        return int(self._lib.ullis_cuda_runtime_stream(self._h) or 0)
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.ullis_cuda_runtime_launch_count(self._h))
+
+    @property
+    def is_sm100(self) -> bool:
+        return bool(self._lib.ullis_cuda_runtime_is_sm100(self._h))
+
+    # ---- op level (names and argument meaning of MetalRuntime's methods)
+    def layer_norm(self, x, weight_bits, bias_bits, rows: int, channels: int) -> np.ndarray:
+        x = _arr(x, np.float32, "x", rows * channels)
+        w = _arr(weight_bits, np.uint16, "weight", channels)
+        b = _arr(bias_bits, np.uint16, "bias", channels)
+        y = np.empty(rows * channels, np.float32)
+        self._check(self._lib.ullis_cuda_layer_norm(self._h, _ptr(x), _ptr(w), _ptr(b), _ptr(y), _z(rows), _z(channels)))
+        return y
+
+    def time_shift_delta(self, x, rows: int, time: int, channels: int) -> np.ndarray:
+        x = _arr(x, np.float32, "x", rows * channels)
+        xx = np.empty(rows * channels, np.float32)
+        self._check(self._lib.ullis_cuda_time_shift_delta(self._h, _ptr(x), _ptr(xx), _z(rows), _z(time), _z(channels)))
+        return xx
+
+    def binary_linear(self, x, bits, scale_bits, bias_bits, rows: int, in_features: int, out_features: int):
+        x = _arr(x, np.float32, "x", rows * in_features)
+        bits = _arr(bits, np.uint32, "bits", (in_features * out_features + 31) // 32)
+        s = _arr(scale_bits, np.uint16, "scale", out_features)
+        b = _arr(bias_bits, np.uint16, "bias", out_features, allow_none=True)
+        y = np.empty(rows * out_features, np.float32)
+        self._check(self._lib.ullis_cuda_binary_linear(self._h, _ptr(x), _ptr(bits), _ptr(s), _ptr(b), _ptr(y),
+                                                       _z(rows), _z(in_features), _z(out_features)))
+        return y
+
+    def fp16_linear(self, x, weight_bits, rows: int, in_features: int, out_features: int) -> np.ndarray:
+        x = _arr(x, np.float32, "x", rows * in_features)
+        w = _arr(weight_bits, np.uint16, "weight", in_features * out_features)
+        y = np.empty(rows * out_features, np.float32)
+        self._check(self._lib.ullis_cuda_fp16_linear(self._h, _ptr(x), _ptr(w), _ptr(y), _z(rows), _z(in_features),
+                                                     _z(out_features)))
+        return y
+
+    def sign_pack_bits(self, x) -> np.ndarray:
+        x = _arr(x, np.float32, "x")
+        bits = np.zeros((x.size + 31) // 32, np.uint32)
+        self._check(self._lib.ullis_cuda_sign_pack_bits(self._h, _ptr(x), _ptr(bits), _z(x.size)))
+        return bits
+
+    def cmix_relu2(self, x) -> np.ndarray:
+        x = _arr(x, np.float32, "x")
+        y = np.empty(x.size, np.float32)
+        self._check(self._lib.ullis_cuda_cmix_relu2(self._h, _ptr(x), _ptr(y), _z(x.size)))
+        return y
+
+    def residual_add(self, residual, update) -> np.ndarray:
+        a = _arr(residual, np.float32, "residual")
+        b = _arr(update, np.float32, "update", a.size)
+        out = np.empty(a.size, np.float32)
+        self._check(self._lib.ullis_cuda_residual_add(self._h, _ptr(a), _ptr(b), _ptr(out), _z(a.size)))
+        return out
+
+    def rosa_qkv_1bit_fwd(self, q_bits, k_bits, v_bits, e_bits, batch: int, time: int, channels: int):
+        """Returns (idx u8 [B,T,C], out f32 [B,T,C]) like RosaQkvForward{idx,out}
+        (src/metal.rs:253-256)."""
+        n = batch * time * channels
+        words = (n + 31) // 32
+        q = _arr(q_bits, np.uint32, "q_bits", words)
+        k = _arr(k_bits, np.uint32, "k_bits", words)
+        v = _arr(v_bits, np.uint32, "v_bits", words)
+        e = _arr(e_bits, np.uint16, "e", channels)
+        idx = np.empty(n, np.uint8)
+        out = np.empty(n, np.float32)
+        self._check(self._lib.ullis_cuda_rosa_qkv_1bit_fwd(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(e), _ptr(idx),
+                                                           _ptr(out), _z(batch), _z(time), _z(channels)))
+        return idx, out
+
+    def rosa_block_forward(self, x, p: dict, batch: int, time: int, channels: int) -> dict:
+        """p: x_q, x_k, x_v, e (FP16 bits) and q/k/v/o dicts of bits, scale, bias.
+        Returns q_plane, k_plane, v_plane (packed [B,T,C] sign planes), idx, y, out."""
+        d = channels
+        n = batch * time * d
+        x = _arr(x, np.float32, "x", n)
+        args = [_arr(p[m], np.uint16, m, d) for m in ("x_q", "x_k", "x_v")]
+        lin = []
+        for m in ("q", "k", "v"):
+            lin += [_arr(p[m]["bits"], np.uint32, m + ".bits", (d * d + 31) // 32),
+                    _arr(p[m]["scale"], np.uint16, m + ".scale", d), _arr(p[m]["bias"], np.uint16, m + ".bias", d)]
+        e = _arr(p["e"], np.uint16, "e", d)
+        o = [_arr(p["o"]["bits"], np.uint32, "o.bits", (d * d + 31) // 32),
+             _arr(p["o"]["scale"], np.uint16, "o.scale", d), _arr(p["o"]["bias"], np.uint16, "o.bias", d)]
+        words = (n + 31) // 32
+        r = {"q_plane": np.empty(words, np.uint32), "k_plane": np.empty(words, np.uint32),
+             "v_plane": np.empty(words, np.uint32), "idx": np.empty(n, np.uint8),
+             "y": np.empty(n, np.float32), "out": np.empty(n, np.float32)}
+        self._check(self._lib.ullis_cuda_rosa_block_forward(
+            self._h, _ptr(x), *[_ptr(a) for a in args], *[_ptr(a) for a in lin], _ptr(e), *[_ptr(a) for a in o],
+            _z(batch), _z(time), _z(d), _ptr(r["q_plane"]), _ptr(r["k_plane"]), _ptr(r["v_plane"]), _ptr(r["idx"]),
+            _ptr(r["y"]), _ptr(r["out"])))
+        return r
+
+    def cmix_block_forward(self, x, mix_bits, key_bits, key_scale_bits, value_bits, batch: int, time: int,
+                           d_model: int, dim_ffn: int) -> np.ndarray:
+        n = batch * time * d_model
+        x = _arr(x, np.float32, "x", n)
+        mix = _arr(mix_bits, np.uint16, "mix", d_model)
+        kb = _arr(key_bits, np.uint32, "key_bits", (d_model * dim_ffn + 31) // 32)
+        ks = _arr(key_scale_bits, np.uint16, "key_scale", dim_ffn)
+        val = _arr(value_bits, np.uint16, "value", d_model * dim_ffn)
+        out = np.empty(n, np.float32)
+        self._check(self._lib.ullis_cuda_cmix_block_forward(self._h, _ptr(x), _ptr(mix), _ptr(kb), _ptr(ks),
+                                                            _ptr(val), _z(batch), _z(time), _z(d_model),
+                                                            _z(dim_ffn), _ptr(out)))
+        return out
+
+    def streamed_ce(self, hidden, bits, scale_bits, bias_bits, labels, ignore_id: int, rows: int, time: int,
+                    channels: int, vocab: int):
+        """Returns (mean_loss, n_valid, row_loss)."""
+        h = _arr(hidden, np.float32, "hidden", rows * channels)
+        bits = _arr(bits, np.uint32, "bits", (vocab * channels + 31) // 32)
+        s = _arr(scale_bits, np.uint16, "scale", vocab)
+        b = _arr(bias_bits, np.uint16, "bias", vocab, allow_none=True)
+        lab = _arr(labels, np.uint32, "labels", rows)
+        row_loss = np.empty(rows, np.float32)
+        mean = C.c_float(0)
+        n_valid = C.c_uint64(0)
+        self._check(self._lib.ullis_cuda_streamed_ce(self._h, _ptr(h), _ptr(bits), _ptr(s), _ptr(b), _ptr(lab),
+                                                     C.c_uint32(ignore_id), _z(rows), _z(time), _z(channels),
+                                                     _z(vocab), _ptr(row_loss), C.byref(mean), C.byref(n_valid)))
+        return float(mean.value), int(n_valid.value), row_loss
+
+    # ---- data parallel
+    @staticmethod
+    def dp_unique_id() -> bytes:
+        buf = (C.c_uint8 * 128)()
+        rc = load_library().ullis_cuda_dp_unique_id(buf)
+        if rc != OK:
+            raise UllisCudaError(rc, "ncclGetUniqueId failed")
+        return bytes(buf)
+
+    def dp_init(self, rank: int, world: int, unique_id: bytes):
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        self._check(self._lib.ullis_cuda_dp_init(self._h, C.c_int32(rank), C.c_int32(world), buf))
+
+    def dp_allreduce_loss(self, loss_sum: float, n_valid: int):
+        s = C.c_double(loss_sum)
+        n = C.c_uint64(n_valid)
+        self._check(self._lib.ullis_cuda_dp_allreduce_loss(self._h, C.byref(s), C.byref(n)))
+        return float(s.value), int(n.value)
+
+    def dp_finalize(self):
+        self._check(self._lib.ullis_cuda_dp_finalize(self._h))
+
+
+class CudaHeron:
+    """Device-resident Heron model loaded from v2 checkpoint.safetensors bytes."""
+
+    def __init__(self, runtime: CudaRuntime, checkpoint_bytes: bytes):
+        self.rt = runtime
+        self._lib = runtime._lib
+        buf = np.frombuffer(checkpoint_bytes, dtype=np.uint8)
+        h = C.c_void_p()
+        runtime._check(self._lib.ullis_cuda_model_load_safetensors(runtime._h, _ptr(buf), _z(buf.size), C.byref(h)))
+        self._h = h
+        dims = (C.c_size_t * 6)()
+        self._lib.ullis_cuda_model_dims(self._h, dims)
+        self.d_model, self.n_layers, self.vocab_size, self.context_len, self.batch_size, self.dim_ffn = \
+            [int(v) for v in dims]
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.ullis_cuda_model_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass
+
+    def forward_ce(self, tokens, labels, ignore_id: int, batch: int, time: int, want_row_loss: bool = False):
+        """Returns (mean_loss, loss_sum, n_valid[, row_loss])."""
+        t = _arr(tokens, np.uint32, "tokens", batch * time)
+        lab = _arr(labels, np.uint32, "labels", batch * time)
+        mean, s, n = C.c_float(0), C.c_double(0), C.c_uint64(0)
+        rl = np.empty(batch * time, np.float32) if want_row_loss else None
+        self.rt._check(self._lib.ullis_cuda_model_forward_ce(self._h, _ptr(t), _ptr(lab), C.c_uint32(ignore_id),
+                                                             _z(batch), _z(time), C.byref(mean), C.byref(s),
+                                                             C.byref(n), _ptr(rl)))
+        out = (float(mean.value), float(s.value), int(n.value))
+        return out + (rl,) if want_row_loss else out
+
+    def upload_tokens(self, tokens, labels, batch: int, time: int):
+        t = _arr(tokens, np.uint32, "tokens", batch * time)
+        lab = _arr(labels, np.uint32, "labels", batch * time, allow_none=True)
+        self.rt._check(self._lib.ullis_cuda_model_upload_tokens(self._h, _ptr(t), _ptr(lab), _z(batch), _z(time)))
+
+    def enqueue_forward_ce(self, ignore_id: int, batch: int, time: int):
+        self.rt._check(self._lib.ullis_cuda_model_enqueue_forward_ce(self._h, C.c_uint32(ignore_id), _z(batch),
+                                                                     _z(time)))
+
+    def read_loss(self, rows: int = 0, want_row_loss: bool = False):
+        mean, s, n = C.c_float(0), C.c_double(0), C.c_uint64(0)
+        rl = np.empty(rows, np.float32) if want_row_loss else None
+        self.rt._check(self._lib.ullis_cuda_model_read_loss(self._h, C.byref(mean), C.byref(s), C.byref(n),
+                                                            _ptr(rl), _z(rows)))
+        out = (float(mean.value), float(s.value), int(n.value))
+        return out + (rl,) if want_row_loss else out
+
+    def logits(self, tokens, batch: int, time: int) -> np.ndarray:
+        t = _arr(tokens, np.uint32, "tokens", batch * time)
+        out = np.empty(batch * time * self.vocab_size, np.float32)
+        self.rt._check(self._lib.ullis_cuda_model_logits(self._h, _ptr(t), _z(batch), _z(time), _ptr(out)))
+        return out
+
+    def hidden(self, tokens, batch: int, time: int) -> np.ndarray:
+        t = _arr(tokens, np.uint32, "tokens", batch * time)
+        out = np.empty(batch * time * self.d_model, np.float32)
+        self.rt._check(self._lib.ullis_cuda_model_hidden(self._h, _ptr(t), _z(batch), _z(time), _ptr(out)))
+        return out
+
+    def set_taps(self, enabled: bool):
+        self.rt._check(self._lib.ullis_cuda_model_set_taps(self._h, C.c_int32(1 if enabled else 0)))
+
+    def tap(self, layer: int, which: str, rows: int) -> np.ndarray:
+        code = TAPS[which]
+        dtype = np.uint8 if 2 <= code <= 5 else np.float32
+        out = np.empty(rows * self.d_model, dtype)
+        self.rt._check(self._lib.ullis_cuda_model_tap(self._h, C.c_int32(layer), C.c_int32(code), _ptr(out),
+                                                      _z(out.nbytes)))
+        return out
+
+    def set_profile(self, enabled: bool):
+        self.rt._check(self._lib.ullis_cuda_model_set_profile(self._h, C.c_int32(1 if enabled else 0)))
+
+    def phase_ms(self) -> dict:
+        ms = (C.c_float * 6)()
+        self.rt._check(self._lib.ullis_cuda_model_phase_ms(self._h, ms))
+        return {name: float(ms[i]) for i, name in enumerate(PHASES)}
