@@ -134,6 +134,10 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         ULLIS_CUDA_CHECK(cudaMallocHost(&rt->host_status, 16));
         rt->clear_status();
         rt->sync();
+        if (const char* env = getenv("ULLIS_CUDA_SAM_LANES")) {
+            const int v = atoi(env);
+            if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16 || v == 32) rt->sam_lanes = v;
+        }
     } catch (const Error& err) {
         g_create_error = err.msg;
         ullis_cuda_runtime_destroy(rt);

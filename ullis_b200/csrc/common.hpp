@@ -81,6 +81,7 @@ struct ullis_cuda_runtime {
     int cc_major = 0, cc_minor = 0;
     int mode = ULLIS_CUDA_MODE_FAST;
     int sam_algo = ULLIS_CUDA_SAM_EULER;
+    int sam_lanes = 4;                  // streams carried per warp by the suffix-automaton kernel (1,2,4,...,32)
     uint64_t launches = 0;
     std::string last_error;
     uint32_t* dev_status = nullptr;     // 4 words, device

@@ -15,12 +15,20 @@ namespace k {
 
 namespace {
 
+// Only `lanes` threads of each warp carry a stream (the others exit at once).
+// A warp-level load completes when its slowest lane does, and a stream's
+// accesses are pointer chases into its own state block, so fewer streams per
+// warp (and more warps) shortens every dependent step.
 template <typename Ix, int ALGO>
-__global__ void __launch_bounds__(64)
+__global__ void __launch_bounds__(128)
 rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
                 const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ v_sw,
-                uint32_t* __restrict__ idx_sw, size_t streams, uint32_t T, size_t wps) {
-    const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+                uint32_t* __restrict__ idx_sw, size_t streams, uint32_t T, size_t wps, int lanes) {
+    const int lane = threadIdx.x & 31;
+    const int spread = 32 / lanes;
+    if (lane % spread != 0) return;
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const size_t s = warp * lanes + lane / spread;
     if (s >= streams) return;
     uint8_t* block = scratch + s * scratch_stride;
     const uint32_t* qw = q_sw + s * wps;
@@ -66,25 +74,27 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     uint8_t* scratch = static_cast<uint8_t*>(rt->sam_scratch.ensure(wave * stride));
     for (size_t s0 = 0; s0 < streams; s0 += wave) {
         const size_t n = streams - s0 < wave ? streams - s0 : wave;
-        const unsigned grid = (unsigned)((n + 63) / 64);
+        const int lanes = rt->sam_lanes;
+        const size_t warps = (n + lanes - 1) / lanes;
+        const unsigned grid = (unsigned)((warps * 32 + 127) / 128);
         const uint32_t* q = q_sw + s0 * wps;
         const uint32_t* kk = k_sw + s0 * wps;
         const uint32_t* v = v_sw + s0 * wps;
         uint32_t* o = idx_sw + s0 * wps;
         if (narrow) {
             if (algo == ULLIS_CUDA_SAM_EAGER)
-                rosa_sam_kernel<uint16_t, ULLIS_CUDA_SAM_EAGER><<<grid, 64, 0, rt->stream>>>(
-                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps);
+                rosa_sam_kernel<uint16_t, ULLIS_CUDA_SAM_EAGER><<<grid, 128, 0, rt->stream>>>(
+                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps, lanes);
             else
-                rosa_sam_kernel<uint16_t, ULLIS_CUDA_SAM_EULER><<<grid, 64, 0, rt->stream>>>(
-                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps);
+                rosa_sam_kernel<uint16_t, ULLIS_CUDA_SAM_EULER><<<grid, 128, 0, rt->stream>>>(
+                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps, lanes);
         } else {
             if (algo == ULLIS_CUDA_SAM_EAGER)
-                rosa_sam_kernel<uint32_t, ULLIS_CUDA_SAM_EAGER><<<grid, 64, 0, rt->stream>>>(
-                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps);
+                rosa_sam_kernel<uint32_t, ULLIS_CUDA_SAM_EAGER><<<grid, 128, 0, rt->stream>>>(
+                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps, lanes);
             else
-                rosa_sam_kernel<uint32_t, ULLIS_CUDA_SAM_EULER><<<grid, 64, 0, rt->stream>>>(
-                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps);
+                rosa_sam_kernel<uint32_t, ULLIS_CUDA_SAM_EULER><<<grid, 128, 0, rt->stream>>>(
+                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps, lanes);
         }
         rt->launched("rosa_sam");
     }
