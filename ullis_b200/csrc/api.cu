@@ -2,6 +2,7 @@
 // the device-resident model entry points and the op-level calls that mirror
 // the reference's MetalRuntime methods.  No C++ exception leaves this file.
 #include <algorithm>
+#include <cstdio>
 #include <cstring>
 #include <exception>
 #include <new>
@@ -14,12 +15,12 @@ using namespace ullis;
 
 namespace {
 
-std::string g_create_error;  // last failure of a call that had no runtime to blame
+char g_global_error[512] = "";  // last failure of a call that had no runtime to blame (fixed buffer: no allocation)
 
 template <typename F>
 int32_t guard(ullis_cuda_runtime* rt, F&& body) {
     if (!rt) {
-        g_create_error = "runtime handle is null";
+        set_global_error("runtime handle is null");
         return ULLIS_CUDA_ERR_ARG;
     }
     try {
@@ -41,7 +42,7 @@ int32_t guard(ullis_cuda_runtime* rt, F&& body) {
 template <typename F>
 int32_t guard_model(ullis_cuda_model* m, F&& body) {
     if (!m) {
-        g_create_error = "model handle is null";
+        set_global_error("model handle is null");
         return ULLIS_CUDA_ERR_ARG;
     }
     return guard(m->rt, body);
@@ -77,6 +78,12 @@ void dense_linear_dev(ullis_cuda_runtime* rt, const float* x, const uint16_t* w,
 
 }  // namespace
 
+namespace ullis {
+void set_global_error(const char* msg) {
+    snprintf(g_global_error, sizeof(g_global_error), "%s", msg ? msg : "");
+}
+}  // namespace ullis
+
 void ullis_cuda_runtime::launched(const char* what) {
     ++launches;
     cudaError_t e = cudaGetLastError();
@@ -100,7 +107,7 @@ extern "C" {
 
 int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
     if (!out) {
-        g_create_error = "out is null";
+        set_global_error("out is null");
         return ULLIS_CUDA_ERR_ARG;
     }
     *out = nullptr;
@@ -108,17 +115,17 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
     cudaError_t e = cudaGetDeviceCount(&count);
     if (e != cudaSuccess || count == 0) {
         cudaGetLastError();
-        g_create_error = std::string("--backend cuda requires a CUDA device: ") +
-                         (e != cudaSuccess ? cudaGetErrorString(e) : "no device found");
+        set_global_error((std::string("--backend cuda requires a CUDA device: ") +
+                          (e != cudaSuccess ? cudaGetErrorString(e) : "no device found")).c_str());
         return ULLIS_CUDA_ERR_CUDA;
     }
     if (device < 0 || device >= count) {
-        g_create_error = "device index out of range";
+        set_global_error("device index out of range");
         return ULLIS_CUDA_ERR_ARG;
     }
     ullis_cuda_runtime* rt = new (std::nothrow) ullis_cuda_runtime();
     if (!rt) {
-        g_create_error = "host allocation failed";
+        set_global_error("host allocation failed");
         return ULLIS_CUDA_ERR_NOMEM;
     }
     rt->device = device;
@@ -139,7 +146,7 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
             if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16 || v == 32) rt->sam_lanes = v;
         }
     } catch (const Error& err) {
-        g_create_error = err.msg;
+        set_global_error(err.msg.c_str());
         ullis_cuda_runtime_destroy(rt);
         return err.code;
     }
@@ -161,7 +168,7 @@ void ullis_cuda_runtime_destroy(ullis_cuda_runtime* rt) {
 }
 
 const char* ullis_cuda_last_error(const ullis_cuda_runtime* rt) {
-    return rt ? rt->last_error.c_str() : g_create_error.c_str();
+    return rt ? rt->last_error.c_str() : g_global_error;
 }
 
 int32_t ullis_cuda_runtime_set_mode(ullis_cuda_runtime* rt, int32_t mode) {

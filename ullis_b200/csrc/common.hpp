@@ -66,6 +66,9 @@ class DeviceBuffer {
 
 struct NcclState;  // dp.cpp
 
+// Message returned by ullis_cuda_last_error(NULL); copied into a fixed buffer.
+void set_global_error(const char* msg);
+
 }  // namespace ullis
 
 // Device-side status word layout (one per runtime, zeroed before each call
