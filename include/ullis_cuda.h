@@ -209,6 +209,30 @@ ULLIS_CUDA_API int32_t ullis_cuda_streamed_ce(ullis_cuda_runtime* rt, const floa
                                uint32_t ignore_id, size_t rows, size_t time, size_t channels, size_t vocab,
                                float* row_loss, float* mean_loss, uint64_t* n_valid);
 
+/* Allocation-free form of the suffix-automaton match.  It has no counterpart
+ * in the reference.  For callers that may not allocate device memory while
+ * they run (a fixed memory budget owned by the host application, a
+ * latency-critical thread that cannot afford cudaMalloc's device-wide
+ * synchronisation, a process whose own pool already holds all GPU memory).
+ * The caller passes DEVICE buffers: q_sw / k_sw / v_sw / idx_sw hold one row
+ * of ceil(time/32) words per stream (stream s = sequence*channels + channel;
+ * bit t of the stream at word t/32, bit t%32); idx_sw receives the idx bits
+ * in the same layout.  Per-stream automaton state lives in a 64 MiB array
+ * built into the library (ULLIS_CUDA_SAM_STATIC_BYTES, resident on every GPU
+ * that loads it): 74368 bytes per stream at time 2048, so at most 902
+ * streams there; requests beyond it fail with ULLIS_CUDA_ERR_NOMEM.  No
+ * cudaMalloc / cudaFree / host allocation happens.  The first call on a
+ * device resolves the array's address - make it before any stream capture.
+ * All calls share the array (nothing needs clearing between calls, every
+ * field is written before it is read), so calls that overlap on the GPU race:
+ * serialise them.  The kernel is enqueued on `cuda_stream` (a cudaStream_t,
+ * NULL = default stream) and the call returns after that stream has drained.
+ * Failure text: ullis_cuda_last_error(NULL). */
+#define ULLIS_CUDA_SAM_STATIC_BYTES ((size_t)64 << 20)
+ULLIS_CUDA_API int32_t ullis_cuda_rosa_sam_static(int32_t device, void* cuda_stream, const uint32_t* q_sw,
+                                                  const uint32_t* k_sw, const uint32_t* v_sw, uint32_t* idx_sw,
+                                                  size_t streams, size_t time);
+
 /* ------------------------------------------------------------ data parallel
  * Sequences are independent; ranks own disjoint blocks of sequences and only
  * {loss_sum, n_valid} is summed across ranks (NCCL all-reduce, 16 bytes).

@@ -44,7 +44,8 @@ ABI_SYMBOLS = (
     "ullis_cuda_model_phase_ms", "ullis_cuda_layer_norm", "ullis_cuda_time_shift_delta",
     "ullis_cuda_binary_linear", "ullis_cuda_fp16_linear", "ullis_cuda_sign_pack_bits", "ullis_cuda_cmix_relu2",
     "ullis_cuda_residual_add", "ullis_cuda_rosa_qkv_1bit_fwd", "ullis_cuda_rosa_block_forward",
-    "ullis_cuda_cmix_block_forward", "ullis_cuda_streamed_ce", "ullis_cuda_dp_unique_id", "ullis_cuda_dp_init",
+    "ullis_cuda_cmix_block_forward", "ullis_cuda_streamed_ce", "ullis_cuda_rosa_sam_static",
+    "ullis_cuda_dp_unique_id", "ullis_cuda_dp_init",
     "ullis_cuda_dp_allreduce_loss", "ullis_cuda_dp_finalize",
 )
 
@@ -290,6 +291,22 @@ class CudaRuntime:
 
     def dp_finalize(self):
         self._check(self._lib.ullis_cuda_dp_finalize(self._h))
+
+
+SAM_STATIC_BYTES = 64 << 20
+
+
+def rosa_sam_static(device: int, cuda_stream: int, q_sw_ptr: int, k_sw_ptr: int, v_sw_ptr: int, idx_sw_ptr: int,
+                    streams: int, time: int) -> None:
+    """Allocation-free suffix-automaton match over caller-owned DEVICE buffers
+    (raw addresses) using the library's built-in 64 MiB state array; see
+    ullis_cuda_rosa_sam_static in include/ullis_cuda.h.  Raises on refusal."""
+    lib = load_library()
+    rc = lib.ullis_cuda_rosa_sam_static(C.c_int32(device), C.c_void_p(cuda_stream or None), C.c_void_p(q_sw_ptr),
+                                        C.c_void_p(k_sw_ptr), C.c_void_p(v_sw_ptr), C.c_void_p(idx_sw_ptr),
+                                        _z(streams), _z(time))
+    if rc != OK:
+        raise UllisCudaError(rc, lib.ullis_cuda_last_error(None).decode())
 
 
 class CudaHeron:
