@@ -1,24 +1,401 @@
+// Host side of the tensor-core stages: TMA descriptors, the small kernels that
+// prepare 16-bit operands (time-shift mixes with a hi+lo FP16 split, +/-e
+// emit, f32 -> 16-bit casts), the exact fix-up of sign bits that fall inside
+// the tensor-core error band, the CE finishing reduction, and the launch of
+// the tcgen05 GEMM (tc_gemm.cuh) with the epilogue each stage needs.
 #include "linear_tc.hpp"
+
+#include <cudaTypedefs.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "kernels.hpp"
+#include "tc_gemm.cuh"
 
 namespace ullis {
 namespace tc {
 
-bool binary_linear(ullis_cuda_runtime*, const float*, const uint32_t*, const uint16_t*, const uint16_t*, float*,
-                   size_t, size_t, size_t) {
-    return false;
+namespace {
+
+// ------------------------------------------------------------ TMA descriptors
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        ULLIS_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        if (!p || q != cudaDriverEntryPointSuccess) fail(ULLIS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
+        fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    }
+    return fn;
 }
-bool fp16_linear(ullis_cuda_runtime*, const float*, const uint16_t*, float*, size_t, size_t, size_t) { return false; }
-bool rosa_qkv_bits(ullis_cuda_runtime*, const float*, const LayerWeights&, uint32_t*, uint32_t*, uint32_t*, size_t,
-                   size_t, size_t) {
-    return false;
+
+// [rows, K] 16-bit row-major matrix, 64 x 128 boxes, 128-byte swizzle, zero fill
+CUtensorMap make_map(const void* ptr, size_t rows, size_t K, bool bf16) {
+    CUtensorMap m;
+    cuuint64_t dims[2] = {K, rows};
+    cuuint64_t strides[1] = {K * 2};
+    cuuint32_t box[2] = {BK, BM};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                             const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) fail(ULLIS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    return m;
 }
-bool rosa_out_residual(ullis_cuda_runtime*, const uint32_t*, const LayerWeights&, float*, size_t, size_t, size_t) {
-    return false;
+
+__device__ __forceinline__ float h2f(uint16_t b) { return __half2float(__ushort_as_half(b)); }
+
+// ------------------------------------------------------------ operand kernels
+// f32 -> f16 / bf16
+__global__ void cast16_kernel(const float* __restrict__ x, uint16_t* __restrict__ y, size_t n, int bf16) {
+    size_t e = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (e >= n) return;
+    float v[4];
+    for (int k = 0; k < 4; ++k) v[k] = e + k < n ? x[e + k] : 0.0f;
+    for (int k = 0; k < 4; ++k) {
+        if (e + k >= n) break;
+        y[e + k] = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v[k])) : __half_as_ushort(__float2half_rn(v[k]));
+    }
 }
-bool cmix_residual(ullis_cuda_runtime*, const LayerWeights&, float*, size_t, size_t, size_t, size_t) { return false; }
-bool head_ce(ullis_cuda_runtime*, const float*, const PackedWeights&, const uint32_t*, uint32_t, size_t, size_t,
-             size_t, size_t, float*) {
-    return false;
+
+// FP16 bits -> bf16 bits (the MMA takes A and B in one 16-bit format)
+__global__ void f16_to_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, size_t n) {
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < n) y[e] = __bfloat16_as_ushort(__float2bfloat16_rn(h2f(x[e])));
+}
+
+// Time-shift mixes of one LayerNorm output (reference src/model.rs:1291-1298:
+// in = x + (x[t-1]-x[t])*mix, unfused) written as FP16 hi and lo = FP16(in - hi)
+// for up to three mixes, plus the row's sum |in| that scales the sign-bit error
+// band. One warp per row.
+__global__ void __launch_bounds__(256)
+mix_split_kernel(const float* __restrict__ x, const uint16_t* __restrict__ m0, const uint16_t* __restrict__ m1,
+                 const uint16_t* __restrict__ m2, uint16_t* __restrict__ hi0, uint16_t* __restrict__ lo0,
+                 uint16_t* __restrict__ hi1, uint16_t* __restrict__ lo1, uint16_t* __restrict__ hi2,
+                 uint16_t* __restrict__ lo2, float* __restrict__ s1, size_t rows, size_t time, size_t C) {
+    const int lane = threadIdx.x & 31;
+    const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const bool first = row % time == 0;
+    const uint16_t* mix[3] = {m0, m1, m2};
+    uint16_t* hi[3] = {hi0, hi1, hi2};
+    uint16_t* lo[3] = {lo0, lo1, lo2};
+    float sum[3] = {0.0f, 0.0f, 0.0f};
+    for (size_t c = lane; c < C; c += 32) {
+        const float xt = x[row * C + c];
+        const float xx = first ? -xt : __fsub_rn(x[(row - 1) * C + c], xt);
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            if (!mix[k]) continue;
+            const float v = __fadd_rn(xt, __fmul_rn(xx, h2f(mix[k][c])));
+            const __half h = __float2half_rn(v);
+            hi[k][row * C + c] = __half_as_ushort(h);
+            if (lo[k]) lo[k][row * C + c] = __half_as_ushort(__float2half_rn(v - __half2float(h)));
+            sum[k] += fabsf(v);
+        }
+    }
+    if (s1) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            float s = sum[k];
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0 && mix[k]) s1[k * rows + row] = s;
+        }
+    }
+}
+
+// idx bits (stream-major) -> y = +/-e as FP16 [B*T, C] (reference src/model.rs:1313)
+__global__ void __launch_bounds__(1024)
+emit_f16_kernel(const uint32_t* __restrict__ idx_sw, const uint16_t* __restrict__ e, uint16_t* __restrict__ y,
+                size_t T, size_t C, size_t wps) {
+    __shared__ uint32_t wsm[32];
+    const size_t b = blockIdx.z, t0 = (size_t)blockIdx.x * 32, c0 = (size_t)blockIdx.y * 32;
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    if (ty == 0) wsm[tx] = (c0 + tx < C) ? idx_sw[(b * C + c0 + tx) * wps + blockIdx.x] : 0u;
+    __syncthreads();
+    if (t0 + ty >= T || c0 + tx >= C) return;
+    const uint32_t bit = (wsm[tx] >> ty) & 1u;
+    y[(b * T + t0 + ty) * C + c0 + tx] = e[c0 + tx] ^ (bit ? 0u : 0x8000u);  // flip the FP16 sign for idx 0
+}
+
+// Sign bits whose tensor-core pre-activation fell inside the error band are
+// recomputed exactly as the reference does (src/model.rs:724-742 on the
+// time-shift mix of x): sequential f32 sum over i, then bias + scale*sum.
+__global__ void __launch_bounds__(128)
+sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, const uint16_t* __restrict__ mk,
+                  const uint16_t* __restrict__ mv, PackedWeights wq, PackedWeights wk, PackedWeights wv,
+                  uint32_t* __restrict__ bq, uint32_t* __restrict__ bk, uint32_t* __restrict__ bv,
+                  const uint32_t* __restrict__ fq, const uint32_t* __restrict__ fk, const uint32_t* __restrict__ fv,
+                  size_t batch, size_t T, size_t C, size_t wps) {
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= batch * C * wps) return;
+    const int which = blockIdx.y;
+    const uint32_t* flags = which == 0 ? fq : which == 1 ? fk : fv;
+    uint32_t f = flags[e];
+    if (!f) return;
+    uint32_t* bits = which == 0 ? bq : which == 1 ? bk : bv;
+    const uint16_t* mix = which == 0 ? mq : which == 1 ? mk : mv;
+    const PackedWeights& W = which == 0 ? wq : which == 1 ? wk : wv;
+    const size_t s = e / wps, word = e % wps, b = s / C, c = s % C;
+    const float scale = h2f(W.scale[c]), bias = W.bias ? h2f(W.bias[c]) : 0.0f;
+    uint32_t out = bits[e];
+    while (f) {
+        const int tt = __ffs(f) - 1;
+        f &= f - 1;
+        const size_t t = word * 32 + tt, row = b * T + t;
+        const float* xr = x + row * C;
+        float sum = 0.0f;
+        for (size_t i = 0; i < C; ++i) {
+            const float xt = xr[i];
+            const float xx = t == 0 ? -xt : __fsub_rn((xr - C)[i], xt);
+            const float in = __fadd_rn(xt, __fmul_rn(xx, h2f(mix[i])));
+            const size_t index = c * C + i;
+            const float sgn = (W.bits[index >> 5] >> (index & 31)) & 1u ? 1.0f : -1.0f;
+            sum = __fmaf_rn(sgn, in, sum);
+        }
+        const float y = __fadd_rn(bias, __fmul_rn(scale, sum));
+        out = (out & ~(1u << tt)) | ((y > 0.0f ? 1u : 0u) << tt);
+    }
+    bits[e] = out;
+}
+
+// Merge the per-tile (max, sum exp) partials of a row and subtract the target
+// logit (reference src/model.rs:3219-3227; valid-row rule 27-39).
+__global__ void ce_finish_kernel(const float2* __restrict__ part, const float* __restrict__ target_logit,
+                                 const uint32_t* __restrict__ labels, uint32_t ignore_id, size_t rows, size_t time,
+                                 size_t vocab, uint32_t n_tiles, float* __restrict__ row_loss, uint32_t* status) {
+    const size_t m = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= rows) return;
+    const bool valid = time != 0 && (m % time) + 1 < time && m + 1 < rows && labels[m + 1] != ignore_id;
+    if (!valid) {
+        row_loss[m] = 0.0f;
+        return;
+    }
+    if (labels[m + 1] >= vocab) {
+        if (atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_BAD_TOKEN) == ULLIS_DEV_OK) status[1] = (uint32_t)m;
+        row_loss[m] = 0.0f;
+        return;
+    }
+    float gmax = -INFINITY;
+    for (uint32_t i = 0; i < n_tiles; ++i) gmax = fmaxf(gmax, part[m * n_tiles + i].x);
+    float sum = 0.0f;
+    for (uint32_t i = 0; i < n_tiles; ++i) {
+        const float2 pr = part[m * n_tiles + i];
+        sum += pr.y * expf(pr.x - gmax);
+    }
+    row_loss[m] = gmax + logf(sum) - target_logit[m];
+}
+
+inline unsigned blocks_for(size_t n, unsigned per) { return (unsigned)((n + per - 1) / per); }
+
+}  // namespace
+
+namespace {
+
+bool usable(ullis_cuda_runtime* rt) {
+    if (rt->mode == ULLIS_CUDA_MODE_EXACT) return false;
+    if (rt->tc_ready == 0) {
+        rt->tc_ready = -1;
+        if (rt->cc_major == 10 && !getenv("ULLIS_CUDA_NO_TC")) {
+            encode_fn();
+            const int smem = (int)gemm_smem_bytes(2);
+#define ULLIS_SET_SMEM(EPI, PACKED) \
+    ULLIS_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<EPI, PACKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))
+            ULLIS_SET_SMEM(EPI_STORE, true);
+            ULLIS_SET_SMEM(EPI_STORE, false);
+            ULLIS_SET_SMEM(EPI_RESIDUAL, true);
+            ULLIS_SET_SMEM(EPI_RESIDUAL, false);
+            ULLIS_SET_SMEM(EPI_RELU2, true);
+            ULLIS_SET_SMEM(EPI_SIGNBITS, true);
+            ULLIS_SET_SMEM(EPI_CE, true);
+#undef ULLIS_SET_SMEM
+            rt->tc_ready = 1;
+        }
+    }
+    return rt->tc_ready == 1;
+}
+
+bool shape_ok(size_t M, size_t K, size_t N) {
+    return M > 0 && K >= BK && K % BK == 0 && N >= 8 && N % 8 == 0 && M < (1u << 30) && N < (1u << 30) &&
+           (M + BM - 1) / BM <= 65535;
+}
+
+template <int EPI, bool PACKED>
+void launch(ullis_cuda_runtime* rt, const GemmMaps& maps, const GemmParams& p, unsigned n_prob, const char* what) {
+    dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, n_prob);
+    gemm_kernel<EPI, PACKED><<<grid, GEMM_THREADS, gemm_smem_bytes(p.n_a), rt->stream>>>(maps, p);
+    rt->launched(what);
+}
+
+GemmParams base_params(ullis_cuda_runtime* rt, size_t M, size_t N, size_t K) {
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = (uint32_t)M;
+    p.N = (uint32_t)N;
+    p.K = (uint32_t)K;
+    p.n_a = 1;
+    p.status = rt->dev_status;
+    return p;
+}
+
+void cast16(ullis_cuda_runtime* rt, const float* x, uint16_t* y, size_t n, bool bf16) {
+    cast16_kernel<<<blocks_for((n + 3) / 4, 256), 256, 0, rt->stream>>>(x, y, n, bf16 ? 1 : 0);
+    rt->launched("cast16");
+}
+
+}  // namespace
+
+bool binary_linear(ullis_cuda_runtime* rt, const float* x, const uint32_t* bits, const uint16_t* scale,
+                   const uint16_t* bias, float* y, size_t rows, size_t in_features, size_t out_features) {
+    if (!usable(rt) || !shape_ok(rows, in_features, out_features) || out_features % 4) return false;
+    uint16_t* a = rt->tc_ws[0].as<uint16_t>(rows * in_features);
+    cast16(rt, x, a, rows * in_features, false);
+    GemmMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    maps.a[0][0] = make_map(a, rows, in_features, false);
+    GemmParams p = base_params(rt, rows, out_features, in_features);
+    p.prob[0] = GemmProblem{bits, scale, bias, y, nullptr, nullptr};
+    launch<EPI_STORE, true>(rt, maps, p, 1, "gemm_packed_store");
+    return true;
+}
+
+void value_to_bf16(ullis_cuda_runtime* rt, const uint16_t* w, uint16_t* out, size_t n) {
+    f16_to_bf16_kernel<<<blocks_for(n, 256), 256, 0, rt->stream>>>(w, out, n);
+    rt->launched("f16_to_bf16");
+}
+
+bool fp16_linear(ullis_cuda_runtime* rt, const float* x, const uint16_t* w, float* y, size_t rows,
+                 size_t in_features, size_t out_features) {
+    if (!usable(rt) || !shape_ok(rows, in_features, out_features)) return false;
+    // both operands as bf16: the activations (relu^2 in the model) span the f32
+    // exponent range, and the MMA wants A and B in the same 16-bit format
+    uint16_t* a = rt->tc_ws[0].as<uint16_t>(rows * in_features);
+    uint16_t* wb = rt->tc_ws[8].as<uint16_t>(out_features * in_features);
+    cast16(rt, x, a, rows * in_features, true);
+    value_to_bf16(rt, w, wb, out_features * in_features);
+    GemmMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    maps.a[0][0] = make_map(a, rows, in_features, true);
+    maps.b[0] = make_map(wb, out_features, in_features, true);
+    GemmParams p = base_params(rt, rows, out_features, in_features);
+    p.a_fmt = 1;
+    p.b_fmt = 1;
+    p.prob[0] = GemmProblem{nullptr, nullptr, nullptr, y, nullptr, nullptr};
+    launch<EPI_STORE, false>(rt, maps, p, 1, "gemm_dense_store");
+    return true;
+}
+
+bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeights& L, uint32_t* q_sw,
+                   uint32_t* k_sw, uint32_t* v_sw, size_t batch, size_t time, size_t d) {
+    const size_t rows = batch * time;
+    if (!usable(rt) || !shape_ok(rows, d, d) || time % 32) return false;
+    const size_t n = rows * d, wps = time / 32, sw = batch * d * wps;
+    uint16_t* op = rt->tc_ws[1].as<uint16_t>(6 * n);   // q/k/v hi, then q/k/v lo
+    float* s1 = rt->tc_ws[2].as<float>(3 * rows);
+    uint32_t* flags = rt->tc_ws[3].as<uint32_t>(3 * sw);
+    mix_split_kernel<<<blocks_for(rows, 8), 256, 0, rt->stream>>>(ln3_out, L.x_q, L.x_k, L.x_v, op, op + 3 * n, op + n,
+                                                                 op + 4 * n, op + 2 * n, op + 5 * n, s1, rows, time, d);
+    rt->launched("mix_split");
+    GemmMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    for (int z = 0; z < 3; ++z) {
+        maps.a[z][0] = make_map(op + z * n, rows, d, false);
+        maps.a[z][1] = make_map(op + (3 + z) * n, rows, d, false);
+    }
+    GemmParams p = base_params(rt, rows, d, d);
+    p.n_a = 2;
+    p.time = (uint32_t)time;
+    p.wps = (uint32_t)wps;
+    const PackedWeights* W[3] = {&L.q, &L.k, &L.v};
+    uint32_t* outs[3] = {q_sw, k_sw, v_sw};
+    for (int z = 0; z < 3; ++z)
+        p.prob[z] = GemmProblem{W[z]->bits, W[z]->scale, W[z]->bias, outs[z], flags + z * sw, s1 + z * rows};
+    launch<EPI_SIGNBITS, true>(rt, maps, p, 3, "gemm_qkv_signbits");
+    dim3 grid(blocks_for(sw, 128), 3);
+    sign_fixup_kernel<<<grid, 128, 0, rt->stream>>>(ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, flags,
+                                                   flags + sw, flags + 2 * sw, batch, time, d, wps);
+    rt->launched("sign_fixup");
+    return true;
+}
+
+bool rosa_out_residual(ullis_cuda_runtime* rt, const uint32_t* idx_sw, const LayerWeights& L, float* x, size_t batch,
+                       size_t time, size_t d) {
+    const size_t rows = batch * time;
+    if (!usable(rt) || !shape_ok(rows, d, d) || d % 4) return false;
+    uint16_t* y16 = rt->tc_ws[0].as<uint16_t>(rows * d);
+    const size_t wps = (time + 31) / 32;
+    dim3 grid((unsigned)wps, (unsigned)((d + 31) / 32), (unsigned)batch);
+    emit_f16_kernel<<<grid, dim3(32, 32), 0, rt->stream>>>(idx_sw, L.e, y16, time, d, wps);
+    rt->launched("emit_f16");
+    GemmMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    maps.a[0][0] = make_map(y16, rows, d, false);
+    GemmParams p = base_params(rt, rows, d, d);
+    p.prob[0] = GemmProblem{L.o.bits, L.o.scale, L.o.bias, x, nullptr, nullptr};
+    launch<EPI_RESIDUAL, true>(rt, maps, p, 1, "gemm_o_residual");
+    return true;
+}
+
+bool cmix_residual(ullis_cuda_runtime* rt, const LayerWeights& L, float* x, size_t batch, size_t time, size_t d,
+                   size_t ffn) {
+    const size_t rows = batch * time;
+    if (!usable(rt) || !shape_ok(rows, d, ffn) || !shape_ok(rows, ffn, d) || d % 4) return false;
+    const uint16_t* value16 = L.value_bf16;
+    if (!value16) {  // weights that did not come through the model loader: convert per call
+        uint16_t* wb = rt->tc_ws[8].as<uint16_t>(ffn * d);
+        value_to_bf16(rt, L.value, wb, ffn * d);
+        value16 = wb;
+    }
+    float* ln = rt->tc_ws[4].as<float>(rows * d);
+    uint16_t* a16 = rt->tc_ws[0].as<uint16_t>(rows * d);
+    uint16_t* k16 = rt->tc_ws[5].as<uint16_t>(rows * ffn);
+    k::layer_norm(rt, x, L.ln2.weight, L.ln2.bias, ln, rows, d, false);
+    mix_split_kernel<<<blocks_for(rows, 8), 256, 0, rt->stream>>>(ln, L.ffn_x_k, nullptr, nullptr, a16, nullptr, nullptr,
+                                                                 nullptr, nullptr, nullptr, nullptr, rows, time, d);
+    rt->launched("mix_f16");
+    GemmMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    maps.a[0][0] = make_map(a16, rows, d, false);
+    GemmParams p = base_params(rt, rows, ffn, d);
+    p.out_fmt = 1;  // relu^2 spans the f32 exponent range: keep it as bf16
+    p.prob[0] = GemmProblem{L.key.bits, L.key.scale, nullptr, k16, nullptr, nullptr};
+    launch<EPI_RELU2, true>(rt, maps, p, 1, "gemm_key_relu2");
+    memset(&maps, 0, sizeof(maps));
+    maps.a[0][0] = make_map(k16, rows, ffn, true);
+    maps.b[0] = make_map(value16, d, ffn, true);
+    GemmParams pv = base_params(rt, rows, d, ffn);
+    pv.a_fmt = 1;
+    pv.b_fmt = 1;
+    pv.prob[0] = GemmProblem{nullptr, nullptr, nullptr, x, nullptr, nullptr};
+    launch<EPI_RESIDUAL, false>(rt, maps, pv, 1, "gemm_value_residual");
+    return true;
+}
+
+bool head_ce(ullis_cuda_runtime* rt, const float* hidden, const PackedWeights& head, const uint32_t* labels,
+             uint32_t ignore_id, size_t rows, size_t time, size_t d, size_t vocab, float* row_loss) {
+    if (!usable(rt) || !shape_ok(rows, d, vocab)) return false;
+    const uint32_t n_tiles = (uint32_t)((vocab + BN - 1) / BN);
+    uint16_t* a16 = rt->tc_ws[0].as<uint16_t>(rows * d);
+    float2* part = rt->tc_ws[6].as<float2>(rows * n_tiles);
+    float* tl = rt->tc_ws[7].as<float>(rows);
+    cast16(rt, hidden, a16, rows * d, false);
+    GemmMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    maps.a[0][0] = make_map(a16, rows, d, false);
+    GemmParams p = base_params(rt, rows, vocab, d);
+    p.labels = labels;
+    p.ignore_id = ignore_id;
+    p.n_tiles = n_tiles;
+    p.time = (uint32_t)time;
+    p.prob[0] = GemmProblem{head.bits, head.scale, head.bias, part, tl, nullptr};
+    launch<EPI_CE, true>(rt, maps, p, 1, "gemm_head_ce");
+    ce_finish_kernel<<<blocks_for(rows, 256), 256, 0, rt->stream>>>(part, tl, labels, ignore_id, rows, time, vocab, n_tiles,
+                                                                  row_loss, rt->dev_status);
+    rt->launched("ce_finish");
+    return true;
 }
 
 }  // namespace tc

@@ -256,70 +256,86 @@ SAM_HD void run_eager(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, 
 // ------------------------------------------------------------------ euler
 
 template <typename Ix>
-SAM_HD void run_euler(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw,
-                      uint32_t* out, uint32_t T, Counters* cnt) {
-    constexpr uint32_t NIL = Nil<Ix>::value;
-    EulerLayout<Ix> L(T);
-    Node<Ix>* N = reinterpret_cast<Node<Ix>*>(scratch + L.nodes);
-    Ix* vq = reinterpret_cast<Ix*>(scratch + L.vq);
-    Ix* jid = reinterpret_cast<Ix*>(scratch + L.jid);
-    Ix* head = reinterpret_cast<Ix*>(scratch + L.head);
-    Ix* next = reinterpret_cast<Ix*>(scratch + L.next);
-    Ix* lo = reinterpret_cast<Ix*>(scratch + L.lo);
-    Ix* hi = reinterpret_cast<Ix*>(scratch + L.hi);
-    uint32_t* clone_bits = reinterpret_cast<uint32_t*>(scratch + L.clone_bits);
-    unsigned long long* visits = cnt ? &cnt->node_visits : nullptr;
+struct EulerBlock {
+    Node<Ix>* N;
+    Ix *vq, *jid, *head, *next, *lo, *hi;
+    uint32_t* clone_bits;
+    SAM_HD EulerBlock(uint8_t* scratch, uint32_t T) {
+        EulerLayout<Ix> L(T);
+        N = reinterpret_cast<Node<Ix>*>(scratch + L.nodes);
+        vq = reinterpret_cast<Ix*>(scratch + L.vq);
+        jid = reinterpret_cast<Ix*>(scratch + L.jid);
+        head = reinterpret_cast<Ix*>(scratch + L.head);
+        next = reinterpret_cast<Ix*>(scratch + L.next);
+        lo = reinterpret_cast<Ix*>(scratch + L.lo);
+        hi = reinterpret_cast<Ix*>(scratch + L.hi);
+        clone_bits = reinterpret_cast<uint32_t*>(scratch + L.clone_bits);
+    }
+};
 
-    // ---- pass 1: automaton + query states
+// pass 1: automaton + query states; returns the number of states created
+template <typename Ix>
+SAM_HD uint32_t euler_pass1(EulerBlock<Ix>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T, Counters* cnt) {
+    constexpr uint32_t NIL = Nil<Ix>::value;
+    unsigned long long* visits = cnt ? &cnt->node_visits : nullptr;
     const uint32_t cap = node_capacity(T);
-    for (uint32_t wd = 0; wd < (cap + 31) / 32; ++wd) clone_bits[wd] = 0;
+    for (uint32_t wd = 0; wd < (cap + 31) / 32; ++wd) B.clone_bits[wd] = 0;
     Walker<Ix> wk;
-    wk.init(N);
+    wk.init(B.N);
+    uint32_t qword = 0, kword = 0;
     for (uint32_t i = 0; i < T; ++i) {
-        const uint32_t qb = stream_bit(qw, i), kb = stream_bit(kw, i);
-        vq[i] = (Ix)wk.query(qb, visits);
+        if ((i & 31) == 0) { qword = qw[i >> 5]; kword = kw[i >> 5]; }
+        const uint32_t qb = (qword >> (i & 31)) & 1u, kb = (kword >> (i & 31)) & 1u;
+        B.vq[i] = (Ix)wk.query(qb, visits);
         uint32_t j, b, d;
         wk.extend(kb, &j, &b, &d, visits);
-        jid[i] = (Ix)j;
-        if (b != NIL) clone_bits[b >> 5] |= 1u << (b & 31);
+        B.jid[i] = (Ix)j;
+        if (b != NIL) B.clone_bits[b >> 5] |= 1u << (b & 31);
     }
-    const uint32_t n = wk.u;
+    return wk.u;
+}
 
-    // ---- tour: children lists, then preorder ranks of the stamped states
-    for (uint32_t v = 0; v < n; ++v) head[v] = (Ix)NIL;
+// tour: children lists, then preorder rank ranges [lo, hi) of the stamped
+// (non-clone, non-root) states below each state
+template <typename Ix>
+SAM_HD void euler_tour(EulerBlock<Ix>& B, uint32_t n) {
+    constexpr uint32_t NIL = Nil<Ix>::value;
+    for (uint32_t v = 0; v < n; ++v) B.head[v] = (Ix)NIL;
     for (uint32_t v = 1; v < n; ++v) {
-        const uint32_t f = N[v].fail;
-        next[v] = head[f];
-        head[f] = (Ix)v;
+        const uint32_t f = B.N[v].fail;
+        B.next[v] = B.head[f];
+        B.head[f] = (Ix)v;
     }
-    {
-        uint32_t r = 0, v = 0;
-        bool entering = true;
-        for (;;) {
-            if (entering) {
-                lo[v] = (Ix)r;
-                if (v != 0 && !((clone_bits[v >> 5] >> (v & 31)) & 1u)) ++r;
-                const uint32_t c = head[v];
-                if (c != NIL) { v = c; continue; }
-                entering = false;
-            }
-            hi[v] = (Ix)r;
-            if (v == 0) break;
-            const uint32_t s = next[v];
-            if (s != NIL) { v = s; entering = true; } else { v = N[v].fail; }
+    uint32_t r = 0, v = 0;
+    bool entering = true;
+    for (;;) {
+        if (entering) {
+            B.lo[v] = (Ix)r;
+            if (v != 0 && !((B.clone_bits[v >> 5] >> (v & 31)) & 1u)) ++r;
+            const uint32_t c = B.head[v];
+            if (c != NIL) { v = c; continue; }
+            entering = false;
         }
+        B.hi[v] = (Ix)r;
+        if (v == 0) break;
+        const uint32_t s = B.next[v];
+        if (s != NIL) { v = s; entering = true; } else { v = B.N[v].fail; }
     }
+}
 
-    // ---- pass 2: replay time over a max segment tree keyed by rank
+// pass 2: replay time over a max segment tree keyed by preorder rank
+template <typename Ix>
+SAM_HD void euler_pass2(EulerBlock<Ix>& B, const uint32_t* vw, uint32_t* out, uint32_t T) {
+    constexpr uint32_t NIL = Nil<Ix>::value;
     const uint32_t Lp = pow2_at_least(T);
-    Ix* seg = head;  // reuse (head/next are contiguous and large enough)
+    Ix* seg = B.head;  // head/next are dead now, contiguous and large enough
     for (uint32_t k = 0; k < 2 * Lp; ++k) seg[k] = 0;
     uint32_t acc = 0;
     for (uint32_t t = 0; t < T; ++t) {
-        const uint32_t v = vq[t];
+        const uint32_t v = B.vq[t];
         uint32_t bit = 0;
         if (v != NIL) {
-            uint32_t l = (uint32_t)lo[v] + Lp, r = (uint32_t)hi[v] + Lp, m = 0;
+            uint32_t l = (uint32_t)B.lo[v] + Lp, r = (uint32_t)B.hi[v] + Lp, m = 0;
             while (l < r) {
                 if (l & 1u) { const uint32_t s = seg[l++]; m = s > m ? s : m; }
                 if (r & 1u) { const uint32_t s = seg[--r]; m = s > m ? s : m; }
@@ -331,8 +347,17 @@ SAM_HD void run_euler(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, 
         }
         acc |= bit << (t & 31);
         if ((t & 31) == 31 || t + 1 == T) { out[t >> 5] = acc; acc = 0; }
-        for (uint32_t p = (uint32_t)lo[jid[t]] + Lp; p >= 1; p >>= 1) seg[p] = (Ix)(t + 1u);
+        for (uint32_t p = (uint32_t)B.lo[B.jid[t]] + Lp; p >= 1; p >>= 1) seg[p] = (Ix)(t + 1u);
     }
+}
+
+template <typename Ix>
+SAM_HD void run_euler(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw,
+                      uint32_t* out, uint32_t T, Counters* cnt) {
+    EulerBlock<Ix> B(scratch, T);
+    const uint32_t n = euler_pass1<Ix>(B, qw, kw, T, cnt);
+    euler_tour<Ix>(B, n);
+    euler_pass2<Ix>(B, vw, out, T);
 }
 
 }  // namespace sam

@@ -1,0 +1,332 @@
+// Tensor-core GEMM for the Heron linears on sm_100a: D[M,N] = A[M,K] . W[N,K]^T
+// with f32 accumulation in TMEM (tcgen05.mma, kind::f16) and a fused epilogue.
+//
+//  * A (activations, 16-bit, K-major) arrives by TMA into 128-byte-swizzled
+//    shared tiles; an optional second A operand ("lo" part of a hi+lo split of
+//    f32 activations) is multiplied into the same accumulator.
+//  * W is either packed +/-1 bits - expanded inside the kernel from 32-bit
+//    words into FP16 +/-1.0 rows written straight into the swizzled layout the
+//    MMA reads (reference weight order: bit o*K+i, LSB first, 1 => +1,
+//    src/model.rs:146-148) - or a dense FP16 [N,K] matrix loaded by TMA.
+//  * One CTA computes one 128x128 tile: warp 0 issues TMA, warp 1 owns TMEM and
+//    issues the MMAs, warps 2-5 expand weight bits during the main loop and
+//    then run the epilogue, one TMEM lane (= output row) per thread.
+//  * Pipeline: STAGES shared-memory stages guarded by full/empty mbarriers;
+//    every wait is bounded and reports through the status word.
+//
+// Epilogues (y = bias + scale * acc, FP16 row scale / bias, either may be null):
+//   EPI_STORE     f32 store                      (src/model.rs:724-742)
+//   EPI_RESIDUAL  out += y                       (src/model.rs:2232-2239)
+//   EPI_RELU2     16-bit store of max(y,0)^2     (src/model.rs:999)
+//   EPI_SIGNBITS  sign bit y > 0 per element, 32 consecutive steps of a channel
+//                 per word (stream-major), plus a "too close to zero to trust
+//                 the tensor-core sum" flag word  (src/rosa.rs:372-374)
+//   EPI_CE        per-row partial (max, sum exp, target logit) over the tile's
+//                 vocabulary slice               (src/model.rs:3219-3226)
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.hpp"
+#include "tc_ptx.cuh"
+
+namespace ullis {
+namespace tc {
+
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_RELU2 = 2, EPI_SIGNBITS = 3, EPI_CE = 4 };
+
+constexpr int BM = 128, BN = 128, BK = 64, STAGES = 4;
+constexpr int TILE_BYTES = BM * BK * 2;  // 16 KiB, also the B tile (BN == BM)
+constexpr int GEMM_THREADS = 192;
+
+struct GemmProblem {
+    const uint32_t* bits;   // packed weights (PACKED kernels)
+    const uint16_t* scale;  // FP16 [N] or null (= 1)
+    const uint16_t* bias;   // FP16 [N] or null (= 0)
+    void* out;
+    void* out2;
+    const float* aux;       // EPI_SIGNBITS: per-row sum |a| ; EPI_CE: unused
+};
+
+struct GemmMaps {
+    CUtensorMap a[3][2];  // [problem][hi, lo]
+    CUtensorMap b[3];     // dense weights
+};
+
+struct GemmParams {
+    GemmProblem prob[3];
+    uint32_t M, N, K;
+    uint32_t n_a;            // 1 or 2 A operands
+    uint32_t a_fmt, b_fmt;   // 0 = f16, 1 = bf16
+    uint32_t out_fmt;        // EPI_RELU2: 0 = f16, 1 = bf16
+    uint32_t time, wps;      // EPI_SIGNBITS / EPI_CE: steps per sequence, words per stream
+    const uint32_t* labels;  // EPI_CE
+    uint32_t ignore_id;      // EPI_CE
+    uint32_t n_tiles;        // EPI_CE: number of vocabulary tiles (gridDim.x)
+    uint32_t* status;
+};
+
+inline size_t gemm_smem_bytes(uint32_t n_a) {
+    return 1024 /*alignment slack*/ + (size_t)STAGES * (n_a + 1) * TILE_BYTES + 256 * 16 /*LUT*/ + 2 * BN * 4 + 256;
+}
+
+__device__ __forceinline__ float h2f_bits(uint16_t b) { return __half2float(__ushort_as_half(b)); }
+
+// One output row (TMEM lane) per thread, 128 columns in four 32-column loads.
+// The TMEM loads are warp-collective, so row / column guards only wrap stores.
+template <int EPI>
+__device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem& pr, uint32_t taddr, uint32_t m,
+                                         uint32_t n0, const float* s_scale, const float* s_bias, int lane) {
+    const bool row_ok = m < p.M;
+    // EPI_SIGNBITS: the 32 rows of this warp are 32 consecutive steps of one sequence (M, time % 32 == 0)
+    const uint32_t m_warp = m - lane;
+    const float s1 = (EPI == EPI_SIGNBITS && row_ok) ? pr.aux[m] : 0.0f;
+    // EPI_CE running state
+    float run_max = -INFINITY, run_sum = 0.0f;
+    uint32_t target = 0xFFFFFFFFu;
+    if (EPI == EPI_CE && m + 1 < p.M) target = p.labels[m + 1];
+#pragma unroll 1
+    for (uint32_t c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr + c * 32, r);
+        ptx::tmem_ld_wait();
+        const uint32_t nc = n0 + c * 32;
+        if (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+            float* out = static_cast<float*>(pr.out) + (size_t)m * p.N + nc;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                float y[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) y[e] = s_bias[c * 32 + j + e] + s_scale[c * 32 + j + e] * __uint_as_float(r[j + e]);
+                if (!row_ok) continue;
+                if (nc + j + 3 < p.N) {
+                    float4* dst = reinterpret_cast<float4*>(out + j);
+                    float4 v = make_float4(y[0], y[1], y[2], y[3]);
+                    if (EPI == EPI_RESIDUAL) {
+                        const float4 o = *dst;
+                        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                    }
+                    *dst = v;
+                } else {
+                    for (int e = 0; e < 4; ++e)
+                        if (nc + j + e < p.N) out[j + e] = (EPI == EPI_RESIDUAL ? out[j + e] : 0.0f) + y[e];
+                }
+            }
+        } else if (EPI == EPI_RELU2) {
+            uint16_t* out = static_cast<uint16_t*>(pr.out) + (size_t)m * p.N + nc;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    float a = fmaxf(s_bias[c * 32 + j + e] + s_scale[c * 32 + j + e] * __uint_as_float(r[j + e]), 0.0f);
+                    float b = fmaxf(s_bias[c * 32 + j + e + 1] + s_scale[c * 32 + j + e + 1] * __uint_as_float(r[j + e + 1]), 0.0f);
+                    a *= a; b *= b;
+                    if (p.out_fmt == 1) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                        w[e / 2] = *reinterpret_cast<uint32_t*>(&h);
+                    } else {
+                        __half2 h = __floats2half2_rn(a, b);
+                        w[e / 2] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                }
+                if (row_ok && nc + j + 7 < p.N) *reinterpret_cast<uint4*>(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else if (EPI == EPI_SIGNBITS) {
+            uint32_t my_bits = 0, my_flags = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float sc = s_scale[c * 32 + j], bi = s_bias[c * 32 + j];
+                const float t = sc * __uint_as_float(r[j]);
+                const float y = bi + t;
+                // error bound of the tensor-core sum against the reference's sequential f32 sum
+                const float guard = fabsf(sc) * (s1 * 1.3e-4f + 1e-4f) + 1e-6f * (fabsf(bi) + fabsf(t));
+                const uint32_t wb = __ballot_sync(0xffffffffu, row_ok && y > 0.0f);
+                const uint32_t wf = __ballot_sync(0xffffffffu, row_ok && fabsf(y) <= guard);
+                if (lane == j) { my_bits = wb; my_flags = wf; }
+            }
+            const uint32_t n = nc + lane;
+            if (m_warp < p.M && n < p.N) {
+                const uint32_t b = m_warp / p.time, word = (m_warp % p.time) >> 5;
+                const size_t o = ((size_t)b * p.N + n) * p.wps + word;
+                static_cast<uint32_t*>(pr.out)[o] = my_bits;
+                static_cast<uint32_t*>(pr.out2)[o] = my_flags;
+            }
+        } else if (EPI == EPI_CE) {
+            float cmax = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float y = s_bias[c * 32 + j] + s_scale[c * 32 + j] * __uint_as_float(r[j]);
+                r[j] = __float_as_uint(y);
+                if (nc + j < p.N) cmax = fmaxf(cmax, y);
+                if (nc + j == target && row_ok) static_cast<float*>(pr.out2)[m] = y;
+            }
+            if (cmax > -INFINITY) {
+                const float nmax = fmaxf(run_max, cmax);
+                float add = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (nc + j < p.N) add += __expf(__uint_as_float(r[j]) - nmax);
+                run_sum = run_sum * __expf(run_max - nmax) + add;
+                run_max = nmax;
+            }
+        }
+    }
+    if (EPI == EPI_CE && row_ok)
+        static_cast<float2*>(pr.out)[(size_t)m * p.n_tiles + blockIdx.x] = make_float2(run_max, run_sum);
+}
+
+template <int EPI, bool PACKED>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t stage_bytes = (p.n_a + 1) * TILE_BYTES;
+    uint8_t* tiles = smem;
+    uint4* lut = reinterpret_cast<uint4*>(smem + STAGES * stage_bytes);
+    float* s_scale = reinterpret_cast<float*>(lut + 256);
+    float* s_bias = s_scale + BN;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + BN);
+    uint64_t* full_a = bars;                 // [STAGES] TMA bytes landed
+    uint64_t* full_b = bars + STAGES;        // [STAGES] weight tile expanded
+    uint64_t* empty = bars + 2 * STAGES;     // [STAGES] MMAs that read the stage are done
+    uint64_t* tmem_full = bars + 3 * STAGES; // accumulator complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+    uint32_t* s_error = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t z = blockIdx.z;
+    const GemmProblem& pr = p.prob[z];
+    const uint32_t n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const uint32_t KB = p.K / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(&full_a[s], 1);
+            ptx::mbar_init(&full_b[s], 128);
+            ptx::mbar_init(&empty[s], 1);
+        }
+        ptx::mbar_init(tmem_full, 1);
+        *s_error = 0;
+        ptx::fence_mbar_init();
+        ptx::tma_prefetch_desc(&maps.a[z][0]);
+        if (p.n_a == 2) ptx::tma_prefetch_desc(&maps.a[z][1]);
+        if (!PACKED) ptx::tma_prefetch_desc(&maps.b[z]);
+    }
+    if (PACKED) {
+        // 8 weight bits -> 8 FP16 values (+1.0 = 0x3C00, -1.0 = 0xBC00), bit i -> element i
+        for (int b = threadIdx.x; b < 256; b += GEMM_THREADS) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t lo = (b >> (2 * j)) & 1u, hi = (b >> (2 * j + 1)) & 1u;
+                w[j] = (lo ? 0x3C00u : 0xBC00u) | ((hi ? 0x3C00u : 0xBC00u) << 16);
+            }
+            lut[b] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+    if (warp >= 2) {
+        const int c = threadIdx.x - 64;  // 0..127: column of the tile
+        const uint32_t n = n0 + c;
+        s_scale[c] = (pr.scale && n < p.N) ? h2f_bits(pr.scale[n]) : 1.0f;
+        s_bias[c] = (pr.bias && n < p.N) ? h2f_bits(pr.bias[n]) : 0.0f;
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, 128);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (ptx::elect_one()) {
+            const uint32_t tx = (p.n_a + (PACKED ? 0 : 1)) * TILE_BYTES;
+            uint32_t issued = 0;
+            for (uint32_t kb = 0; kb < KB; ++kb, ++issued) {
+                const uint32_t s = kb % STAGES;
+                if (kb >= STAGES && !ptx::mbar_wait(&empty[s], ((kb / STAGES) & 1u) ^ 1u)) { atomicExch(s_error, 1u); break; }
+                uint8_t* st = tiles + s * stage_bytes;
+                ptx::mbar_arrive_expect_tx(&full_a[s], tx);
+                ptx::tma_load_2d(st, &maps.a[z][0], &full_a[s], (int32_t)(kb * BK), (int32_t)m0);
+                if (p.n_a == 2) ptx::tma_load_2d(st + TILE_BYTES, &maps.a[z][1], &full_a[s], (int32_t)(kb * BK), (int32_t)m0);
+                if (!PACKED) ptx::tma_load_2d(st + p.n_a * TILE_BYTES, &maps.b[z], &full_a[s], (int32_t)(kb * BK), (int32_t)n0);
+            }
+            if (*s_error) {
+                // leave no copy in flight: wait (bounded) for every stage this thread filled last
+                const uint32_t first = issued > STAGES ? issued - STAGES : 0;
+                for (uint32_t kb = first; kb < issued; ++kb) ptx::mbar_wait(&full_a[kb % STAGES], (kb / STAGES) & 1u);
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (ptx::elect_one()) {
+            const uint32_t idesc = ptx::idesc_f16(p.a_fmt, p.b_fmt, BM, BN);
+            bool ok = true;
+            for (uint32_t kb = 0; kb < KB && ok; ++kb) {
+                const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
+                ok = ptx::mbar_wait(&full_a[s], ph);
+                if (ok && PACKED) ok = ptx::mbar_wait(&full_b[s], ph);
+                if (!ok) { atomicExch(s_error, 2u); break; }
+                ptx::tc_fence_after_sync();
+                const uint32_t a_addr = ptx::smem_u32(tiles + s * stage_bytes);
+                const uint32_t b_addr = a_addr + p.n_a * TILE_BYTES;
+#pragma unroll
+                for (uint32_t k4 = 0; k4 < BK / 16; ++k4) {
+                    const uint64_t db = ptx::smem_desc_sw128(b_addr + k4 * 32);
+                    ptx::mma_f16_ss(tmem_base, ptx::smem_desc_sw128(a_addr + k4 * 32), db, idesc, (kb | k4) != 0);
+                    if (p.n_a == 2)
+                        ptx::mma_f16_ss(tmem_base, ptx::smem_desc_sw128(a_addr + TILE_BYTES + k4 * 32), db, idesc, 1u);
+                }
+                ptx::mma_commit(&empty[s]);
+            }
+            ptx::mma_commit(tmem_full);  // also fires on the error path so the epilogue does not wait in vain
+        }
+    } else {
+        // ------------------------------------- weight expansion, then epilogue
+        const int r = threadIdx.x - 64;  // tile row of W (0..127) now, output row later
+        if (PACKED) {
+            const uint32_t n = n0 + r;
+            const uint32_t* wrow = pr.bits + ((size_t)n * p.K >> 5);
+            for (uint32_t kb = 0; kb < KB; ++kb) {
+                const uint32_t s = kb % STAGES;
+                if (kb >= STAGES && !ptx::mbar_wait(&empty[s], ((kb / STAGES) & 1u) ^ 1u)) { atomicExch(s_error, 3u); break; }
+                uint32_t w0 = 0, w1 = 0;
+                if (n < p.N) { w0 = wrow[kb * 2]; w1 = wrow[kb * 2 + 1]; }
+                uint8_t* dst = tiles + s * stage_bytes + p.n_a * TILE_BYTES + r * 128;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t byte = ((j < 4 ? w0 : w1) >> (8 * (j & 3))) & 0xFFu;
+                    *reinterpret_cast<uint4*>(dst + ((j ^ (r & 7)) << 4)) = lut[byte];
+                }
+                ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the MMA's async reads
+                ptx::mbar_arrive(&full_b[s]);
+            }
+        }
+        // epilogue: this warp may only touch TMEM lanes 32*(warp%4) .. +31
+        const uint32_t quarter = warp & 3;
+        const uint32_t row_in_tile = quarter * 32 + lane;
+        const uint32_t m = m0 + row_in_tile;
+        const bool waited = ptx::mbar_wait(tmem_full, 0);
+        if (!waited) atomicExch(s_error, 4u);
+        ptx::tc_fence_after_sync();
+        if (waited && *s_error == 0) {
+            const uint32_t taddr = tmem_base + ((quarter * 32) << 16);
+            epilogue<EPI>(p, pr, taddr, m, n0, s_scale, s_bias, lane);
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, 128);
+    }
+    if (threadIdx.x == 0 && *s_error) {
+        if (atomicCAS(p.status, ULLIS_DEV_OK, ULLIS_DEV_WAIT_TIMEOUT) == ULLIS_DEV_OK) p.status[1] = *s_error;
+    }
+}
+
+}  // namespace tc
+}  // namespace ullis
