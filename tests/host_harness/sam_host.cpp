@@ -21,10 +21,15 @@ static int run_batch(int algo, const uint32_t* qw, const uint32_t* kw, const uin
     Counters cnt{0, 0};
     for (size_t s = 0; s < n_streams; ++s) {
         std::memset(base, 0xA5, bytes);  // the routines must not rely on zeroed scratch
+        uint32_t c = 0;
+        if (algo == 2 && k_is_constant(kw + s * wps, T, &c)) {
+            run_constant_k(qw + s * wps, vw + s * wps, out + s * wps, T, c);
+            continue;
+        }
         if (algo == 0)
             run_eager<Ix>(base, qw + s * wps, kw + s * wps, vw + s * wps, out + s * wps, T, &cnt);
-        else
-            run_euler<Ix>(base, qw + s * wps, kw + s * wps, vw + s * wps, out + s * wps, T, &cnt);
+        else if (!run_euler<Ix>(base, qw + s * wps, kw + s * wps, vw + s * wps, out + s * wps, T, &cnt))
+            return 2;  // an internal invariant of the automaton failed
     }
     if (visits) *visits = cnt.node_visits;
     if (chain) *chain = cnt.chain_steps;

@@ -40,13 +40,17 @@ def test_exhaustive_t4_as_one_batch(cuda_rt, oracle):
     run_both(cuda_rt, oracle, pack_plane(bits(0)), pack_plane(bits(1)), pack_plane(bits(2)), 1, T, n)
 
 
-@pytest.mark.parametrize("kind", ["const", "biased", "periodic_clean", "qk_same"])
+@pytest.mark.parametrize("kind", ["const", "k_const_mixed", "biased", "periodic_clean", "qk_same"])
 def test_worst_case_streams(cuda_rt, oracle, kind):
     B, T, C = 1, 2048, 32
     rng = np.random.default_rng(len(kind))
     if kind == "const":
         q = np.repeat(rng.integers(0, 2, (1, C), dtype=np.uint8), T, 0)
         k = np.repeat(rng.integers(0, 2, (1, C), dtype=np.uint8), T, 0)
+    elif kind == "k_const_mixed":  # half of the streams have constant k (closed-form path), random q
+        q = rng.integers(0, 2, (T, C), dtype=np.uint8)
+        k = rng.integers(0, 2, (T, C), dtype=np.uint8)
+        k[:, ::2] = rng.integers(0, 2, (1, C // 2), dtype=np.uint8)
     elif kind == "biased":
         pr = rng.choice([0.001, 0.01, 0.99, 0.999], (1, C))
         q, k = (rng.random((T, C)) < pr).astype(np.uint8), (rng.random((T, C)) < pr).astype(np.uint8)

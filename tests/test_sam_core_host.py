@@ -7,7 +7,7 @@ import pytest
 
 from conftest import pack_streams
 
-ALGOS = {"eager": 0, "euler": 1}
+ALGOS = {"eager": 0, "euler": 1, "euler_with_constant_k_shortcut": 2}
 
 
 @pytest.mark.parametrize("T", [1, 2, 3, 4, 5])
@@ -28,6 +28,9 @@ def _streams(kind, n, T, rng):
     if kind == "const":
         return [np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1),
                 np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1), rng.integers(0, 2, (n, T), dtype=np.uint8)]
+    if kind == "k_const":
+        return [rng.integers(0, 2, (n, T), dtype=np.uint8), np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1),
+                rng.integers(0, 2, (n, T), dtype=np.uint8)]
     if kind == "biased":
         pr = rng.choice([0.001, 0.01, 0.99, 0.999], (n, 1))
         return [(rng.random((n, T)) < pr).astype(np.uint8), (rng.random((n, T)) < pr).astype(np.uint8),
@@ -45,7 +48,7 @@ def _streams(kind, n, T, rng):
     raise ValueError(kind)
 
 
-@pytest.mark.parametrize("kind,T,n", [("iid", 97, 200), ("iid", 2048, 24), ("const", 1024, 16), ("biased", 2048, 16),
+@pytest.mark.parametrize("kind,T,n", [("iid", 97, 200), ("iid", 2048, 24), ("const", 1024, 16), ("k_const", 1000, 16), ("k_const", 64, 8), ("biased", 2048, 16),
                                       ("periodic", 1500, 16), ("periodic_clean", 2048, 8), ("qk_same", 777, 32)])
 def test_long_streams(oracle, sam_host, kind, T, n):
     rng = np.random.default_rng(hash((kind, T)) & 0xFFFF)

@@ -91,6 +91,7 @@ struct ullis_cuda_runtime {
     uint32_t* host_status = nullptr;    // 4 words, pinned
     ullis::DeviceBuffer pool[24];       // op-level scratch slots
     ullis::DeviceBuffer sam_scratch;    // suffix-automaton state blocks
+    ullis::DeviceBuffer sam_list;       // ids of the streams that need the automaton + their count
     ullis::DeviceBuffer tc_ws[16];      // 16-bit operands / partials of the tensor-core stages
     int tc_ready = 0;                   // 0 = not probed, 1 = usable, -1 = unusable on this device
     ullis::NcclState* nccl = nullptr;

@@ -5,8 +5,9 @@
 // in sam_core.cuh; results equal T pushes of the reference's RosaSam
 // (src/rosa.rs:100-176) for every stream.
 //
-// Streams are processed in waves sized to the scratch budget, so any batch
-// works; all waves are enqueued back to back on the runtime stream.
+// Streams with constant k bits are finished by a closed form first; the rest
+// are processed in waves sized to the scratch budget, so any batch works; all
+// waves are enqueued back to back on the runtime stream.
 #include "kernels.hpp"
 #include "sam_core.cuh"
 
@@ -15,30 +16,58 @@ namespace k {
 
 namespace {
 
+// Streams whose k bits are all equal have a closed form (sam_core.cuh,
+// "constant k"): they are finished here with a few word operations; every
+// other stream id is appended to `list` for the automaton kernel.
+__global__ void __launch_bounds__(128)
+rosa_classify_kernel(const uint32_t* __restrict__ q_sw, const uint32_t* __restrict__ k_sw,
+                     const uint32_t* __restrict__ v_sw, uint32_t* __restrict__ idx_sw, size_t streams, uint32_t T,
+                     size_t wps, uint32_t* __restrict__ list, uint32_t* __restrict__ count) {
+    const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= streams) return;
+    uint32_t c = 0;
+    if (sam::k_is_constant(k_sw + s * wps, T, &c))
+        sam::run_constant_k(q_sw + s * wps, v_sw + s * wps, idx_sw + s * wps, T, c);
+    else
+        list[atomicAdd(count, 1u)] = (uint32_t)s;
+}
+
 // Only `lanes` threads of each warp carry a stream (the others exit at once).
 // A warp-level load completes when its slowest lane does, and a stream's
 // accesses are pointer chases into its own state block, so fewer streams per
-// warp (and more warps) shortens every dependent step.
+// warp (and more warps) shortens every dependent step.  Work item i of this
+// launch is stream list[first + i]; its state block is block i of `scratch`.
 template <typename Ix, int ALGO>
 __global__ void __launch_bounds__(128)
 rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
                 const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ v_sw,
-                uint32_t* __restrict__ idx_sw, size_t streams, uint32_t T, size_t wps, int lanes) {
+                uint32_t* __restrict__ idx_sw, const uint32_t* __restrict__ list,
+                const uint32_t* __restrict__ count, size_t first, uint32_t T, size_t wps, int lanes,
+                uint32_t* __restrict__ status) {
     const int lane = threadIdx.x & 31;
     const int spread = 32 / lanes;
     if (lane % spread != 0) return;
     const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const size_t s = warp * lanes + lane / spread;
-    if (s >= streams) return;
-    uint8_t* block = scratch + s * scratch_stride;
+    const size_t item = warp * lanes + lane / spread;
+    if (first + item >= *count) return;
+    const size_t s = list[first + item];
+    uint8_t* block = scratch + item * scratch_stride;
     const uint32_t* qw = q_sw + s * wps;
     const uint32_t* kw = k_sw + s * wps;
     const uint32_t* vw = v_sw + s * wps;
     uint32_t* out = idx_sw + s * wps;
     if (ALGO == ULLIS_CUDA_SAM_EAGER)
         sam::run_eager<Ix>(block, qw, kw, vw, out, T, nullptr);
-    else
-        sam::run_euler<Ix>(block, qw, kw, vw, out, T, nullptr);
+    else if (!sam::run_euler<Ix>(block, qw, kw, vw, out, T, nullptr)) {
+        if (atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_SAM_CAPACITY) == ULLIS_DEV_OK) status[1] = (uint32_t)s;
+    }
+}
+
+// EAGER keeps the reference's schedule for every stream (no shortcut): list = all streams
+__global__ void rosa_list_all_kernel(uint32_t* __restrict__ list, uint32_t* __restrict__ count, size_t streams) {
+    const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (s < streams) list[s] = (uint32_t)s;
+    if (s == 0) *count = (uint32_t)streams;
 }
 
 template <typename Ix>
@@ -72,30 +101,37 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     if (wave == 0) fail(ULLIS_CUDA_ERR_NOMEM, "not enough device memory for one suffix-automaton state block");
     if (wave > streams) wave = streams;
     uint8_t* scratch = static_cast<uint8_t*>(rt->sam_scratch.ensure(wave * stride));
+    if (streams > 0xFFFFFFFFull) fail(ULLIS_CUDA_ERR_SHAPE, "too many ROSA streams");
+    uint32_t* list = rt->sam_list.as<uint32_t>(streams + 1);
+    uint32_t* count = list + streams;
+    const unsigned cgrid = (unsigned)((streams + 127) / 128);
+    if (algo == ULLIS_CUDA_SAM_EAGER) {
+        rosa_list_all_kernel<<<cgrid, 128, 0, rt->stream>>>(list, count, streams);
+        rt->launched("rosa_list_all");
+    } else {
+        rt->zero(count, 4);
+        rosa_classify_kernel<<<cgrid, 128, 0, rt->stream>>>(q_sw, k_sw, v_sw, idx_sw, streams, (uint32_t)time, wps, list,
+                                                             count);
+        rt->launched("rosa_classify");
+    }
+    // The number of streams left for the automaton is only known on the device;
+    // each wave is sized for the worst case and surplus threads exit at once.
     for (size_t s0 = 0; s0 < streams; s0 += wave) {
         const size_t n = streams - s0 < wave ? streams - s0 : wave;
         const int lanes = rt->sam_lanes;
         const size_t warps = (n + lanes - 1) / lanes;
         const unsigned grid = (unsigned)((warps * 32 + 127) / 128);
-        const uint32_t* q = q_sw + s0 * wps;
-        const uint32_t* kk = k_sw + s0 * wps;
-        const uint32_t* v = v_sw + s0 * wps;
-        uint32_t* o = idx_sw + s0 * wps;
+#define ULLIS_SAM_LAUNCH(IX, ALGO)                                                                              \
+    rosa_sam_kernel<IX, ALGO><<<grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, k_sw, v_sw, idx_sw, list, count, s0, \
+                                                           (uint32_t)time, wps, lanes, rt->dev_status)
         if (narrow) {
-            if (algo == ULLIS_CUDA_SAM_EAGER)
-                rosa_sam_kernel<uint16_t, ULLIS_CUDA_SAM_EAGER><<<grid, 128, 0, rt->stream>>>(
-                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps, lanes);
-            else
-                rosa_sam_kernel<uint16_t, ULLIS_CUDA_SAM_EULER><<<grid, 128, 0, rt->stream>>>(
-                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps, lanes);
+            if (algo == ULLIS_CUDA_SAM_EAGER) ULLIS_SAM_LAUNCH(uint16_t, ULLIS_CUDA_SAM_EAGER);
+            else ULLIS_SAM_LAUNCH(uint16_t, ULLIS_CUDA_SAM_EULER);
         } else {
-            if (algo == ULLIS_CUDA_SAM_EAGER)
-                rosa_sam_kernel<uint32_t, ULLIS_CUDA_SAM_EAGER><<<grid, 128, 0, rt->stream>>>(
-                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps, lanes);
-            else
-                rosa_sam_kernel<uint32_t, ULLIS_CUDA_SAM_EULER><<<grid, 128, 0, rt->stream>>>(
-                    scratch, stride, q, kk, v, o, n, (uint32_t)time, wps, lanes);
+            if (algo == ULLIS_CUDA_SAM_EAGER) ULLIS_SAM_LAUNCH(uint32_t, ULLIS_CUDA_SAM_EAGER);
+            else ULLIS_SAM_LAUNCH(uint32_t, ULLIS_CUDA_SAM_EULER);
         }
+#undef ULLIS_SAM_LAUNCH
         rt->launched("rosa_sam");
     }
 }

@@ -66,22 +66,35 @@ SAM_HD uint32_t pow2_at_least(uint32_t n) {
 }
 SAM_HD size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Entries of the 16-ary max tree over T ranks: level sizes T', T'/16, ... down
+// to one group (T' = T rounded up to a multiple of 16 per level).
+SAM_HD uint32_t tree_entries(uint32_t T) {
+    uint32_t total = 0, n = T;
+    for (;;) {
+        n = (n + 15u) & ~15u;
+        total += n;
+        if (n <= 16u) break;
+        n >>= 4;
+    }
+    return total;
+}
+
 // Byte layout of one stream's scratch block for run_euler.
 template <typename Ix>
 struct EulerLayout {
-    size_t nodes, vq, jid, head, next, lo, hi, clone_bits, total;
+    size_t nodes, vq, jid, head, next, lh, clone_bits, total;
     SAM_HD explicit EulerLayout(uint32_t T) {
         const size_t cap = node_capacity(T);
         size_t off = 0;
         nodes = off; off = align_up(off + cap * sizeof(Node<Ix>), 16);
         vq = off;    off = align_up(off + (size_t)T * sizeof(Ix), 16);
         jid = off;   off = align_up(off + (size_t)T * sizeof(Ix), 16);
-        // head/next are dead once the tour is done; the segment tree (2*L
-        // entries, L = pow2 >= T, so at most 4T <= 2*cap) reuses their space.
+        // head/next (children lists of the suffix-link tree) are dead once the
+        // tour is done; the max tree of pass 2 (about 1.07 T entries <= 2*cap)
+        // reuses their space.
         head = off;  off = align_up(off + cap * sizeof(Ix), 16);
         next = off;  off = align_up(off + cap * sizeof(Ix), 16);
-        lo = off;    off = align_up(off + cap * sizeof(Ix), 16);
-        hi = off;    off = align_up(off + cap * sizeof(Ix), 16);
+        lh = off;    off = align_up(off + cap * 2 * sizeof(Ix), 16);   // {lo, hi} rank range per state
         clone_bits = off; off = align_up(off + ((cap + 31) / 32) * 4, 16);
         total = align_up(off, 128);
     }
@@ -256,9 +269,15 @@ SAM_HD void run_eager(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, 
 // ------------------------------------------------------------------ euler
 
 template <typename Ix>
+struct Pair {
+    Ix a, b;
+};
+
+template <typename Ix>
 struct EulerBlock {
     Node<Ix>* N;
-    Ix *vq, *jid, *head, *next, *lo, *hi;
+    Ix *vq, *jid, *head, *next;
+    Pair<Ix>* lh;    // rank range [a, b) of the stamped states below each state
     uint32_t* clone_bits;
     SAM_HD EulerBlock(uint8_t* scratch, uint32_t T) {
         EulerLayout<Ix> L(T);
@@ -267,8 +286,7 @@ struct EulerBlock {
         jid = reinterpret_cast<Ix*>(scratch + L.jid);
         head = reinterpret_cast<Ix*>(scratch + L.head);
         next = reinterpret_cast<Ix*>(scratch + L.next);
-        lo = reinterpret_cast<Ix*>(scratch + L.lo);
-        hi = reinterpret_cast<Ix*>(scratch + L.hi);
+        lh = reinterpret_cast<Pair<Ix>*>(scratch + L.lh);
         clone_bits = reinterpret_cast<uint32_t*>(scratch + L.clone_bits);
     }
 };
@@ -295,8 +313,8 @@ SAM_HD uint32_t euler_pass1(EulerBlock<Ix>& B, const uint32_t* qw, const uint32_
     return wk.u;
 }
 
-// tour: children lists, then preorder rank ranges [lo, hi) of the stamped
-// (non-clone, non-root) states below each state
+// tour: children lists, then a preorder walk; every state gets the half-open
+// rank range of the stamped (non-clone, non-root) states in its subtree
 template <typename Ix>
 SAM_HD void euler_tour(EulerBlock<Ix>& B, uint32_t n) {
     constexpr uint32_t NIL = Nil<Ix>::value;
@@ -310,36 +328,54 @@ SAM_HD void euler_tour(EulerBlock<Ix>& B, uint32_t n) {
     bool entering = true;
     for (;;) {
         if (entering) {
-            B.lo[v] = (Ix)r;
+            B.lh[v].a = (Ix)r;
             if (v != 0 && !((B.clone_bits[v >> 5] >> (v & 31)) & 1u)) ++r;
             const uint32_t c = B.head[v];
             if (c != NIL) { v = c; continue; }
             entering = false;
         }
-        B.hi[v] = (Ix)r;
+        B.lh[v].b = (Ix)r;
         if (v == 0) break;
         const uint32_t s = B.next[v];
         if (s != NIL) { v = s; entering = true; } else { v = B.N[v].fail; }
     }
 }
 
-// pass 2: replay time over a max segment tree keyed by preorder rank
+// pass 2: replay time over a 16-ary max tree keyed by preorder rank. Level 0
+// holds i+1 at the rank of j_i once i < t (0 = not yet); level k+1 holds the
+// maximum of each group of 16 entries of level k. Stamps only grow with time,
+// so an insert is one plain store per level.
 template <typename Ix>
 SAM_HD void euler_pass2(EulerBlock<Ix>& B, const uint32_t* vw, uint32_t* out, uint32_t T) {
     constexpr uint32_t NIL = Nil<Ix>::value;
-    const uint32_t Lp = pow2_at_least(T);
-    Ix* seg = B.head;  // head/next are dead now, contiguous and large enough
-    for (uint32_t k = 0; k < 2 * Lp; ++k) seg[k] = 0;
+    Ix* tree = B.head;  // head/next are dead now, contiguous and large enough
+    const uint32_t entries = tree_entries(T);
+    for (uint32_t k = 0; k < entries; ++k) tree[k] = 0;
     uint32_t acc = 0;
     for (uint32_t t = 0; t < T; ++t) {
         const uint32_t v = B.vq[t];
         uint32_t bit = 0;
         if (v != NIL) {
-            uint32_t l = (uint32_t)B.lo[v] + Lp, r = (uint32_t)B.hi[v] + Lp, m = 0;
+            const Pair<Ix> range = B.lh[v];
+            uint32_t l = range.a, r = range.b, m = 0, base = 0, size = (T + 15u) & ~15u;
             while (l < r) {
-                if (l & 1u) { const uint32_t s = seg[l++]; m = s > m ? s : m; }
-                if (r & 1u) { const uint32_t s = seg[--r]; m = s > m ? s : m; }
-                l >>= 1; r >>= 1;
+                const uint32_t lg = l >> 4, rg = (r - 1u) >> 4;
+                if (lg == rg) {
+                    for (uint32_t e = l; e < r; ++e) { const uint32_t s = tree[base + e]; m = s > m ? s : m; }
+                    break;
+                }
+                uint32_t l2 = lg, r2 = rg + 1u;
+                if (l & 15u) {
+                    for (uint32_t e = l; e < ((lg + 1u) << 4); ++e) { const uint32_t s = tree[base + e]; m = s > m ? s : m; }
+                    l2 = lg + 1u;
+                }
+                if (r & 15u) {
+                    for (uint32_t e = rg << 4; e < r; ++e) { const uint32_t s = tree[base + e]; m = s > m ? s : m; }
+                    r2 = rg;
+                }
+                base += size;
+                size = ((size >> 4) + 15u) & ~15u;
+                l = l2; r = r2;
             }
             // m = last + 1 >= 1: every state that exists at time t has a stamped
             // descendant (itself, or the state whose creation cloned it).
@@ -347,17 +383,57 @@ SAM_HD void euler_pass2(EulerBlock<Ix>& B, const uint32_t* vw, uint32_t* out, ui
         }
         acc |= bit << (t & 31);
         if ((t & 31) == 31 || t + 1 == T) { out[t >> 5] = acc; acc = 0; }
-        for (uint32_t p = (uint32_t)B.lo[B.jid[t]] + Lp; p >= 1; p >>= 1) seg[p] = (Ix)(t + 1u);
+        uint32_t pos = B.lh[B.jid[t]].a, base = 0, size = (T + 15u) & ~15u;
+        for (;;) {
+            tree[base + pos] = (Ix)(t + 1u);
+            if (size <= 16u) break;
+            base += size;
+            size = ((size >> 4) + 15u) & ~15u;
+            pos >>= 4;
+        }
+    }
+}
+
+// ------------------------------------------------------------ constant k
+//
+// If every k bit of a stream equals c, the automaton is the chain
+// root -> c -> cc -> ... with no clone, every chain state is stamped at every
+// step, and the query state either advances along the chain (q_t == c) or
+// falls off it to "no match" (q_t != c).  T pushes of the reference then give
+//     idx_t = v_t  if t >= 1 and q_t == c,   else 0
+// (at t = 0 the automaton is still empty).  Checked exhaustively against the
+// step-by-step form in the host harness.
+SAM_HD bool k_is_constant(const uint32_t* kw, uint32_t T, uint32_t* c_out) {
+    if (T == 0) return false;
+    const uint32_t c = kw[0] & 1u, full = c ? 0xFFFFFFFFu : 0u, wps = (T + 31) >> 5;
+    const uint32_t tail = (T & 31u) ? ((1u << (T & 31u)) - 1u) : 0xFFFFFFFFu;
+    for (uint32_t w = 0; w + 1 < wps; ++w)
+        if (kw[w] != full) return false;
+    if ((kw[wps - 1] & tail) != (full & tail)) return false;
+    *c_out = c;
+    return true;
+}
+
+SAM_HD void run_constant_k(const uint32_t* qw, const uint32_t* vw, uint32_t* out, uint32_t T, uint32_t c) {
+    const uint32_t wps = (T + 31) >> 5;
+    const uint32_t tail = (T & 31u) ? ((1u << (T & 31u)) - 1u) : 0xFFFFFFFFu;
+    for (uint32_t w = 0; w < wps; ++w) {
+        uint32_t word = (c ? qw[w] : ~qw[w]) & vw[w];
+        if (w == 0) word &= ~1u;
+        if (w + 1 == wps) word &= tail;
+        out[w] = word;
     }
 }
 
 template <typename Ix>
-SAM_HD void run_euler(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw,
+SAM_HD bool run_euler(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw,
                       uint32_t* out, uint32_t T, Counters* cnt) {
     EulerBlock<Ix> B(scratch, T);
     const uint32_t n = euler_pass1<Ix>(B, qw, kw, T, cnt);
+    if (n > node_capacity(T)) return false;  // cannot happen: an automaton over T symbols has at most 2T states
     euler_tour<Ix>(B, n);
     euler_pass2<Ix>(B, vw, out, T);
+    return true;
 }
 
 }  // namespace sam
