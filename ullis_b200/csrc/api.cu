@@ -141,6 +141,7 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         ULLIS_CUDA_CHECK(cudaMallocHost(&rt->host_status, 16));
         rt->clear_status();
         rt->sync();
+        if (const char* env = getenv("ULLIS_CUDA_SAM_COOP")) rt->sam_coop = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_LANES")) {
             const int v = atoi(env);
             if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16 || v == 32) rt->sam_lanes = v;

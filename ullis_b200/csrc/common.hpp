@@ -84,6 +84,8 @@ struct ullis_cuda_runtime {
     int cc_major = 0, cc_minor = 0;
     int mode = ULLIS_CUDA_MODE_FAST;
     int sam_algo = ULLIS_CUDA_SAM_EULER;
+    bool sam_coop = true;               // warp-cooperative tour / pass 2 when the stream fits shared memory
+    bool sam_coop_ready = false;
     int sam_lanes = 4;                  // streams carried per warp by the suffix-automaton kernel (1,2,4,...,32)
     uint64_t launches = 0;
     std::string last_error;

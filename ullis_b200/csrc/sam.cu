@@ -9,6 +9,7 @@
 // are processed in waves sized to the scratch budget, so any batch works; all
 // waves are enqueued back to back on the runtime stream.
 #include "kernels.hpp"
+#include "sam_coop.cuh"
 #include "sam_core.cuh"
 
 namespace ullis {
@@ -60,6 +61,39 @@ rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint
         sam::run_eager<Ix>(block, qw, kw, vw, out, T, nullptr);
     else if (!sam::run_euler<Ix>(block, qw, kw, vw, out, T, nullptr)) {
         if (atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_SAM_CAPACITY) == ULLIS_DEV_OK) status[1] = (uint32_t)s;
+    }
+}
+
+// Two-kernel form of the O(T log T) schedule for streams whose tour / pass 2
+// working set fits shared memory: pass 1 one thread per stream (below), then
+// one warp per stream for the parallel phases (sam_coop.cuh).
+__global__ void __launch_bounds__(128)
+rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
+                  const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ list,
+                  const uint32_t* __restrict__ count, size_t first, uint32_t T, size_t wps, int lanes) {
+    const int lane = threadIdx.x & 31;
+    const int spread = 32 / lanes;
+    if (lane % spread != 0) return;
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const size_t item = warp * lanes + lane / spread;
+    if (first + item >= *count) return;
+    const size_t s = list[first + item];
+    sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
+    sam::euler_pass1<uint16_t>(B, q_sw + s * wps, k_sw + s * wps, T, nullptr);
+}
+
+__global__ void __launch_bounds__(32)
+rosa_coop_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ v_sw,
+                 uint32_t* __restrict__ idx_sw, const uint32_t* __restrict__ list, const uint32_t* __restrict__ count,
+                 size_t first, uint32_t T, size_t wps, uint32_t* __restrict__ status) {
+    extern __shared__ __align__(16) uint8_t coop_smem[];
+    const size_t item = blockIdx.x;
+    if (first + item >= *count) return;
+    const size_t s = list[first + item];
+    sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
+    if (!sam::coop_tour_pass2(coop_smem, B, v_sw + s * wps, idx_sw + s * wps, T)) {
+        if (threadIdx.x == 0 && atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_SAM_CAPACITY) == ULLIS_DEV_OK)
+            status[1] = (uint32_t)s;
     }
 }
 
@@ -116,11 +150,27 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     }
     // The number of streams left for the automaton is only known on the device;
     // each wave is sized for the worst case and surplus threads exit at once.
+    const sam::CoopLayout coop((uint32_t)time);
+    const bool use_coop = algo == ULLIS_CUDA_SAM_EULER && narrow && rt->sam_coop && coop.total <= 110 * 1024 &&
+                          2 * sam::node_capacity((uint32_t)time) < 0xFFFFu;
+    if (use_coop && !rt->sam_coop_ready) {
+        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+        rt->sam_coop_ready = true;
+    }
     for (size_t s0 = 0; s0 < streams; s0 += wave) {
         const size_t n = streams - s0 < wave ? streams - s0 : wave;
         const int lanes = rt->sam_lanes;
         const size_t warps = (n + lanes - 1) / lanes;
         const unsigned grid = (unsigned)((warps * 32 + 127) / 128);
+        if (use_coop) {
+            rosa_pass1_kernel<<<grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, k_sw, list, count, s0, (uint32_t)time,
+                                                             wps, lanes);
+            rt->launched("rosa_pass1");
+            rosa_coop_kernel<<<(unsigned)n, 32, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, count, s0,
+                                                                         (uint32_t)time, wps, rt->dev_status);
+            rt->launched("rosa_coop");
+            continue;
+        }
 #define ULLIS_SAM_LAUNCH(IX, ALGO)                                                                              \
     rosa_sam_kernel<IX, ALGO><<<grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, k_sw, v_sw, idx_sw, list, count, s0, \
                                                            (uint32_t)time, wps, lanes, rt->dev_status)

@@ -82,7 +82,7 @@ SAM_HD uint32_t tree_entries(uint32_t T) {
 // Byte layout of one stream's scratch block for run_euler.
 template <typename Ix>
 struct EulerLayout {
-    size_t nodes, vq, jid, head, next, lh, clone_bits, total;
+    size_t nodes, vq, jid, head, next, lh, clone_bits, meta, total;
     SAM_HD explicit EulerLayout(uint32_t T) {
         const size_t cap = node_capacity(T);
         size_t off = 0;
@@ -96,6 +96,7 @@ struct EulerLayout {
         next = off;  off = align_up(off + cap * sizeof(Ix), 16);
         lh = off;    off = align_up(off + cap * 2 * sizeof(Ix), 16);   // {lo, hi} rank range per state
         clone_bits = off; off = align_up(off + ((cap + 31) / 32) * 4, 16);
+        meta = off;  off += 16;   // [0] = number of states after pass 1
         total = align_up(off, 128);
     }
 };
@@ -279,6 +280,7 @@ struct EulerBlock {
     Ix *vq, *jid, *head, *next;
     Pair<Ix>* lh;    // rank range [a, b) of the stamped states below each state
     uint32_t* clone_bits;
+    uint32_t* meta;
     SAM_HD EulerBlock(uint8_t* scratch, uint32_t T) {
         EulerLayout<Ix> L(T);
         N = reinterpret_cast<Node<Ix>*>(scratch + L.nodes);
@@ -288,6 +290,7 @@ struct EulerBlock {
         next = reinterpret_cast<Ix*>(scratch + L.next);
         lh = reinterpret_cast<Pair<Ix>*>(scratch + L.lh);
         clone_bits = reinterpret_cast<uint32_t*>(scratch + L.clone_bits);
+        meta = reinterpret_cast<uint32_t*>(scratch + L.meta);
     }
 };
 
@@ -310,6 +313,7 @@ SAM_HD uint32_t euler_pass1(EulerBlock<Ix>& B, const uint32_t* qw, const uint32_
         B.jid[i] = (Ix)j;
         if (b != NIL) B.clone_bits[b >> 5] |= 1u << (b & 31);
     }
+    B.meta[0] = wk.u;
     return wk.u;
 }
 
