@@ -82,7 +82,7 @@ rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const ui
     sam::euler_pass1<uint16_t>(B, q_sw + s * wps, k_sw + s * wps, T, nullptr);
 }
 
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(sam::COOP_THREADS)
 rosa_coop_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ v_sw,
                  uint32_t* __restrict__ idx_sw, const uint32_t* __restrict__ list, const uint32_t* __restrict__ count,
                  size_t first, uint32_t T, size_t wps, uint32_t* __restrict__ status) {
@@ -91,10 +91,12 @@ rosa_coop_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uin
     if (first + item >= *count) return;
     const size_t s = list[first + item];
     sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
-    if (!sam::coop_tour_pass2(coop_smem, B, v_sw + s * wps, idx_sw + s * wps, T)) {
+    if (B.meta[0] > sam::node_capacity(T)) {  // cannot happen: at most 2T states
         if (threadIdx.x == 0 && atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_SAM_CAPACITY) == ULLIS_DEV_OK)
             status[1] = (uint32_t)s;
+        return;
     }
+    sam::coop_tour_pass2(coop_smem, B, v_sw + s * wps, idx_sw + s * wps, T);
 }
 
 // EAGER keeps the reference's schedule for every stream (no shortcut): list = all streams
@@ -166,7 +168,7 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
             rosa_pass1_kernel<<<grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, k_sw, list, count, s0, (uint32_t)time,
                                                              wps, lanes);
             rt->launched("rosa_pass1");
-            rosa_coop_kernel<<<(unsigned)n, 32, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, count, s0,
+            rosa_coop_kernel<<<(unsigned)n, sam::COOP_THREADS, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, count, s0,
                                                                          (uint32_t)time, wps, rt->dev_status);
             rt->launched("rosa_coop");
             continue;
