@@ -124,42 +124,72 @@ emit_f16_kernel(const uint32_t* __restrict__ idx_sw, const uint16_t* __restrict_
 // Sign bits whose tensor-core pre-activation fell inside the error band are
 // recomputed exactly as the reference does (src/model.rs:724-742 on the
 // time-shift mix of x): sequential f32 sum over i, then bias + scale*sum.
-__global__ void __launch_bounds__(128)
+// Flags are sparse (a few per thousand), so a CTA first gathers the flagged
+// (word, bit) pairs of its chunk into a shared queue and then spreads them
+// over all of its threads - one exact dot product per thread.
+constexpr int FIX_THREADS = 256, FIX_WORDS = 2048, FIX_QUEUE = 16384;
+
+__global__ void __launch_bounds__(FIX_THREADS)
 sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, const uint16_t* __restrict__ mk,
                   const uint16_t* __restrict__ mv, PackedWeights wq, PackedWeights wk, PackedWeights wv,
                   uint32_t* __restrict__ bq, uint32_t* __restrict__ bk, uint32_t* __restrict__ bv,
                   const uint32_t* __restrict__ fq, const uint32_t* __restrict__ fk, const uint32_t* __restrict__ fv,
                   size_t batch, size_t T, size_t C, size_t wps) {
-    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= batch * C * wps) return;
+    extern __shared__ uint32_t fix_queue[];  // entries: (word offset in chunk) << 5 | bit
+    __shared__ uint32_t q_count;
     const int which = blockIdx.y;
     const uint32_t* flags = which == 0 ? fq : which == 1 ? fk : fv;
-    uint32_t f = flags[e];
-    if (!f) return;
     uint32_t* bits = which == 0 ? bq : which == 1 ? bk : bv;
     const uint16_t* mix = which == 0 ? mq : which == 1 ? mk : mv;
     const PackedWeights& W = which == 0 ? wq : which == 1 ? wk : wv;
-    const size_t s = e / wps, word = e % wps, b = s / C, c = s % C;
-    const float scale = h2f(W.scale[c]), bias = W.bias ? h2f(W.bias[c]) : 0.0f;
-    uint32_t out = bits[e];
-    while (f) {
-        const int tt = __ffs(f) - 1;
-        f &= f - 1;
-        const size_t t = word * 32 + tt, row = b * T + t;
-        const float* xr = x + row * C;
-        float sum = 0.0f;
-        for (size_t i = 0; i < C; ++i) {
-            const float xt = xr[i];
-            const float xx = t == 0 ? -xt : __fsub_rn((xr - C)[i], xt);
-            const float in = __fadd_rn(xt, __fmul_rn(xx, h2f(mix[i])));
-            const size_t index = c * C + i;
-            const float sgn = (W.bits[index >> 5] >> (index & 31)) & 1u ? 1.0f : -1.0f;
-            sum = __fmaf_rn(sgn, in, sum);
+    const size_t total = batch * C * wps, chunk0 = (size_t)blockIdx.x * FIX_WORDS;
+    if (threadIdx.x == 0) q_count = 0;
+    __syncthreads();
+    for (size_t sub = 0; sub < FIX_WORDS; sub += FIX_THREADS) {
+        const size_t e = chunk0 + sub + threadIdx.x;
+        uint32_t f = e < total ? flags[e] : 0u;
+        if (f) {
+            const uint32_t at = atomicAdd(&q_count, (uint32_t)__popc(f));
+            uint32_t k = 0;
+            while (f) {
+                const uint32_t tt = __ffs(f) - 1;
+                f &= f - 1;
+                fix_queue[at + k++] = ((uint32_t)(sub + threadIdx.x) << 5) | tt;
+            }
         }
-        const float y = __fadd_rn(bias, __fmul_rn(scale, sum));
-        out = (out & ~(1u << tt)) | ((y > 0.0f ? 1u : 0u) << tt);
+        __syncthreads();
+        const bool last = sub + FIX_THREADS >= FIX_WORDS;
+        if (q_count + FIX_THREADS * 32 <= FIX_QUEUE && !last) continue;  // room for another slice: keep gathering
+        const uint32_t count = q_count;
+        for (uint32_t i = threadIdx.x; i < count; i += FIX_THREADS) {
+            const uint32_t entry = fix_queue[i], tt = entry & 31u;
+            const size_t ew = chunk0 + (entry >> 5);
+            const size_t s = ew / wps, word = ew % wps, b = s / C, c = s % C;
+            const size_t t = word * 32 + tt, row = b * T + t;
+            const float* xr = x + row * C;
+            const uint32_t* wbits = W.bits + (c * C >> 5);  // C % 32 == 0 on this path
+            float sum = 0.0f;
+            for (size_t i4 = 0; i4 < C; i4 += 4) {
+                const float4 cur = *reinterpret_cast<const float4*>(xr + i4);
+                float4 prev = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (t != 0) prev = *reinterpret_cast<const float4*>(xr - C + i4);
+                const float xs[4] = {cur.x, cur.y, cur.z, cur.w}, ps[4] = {prev.x, prev.y, prev.z, prev.w};
+                const uint32_t wword = wbits[i4 >> 5] >> (i4 & 31);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float xt = xs[k];
+                    const float xx = t == 0 ? -xt : __fsub_rn(ps[k], xt);
+                    const float in = __fadd_rn(xt, __fmul_rn(xx, h2f(mix[i4 + k])));
+                    sum = __fmaf_rn((wword >> k) & 1u ? 1.0f : -1.0f, in, sum);
+                }
+            }
+            const float y = __fadd_rn(W.bias ? h2f(W.bias[c]) : 0.0f, __fmul_rn(h2f(W.scale[c]), sum));
+            if (y > 0.0f) atomicOr(&bits[ew], 1u << tt); else atomicAnd(&bits[ew], ~(1u << tt));
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) q_count = 0;
+        __syncthreads();
     }
-    bits[e] = out;
 }
 
 // Merge the per-tile (max, sum exp) partials of a row and subtract the target
@@ -212,6 +242,8 @@ bool usable(ullis_cuda_runtime* rt) {
             ULLIS_SET_SMEM(EPI_SIGNBITS, true);
             ULLIS_SET_SMEM(EPI_CE, true);
 #undef ULLIS_SET_SMEM
+            ULLIS_CUDA_CHECK(cudaFuncSetAttribute(sign_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  FIX_QUEUE * 4));
             rt->tc_ready = 1;
         }
     }
@@ -314,8 +346,8 @@ bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeig
     for (int z = 0; z < 3; ++z)
         p.prob[z] = GemmProblem{W[z]->bits, W[z]->scale, W[z]->bias, outs[z], flags + z * sw, s1 + z * rows};
     launch<EPI_SIGNBITS, true>(rt, maps, p, 3, "gemm_qkv_signbits");
-    dim3 grid(blocks_for(sw, 128), 3);
-    sign_fixup_kernel<<<grid, 128, 0, rt->stream>>>(ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, flags,
+    dim3 grid(blocks_for(sw, FIX_WORDS), 3);
+    sign_fixup_kernel<<<grid, FIX_THREADS, FIX_QUEUE * 4, rt->stream>>>(ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, flags,
                                                    flags + sw, flags + 2 * sw, batch, time, d, wps);
     rt->launched("sign_fixup");
     return true;
