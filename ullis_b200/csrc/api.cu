@@ -141,6 +141,10 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         ULLIS_CUDA_CHECK(cudaMallocHost(&rt->host_status, 16));
         rt->clear_status();
         rt->sync();
+        if (const char* env = getenv("ULLIS_CUDA_TC_STAGES")) {
+            const int a = atoi(env) / 10, b = atoi(env) % 10;   // e.g. 32 = 3 stages (one operand), 2 stages (two)
+            if (a >= 2 && a <= 4 && b >= 2 && b <= 4) { rt->tc_stages = a; rt->tc_stages2 = b; }
+        }
         if (const char* env = getenv("ULLIS_CUDA_SAM_COOP")) rt->sam_coop = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_LANES")) {
             const int v = atoi(env);

@@ -95,6 +95,7 @@ struct ullis_cuda_runtime {
     ullis::DeviceBuffer sam_scratch;    // suffix-automaton state blocks
     ullis::DeviceBuffer sam_list;       // ids of the streams that need the automaton + their count
     ullis::DeviceBuffer tc_ws[16];      // 16-bit operands / partials of the tensor-core stages
+    int tc_stages = 2, tc_stages2 = 2;  // GEMM pipeline depth with one / two activation operands
     int tc_ready = 0;                   // 0 = not probed, 1 = usable, -1 = unusable on this device
     ullis::NcclState* nccl = nullptr;
 

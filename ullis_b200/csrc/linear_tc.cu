@@ -231,7 +231,7 @@ bool usable(ullis_cuda_runtime* rt) {
         rt->tc_ready = -1;
         if (rt->cc_major == 10 && !getenv("ULLIS_CUDA_NO_TC")) {
             encode_fn();
-            const int smem = (int)gemm_smem_bytes(2);
+            const int smem = (int)gemm_smem_bytes(2, MAX_STAGES);
 #define ULLIS_SET_SMEM(EPI, PACKED) \
     ULLIS_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<EPI, PACKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))
             ULLIS_SET_SMEM(EPI_STORE, true);
@@ -258,7 +258,7 @@ bool shape_ok(size_t M, size_t K, size_t N) {
 template <int EPI, bool PACKED>
 void launch(ullis_cuda_runtime* rt, const GemmMaps& maps, const GemmParams& p, unsigned n_prob, const char* what) {
     dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, n_prob);
-    gemm_kernel<EPI, PACKED><<<grid, GEMM_THREADS, gemm_smem_bytes(p.n_a), rt->stream>>>(maps, p);
+    gemm_kernel<EPI, PACKED><<<grid, GEMM_THREADS, gemm_smem_bytes(p.n_a, p.stages), rt->stream>>>(maps, p);
     rt->launched(what);
 }
 
@@ -269,6 +269,7 @@ GemmParams base_params(ullis_cuda_runtime* rt, size_t M, size_t N, size_t K) {
     p.N = (uint32_t)N;
     p.K = (uint32_t)K;
     p.n_a = 1;
+    p.stages = rt->tc_stages;   // shallow pipeline, several CTAs per SM: one CTA's epilogue runs under another's MMAs
     p.status = rt->dev_status;
     return p;
 }
@@ -339,6 +340,7 @@ bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeig
     }
     GemmParams p = base_params(rt, rows, d, d);
     p.n_a = 2;
+    p.stages = rt->tc_stages2;
     p.time = (uint32_t)time;
     p.wps = (uint32_t)wps;
     const PackedWeights* W[3] = {&L.q, &L.k, &L.v};

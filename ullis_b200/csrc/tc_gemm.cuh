@@ -35,7 +35,7 @@ namespace tc {
 
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_RELU2 = 2, EPI_SIGNBITS = 3, EPI_CE = 4 };
 
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 4;
+constexpr int BM = 128, BN = 128, BK = 64, MAX_STAGES = 4;
 constexpr int TILE_BYTES = BM * BK * 2;  // 16 KiB, also the B tile (BN == BM)
 constexpr int GEMM_THREADS = 192;
 
@@ -57,6 +57,7 @@ struct GemmParams {
     GemmProblem prob[3];
     uint32_t M, N, K;
     uint32_t n_a;            // 1 or 2 A operands
+    uint32_t stages;         // shared-memory pipeline depth, 2..MAX_STAGES
     uint32_t a_fmt, b_fmt;   // 0 = f16, 1 = bf16
     uint32_t out_fmt;        // EPI_RELU2: 0 = f16, 1 = bf16
     uint32_t time, wps;      // EPI_SIGNBITS / EPI_CE: steps per sequence, words per stream
@@ -66,8 +67,8 @@ struct GemmParams {
     uint32_t* status;
 };
 
-inline size_t gemm_smem_bytes(uint32_t n_a) {
-    return 1024 /*alignment slack*/ + (size_t)STAGES * (n_a + 1) * TILE_BYTES + 256 * 16 /*LUT*/ + 2 * BN * 4 + 256;
+inline size_t gemm_smem_bytes(uint32_t n_a, uint32_t stages) {
+    return 1024 /*alignment slack*/ + (size_t)stages * (n_a + 1) * TILE_BYTES + 256 * 16 /*LUT*/ + 2 * BN * 4 + 256;
 }
 
 __device__ __forceinline__ float h2f_bits(uint16_t b) { return __half2float(__ushort_as_half(b)); }
@@ -177,21 +178,22 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
 }
 
 template <int EPI, bool PACKED>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 3)
 gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t stage_bytes = (p.n_a + 1) * TILE_BYTES;
+    const uint32_t STAGES = p.stages;
     uint8_t* tiles = smem;
     uint4* lut = reinterpret_cast<uint4*>(smem + STAGES * stage_bytes);
     float* s_scale = reinterpret_cast<float*>(lut + 256);
     float* s_bias = s_scale + BN;
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + BN);
     uint64_t* full_a = bars;                 // [STAGES] TMA bytes landed
-    uint64_t* full_b = bars + STAGES;        // [STAGES] weight tile expanded
-    uint64_t* empty = bars + 2 * STAGES;     // [STAGES] MMAs that read the stage are done
-    uint64_t* tmem_full = bars + 3 * STAGES; // accumulator complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+    uint64_t* full_b = bars + MAX_STAGES;        // [STAGES] weight tile expanded
+    uint64_t* empty = bars + 2 * MAX_STAGES;     // [STAGES] MMAs that read the stage are done
+    uint64_t* tmem_full = bars + 3 * MAX_STAGES; // accumulator complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * MAX_STAGES + 1);
     uint32_t* s_error = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -201,7 +203,7 @@ gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     const uint32_t KB = p.K / BK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (uint32_t s = 0; s < STAGES; ++s) {
             ptx::mbar_init(&full_a[s], 1);
             ptx::mbar_init(&full_b[s], 128);
             ptx::mbar_init(&empty[s], 1);
