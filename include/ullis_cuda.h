@@ -94,6 +94,18 @@ ULLIS_CUDA_API int32_t ullis_cuda_runtime_synchronize(ullis_cuda_runtime* rt);
 ULLIS_CUDA_API void* ullis_cuda_runtime_stream(ullis_cuda_runtime* rt);
 /* Number of this library's kernels launched through `rt` so far. */
 ULLIS_CUDA_API uint64_t ullis_cuda_runtime_launch_count(const ullis_cuda_runtime* rt);
+/* Per-kernel device times (no counterpart in the reference; the Metal runtime
+ * is timed from the host, src/main.rs:706-736).  While enabled, an event is
+ * recorded behind every launch of this runtime; `kernel_time` synchronises the
+ * stream and returns the total milliseconds and the number of launches recorded
+ * under `name` since timing was enabled (all kernels when `name` is NULL or
+ * empty).  `kernel_names` writes the distinct names, newline-separated and
+ * NUL-terminated, into `buf` (truncated to `len`) and the size needed into
+ * `*needed`. */
+ULLIS_CUDA_API int32_t ullis_cuda_runtime_kernel_timing(ullis_cuda_runtime* rt, int32_t enabled);
+ULLIS_CUDA_API int32_t ullis_cuda_runtime_kernel_time(ullis_cuda_runtime* rt, const char* name, float* total_ms,
+                                                      uint32_t* launches);
+ULLIS_CUDA_API int32_t ullis_cuda_runtime_kernel_names(ullis_cuda_runtime* rt, char* buf, size_t len, size_t* needed);
 /* Compute capability check: 1 when the device is sm_100 class. */
 ULLIS_CUDA_API int32_t ullis_cuda_runtime_is_sm100(const ullis_cuda_runtime* rt);
 

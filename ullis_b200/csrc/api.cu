@@ -88,6 +88,56 @@ void ullis_cuda_runtime::launched(const char* what) {
     ++launches;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) fail(ULLIS_CUDA_ERR_CUDA, std::string("launch of ") + what + ": " + cudaGetErrorString(e));
+    if (kernel_timing) {
+        if (marks_used == marks.size()) {
+            LaunchMark m{what, nullptr};
+            ULLIS_CUDA_CHECK(cudaEventCreate(&m.done));
+            marks.push_back(m);
+        }
+        marks[marks_used].name = what;
+        ULLIS_CUDA_CHECK(cudaEventRecord(marks[marks_used].done, stream));
+        ++marks_used;
+    }
+}
+
+void ullis_cuda_runtime::kernel_timing_begin() {
+    if (!marks_start) ULLIS_CUDA_CHECK(cudaEventCreate(&marks_start));
+    marks_used = 0;
+    ULLIS_CUDA_CHECK(cudaEventRecord(marks_start, stream));
+}
+
+void ullis_cuda_runtime::kernel_time(const char* name, float* total_ms, uint32_t* n_launches) {
+    sync();
+    float total = 0.f;
+    uint32_t n = 0;
+    for (size_t i = 0; i < marks_used; ++i) {
+        if (name && name[0] && std::strcmp(name, marks[i].name) != 0) continue;
+        float t = 0.f;
+        ULLIS_CUDA_CHECK(cudaEventElapsedTime(&t, i ? marks[i - 1].done : marks_start, marks[i].done));
+        total += t;
+        ++n;
+    }
+    if (total_ms) *total_ms = total;
+    if (n_launches) *n_launches = n;
+}
+
+size_t ullis_cuda_runtime::kernel_names(char* buf, size_t len) {
+    std::vector<const char*> seen;
+    std::string out;
+    for (size_t i = 0; i < marks_used; ++i) {
+        bool dup = false;
+        for (const char* s : seen) dup = dup || std::strcmp(s, marks[i].name) == 0;
+        if (dup) continue;
+        seen.push_back(marks[i].name);
+        out += marks[i].name;
+        out += '\n';
+    }
+    if (buf && len) {
+        const size_t n = out.size() < len - 1 ? out.size() : len - 1;
+        std::memcpy(buf, out.data(), n);
+        buf[n] = 0;
+    }
+    return out.size() + 1;
 }
 
 void ullis_cuda_runtime::check_status() {
@@ -169,6 +219,8 @@ void ullis_cuda_runtime_destroy(ullis_cuda_runtime* rt) {
     }
     if (rt->dev_status) cudaFree(rt->dev_status);
     if (rt->host_status) cudaFreeHost(rt->host_status);
+    for (auto& m : rt->marks) cudaEventDestroy(m.done);
+    if (rt->marks_start) cudaEventDestroy(rt->marks_start);
     delete rt;
 }
 
@@ -198,6 +250,28 @@ int32_t ullis_cuda_runtime_synchronize(ullis_cuda_runtime* rt) {
 void* ullis_cuda_runtime_stream(ullis_cuda_runtime* rt) { return rt ? (void*)rt->stream : nullptr; }
 
 uint64_t ullis_cuda_runtime_launch_count(const ullis_cuda_runtime* rt) { return rt ? rt->launches : 0; }
+
+int32_t ullis_cuda_runtime_kernel_timing(ullis_cuda_runtime* rt, int32_t enabled) {
+    return guard(rt, [&] {
+        rt->bind();
+        rt->kernel_timing = enabled != 0;
+        if (rt->kernel_timing) rt->kernel_timing_begin();
+    });
+}
+
+int32_t ullis_cuda_runtime_kernel_time(ullis_cuda_runtime* rt, const char* name, float* total_ms, uint32_t* launches) {
+    return guard(rt, [&] {
+        rt->bind();
+        rt->kernel_time(name, total_ms, launches);
+    });
+}
+
+int32_t ullis_cuda_runtime_kernel_names(ullis_cuda_runtime* rt, char* buf, size_t len, size_t* needed) {
+    return guard(rt, [&] {
+        const size_t n = rt->kernel_names(buf, len);
+        if (needed) *needed = n;
+    });
+}
 
 int32_t ullis_cuda_runtime_is_sm100(const ullis_cuda_runtime* rt) { return rt && rt->cc_major == 10 ? 1 : 0; }
 

@@ -99,6 +99,19 @@ struct ullis_cuda_runtime {
     int tc_ready = 0;                   // 0 = not probed, 1 = usable, -1 = unusable on this device
     ullis::NcclState* nccl = nullptr;
 
+    // Per-kernel device times: while enabled, an event is recorded behind every
+    // launch; the stream is in order, so consecutive events bracket one kernel
+    // (plus any small copy queued just before it).
+    struct LaunchMark { const char* name; cudaEvent_t done; };
+    bool kernel_timing = false;
+    std::vector<LaunchMark> marks;
+    size_t marks_used = 0;
+    cudaEvent_t marks_start = nullptr;
+    void kernel_timing_begin();
+    // total milliseconds and launches of the kernels recorded under `name` (all kernels when name is empty)
+    void kernel_time(const char* name, float* total_ms, uint32_t* n_launches);
+    size_t kernel_names(char* buf, size_t len);  // newline-separated distinct names; returns bytes needed
+
     void bind() const { ULLIS_CUDA_CHECK(cudaSetDevice(device)); }
     void sync() { ULLIS_CUDA_CHECK(cudaStreamSynchronize(stream)); }
     void h2d(void* dst, const void* src, size_t bytes) {

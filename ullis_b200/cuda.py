@@ -37,6 +37,7 @@ ABI_SYMBOLS = (
     "ullis_cuda_runtime_create", "ullis_cuda_runtime_destroy", "ullis_cuda_last_error",
     "ullis_cuda_runtime_set_mode", "ullis_cuda_runtime_set_sam", "ullis_cuda_runtime_synchronize",
     "ullis_cuda_runtime_stream", "ullis_cuda_runtime_launch_count", "ullis_cuda_runtime_is_sm100",
+    "ullis_cuda_runtime_kernel_timing", "ullis_cuda_runtime_kernel_time", "ullis_cuda_runtime_kernel_names",
     "ullis_cuda_model_load_safetensors", "ullis_cuda_model_destroy", "ullis_cuda_model_dims",
     "ullis_cuda_model_forward_ce", "ullis_cuda_model_upload_tokens", "ullis_cuda_model_enqueue_forward_ce",
     "ullis_cuda_model_read_loss", "ullis_cuda_model_logits", "ullis_cuda_model_hidden",
@@ -144,6 +145,23 @@ class CudaRuntime:
     @property
     def launch_count(self) -> int:
         return int(self._lib.ullis_cuda_runtime_launch_count(self._h))
+
+    def kernel_timing(self, enabled: bool) -> None:
+        """Start (or stop) recording an event behind every launch; starting clears earlier records."""
+        self._check(self._lib.ullis_cuda_runtime_kernel_timing(self._h, C.c_int32(1 if enabled else 0)))
+
+    def kernel_times(self) -> dict:
+        """{kernel name: (total device ms, launches)} since kernel_timing(True)."""
+        need = C.c_size_t(0)
+        self._check(self._lib.ullis_cuda_runtime_kernel_names(self._h, None, C.c_size_t(0), C.byref(need)))
+        buf = C.create_string_buffer(max(int(need.value), 1))
+        self._check(self._lib.ullis_cuda_runtime_kernel_names(self._h, buf, C.c_size_t(len(buf)), C.byref(need)))
+        out = {}
+        for name in buf.value.decode().split():
+            ms, n = C.c_float(0), C.c_uint32(0)
+            self._check(self._lib.ullis_cuda_runtime_kernel_time(self._h, name.encode(), C.byref(ms), C.byref(n)))
+            out[name] = (float(ms.value), int(n.value))
+        return out
 
     @property
     def is_sm100(self) -> bool:
