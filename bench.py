@@ -293,8 +293,10 @@ def run_cuda(args):
     # ---------------- end-to-end timing through the public call, pinned host buffers
     if args.profile_run:
         if rank == 0:
+            top = sorted(kernel_ms.items(), key=lambda kv: -kv[1][0])[:8]
             print(json.dumps({"profile_run": True, "ms_per_step": ms_total / args.steps, "phases_ms": phases,
-                              "gpu_launches": int(launches)}), flush=True)
+                              "gpu_launches": int(launches),
+                              "kernel_ms_per_launch": {k: round(t / max(c, 1), 4) for k, (t, c) in top}}), flush=True)
         model.close()
         rt.close()
         return

@@ -8,15 +8,15 @@
 //
 //  tour   (whole CTA, 128 threads) Euler tour of the link tree as a linked
 //         list of 2n events (enter v, leave v); the rank of every event
-//         (number of stamped states entered before it) by in-place pointer
-//         jumping over packed (successor, partial sum) words - log2(2n)
-//         rounds, all lanes busy.
-//  pass 2 (whole CTA) 128 steps per round, one step per thread: each thread
-//         answers its range maximum from a 16-ary max tree holding the stamps
-//         of earlier rounds, takes the stamps of earlier steps of the same round
-//         from the round's published ranks (shuffles inside the warp, broadcast
-//         loads for earlier warps), then all threads insert their own stamp (one
-//         shared-memory atomicMax per tree level).
+//         (number of stamped states entered before it) by two-level list
+//         ranking: serial walks of short sublists between hashed splitters,
+//         then pointer jumping over the splitters only.
+//  pass 2 (whole CTA) the stamp of every rank is known up front (a state is
+//         stamped once, when created), so a step with a narrow rank range scans
+//         that array directly, all steps in parallel.  Steps with wide ranges
+//         use a 16-ary max tree whose upper levels are replayed in rounds of 128
+//         steps (one shared-memory atomicMax per level and step); a stream
+//         without wide ranges skips the replay.
 //
 // 16-bit state ids only (2T+2 <= 65535); the caller falls back to the
 // one-thread-per-stream routine for longer streams or when the block does not
@@ -36,7 +36,7 @@ constexpr int COOP_THREADS = 128;
 #endif
 
 struct CoopLayout {
-    uint32_t ev, kid, parent, clone_bits, vbits, round_rank, total;
+    uint32_t ev, kid, parent, clone_bits, vbits, round_rank, wide, total;
     __host__ __device__ explicit CoopLayout(uint32_t T) {
         const uint32_t cap = node_capacity(T), wps = (T + 31) / 32;
         uint32_t off = 0;
@@ -47,6 +47,7 @@ struct CoopLayout {
         clone_bits = off; off += (((cap + 31) / 32) * 4 + 15) & ~15u;
         vbits = off;      off += (wps * 4 + 15) & ~15u;
         round_rank = off; off += COOP_THREADS * 4;                                // ranks of the steps of one pass-2 round
+        wide = off;       off += (wps * 4 + 15) & ~15u;                           // steps whose rank range is wide
         total = off;
     }
 };
@@ -61,6 +62,18 @@ __device__ __forceinline__ uint32_t group_max(const uint32_t* g, uint32_t first,
 #pragma unroll
     for (uint32_t e = 0; e < 16; ++e)
         if (first + e - l < r - l) m = max(m, val[e]);
+    return m;
+}
+
+// the same over the entries that are <= t (level 0 holds every stamp from the start)
+__device__ __forceinline__ uint32_t group_max_le(const uint32_t* g, uint32_t first, uint32_t l, uint32_t r, uint32_t t) {
+    const uint4* q = reinterpret_cast<const uint4*>(g);
+    const uint4 a = q[0], b = q[1], c = q[2], d = q[3];
+    const uint32_t val[16] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w, c.x, c.y, c.z, c.w, d.x, d.y, d.z, d.w};
+    uint32_t m = 0;
+#pragma unroll
+    for (uint32_t e = 0; e < 16; ++e)
+        if (first + e - l < r - l && val[e] <= t) m = max(m, val[e]);
     return m;
 }
 
@@ -90,9 +103,7 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     // second array borrows the upper half of the event area for a moment.
     uint32_t* kid_min = kid;
     uint32_t* kid_max = ev + cap;
-    const uint2* nodes = reinterpret_cast<const uint2*>(B.N);
     for (uint32_t v = tid; v < n; v += COOP_THREADS) {
-        parent[v] = (uint16_t)(nodes[v].y & 0xFFFFu);  // Node = {t0, t1 | fail, maxlen}
         kid_min[v] = 0xFFFFFFFFu;
         kid_max[v] = 0u;
     }
@@ -100,13 +111,27 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     for (uint32_t w = tid; w < wps; w += COOP_THREADS) vbits[w] = vw[w];
     if (tid == 0) round_rank[0] = 0;   // doubles as the splitter counter of the list ranking
     __syncthreads();
-    ULLIS_COOP_MARK(0);
-    for (uint32_t v = 1 + tid; v < n; v += COOP_THREADS) {
-        const uint32_t p = parent[v];
-        atomicMin(&kid_min[p], v);
-        atomicMax(&kid_max[p], v);
+    // global loads go out eight at a time, so that their latencies overlap
+    const uint32_t* link_words = reinterpret_cast<const uint32_t*>(B.N) + 1;   // Node = {t0, t1 | fail, maxlen}
+    for (uint32_t v0 = tid; v0 < n; v0 += COOP_THREADS * 8) {
+        uint32_t p[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t v = v0 + COOP_THREADS * u;
+            p[u] = v < n ? link_words[2 * v] & 0xFFFFu : NIL;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t v = v0 + COOP_THREADS * u;
+            if (v < n) parent[v] = (uint16_t)p[u];
+            if (v < n && v != 0) {
+                atomicMin(&kid_min[p[u]], v);
+                atomicMax(&kid_max[p[u]], v);
+            }
+        }
     }
     __syncthreads();
+    ULLIS_COOP_MARK(0);
     for (uint32_t v = tid; v < n; v += COOP_THREADS) {
         const uint32_t a = kid_min[v], b = kid_max[v];
         kid[v] = a == 0xFFFFFFFFu ? 0xFFFFFFFFu : (a | ((a == b ? NIL : b) << 16));
@@ -128,6 +153,23 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     }
     __syncthreads();
     ULLIS_COOP_MARK(2);
+    // the suffix links are dead: their space takes the query states and the new states of every step
+    uint16_t* vq_s = parent;
+    uint16_t* jid_s = parent + T;
+    for (uint32_t i0 = tid; i0 < T; i0 += COOP_THREADS * 8) {
+        uint16_t a[8], b[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t i = i0 + COOP_THREADS * u;
+            a[u] = i < T ? B.vq[i] : (uint16_t)0;
+            b[u] = i < T ? B.jid[i] : (uint16_t)0;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t i = i0 + COOP_THREADS * u;
+            if (i < T) { vq_s[i] = a[u]; jid_s[i] = b[u]; }
+        }
+    }
     // List ranking in two levels.  About one event in eight is a splitter
     // (chosen by a hash of the event index, so that no shape of the tree lines
     // up with it; event 0, the head of the list, always is).  Level 1: the
@@ -143,26 +185,41 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
         if (is_splitter(e)) splitters[atomicAdd(n_splitters, 1u)] = (uint16_t)e;
     __syncthreads();
     {
-        // one hop per thread and iteration; a thread that reaches the end of a
+        // One hop per chain and iteration, two independent chains per thread (their
+        // shared-memory latencies overlap).  A chain that reaches the end of a
         // sublist takes its next splitter in the same iteration, so the lanes of
-        // a warp stay busy however the sublist lengths fall
+        // a warp stay busy however the sublist lengths fall.
         const uint32_t count = *n_splitters;
-        uint32_t k = tid, head = 0, cur = 0, before = 0;
-        bool busy = k < count;
-        if (busy) head = cur = splitters[k];
-        for (uint32_t hops = 0; busy && hops < 2 * n; ++hops) {   // all sublists together are no longer than the list
-            const uint32_t w = ev[cur];
-            const uint32_t nxt = w & 0xFFFFu;
-            if (cur != head) ev[cur] = (before << 16) | head;
-            before += w >> 16;
-            if (nxt == END || is_splitter(nxt)) {
-                ev[head] = (before << 16) | nxt;
-                k += COOP_THREADS;
-                busy = k < count;
-                if (busy) head = cur = splitters[k];
-                before = 0;
-            } else {
-                cur = nxt;
+        struct Chain {
+            uint32_t k, head, cur, before;
+            bool busy;
+        } c[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            c[u].k = tid + COOP_THREADS * u;
+            c[u].busy = c[u].k < count;
+            c[u].head = c[u].cur = c[u].busy ? splitters[c[u].k] : 0u;
+            c[u].before = 0;
+        }
+        for (uint32_t hops = 0; (c[0].busy || c[1].busy) && hops < 2 * n; ++hops) {   // no sublist is longer than the list
+            uint32_t w[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) w[u] = c[u].busy ? ev[c[u].cur] : 0u;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (!c[u].busy) continue;
+                const uint32_t nxt = w[u] & 0xFFFFu;
+                if (c[u].cur != c[u].head) ev[c[u].cur] = (c[u].before << 16) | c[u].head;
+                c[u].before += w[u] >> 16;
+                if (nxt == END || is_splitter(nxt)) {
+                    ev[c[u].head] = (c[u].before << 16) | nxt;
+                    c[u].k += COOP_THREADS * 2;
+                    c[u].busy = c[u].k < count;
+                    if (c[u].busy) c[u].head = c[u].cur = splitters[c[u].k];
+                    c[u].before = 0;
+                } else {
+                    c[u].cur = nxt;
+                }
             }
         }
     }
@@ -173,13 +230,24 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     while ((1u << rounds) < ns) ++rounds;
     for (uint32_t it = 0; it <= rounds; ++it) {
         int any = 0;
-        for (uint32_t k = tid; k < ns; k += COOP_THREADS) {
-            const uint32_t sp = splitters[k];
-            const uint32_t w = ev[sp];
-            if ((w & 0xFFFFu) != END) {
-                const uint32_t w2 = ev[w & 0xFFFFu];
-                ev[sp] = (w2 & 0xFFFFu) | ((w & 0xFFFF0000u) + (w2 & 0xFFFF0000u));
-                any = 1;
+        // eight independent splitters per thread and step: their dependent loads overlap
+        for (uint32_t k0 = tid; k0 < ns; k0 += COOP_THREADS * 8) {
+            uint32_t sp[8], w[8], w2[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t k = k0 + COOP_THREADS * u;
+                sp[u] = k < ns ? splitters[k] : 0xFFFFFFFFu;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) w[u] = sp[u] != 0xFFFFFFFFu ? ev[sp[u]] : END;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) w2[u] = (w[u] & 0xFFFFu) != END ? ev[w[u] & 0xFFFFu] : 0u;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if ((w[u] & 0xFFFFu) != END) {
+                    ev[sp[u]] = (w2[u] & 0xFFFFu) | ((w[u] & 0xFFFF0000u) + (w2[u] & 0xFFFF0000u));
+                    any = 1;
+                }
             }
         }
         if (!__syncthreads_or(any)) break;
@@ -199,76 +267,100 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     }
     __syncthreads();
 
-    // ---- pass 2: 16-ary max tree (level 0 = ranks, level k+1 = maxima of groups of 16)
+    // ---- pass 2.  Every stamped state is stamped exactly once, by the step that
+    // creates it, so level 0 of the max tree is a fixed array: stamp[rank of j_i]
+    // = i + 1.  The answer of step t is the largest stamp <= t with a rank in
+    // [lo, hi) of v_t.
+    //   narrow ranges (at most NARROW ranks; almost all of them on typical
+    //     streams) are scanned directly in that array, all steps in parallel;
+    //   wide ranges go through the upper tree levels (maxima of groups of 16),
+    //     which do depend on time: they are replayed in rounds of COOP_THREADS
+    //     steps, and only if the stream has a wide range at all.
+    constexpr uint32_t NARROW = 16;
     uint32_t* tree = ev;  // events are dead
+    uint32_t* wide = reinterpret_cast<uint32_t*>(smem + L.wide);   // bit t: step t has a wide range
     const uint32_t entries = tree_entries(T);
-    for (uint32_t k = tid; k < entries; k += COOP_THREADS) tree[k] = 0;
-    __syncthreads();
-    ULLIS_COOP_MARK(5);
-    // One round = COOP_THREADS consecutive steps, one per thread.  A step may be
-    // answered by a stamp of an earlier step of the same round; those are not in
-    // the tree yet, so the ranks of the round are published in shared memory
-    // (`round_rank`) and searched newest first: the
-    // own warp's earlier lanes by shuffles, the earlier warps' by broadcast loads.
     const uint32_t size0 = (T + 15u) & ~15u;
     const int warp = tid >> 5;
-    uint32_t v_next = (uint32_t)tid < T ? B.vq[tid] : NIL, j_next = (uint32_t)tid < T ? B.jid[tid] : 0u;
+    for (uint32_t k = tid; k < entries; k += COOP_THREADS) tree[k] = 0;
+    __syncthreads();
+    for (uint32_t i = tid; i < T; i += COOP_THREADS) tree[lh[jid_s[i]] & 0xFFFFu] = i + 1u;
+    __syncthreads();
+    ULLIS_COOP_MARK(5);
+    int any_wide = 0;
+    for (uint32_t t0 = 0; t0 < T; t0 += COOP_THREADS) {
+        const uint32_t t = t0 + tid;
+        uint32_t m = 0;
+        bool is_wide = false;
+        if (t < T) {
+            const uint32_t v = vq_s[t];
+            if (v != NIL) {
+                const uint32_t r = lh[v];
+                const uint32_t lo = r & 0xFFFFu, hi = r >> 16;
+                if (hi - lo <= NARROW) {
+                    for (uint32_t k = lo; k < hi; ++k) {
+                        const uint32_t stamp = tree[k];
+                        if (stamp <= t) m = max(m, stamp);
+                    }
+                } else {
+                    is_wide = true;
+                }
+            }
+        }
+        const uint32_t bit = m ? (vbits[m >> 5] >> (m & 31)) & 1u : 0u;
+        const uint32_t word = __ballot_sync(0xffffffffu, bit != 0);
+        const uint32_t wide_word = __ballot_sync(0xffffffffu, is_wide);
+        if (lane == 0 && t0 + warp * 32 < T) {
+            out[(t0 >> 5) + warp] = word;
+            wide[(t0 >> 5) + warp] = wide_word;
+        }
+        any_wide |= wide_word != 0;
+    }
+    ULLIS_COOP_MARK(6);
+    if (!__syncthreads_or(any_wide)) return;
+
+    // Replay for the wide ranges.  Whole groups of a range are answered by the
+    // upper levels, which hold the stamps of earlier rounds; the partial groups
+    // at both ends by level 0 with the `<= t` filter; stamps of earlier steps of
+    // the same round by the round's published ranks, newest first.
     for (uint32_t t0 = 0; t0 < T; t0 += COOP_THREADS) {
         const uint32_t t = t0 + tid;
         const bool live = t < T;
-        const uint32_t v = v_next, j = j_next;
-        if (t + COOP_THREADS < T) { v_next = B.vq[t + COOP_THREADS]; j_next = B.jid[t + COOP_THREADS]; }
-        uint32_t lo = 0, hi = 0, my_rank = 0xFFFFFFFFu, m = 0;
-        if (live) {
-            my_rank = lh[j] & 0xFFFFu;
-            if (v != NIL) {
-                const uint32_t r = lh[v];
-                lo = r & 0xFFFFu;
-                hi = r >> 16;
-            }
-        }
+        const uint32_t my_rank = live ? lh[jid_s[t]] & 0xFFFFu : 0xFFFFFFFFu;
         round_rank[tid] = my_rank;
-        if (lo < hi) {
-            // whole 16-entry groups are loaded with 128-bit loads and masked in
-            // registers: no data-dependent trip counts, no dependent loads
-            uint32_t l = lo, rr = hi, base = 0, size = size0;
-            while (l < rr) {
-                const uint32_t lg = l >> 4, rg = (rr - 1u) >> 4;
-                m = max(m, group_max(tree + base + (lg << 4), lg << 4, l, rr));
-                if (rg != lg) m = max(m, group_max(tree + base + (rg << 4), rg << 4, l, rr));
-                if (rg <= lg + 1u) break;      // no whole group in between
-                l = lg + 1u; rr = rg;          // the groups in between, one level up
+        const bool is_wide = live && ((wide[t >> 5] >> (t & 31)) & 1u);
+        uint32_t lo = 0, hi = 0, m = 0;
+        if (is_wide) {
+            const uint32_t r = lh[vq_s[t]];
+            lo = r & 0xFFFFu;
+            hi = r >> 16;
+            const uint32_t lg = lo >> 4, rg = (hi - 1u) >> 4;    // hi - lo > 16: at least two groups
+            m = max(group_max_le(tree + (lg << 4), lg << 4, lo, hi, t), group_max_le(tree + (rg << 4), rg << 4, lo, hi, t));
+            uint32_t l = lg + 1u, rr = rg, base = size0, size = ((size0 >> 4) + 15u) & ~15u;
+            while (l < rr) {                                       // the whole groups in between, one level up
+                const uint32_t lg2 = l >> 4, rg2 = (rr - 1u) >> 4;
+                m = max(m, group_max(tree + base + (lg2 << 4), lg2 << 4, l, rr));
+                if (rg2 != lg2) m = max(m, group_max(tree + base + (rg2 << 4), rg2 << 4, l, rr));
+                if (rg2 <= lg2 + 1u) break;
+                l = lg2 + 1u; rr = rg2;
                 base += size;
                 size = ((size >> 4) + 15u) & ~15u;
             }
         }
         __syncthreads();   // ranks of the round published; every tree read of the round done
-        // earlier lanes of the own warp: the highest one whose rank is in range
-        uint32_t hits = 0;
-        const uint32_t width = hi - lo;
-#pragma unroll
-        for (int i = 0; i < 31; ++i) {
-            const uint32_t r_i = __shfl_sync(0xffffffffu, my_rank, i);
-            hits |= (r_i - lo < width ? 1u : 0u) << i;   // lanes past T carry rank 0xFFFFFFFF: never in range
-        }
-        hits &= (1u << lane) - 1u;
-        if (hits) {
-            m = t0 + warp * 32 + (31 - __clz(hits)) + 1;   // newer than anything in the tree
-        } else if (width != 0 && warp != 0) {
-            // earlier warps of the round, newest group of four first
-            for (int e = warp * 32 - 4; e >= 0; e -= 4) {
+        if (is_wide) {
+            const uint32_t width = hi - lo;
+            for (int e = (tid - 1) & ~3; e >= 0 && tid != 0; e -= 4) {
                 const uint4 r4 = *reinterpret_cast<const uint4*>(round_rank + e);
-                const uint32_t f = (r4.x - lo < width ? 1u : 0u) | (r4.y - lo < width ? 2u : 0u) |
-                                   (r4.z - lo < width ? 4u : 0u) | (r4.w - lo < width ? 8u : 0u);
-                if (f) { m = t0 + e + (31 - __clz(f)) + 1; break; }
+                uint32_t f = (r4.x - lo < width ? 1u : 0u) | (r4.y - lo < width ? 2u : 0u) |
+                             (r4.z - lo < width ? 4u : 0u) | (r4.w - lo < width ? 8u : 0u);
+                if (e + 4 > tid) f &= (1u << (tid - e)) - 1u;     // only steps before this one
+                if (f) { m = t0 + e + (31 - __clz(f)) + 1; break; }  // newer than anything in the tree
             }
+            if (m && ((vbits[m >> 5] >> (m & 31)) & 1u)) atomicOr(&out[t >> 5], 1u << (t & 31));
         }
-        uint32_t bit = 0;
-        if (live && v != NIL && m) bit = (vbits[m >> 5] >> (m & 31)) & 1u;
-        const uint32_t word = __ballot_sync(0xffffffffu, bit != 0);
-        if (lane == 0 && t0 + warp * 32 < T) out[(t0 >> 5) + warp] = word;
-        if (live) {
-            uint32_t pos = my_rank, base = 0, size = size0;
+        if (live && size0 > 16u) {
+            uint32_t pos = my_rank >> 4, base = size0, size = ((size0 >> 4) + 15u) & ~15u;
             for (;;) {
                 atomicMax(&tree[base + pos], t + 1);
                 if (size <= 16u) break;
@@ -277,9 +369,9 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
                 pos >>= 4;
             }
         }
-        __syncthreads();   // the round's stamps are in the tree; round_rank may be overwritten
+        __syncthreads();   // the round's stamps are in the upper levels; round_rank may be overwritten
     }
-    ULLIS_COOP_MARK(6);
+    ULLIS_COOP_MARK(7);
 }
 #endif
 
