@@ -127,15 +127,20 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     const bool narrow = sam::node_capacity((uint32_t)time) <= 0xFFFFu;
     const size_t stride = rosa_sam_scratch_bytes_per_stream(algo, time);
     const size_t wps = (time + 31) / 32;
-    // wave size: bounded scratch (default 12 GiB, or what fits in free memory)
-    size_t free_b = 0, total_b = 0;
-    ULLIS_CUDA_CHECK(cudaMemGetInfo(&free_b, &total_b));
-    size_t budget = (size_t)12 << 30;
-    const size_t avail = free_b + rt->sam_scratch.bytes();  // what the scratch buffer could grow to
-    if (avail < budget + ((size_t)2 << 30)) budget = avail > ((size_t)4 << 30) ? avail - ((size_t)2 << 30) : avail / 2;
-    size_t wave = budget / stride;
-    if (wave == 0) fail(ULLIS_CUDA_ERR_NOMEM, "not enough device memory for one suffix-automaton state block");
-    if (wave > streams) wave = streams;
+    // wave size: all streams at once when the scratch buffer already holds them;
+    // otherwise bounded scratch (default 12 GiB, or what fits in free memory).
+    // The memory query is a blocking driver call, so it is kept off the steady state.
+    size_t wave = streams;
+    if (rt->sam_scratch.bytes() < streams * stride) {
+        size_t free_b = 0, total_b = 0;
+        ULLIS_CUDA_CHECK(cudaMemGetInfo(&free_b, &total_b));
+        size_t budget = (size_t)12 << 30;
+        const size_t avail = free_b + rt->sam_scratch.bytes();  // what the scratch buffer could grow to
+        if (avail < budget + ((size_t)2 << 30)) budget = avail > ((size_t)4 << 30) ? avail - ((size_t)2 << 30) : avail / 2;
+        wave = budget / stride;
+        if (wave == 0) fail(ULLIS_CUDA_ERR_NOMEM, "not enough device memory for one suffix-automaton state block");
+        if (wave > streams) wave = streams;
+    }
     uint8_t* scratch = static_cast<uint8_t*>(rt->sam_scratch.ensure(wave * stride));
     if (streams > 0xFFFFFFFFull) fail(ULLIS_CUDA_ERR_SHAPE, "too many ROSA streams");
     uint32_t* list = rt->sam_list.as<uint32_t>(streams + 1);

@@ -36,7 +36,7 @@ constexpr int COOP_THREADS = 128;
 #endif
 
 struct CoopLayout {
-    uint32_t ev, kid, parent, clone_bits, vbits, round_rank, wide, total;
+    uint32_t ev, kid, parent, clone_bits, vbits, round_rank, wide, ctrl, total;
     __host__ __device__ explicit CoopLayout(uint32_t T) {
         const uint32_t cap = node_capacity(T), wps = (T + 31) / 32;
         uint32_t off = 0;
@@ -48,6 +48,7 @@ struct CoopLayout {
         vbits = off;      off += (wps * 4 + 15) & ~15u;
         round_rank = off; off += COOP_THREADS * 4;                                // ranks of the steps of one pass-2 round
         wide = off;       off += (wps * 4 + 15) & ~15u;                           // steps whose rank range is wide
+        ctrl = off;       off += 16;                                              // [0] = end of the last round with a wide range
         total = off;
     }
 };
@@ -77,8 +78,17 @@ __device__ __forceinline__ uint32_t group_max_le(const uint32_t* g, uint32_t fir
     return m;
 }
 
-// about one event index in eight, spread by a multiplicative hash; event 0 always
-__device__ __forceinline__ bool is_splitter(uint32_t e) { return e == 0u || ((e * 0x9E3779B1u) >> 29) == 0u; }
+// List-ranking splitters: exactly one event index in every block of eight, at
+// a hashed position inside the block so that no shape of the tree lines up with
+// them; event 0 (the head of the list) always is one.
+__device__ __forceinline__ uint32_t splitter_of_block(uint32_t k) {
+    return k == 0u ? 0u : (k << 3) + ((k * 0x9E3779B1u) >> 29);
+}
+// `blocks` = number of whole blocks of the list; a trailing partial block has no splitter
+__device__ __forceinline__ bool is_splitter(uint32_t e, uint32_t blocks) {
+    return e == 0u || ((e >> 3) < blocks && splitter_of_block(e >> 3) == e);
+}
+constexpr uint32_t LAST_OF_SUBLIST = 0x80000000u;   // flag in an event word: the successor is a splitter or the end
 
 // One CTA of COOP_THREADS threads; `B` is the stream's global scratch block
 // after euler_pass1.  Every thread of the CTA must call this.
@@ -95,6 +105,8 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     uint32_t* round_rank = reinterpret_cast<uint32_t*>(smem + L.round_rank);
     const uint32_t n = B.meta[0], wps = (T + 31) / 32;
     const uint32_t cap = node_capacity(T);
+    const uint32_t blocks = (2 * n) >> 3;       // whole blocks of eight events: one list-ranking splitter each
+    const uint32_t ns = blocks ? blocks : 1u;   // event 0 is a splitter in any case
     ULLIS_COOP_MARK_BEGIN();
 
     // ---- stage: suffix links, clone bitmap, v bits.  The smallest / largest
@@ -109,7 +121,8 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     }
     for (uint32_t w = tid; w < (n + 31) / 32; w += COOP_THREADS) cbits[w] = B.clone_bits[w];
     for (uint32_t w = tid; w < wps; w += COOP_THREADS) vbits[w] = vw[w];
-    if (tid == 0) round_rank[0] = 0;   // doubles as the splitter counter of the list ranking
+    uint32_t* replay_end = reinterpret_cast<uint32_t*>(smem + L.ctrl);
+    if (tid == 0) *replay_end = 0;
     __syncthreads();
     // global loads go out eight at a time, so that their latencies overlap
     const uint32_t* link_words = reinterpret_cast<const uint32_t*>(B.N) + 1;   // Node = {t0, t1 | fail, maxlen}
@@ -143,13 +156,14 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     for (uint32_t v = tid; v < n; v += COOP_THREADS) {
         const uint32_t k = kid[v], a = k & 0xFFFFu;
         const uint32_t stamped = (v != 0 && !((cbits[v >> 5] >> (v & 31)) & 1u)) ? 1u : 0u;
-        ev[2 * v] = (a != NIL ? 2 * a : 2 * v + 1) | (stamped << 16);
+        const uint32_t first = a != NIL ? 2 * a : 2 * v + 1;
+        ev[2 * v] = first | (stamped << 16) | (is_splitter(first, blocks) ? LAST_OF_SUBLIST : 0u);
         uint32_t succ = END;
         if (v != 0) {
             const uint32_t p = parent[v], kp = kid[p];
             succ = ((kp & 0xFFFFu) == v && (kp >> 16) != NIL) ? 2 * (kp >> 16) : 2 * p + 1;
         }
-        ev[2 * v + 1] = succ;
+        ev[2 * v + 1] = succ | (succ == END || is_splitter(succ, blocks) ? LAST_OF_SUBLIST : 0u);
     }
     __syncthreads();
     ULLIS_COOP_MARK(2);
@@ -170,36 +184,33 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
             if (i < T) { vq_s[i] = a[u]; jid_s[i] = b[u]; }
         }
     }
-    // List ranking in two levels.  About one event in eight is a splitter
-    // (chosen by a hash of the event index, so that no shape of the tree lines
-    // up with it; event 0, the head of the list, always is).  Level 1: the
+    // List ranking in two levels.  One event in eight is a splitter.  Level 1: the
     // thread that owns a splitter walks its sublist up to the next splitter and
     // leaves in every element (weight of the sublist before it, its splitter);
     // the splitter gets (weight of the whole sublist, next splitter).  Level 2:
     // pointer jumping over the splitters only, in place - a word is read and
     // written as a whole, so a reader always sees a consistent (successor, sum
     // over [s, successor)) pair.  O(events) work instead of O(events log events).
-    uint16_t* splitters = reinterpret_cast<uint16_t*>(kid);   // child pairs are dead
-    uint32_t* n_splitters = round_rank;                          // free until pass 2
-    for (uint32_t e = tid; e < 2 * n; e += COOP_THREADS)
-        if (is_splitter(e)) splitters[atomicAdd(n_splitters, 1u)] = (uint16_t)e;
-    __syncthreads();
+    ULLIS_COOP_MARK(8);
     {
         // One hop per chain and iteration, two independent chains per thread (their
         // shared-memory latencies overlap).  A chain that reaches the end of a
-        // sublist takes its next splitter in the same iteration, so the lanes of
-        // a warp stay busy however the sublist lengths fall.
-        const uint32_t count = *n_splitters;
+        // sublist takes the splitter of its next block in the same iteration, so
+        // the lanes of a warp stay busy however the sublist lengths fall.
         struct Chain {
             uint32_t k, head, cur, before;
             bool busy;
         } c[2];
+        auto next_block = [&](Chain& ch) {
+            ch.busy = ch.k < ns;
+            ch.head = ch.cur = splitter_of_block(ch.k);
+            ch.before = 0;
+        };
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             c[u].k = tid + COOP_THREADS * u;
-            c[u].busy = c[u].k < count;
-            c[u].head = c[u].cur = c[u].busy ? splitters[c[u].k] : 0u;
-            c[u].before = 0;
+            c[u].head = c[u].cur = c[u].before = 0;
+            next_block(c[u]);
         }
         for (uint32_t hops = 0; (c[0].busy || c[1].busy) && hops < 2 * n; ++hops) {   // no sublist is longer than the list
             uint32_t w[2];
@@ -208,24 +219,20 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 if (!c[u].busy) continue;
-                const uint32_t nxt = w[u] & 0xFFFFu;
                 if (c[u].cur != c[u].head) ev[c[u].cur] = (c[u].before << 16) | c[u].head;
-                c[u].before += w[u] >> 16;
-                if (nxt == END || is_splitter(nxt)) {
-                    ev[c[u].head] = (c[u].before << 16) | nxt;
+                c[u].before += (w[u] >> 16) & 1u;
+                if (w[u] & LAST_OF_SUBLIST) {
+                    ev[c[u].head] = (c[u].before << 16) | (w[u] & 0xFFFFu);
                     c[u].k += COOP_THREADS * 2;
-                    c[u].busy = c[u].k < count;
-                    if (c[u].busy) c[u].head = c[u].cur = splitters[c[u].k];
-                    c[u].before = 0;
+                    next_block(c[u]);
                 } else {
-                    c[u].cur = nxt;
+                    c[u].cur = w[u] & 0xFFFFu;
                 }
             }
         }
     }
     __syncthreads();
     ULLIS_COOP_MARK(3);
-    const uint32_t ns = *n_splitters;
     uint32_t rounds = 1;
     while ((1u << rounds) < ns) ++rounds;
     for (uint32_t it = 0; it <= rounds; ++it) {
@@ -236,7 +243,7 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const uint32_t k = k0 + COOP_THREADS * u;
-                sp[u] = k < ns ? splitters[k] : 0xFFFFFFFFu;
+                sp[u] = k < ns ? splitter_of_block(k) : 0xFFFFFFFFu;
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) w[u] = sp[u] != 0xFFFFFFFFu ? ev[sp[u]] : END;
@@ -256,7 +263,7 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     // weight of [e, end of list): the splitter's, less what lies before e in its sublist
     auto weight_from = [&](uint32_t e) {
         const uint32_t w = ev[e];
-        return is_splitter(e) ? (w >> 16) : (ev[w & 0xFFFFu] >> 16) - (w >> 16);
+        return is_splitter(e, blocks) ? (w >> 16) : (ev[w & 0xFFFFu] >> 16) - (w >> 16);
     };
     // rank range of state v: stamped states entered before enter(v) / before leave(v)
     const uint32_t total = ev[0] >> 16;
@@ -287,7 +294,6 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     for (uint32_t i = tid; i < T; i += COOP_THREADS) tree[lh[jid_s[i]] & 0xFFFFu] = i + 1u;
     __syncthreads();
     ULLIS_COOP_MARK(5);
-    int any_wide = 0;
     for (uint32_t t0 = 0; t0 < T; t0 += COOP_THREADS) {
         const uint32_t t = t0 + tid;
         uint32_t m = 0;
@@ -313,17 +319,19 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
         if (lane == 0 && t0 + warp * 32 < T) {
             out[(t0 >> 5) + warp] = word;
             wide[(t0 >> 5) + warp] = wide_word;
+            if (wide_word) atomicMax(replay_end, t0 + COOP_THREADS);
         }
-        any_wide |= wide_word != 0;
     }
+    __syncthreads();
     ULLIS_COOP_MARK(6);
-    if (!__syncthreads_or(any_wide)) return;
+    const uint32_t t_end = min(T, *replay_end);   // nothing after the last wide range needs the upper levels
+    if (t_end == 0) return;
 
     // Replay for the wide ranges.  Whole groups of a range are answered by the
     // upper levels, which hold the stamps of earlier rounds; the partial groups
     // at both ends by level 0 with the `<= t` filter; stamps of earlier steps of
     // the same round by the round's published ranks, newest first.
-    for (uint32_t t0 = 0; t0 < T; t0 += COOP_THREADS) {
+    for (uint32_t t0 = 0; t0 < t_end; t0 += COOP_THREADS) {
         const uint32_t t = t0 + tid;
         const bool live = t < T;
         const uint32_t my_rank = live ? lh[jid_s[t]] & 0xFFFFu : 0xFFFFFFFFu;
