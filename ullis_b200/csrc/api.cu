@@ -88,16 +88,18 @@ void ullis_cuda_runtime::launched(const char* what) {
     ++launches;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) fail(ULLIS_CUDA_ERR_CUDA, std::string("launch of ") + what + ": " + cudaGetErrorString(e));
-    if (kernel_timing) {
-        if (marks_used == marks.size()) {
-            LaunchMark m{what, nullptr};
-            ULLIS_CUDA_CHECK(cudaEventCreate(&m.done));
-            marks.push_back(m);
-        }
-        marks[marks_used].name = what;
-        ULLIS_CUDA_CHECK(cudaEventRecord(marks[marks_used].done, stream));
-        ++marks_used;
+    if (kernel_timing) mark(what);
+}
+
+void ullis_cuda_runtime::mark(const char* what) {
+    if (marks_used == marks.size()) {
+        LaunchMark m{what, nullptr};
+        ULLIS_CUDA_CHECK(cudaEventCreate(&m.done));
+        marks.push_back(m);
     }
+    marks[marks_used].name = what;
+    ULLIS_CUDA_CHECK(cudaEventRecord(marks[marks_used].done, stream));
+    ++marks_used;
 }
 
 void ullis_cuda_runtime::kernel_timing_begin() {

@@ -108,6 +108,7 @@ struct ullis_cuda_runtime {
     size_t marks_used = 0;
     cudaEvent_t marks_start = nullptr;
     void kernel_timing_begin();
+    void mark(const char* what);   // closes the current bracket under the name `what`
     // total milliseconds and launches of the kernels recorded under `name` (all kernels when name is empty)
     void kernel_time(const char* name, float* total_ms, uint32_t* n_launches);
     size_t kernel_names(char* buf, size_t len);  // newline-separated distinct names; returns bytes needed

@@ -253,6 +253,7 @@ void ullis_cuda_model::enqueue_hidden(size_t batch, size_t time) {
     check_shape(batch, time);
     if (batch != cur_batch || time != cur_time) fail(ULLIS_CUDA_ERR_SHAPE, "upload_tokens was not called for this shape");
     rt->bind();
+    if (rt->kernel_timing) rt->mark("(between steps)");   // idle time and copies since the last kernel are not the embed kernel's
     const size_t rows = batch * time, n = rows * d;
     const bool exact = rt->mode == ULLIS_CUDA_MODE_EXACT;
     const size_t wps = (time + 31) / 32, sw_words = batch * d * wps;
