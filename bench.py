@@ -368,33 +368,58 @@ def run_cuda(args):
 
 
 def run_op_loop(args, rt, stream, torch):
-    """Single-op loops (device time via the op-level ABI is dominated by host
-    copies, so these drive the model-free device entry points through small
-    synthetic models instead): used for kernel profiling, not for the headline."""
-    from ullis_b200 import cuda, synth
+    """Single-op loops through the op-level ABI (host buffers in and out).  The
+    host-timed figure is dominated by the copies, so the line also carries the
+    device time of every kernel of the op (events behind each launch): these are
+    the per-shape microbenchmarks, not the headline."""
+    from ullis_b200 import synth
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except Exception:  # noqa: BLE001
+        pass
+
+    def timed(call):
+        for _ in range(max(args.warmup, 1)):
+            call()
+        rt.kernel_timing(True)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            call()
+        dt = (time.perf_counter() - t0) / args.steps
+        per_kernel = {k: t / args.steps for k, (t, _) in rt.kernel_times().items() if not k.startswith("(")}
+        rt.kernel_timing(False)
+        return dt, per_kernel
+
     if args.workload == "rosa":
         B, T, C = args.batch, args.time or 8192, args.channels
         gen = synth.rosa_bits_iid if args.rosa_variant == "iid" else synth.rosa_bits_periodic
         q, k, v = gen(21, B, T, C)
         e = synth.f16_bits(0.02 * synth.normal(5, C))
-        for _ in range(max(args.warmup, 1)):
-            rt.rosa_qkv_1bit_fwd(q, k, v, e, B, T, C)
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            rt.rosa_qkv_1bit_fwd(q, k, v, e, B, T, C)
-        dt = (time.perf_counter() - t0) / args.steps
+        dt, per_kernel = timed(lambda: rt.rosa_qkv_1bit_fwd(q, k, v, e, B, T, C))
+        sam_ms = sum(t for name, t in per_kernel.items() if name.startswith("rosa_") and name != "rosa_emit")
+        units = B * T * C
+        hbm = float(peaks.get("hbm_gbs", 6650.0))
         print(json.dumps({"workload": "rosa", "variant": args.rosa_variant, "B": B, "T": T, "C": C,
-                          "ms_per_call_host_timed": dt * 1e3, "stream_steps_per_s": B * T * C / dt}))
+                          "ms_per_call_host_timed": dt * 1e3, "kernels_ms": per_kernel,
+                          "automaton_ms": sam_ms, "stream_steps_per_s": units / (sam_ms * 1e-3),
+                          "ns_per_stream_step": sam_ms * 1e6 / units,
+                          "algorithmic_GBps": ROSA_BYTES_PER_UNIT * units / (sam_ms * 1e-3) / 1e9,
+                          "frac_of_hbm_peak": ROSA_BYTES_PER_UNIT * units / (sam_ms * 1e-3) / 1e9 / hbm}))
     else:
         M, K, N = (int(x) for x in args.linear_shape.lower().split("x"))
         x, bits, scale, bias = synth.packed_linear_case(3, M, K, N)
-        for _ in range(max(args.warmup, 1)):
-            rt.binary_linear(x, bits, scale, bias, M, K, N)
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            rt.binary_linear(x, bits, scale, bias, M, K, N)
-        dt = (time.perf_counter() - t0) / args.steps
-        print(json.dumps({"workload": "linear", "M": M, "K": K, "N": N, "ms_per_call_host_timed": dt * 1e3}))
+        dt, per_kernel = timed(lambda: rt.binary_linear(x, bits, scale, bias, M, K, N))
+        gemm_ms = sum(t for name, t in per_kernel.items() if name.startswith("gemm_") or name == "binary_linear_exact")
+        flops = 2.0 * M * K * N
+        peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        print(json.dumps({"workload": "linear", "M": M, "K": K, "N": N, "ms_per_call_host_timed": dt * 1e3,
+                          "kernels_ms": per_kernel, "gemm_ms": gemm_ms,
+                          "tflops": flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None,
+                          "frac_of_sustained_peak": flops / (gemm_ms * 1e-3) / 1e12 / peak if gemm_ms else None,
+                          "frac_of_burst_peak": flops / (gemm_ms * 1e-3) / 1e12 / float(peaks.get("bf16_tflops", 1590.0))
+                          if gemm_ms else None}))
     rt.close()
 
 

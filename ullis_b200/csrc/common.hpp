@@ -96,6 +96,7 @@ struct ullis_cuda_runtime {
     ullis::DeviceBuffer sam_list;       // ids of the streams that need the automaton + their count
     ullis::DeviceBuffer tc_ws[16];      // 16-bit operands / partials of the tensor-core stages
     int tc_stages = 2, tc_stages2 = 2;  // GEMM pipeline depth with one / two activation operands
+    bool tc_ws_kernel = true;           // weight-stationary persistent kernel for packed weights with K <= 512
     int tc_ready = 0;                   // 0 = not probed, 1 = usable, -1 = unusable on this device
     ullis::NcclState* nccl = nullptr;
 

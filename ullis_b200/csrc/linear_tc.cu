@@ -12,6 +12,7 @@
 
 #include "kernels.hpp"
 #include "tc_gemm.cuh"
+#include "tc_gemm_ws.cuh"
 
 namespace ullis {
 namespace tc {
@@ -242,6 +243,15 @@ bool usable(ullis_cuda_runtime* rt) {
             ULLIS_SET_SMEM(EPI_SIGNBITS, true);
             ULLIS_SET_SMEM(EPI_CE, true);
 #undef ULLIS_SET_SMEM
+#define ULLIS_SET_SMEM_WS(EPI) \
+    ULLIS_CUDA_CHECK(cudaFuncSetAttribute(gemm_ws_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM_LIMIT))
+            ULLIS_SET_SMEM_WS(EPI_STORE);
+            ULLIS_SET_SMEM_WS(EPI_RESIDUAL);
+            ULLIS_SET_SMEM_WS(EPI_RELU2);
+            ULLIS_SET_SMEM_WS(EPI_SIGNBITS);
+            ULLIS_SET_SMEM_WS(EPI_CE);
+#undef ULLIS_SET_SMEM_WS
+            rt->tc_ws_kernel = !getenv("ULLIS_CUDA_NO_WS");
             ULLIS_CUDA_CHECK(cudaFuncSetAttribute(sign_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   FIX_QUEUE * 4));
             rt->tc_ready = 1;
@@ -257,6 +267,21 @@ bool shape_ok(size_t M, size_t K, size_t N) {
 
 template <int EPI, bool PACKED>
 void launch(ullis_cuda_runtime* rt, const GemmMaps& maps, const GemmParams& p, unsigned n_prob, const char* what) {
+    if (PACKED && rt->tc_ws_kernel && p.K / BK <= WS_MAX_KB) {
+        // weight-stationary kernel: one (problem, column tile) pair per CTA, the CTAs of a pair share the row tiles
+        const WsShape shape = ws_shape(p.K, p.n_a);
+        if (shape.stages >= 2) {
+            GemmParams q = p;
+            q.stages = shape.stages;
+            const uint32_t pairs = n_prob * ((p.N + BN - 1) / BN), m_tiles = (p.M + BM - 1) / BM;
+            uint32_t members = (uint32_t)rt->sm_count / pairs;
+            if (members < 1) members = 1;
+            if (members > m_tiles) members = m_tiles;
+            gemm_ws_kernel<EPI><<<pairs * members, GEMM_THREADS, shape.smem, rt->stream>>>(maps, q, pairs);
+            rt->launched(what);
+            return;
+        }
+    }
     dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, n_prob);
     gemm_kernel<EPI, PACKED><<<grid, GEMM_THREADS, gemm_smem_bytes(p.n_a, p.stages), rt->stream>>>(maps, p);
     rt->launched(what);

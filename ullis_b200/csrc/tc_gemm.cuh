@@ -77,7 +77,7 @@ __device__ __forceinline__ float h2f_bits(uint16_t b) { return __half2float(__us
 // The TMEM loads are warp-collective, so row / column guards only wrap stores.
 template <int EPI>
 __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem& pr, uint32_t taddr, uint32_t m,
-                                         uint32_t n0, const float* s_scale, const float* s_bias, int lane) {
+                                         uint32_t n0, const float* s_scale, const float* s_bias, int lane, uint32_t n_tile) {
     const bool row_ok = m < p.M;
     // EPI_SIGNBITS: the 32 rows of this warp are 32 consecutive steps of one sequence (M, time % 32 == 0)
     const uint32_t m_warp = m - lane;
@@ -174,7 +174,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
         }
     }
     if (EPI == EPI_CE && row_ok)
-        static_cast<float2*>(pr.out)[(size_t)m * p.n_tiles + blockIdx.x] = make_float2(run_max, run_sum);
+        static_cast<float2*>(pr.out)[(size_t)m * p.n_tiles + n_tile] = make_float2(run_max, run_sum);
 }
 
 template <int EPI, bool PACKED>
@@ -316,7 +316,7 @@ gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         ptx::tc_fence_after_sync();
         if (waited && *s_error == 0) {
             const uint32_t taddr = tmem_base + ((quarter * 32) << 16);
-            epilogue<EPI>(p, pr, taddr, m, n0, s_scale, s_bias, lane);
+            epilogue<EPI>(p, pr, taddr, m, n0, s_scale, s_bias, lane, blockIdx.x);
         }
     }
     ptx::tc_fence_before_sync();
