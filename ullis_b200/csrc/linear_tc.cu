@@ -265,19 +265,24 @@ bool shape_ok(size_t M, size_t K, size_t N) {
            (M + BM - 1) / BM <= 65535;
 }
 
+// packed weights with a short K go to the weight-stationary kernel
+bool takes_ws(const ullis_cuda_runtime* rt, size_t K, uint32_t n_a) {
+    return rt->tc_ws_kernel && K / BK <= WS_MAX_KB && ws_shape((uint32_t)K, n_a).stages >= 2;
+}
+
 template <int EPI, bool PACKED>
 void launch(ullis_cuda_runtime* rt, const GemmMaps& maps, const GemmParams& p, unsigned n_prob, const char* what) {
-    if (PACKED && rt->tc_ws_kernel && p.K / BK <= WS_MAX_KB) {
-        // weight-stationary kernel: one (problem, column tile) pair per CTA, the CTAs of a pair share the row tiles
+    if (PACKED && takes_ws(rt, p.K, p.n_a)) {
+        // one (problem, column tile) pair per CTA, the CTAs of a pair share the row tiles
         const WsShape shape = ws_shape(p.K, p.n_a);
-        if (shape.stages >= 2) {
+        {
             GemmParams q = p;
             q.stages = shape.stages;
             const uint32_t pairs = n_prob * ((p.N + BN - 1) / BN), m_tiles = (p.M + BM - 1) / BM;
             uint32_t members = (uint32_t)rt->sm_count / pairs;
             if (members < 1) members = 1;
             if (members > m_tiles) members = m_tiles;
-            gemm_ws_kernel<EPI><<<pairs * members, GEMM_THREADS, shape.smem, rt->stream>>>(maps, q, pairs);
+            gemm_ws_kernel<EPI><<<pairs * members, WS_THREADS, shape.smem, rt->stream>>>(maps, q, pairs);
             rt->launched(what);
             return;
         }
@@ -436,7 +441,8 @@ bool cmix_residual(ullis_cuda_runtime* rt, const LayerWeights& L, float* x, size
 bool head_ce(ullis_cuda_runtime* rt, const float* hidden, const PackedWeights& head, const uint32_t* labels,
              uint32_t ignore_id, size_t rows, size_t time, size_t d, size_t vocab, float* row_loss) {
     if (!usable(rt) || !shape_ok(rows, d, vocab)) return false;
-    const uint32_t n_tiles = (uint32_t)((vocab + BN - 1) / BN);
+    // partials per row: one per vocabulary tile and epilogue warp group of the kernel that will run
+    const uint32_t n_tiles = (uint32_t)((vocab + BN - 1) / BN) * (takes_ws(rt, d, 1) ? WS_EPI_GROUPS : 1u);
     uint16_t* a16 = rt->tc_ws[0].as<uint16_t>(rows * d);
     float2* part = rt->tc_ws[6].as<float2>(rows * n_tiles);
     float* tl = rt->tc_ws[7].as<float>(rows);

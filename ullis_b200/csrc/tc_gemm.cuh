@@ -63,7 +63,7 @@ struct GemmParams {
     uint32_t time, wps;      // EPI_SIGNBITS / EPI_CE: steps per sequence, words per stream
     const uint32_t* labels;  // EPI_CE
     uint32_t ignore_id;      // EPI_CE
-    uint32_t n_tiles;        // EPI_CE: number of vocabulary tiles (gridDim.x)
+    uint32_t n_tiles;        // EPI_CE: (max, sum exp) partials per row: one per vocabulary tile and epilogue warp group
     uint32_t* status;
 };
 
@@ -73,11 +73,13 @@ inline size_t gemm_smem_bytes(uint32_t n_a, uint32_t stages) {
 
 __device__ __forceinline__ float h2f_bits(uint16_t b) { return __half2float(__ushort_as_half(b)); }
 
-// One output row (TMEM lane) per thread, 128 columns in four 32-column loads.
+// One output row (TMEM lane) per thread, the 32-column chunks [c_begin, c_end) of the tile's 128 columns.
+// `part` = index of this call's partial among the row's p.n_tiles partials (EPI_CE).
 // The TMEM loads are warp-collective, so row / column guards only wrap stores.
 template <int EPI>
 __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem& pr, uint32_t taddr, uint32_t m,
-                                         uint32_t n0, const float* s_scale, const float* s_bias, int lane, uint32_t n_tile) {
+                                         uint32_t n0, const float* s_scale, const float* s_bias, int lane, uint32_t part,
+                                         uint32_t c_begin = 0, uint32_t c_end = BN / 32) {
     const bool row_ok = m < p.M;
     // EPI_SIGNBITS: the 32 rows of this warp are 32 consecutive steps of one sequence (M, time % 32 == 0)
     const uint32_t m_warp = m - lane;
@@ -87,7 +89,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
     uint32_t target = 0xFFFFFFFFu;
     if (EPI == EPI_CE && m + 1 < p.M) target = p.labels[m + 1];
 #pragma unroll 1
-    for (uint32_t c = 0; c < BN / 32; ++c) {
+    for (uint32_t c = c_begin; c < c_end; ++c) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(taddr + c * 32, r);
         ptx::tmem_ld_wait();
@@ -174,7 +176,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
         }
     }
     if (EPI == EPI_CE && row_ok)
-        static_cast<float2*>(pr.out)[(size_t)m * p.n_tiles + n_tile] = make_float2(run_max, run_sum);
+        static_cast<float2*>(pr.out)[(size_t)m * p.n_tiles + part] = make_float2(run_max, run_sum);
 }
 
 template <int EPI, bool PACKED>

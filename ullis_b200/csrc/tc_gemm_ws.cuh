@@ -12,8 +12,8 @@
 // for Q/K/V, nothing else) walk M in the same order, so the tile is read from
 // HBM once and from L2 afterwards.
 //
-// Warp roles as in gemm_kernel: warp 0 TMA producer, warp 1 TMEM owner + MMA
-// issuer, warps 2-5 epilogue.  Every wait is bounded and gives up early once
+// Warp roles: warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps 2-9
+// epilogue (two warps per TMEM lane quarter, half of the columns each).  Every wait is bounded and gives up early once
 // another role has recorded an error.
 #pragma once
 #include "tc_gemm.cuh"
@@ -24,6 +24,8 @@ namespace tc {
 constexpr uint32_t WS_MAX_KB = 8;          // K <= 512
 constexpr uint32_t WS_MAX_STAGES = 8;
 constexpr uint32_t WS_SMEM_LIMIT = 227 * 1024;
+constexpr int WS_THREADS = 320;            // TMA warp, MMA warp, eight epilogue warps (two per TMEM lane quarter)
+constexpr uint32_t WS_EPI_GROUPS = 2;      // epilogue warp groups, each takes half of the tile's columns
 
 struct WsShape {
     uint32_t stages;   // activation ring depth
@@ -52,7 +54,7 @@ __device__ __forceinline__ bool ws_wait(uint64_t* bar, uint32_t parity, volatile
 }
 
 template <int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(WS_THREADS, 1)
 gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const uint32_t pairs) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -90,7 +92,7 @@ gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const 
         }
         for (uint32_t b = 0; b < 2; ++b) {
             ptx::mbar_init(&tmem_full[b], 1);
-            ptx::mbar_init(&tmem_empty[b], 128);
+            ptx::mbar_init(&tmem_empty[b], 128 * WS_EPI_GROUPS);
         }
         *s_error = 0;
         ptx::fence_mbar_init();
@@ -98,7 +100,7 @@ gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const 
         if (p.n_a == 2) ptx::tma_prefetch_desc(&maps.a[z][1]);
     }
     // 8 weight bits -> 8 FP16 values (+1.0 = 0x3C00, -1.0 = 0xBC00), bit i -> element i
-    for (int b = threadIdx.x; b < 256; b += GEMM_THREADS) {
+    for (int b = threadIdx.x; b < 256; b += WS_THREADS) {
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -118,7 +120,7 @@ gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const 
     }
     __syncthreads();
     // expand this CTA's weight tile once: row r of k-block kb -> 128 bytes, 16-byte chunk j at j ^ (r % 8)
-    for (uint32_t item = threadIdx.x; item < KB * BN; item += GEMM_THREADS) {
+    for (uint32_t item = threadIdx.x; item < KB * BN; item += WS_THREADS) {
         const uint32_t r = item % BN, kb = item / BN;
         const uint32_t n = n0 + r;
         uint32_t w0 = 0, w1 = 0;
@@ -206,8 +208,11 @@ gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const 
         }
     } else {
         // ---------------------------------------------------------- epilogue
-        // this warp may only touch TMEM lanes 32*(warp%4) .. +31
+        // this warp may only touch TMEM lanes 32*(warp%4) .. +31; warps 2-5 take the
+        // left half of the tile's columns, warps 6-9 the right half
         const uint32_t quarter = warp & 3;
+        const uint32_t group = (uint32_t)(warp - 2) >> 2;
+        const uint32_t chunks = (BN / 32) / WS_EPI_GROUPS;
         const uint32_t row_in_tile = quarter * 32 + lane;
         for (uint32_t t = 0; t < my_tiles; ++t) {
             const uint32_t buf = t & 1u;
@@ -220,7 +225,8 @@ gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const 
             ptx::tc_fence_after_sync();
             if (__any_sync(0xffffffffu, *reinterpret_cast<volatile uint32_t*>(s_error) != 0u)) break;
             const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32) << 16);
-            epilogue<EPI>(p, pr, taddr, m, n0, s_scale, s_bias, lane, n_tile);
+            epilogue<EPI>(p, pr, taddr, m, n0, s_scale, s_bias, lane, n_tile * WS_EPI_GROUPS + group, group * chunks,
+                          (group + 1) * chunks);
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&tmem_empty[buf]);
         }
