@@ -267,14 +267,14 @@ bool shape_ok(size_t M, size_t K, size_t N) {
 
 // packed weights with a short K go to the weight-stationary kernel
 bool takes_ws(const ullis_cuda_runtime* rt, size_t K, uint32_t n_a) {
-    return rt->tc_ws_kernel && K / BK <= WS_MAX_KB && ws_shape((uint32_t)K, n_a).stages >= 2;
+    return rt->tc_ws_kernel && K / BK <= WS_MAX_KB && ws_shape((uint32_t)K, n_a, true).stages >= 2;
 }
 
 template <int EPI, bool PACKED>
 void launch(ullis_cuda_runtime* rt, const GemmMaps& maps, const GemmParams& p, unsigned n_prob, const char* what) {
     if (PACKED && takes_ws(rt, p.K, p.n_a)) {
         // one (problem, column tile) pair per CTA, the CTAs of a pair share the row tiles
-        const WsShape shape = ws_shape(p.K, p.n_a);
+        const WsShape shape = ws_shape(p.K, p.n_a, EPI == EPI_STORE || EPI == EPI_RESIDUAL);
         {
             GemmParams q = p;
             q.stages = shape.stages;

@@ -38,6 +38,8 @@ enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_RELU2 = 2, EPI_SIGNBITS = 3, EPI_CE 
 constexpr int BM = 128, BN = 128, BK = 64, MAX_STAGES = 4;
 constexpr int TILE_BYTES = BM * BK * 2;  // 16 KiB, also the B tile (BN == BM)
 constexpr int GEMM_THREADS = 192;
+constexpr int STAGE_STRIDE = 20;                         // floats per row of an epilogue warp's 32 x 16 transposition buffer
+constexpr int STAGE_BYTES = 32 * STAGE_STRIDE * 4;       // per epilogue warp
 
 struct GemmProblem {
     const uint32_t* bits;   // packed weights (PACKED kernels)
@@ -79,7 +81,7 @@ __device__ __forceinline__ float h2f_bits(uint16_t b) { return __half2float(__us
 template <int EPI>
 __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem& pr, uint32_t taddr, uint32_t m,
                                          uint32_t n0, const float* s_scale, const float* s_bias, int lane, uint32_t part,
-                                         uint32_t c_begin = 0, uint32_t c_end = BN / 32) {
+                                         uint32_t c_begin = 0, uint32_t c_end = BN / 32, float* stage = nullptr) {
     const bool row_ok = m < p.M;
     // EPI_SIGNBITS: the 32 rows of this warp are 32 consecutive steps of one sequence (M, time % 32 == 0)
     const uint32_t m_warp = m - lane;
@@ -95,25 +97,42 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
         ptx::tmem_ld_wait();
         const uint32_t nc = n0 + c * 32;
         if (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
-            float* out = static_cast<float*>(pr.out) + (size_t)m * p.N + nc;
+            // A thread holds one row of the accumulator, so a direct store touches 32
+            // different rows per instruction.  The chunk goes through a small
+            // shared-memory transposition instead (16 columns at a time): afterwards
+            // four lanes cover 64 contiguous bytes of one row and an instruction
+            // covers eight rows.
+            float* out = static_cast<float*>(pr.out);
+            const uint32_t m_first = m - lane;   // first row of this warp
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-                float y[4];
+            for (int h = 0; h < 2; ++h) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) y[e] = s_bias[c * 32 + j + e] + s_scale[c * 32 + j + e] * __uint_as_float(r[j + e]);
-                if (!row_ok) continue;
-                if (nc + j + 3 < p.N) {
-                    float4* dst = reinterpret_cast<float4*>(out + j);
-                    float4 v = make_float4(y[0], y[1], y[2], y[3]);
-                    if (EPI == EPI_RESIDUAL) {
-                        const float4 o = *dst;
-                        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                    }
-                    *dst = v;
-                } else {
-                    for (int e = 0; e < 4; ++e)
-                        if (nc + j + e < p.N) out[j + e] = (EPI == EPI_RESIDUAL ? out[j + e] : 0.0f) + y[e];
+                for (int q = 0; q < 4; ++q) {
+                    const int j = h * 16 + q * 4;
+                    float4 v;
+                    v.x = s_bias[c * 32 + j + 0] + s_scale[c * 32 + j + 0] * __uint_as_float(r[j + 0]);
+                    v.y = s_bias[c * 32 + j + 1] + s_scale[c * 32 + j + 1] * __uint_as_float(r[j + 1]);
+                    v.z = s_bias[c * 32 + j + 2] + s_scale[c * 32 + j + 2] * __uint_as_float(r[j + 2]);
+                    v.w = s_bias[c * 32 + j + 3] + s_scale[c * 32 + j + 3] * __uint_as_float(r[j + 3]);
+                    *reinterpret_cast<float4*>(stage + lane * STAGE_STRIDE + q * 4) = v;
                 }
+                __syncwarp();
+                const uint32_t col = nc + h * 16 + (lane & 3) * 4;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t row = i * 8 + (lane >> 2);
+                    const uint32_t gm = m_first + row;
+                    float4 v = *reinterpret_cast<const float4*>(stage + row * STAGE_STRIDE + (lane & 3) * 4);
+                    if (gm < p.M && col < p.N) {            // N is a multiple of 4: the whole float4 is in range
+                        float4* dst = reinterpret_cast<float4*>(out + (size_t)gm * p.N + col);
+                        if (EPI == EPI_RESIDUAL) {
+                            const float4 o = *dst;
+                            v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                        }
+                        *dst = v;
+                    }
+                }
+                __syncwarp();
             }
         } else if (EPI == EPI_RELU2) {
             uint16_t* out = static_cast<uint16_t*>(pr.out) + (size_t)m * p.N + nc;
@@ -318,7 +337,9 @@ gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         ptx::tc_fence_after_sync();
         if (waited && *s_error == 0) {
             const uint32_t taddr = tmem_base + ((quarter * 32) << 16);
-            epilogue<EPI>(p, pr, taddr, m, n0, s_scale, s_bias, lane, blockIdx.x);
+            // the pipeline stages are dead once the accumulator is complete: their space stages the stores
+            epilogue<EPI>(p, pr, taddr, m, n0, s_scale, s_bias, lane, blockIdx.x, 0, BN / 32,
+                          reinterpret_cast<float*>(tiles + (warp - 2) * STAGE_BYTES));
         }
     }
     ptx::tc_fence_before_sync();

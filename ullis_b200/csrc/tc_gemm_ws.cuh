@@ -33,9 +33,10 @@ struct WsShape {
 };
 
 // ring depth that fits beside the resident weight tile
-inline WsShape ws_shape(uint32_t K, uint32_t n_a) {
+inline WsShape ws_shape(uint32_t K, uint32_t n_a, bool staged_stores) {
     const uint32_t kb = K / BK;
-    const uint32_t fixed = 1024 /*alignment slack*/ + kb * TILE_BYTES + 2 * BN * 4 + 256;
+    const uint32_t fixed = 1024 /*alignment slack*/ + kb * TILE_BYTES + 2 * BN * 4 + 256 +
+                           (staged_stores ? 8 * STAGE_BYTES : 0);
     uint32_t stages = (WS_SMEM_LIMIT - fixed) / (n_a * TILE_BYTES);
     if (stages > WS_MAX_STAGES) stages = WS_MAX_STAGES;
     return WsShape{stages, fixed + stages * n_a * TILE_BYTES};
@@ -73,6 +74,7 @@ gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const 
     uint64_t* tmem_empty = tmem_full + 2;                  // [2] accumulator drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     uint32_t* s_error = tmem_slot + 1;
+    float* stage_base = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);   // STORE / RESIDUAL only
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // work split: pair = (problem, column tile), fixed per CTA; the CTAs of a pair interleave over the row tiles
@@ -226,7 +228,7 @@ gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const 
             if (__any_sync(0xffffffffu, *reinterpret_cast<volatile uint32_t*>(s_error) != 0u)) break;
             const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32) << 16);
             epilogue<EPI>(p, pr, taddr, m, n0, s_scale, s_bias, lane, n_tile * WS_EPI_GROUPS + group, group * chunks,
-                          (group + 1) * chunks);
+                          (group + 1) * chunks, stage_base + (warp - 2) * (STAGE_BYTES / 4));
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&tmem_empty[buf]);
         }
