@@ -85,17 +85,35 @@ mix_split_kernel(const float* __restrict__ x, const uint16_t* __restrict__ m0, c
     uint16_t* hi[3] = {hi0, hi1, hi2};
     uint16_t* lo[3] = {lo0, lo1, lo2};
     float sum[3] = {0.0f, 0.0f, 0.0f};
-    for (size_t c = lane; c < C; c += 32) {
-        const float xt = x[row * C + c];
-        const float xx = first ? -xt : __fsub_rn(x[(row - 1) * C + c], xt);
+    // four channels per lane and step (C % 4 == 0 on this path): 16-byte loads, 8-byte stores
+    for (size_t c = (size_t)lane * 4; c < C; c += 128) {
+        const float4 cur = *reinterpret_cast<const float4*>(x + row * C + c);
+        float4 prev = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!first) prev = *reinterpret_cast<const float4*>(x + (row - 1) * C + c);
+        const float xt[4] = {cur.x, cur.y, cur.z, cur.w}, pt[4] = {prev.x, prev.y, prev.z, prev.w};
+        float xx[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) xx[e] = first ? -xt[e] : __fsub_rn(pt[e], xt[e]);
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
             if (!mix[k]) continue;
-            const float v = __fadd_rn(xt, __fmul_rn(xx, h2f(mix[k][c])));
-            const __half h = __float2half_rn(v);
-            hi[k][row * C + c] = __half_as_ushort(h);
-            if (lo[k]) lo[k][row * C + c] = __half_as_ushort(__float2half_rn(v - __half2float(h)));
-            sum[k] += fabsf(v);
+            const uint2 mw = *reinterpret_cast<const uint2*>(mix[k] + c);
+            const uint16_t mb[4] = {(uint16_t)(mw.x & 0xFFFFu), (uint16_t)(mw.x >> 16), (uint16_t)(mw.y & 0xFFFFu),
+                                    (uint16_t)(mw.y >> 16)};
+            uint16_t hb[4], lb[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float v = __fadd_rn(xt[e], __fmul_rn(xx[e], h2f(mb[e])));
+                const __half h = __float2half_rn(v);
+                hb[e] = __half_as_ushort(h);
+                lb[e] = __half_as_ushort(__float2half_rn(v - __half2float(h)));
+                sum[k] += fabsf(v);
+            }
+            *reinterpret_cast<uint2*>(hi[k] + row * C + c) =
+                make_uint2(hb[0] | ((uint32_t)hb[1] << 16), hb[2] | ((uint32_t)hb[3] << 16));
+            if (lo[k])
+                *reinterpret_cast<uint2*>(lo[k] + row * C + c) =
+                    make_uint2(lb[0] | ((uint32_t)lb[1] << 16), lb[2] | ((uint32_t)lb[3] << 16));
         }
     }
     if (s1) {
@@ -109,17 +127,32 @@ mix_split_kernel(const float* __restrict__ x, const uint16_t* __restrict__ m0, c
 }
 
 // idx bits (stream-major) -> y = +/-e as FP16 [B*T, C] (reference src/model.rs:1313)
-__global__ void __launch_bounds__(1024)
+// One CTA: 32 steps x 256 channels; a thread writes eight channels (16 bytes) of four steps.
+__global__ void __launch_bounds__(256)
 emit_f16_kernel(const uint32_t* __restrict__ idx_sw, const uint16_t* __restrict__ e, uint16_t* __restrict__ y,
                 size_t T, size_t C, size_t wps) {
-    __shared__ uint32_t wsm[32];
-    const size_t b = blockIdx.z, t0 = (size_t)blockIdx.x * 32, c0 = (size_t)blockIdx.y * 32;
-    const int tx = threadIdx.x, ty = threadIdx.y;
-    if (ty == 0) wsm[tx] = (c0 + tx < C) ? idx_sw[(b * C + c0 + tx) * wps + blockIdx.x] : 0u;
+    __shared__ __align__(16) uint32_t wsm[256];
+    const size_t b = blockIdx.z, t0 = (size_t)blockIdx.x * 32, c0 = (size_t)blockIdx.y * 256;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    wsm[threadIdx.x] = (c0 + threadIdx.x < C) ? idx_sw[(b * C + c0 + threadIdx.x) * wps + blockIdx.x] : 0u;
     __syncthreads();
-    if (t0 + ty >= T || c0 + tx >= C) return;
-    const uint32_t bit = (wsm[tx] >> ty) & 1u;
-    y[(b * T + t0 + ty) * C + c0 + tx] = e[c0 + tx] ^ (bit ? 0u : 0x8000u);  // flip the FP16 sign for idx 0
+    const size_t c = c0 + (size_t)tx * 8;
+    if (c >= C) return;   // C % 8 == 0 on this path
+    const uint4 ev = *reinterpret_cast<const uint4*>(e + c);
+    const uint32_t eb[8] = {ev.x & 0xFFFFu, ev.x >> 16, ev.y & 0xFFFFu, ev.y >> 16,
+                            ev.z & 0xFFFFu, ev.z >> 16, ev.w & 0xFFFFu, ev.w >> 16};
+    const uint4 wa = reinterpret_cast<const uint4*>(wsm)[tx * 2], wb = reinterpret_cast<const uint4*>(wsm)[tx * 2 + 1];
+    const uint32_t words[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t tt = ty * 4 + k;
+        if (t0 + tt >= T) break;
+        uint32_t h[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = eb[j] ^ (((words[j] >> tt) & 1u) ? 0u : 0x8000u);  // flip the FP16 sign for idx 0
+        *reinterpret_cast<uint4*>(y + (b * T + t0 + tt) * C + c) =
+            make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+    }
 }
 
 // Sign bits whose tensor-core pre-activation fell inside the error band are
@@ -391,8 +424,8 @@ bool rosa_out_residual(ullis_cuda_runtime* rt, const uint32_t* idx_sw, const Lay
     if (!usable(rt) || !shape_ok(rows, d, d) || d % 4) return false;
     uint16_t* y16 = rt->tc_ws[0].as<uint16_t>(rows * d);
     const size_t wps = (time + 31) / 32;
-    dim3 grid((unsigned)wps, (unsigned)((d + 31) / 32), (unsigned)batch);
-    emit_f16_kernel<<<grid, dim3(32, 32), 0, rt->stream>>>(idx_sw, L.e, y16, time, d, wps);
+    dim3 grid((unsigned)wps, (unsigned)((d + 255) / 256), (unsigned)batch);
+    emit_f16_kernel<<<grid, 256, 0, rt->stream>>>(idx_sw, L.e, y16, time, d, wps);
     rt->launched("emit_f16");
     GemmMaps maps;
     memset(&maps, 0, sizeof(maps));
