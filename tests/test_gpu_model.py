@@ -152,3 +152,30 @@ def test_split_enqueue_api_and_phase_profile(cuda_rt, case):
     ms = m.phase_ms()
     assert ms["sam"] > 0 and ms["qkv"] > 0 and ms["head_ce"] > 0
     m.close()
+
+
+def test_per_kernel_device_times(cuda_rt, case):
+    """Events behind every launch: each kernel of the step is listed with its launch count and a positive time."""
+    m = cuda.CudaHeron(cuda_rt, case["data"])
+    m.upload_tokens(case["tokens"], case["labels"], case["B"], case["T"])
+    m.enqueue_forward_ce(0, case["B"], case["T"])
+    m.read_loss()
+    cuda_rt.kernel_timing(True)
+    before = cuda_rt.launch_count
+    m.enqueue_forward_ce(0, case["B"], case["T"])
+    m.read_loss()
+    times = cuda_rt.kernel_times()
+    launched = cuda_rt.launch_count - before
+    cuda_rt.kernel_timing(False)
+    kernels = {k: v for k, v in times.items() if not k.startswith("(")}
+    assert sum(n for _, n in kernels.values()) == launched
+    assert all(ms >= 0.0 for ms, _ in kernels.values()) and sum(ms for ms, _ in kernels.values()) > 0.0
+    sam = [k for k in kernels if k.startswith("rosa_")]
+    assert sam and all(kernels[k][1] % m.n_layers == 0 for k in sam)
+    # switched off: nothing more is recorded
+    m.enqueue_forward_ce(0, case["B"], case["T"])
+    m.read_loss()
+    cuda_rt.kernel_timing(True)
+    assert cuda_rt.kernel_times() == {}
+    cuda_rt.kernel_timing(False)
+    m.close()

@@ -135,13 +135,15 @@ struct Walker {
     uint32_t u, g, w;
     int32_t h;
     uint32_t gmax;  // maxlen of g
+    uint32_t gfail; // suffix link of g, valid while g_fresh
+    bool g_fresh;   // g was created by the previous extend: no children yet, every field known
 
     SAM_HD void init(Node<Ix>* nodes) {
         N = nodes;
         Node<Ix> root;
         root.t0 = (Ix)NIL; root.t1 = (Ix)NIL; root.fail = (Ix)NIL; root.maxlen = 0;
         N[0] = root;
-        u = 1; g = 0; w = 0; h = 0; gmax = 0;
+        u = 1; g = 0; w = 0; h = 0; gmax = 0; gfail = NIL; g_fresh = true;   // the root has no children yet either
     }
 
     // src/rosa.rs:104-128 (query half of push)
@@ -186,6 +188,11 @@ struct Walker {
         uint32_t p = g, d = NIL, b = NIL;
         Node<Ix> n;
         n.t0 = n.t1 = n.fail = (Ix)NIL; n.maxlen = 0;
+        if (g_fresh) {
+            // the first state of the walk has no children: its visit is known without a load
+            if (kb) N[p].t1 = (Ix)j; else N[p].t0 = (Ix)j;
+            p = gfail;
+        }
         while (p != NIL) {
             n = N[p];
             if (visits) ++*visits;
@@ -222,6 +229,8 @@ struct Walker {
         N[j] = nj;
         g = j;
         gmax = gmax + 1;
+        gfail = nj.fail;
+        g_fresh = true;
         *j_out = j; *b_out = b; *d_out = d;
     }
 };
