@@ -37,6 +37,7 @@ extern "C" {
 
 typedef struct ullis_cuda_runtime ullis_cuda_runtime;
 typedef struct ullis_cuda_model ullis_cuda_model;
+typedef struct ullis_cuda_generate_state ullis_cuda_generate_state;
 
 enum {
     ULLIS_CUDA_OK = 0,
@@ -158,6 +159,32 @@ ULLIS_CUDA_API int32_t ullis_cuda_model_tap(ullis_cuda_model* model, int32_t lay
  * [embed_ln, qkv, sam, o, cmix, head_ce]. */
 ULLIS_CUDA_API int32_t ullis_cuda_model_set_profile(ullis_cuda_model* model, int32_t enabled);
 ULLIS_CUDA_API int32_t ullis_cuda_model_phase_ms(ullis_cuda_model* model, float ms[6]);
+
+/* ----------------------------------------------------------------- generate
+ * Incremental generation with the state on the device (HeronGenerateState,
+ * src/model.rs:2433-2454): per layer one suffix automaton per (sequence,
+ * channel) plus the ROSA and CMix time-shift inputs.  The reference generates
+ * one sequence; here `batch` independent sequences advance in lock step.
+ * Arithmetic is the reference's (CUDA cores, its summation order), whatever
+ * the runtime's mode: the logits of step t are bit-identical to row t of
+ * ullis_cuda_model_logits in ULLIS_CUDA_MODE_EXACT (src/model.rs:4991-5004). */
+
+/* UllisHeron::generate_state (src/model.rs:2691-2715): empty automata sized for
+ * the model's context_len, no time-shift history, time 0.  The state borrows
+ * `model`; destroy it before the model. */
+ULLIS_CUDA_API int32_t ullis_cuda_generate_state_create(ullis_cuda_model* model, size_t batch,
+                                                        ullis_cuda_generate_state** out);
+ULLIS_CUDA_API void ullis_cuda_generate_state_destroy(ullis_cuda_generate_state* state);
+/* Back to time 0 without reallocating (RosaSam::reset, src/rosa.rs:66-74). */
+ULLIS_CUDA_API int32_t ullis_cuda_generate_state_reset(ullis_cuda_generate_state* state);
+/* HeronGenerateState::time (src/model.rs:2449-2453): tokens consumed so far. */
+ULLIS_CUDA_API size_t ullis_cuda_generate_state_time(const ullis_cuda_generate_state* state);
+/* UllisHeron::generate_step (src/model.rs:2717-2753): one token per sequence
+ * (tokens [batch]) -> last-token logits [batch, vocab].  ULLIS_CUDA_ERR_TOKEN
+ * for a token id >= vocab, ULLIS_CUDA_ERR_SHAPE once time == context_len; in
+ * both cases the state is unchanged. */
+ULLIS_CUDA_API int32_t ullis_cuda_generate_step(ullis_cuda_generate_state* state, const uint32_t* tokens,
+                                                float* logits);
 
 /* ------------------------------------------------------------------ op level
  * Host pointers in, caller-allocated host buffers out; one synchronous call

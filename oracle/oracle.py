@@ -407,3 +407,59 @@ class HeronOracle:
         if taps is not None:
             taps["hidden"] = h
         return mean, n_valid, row_loss, logits
+
+    # ---- incremental generation (src/model.rs:2433-2454, 2691-2753)
+    def generate_state(self):
+        """Empty automata (one per layer and channel), no time-shift history."""
+        T = self.cfg["context_len"]
+        return {"time": 0,
+                "layers": [{"sams": [RosaSam(T) for _ in range(self.d)], "rosa_x_prev": None, "cmix_x_prev": None}
+                           for _ in range(self.layers)]}
+
+    @staticmethod
+    def _shift_one(x, prev):
+        """time_shift_one, src/model.rs:214-228."""
+        return -x if prev is None else (prev - x).astype(np.float32)
+
+    def generate_step(self, state, token: int) -> np.ndarray:
+        """One token -> last-token logits [vocab]; HeronBlock::forward_one src/model.rs:2243-2262,
+        ROSA forward_one 1320-1352, CMix forward_one 1003-1016."""
+        t, d = self.t, self.d
+        if token >= self.vocab:
+            raise ValueError("token id exceeds vocabulary")
+        if state["time"] >= self.cfg["context_len"]:
+            raise ValueError(f"generate exceeded context_len ({self.cfg['context_len']})")
+        x = embed(np.array([token], np.uint32), t["embedding"], d, self.vocab)
+        for l, layer in enumerate(state["layers"]):
+            pre = f"blocks.{l}"
+            if l == 0:
+                x = layer_norm(x, t[pre + ".ln0.weight"], t[pre + ".ln0.bias"], 1, d)
+            rosa_in = layer_norm(x, t[pre + ".ln3.weight"], t[pre + ".ln3.bias"], 1, d)
+            xx = self._shift_one(rosa_in, layer["rosa_x_prev"])
+            acts = []
+            for m in "qkv":
+                mix = fp16_to_f32(t[f"{pre}.rosa.x_{m}"])
+                inp = (rosa_in + (xx * mix).astype(np.float32)).astype(np.float32)  # multiply, then add
+                w = self._packed(f"{pre}.rosa.{m}")
+                acts.append(binary_linear(inp, w["bits"], w["scale"], w["bias"], 1, d, d))
+            e = fp16_to_f32(t[pre + ".rosa.e"])
+            y = np.empty(d, np.float32)
+            for c, sam in enumerate(layer["sams"]):
+                idx = sam.push(int(acts[0][c] > 0), int(acts[1][c] > 0), int(acts[2][c] > 0))
+                y[c] = np.float32(2.0 * idx - 1.0) * e[c]
+            o = self._packed(f"{pre}.rosa.o")
+            rosa_out = binary_linear(y, o["bits"], o["scale"], o["bias"], 1, d, d)
+            layer["rosa_x_prev"] = rosa_in
+            x = (x + rosa_out).astype(np.float32)
+            ffn_in = layer_norm(x, t[pre + ".ln2.weight"], t[pre + ".ln2.bias"], 1, d)
+            xx = self._shift_one(ffn_in, layer["cmix_x_prev"])
+            shifted = (ffn_in + (xx * fp16_to_f32(t[pre + ".ffn.x_k"])).astype(np.float32)).astype(np.float32)
+            key = binary_linear(shifted, t[pre + ".ffn.key.bits"], t[pre + ".ffn.key.scale"], None, 1, d, self.ffn)
+            pos = np.maximum(key, np.float32(0.0))
+            relu2 = (pos * pos).astype(np.float32)
+            ffn_out = fp16_linear(relu2, t[pre + ".ffn.value"], 1, self.ffn, d)
+            layer["cmix_x_prev"] = ffn_in
+            x = (x + ffn_out).astype(np.float32)
+        hidden = layer_norm(x, t["ln_out.weight"], t["ln_out.bias"], 1, d)
+        state["time"] += 1
+        return binary_linear(hidden, t["head.bits"], t["head.scale"], self._head_bias(), 1, d, self.vocab)

@@ -1,0 +1,91 @@
+"""Incremental generation on the device (ullis_cuda_generate_*) against the
+oracle: the logits of step t are bit-identical to row t of the one-shot
+forward (reference test src/model.rs:4991-5004), for one and for several
+sequences advancing in lock step, after a reset, and whatever arithmetic mode
+the runtime is in; the reference's error cases leave the state untouched."""
+import numpy as np
+import pytest
+
+from ullis_b200 import cuda, synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", params=[("tiny", 1, 64, False), ("tiny", 3, 37, True), ("small", 2, 48, False)],
+                ids=["tiny-b1-full-context", "tiny-gain1-b3", "config0-b2"])
+def gen_case(request, oracle):
+    name, B, T, gain = request.param
+    data = synth.heron_checkpoint(name, batch_size=max(B, 2), ln_gain_one=gain)
+    m = oracle.HeronOracle(data)
+    tokens = synth.zipf_tokens(17, B * T, m.vocab).reshape(B, T)
+    one_shot = m.logits(tokens.reshape(-1), B, T).reshape(B, T, m.vocab)
+    return dict(data=data, B=B, T=T, tokens=tokens, one_shot=one_shot, vocab=m.vocab)
+
+
+@pytest.mark.parametrize("mode", [cuda.MODE_FAST, cuda.MODE_EXACT], ids=["runtime-fast", "runtime-exact"])
+def test_generate_matches_one_shot_bit_for_bit(cuda_rt, gen_case, mode):
+    cuda_rt.set_mode(mode)
+    try:
+        m = cuda.CudaHeron(cuda_rt, gen_case["data"])
+        state = m.generate_state(gen_case["B"])
+        assert state.time == 0
+        for t in range(gen_case["T"]):
+            logits = m.generate_step(state, gen_case["tokens"][:, t])
+            assert logits.shape == (gen_case["B"], gen_case["vocab"])
+            assert np.array_equal(logits, gen_case["one_shot"][:, t, :]), t
+            assert state.time == t + 1
+        # a reset state replays the same logits; so does a second state of the same model
+        state.reset()
+        assert state.time == 0
+        other = m.generate_state(gen_case["B"])
+        for t in range(min(gen_case["T"], 9)):
+            a = m.generate_step(state, gen_case["tokens"][:, t])
+            b = m.generate_step(other, gen_case["tokens"][:, t])
+            assert np.array_equal(a, gen_case["one_shot"][:, t, :]) and np.array_equal(a, b), t
+        other.close()
+        state.close()
+        m.close()
+    finally:
+        cuda_rt.set_mode(cuda.MODE_FAST)
+
+
+def test_generate_equals_device_one_shot_in_exact_mode(cuda_rt, gen_case):
+    cuda_rt.set_mode(cuda.MODE_EXACT)
+    try:
+        m = cuda.CudaHeron(cuda_rt, gen_case["data"])
+        B, T = gen_case["B"], gen_case["T"]
+        one = m.logits(gen_case["tokens"].reshape(-1), B, T).reshape(B, T, -1)
+        state = m.generate_state(B)
+        for t in range(T):
+            assert np.array_equal(m.generate_step(state, gen_case["tokens"][:, t]), one[:, t, :]), t
+        state.close()
+        m.close()
+    finally:
+        cuda_rt.set_mode(cuda.MODE_FAST)
+
+
+def test_generate_error_cases_leave_the_state_unchanged(cuda_rt, oracle):  # src/model.rs:2718-2723, 5044-5056
+    data = synth.heron_checkpoint("tiny", batch_size=2, context_len=6)
+    ref = oracle.HeronOracle(data)
+    m = cuda.CudaHeron(cuda_rt, data)
+    with pytest.raises(cuda.UllisCudaError) as e:
+        m.generate_state(0)
+    assert e.value.code == cuda.ERR_SHAPE
+    state = m.generate_state(2)
+    tokens = synth.zipf_tokens(5, 12, ref.vocab).reshape(2, 6)
+    one_shot = ref.logits(tokens.reshape(-1), 2, 6).reshape(2, 6, -1)
+    for t in range(3):
+        m.generate_step(state, tokens[:, t])
+    with pytest.raises(cuda.UllisCudaError) as e:
+        m.generate_step(state, np.array([1, ref.vocab], np.uint32))
+    assert e.value.code == cuda.ERR_TOKEN and "vocabulary" in str(e.value) and state.time == 3
+    with pytest.raises(cuda.UllisCudaError) as e:
+        m.generate_step(state, np.array([1], np.uint32))  # one token for two sequences
+    assert e.value.code == cuda.ERR_SHAPE and state.time == 3
+    for t in range(3, 6):  # the failed calls consumed nothing
+        assert np.array_equal(m.generate_step(state, tokens[:, t]), one_shot[:, t, :]), t
+    with pytest.raises(cuda.UllisCudaError) as e:
+        m.generate_step(state, tokens[:, 0])
+    assert e.value.code == cuda.ERR_SHAPE and "context_len" in str(e.value) and state.time == 6
+    state.close()
+    m.close()

@@ -9,6 +9,7 @@
 
 #include "kernels.hpp"
 #include "linear_tc.hpp"
+#include "generate.hpp"
 #include "model.hpp"
 
 using namespace ullis;
@@ -393,6 +394,44 @@ int32_t ullis_cuda_model_phase_ms(ullis_cuda_model* model, float ms[6]) {
 }
 
 // ---------------------------------------------------------------- op level
+
+// ------------------------------------------------------------------ generate
+
+int32_t ullis_cuda_generate_state_create(ullis_cuda_model* model, size_t batch, ullis_cuda_generate_state** out) {
+    return guard_model(model, [&] {
+        need_ptr(out, "out");
+        *out = nullptr;
+        *out = new ullis_cuda_generate_state(model, batch);
+    });
+}
+
+void ullis_cuda_generate_state_destroy(ullis_cuda_generate_state* state) {
+    if (!state) return;
+    if (state->model && state->model->rt) cudaSetDevice(state->model->rt->device);
+    delete state;
+}
+
+int32_t ullis_cuda_generate_state_reset(ullis_cuda_generate_state* state) {
+    if (!state) {
+        set_global_error("generate state handle is null");
+        return ULLIS_CUDA_ERR_ARG;
+    }
+    return guard_model(state->model, [&] { state->reset(); });
+}
+
+size_t ullis_cuda_generate_state_time(const ullis_cuda_generate_state* state) { return state ? state->time : 0; }
+
+int32_t ullis_cuda_generate_step(ullis_cuda_generate_state* state, const uint32_t* tokens, float* logits) {
+    if (!state) {
+        set_global_error("generate state handle is null");
+        return ULLIS_CUDA_ERR_ARG;
+    }
+    return guard_model(state->model, [&] {
+        need_ptr(tokens, "tokens");
+        need_ptr(logits, "logits");
+        state->step(tokens, logits);
+    });
+}
 
 int32_t ullis_cuda_layer_norm(ullis_cuda_runtime* rt, const float* x, const uint16_t* weight,
                               const uint16_t* bias, float* y, size_t rows, size_t channels) {

@@ -1,0 +1,194 @@
+// Incremental generation: one token per sequence and call, with the automata
+// of every (sequence, layer, channel) kept on the device between calls
+// (reference UllisHeron::generate_state / generate_step, src/model.rs:2691-2753;
+// per-block forward_one src/model.rs:2243-2262, ROSA 1320-1352, CMix 1003-1016).
+//
+// A step is a handful of [batch, d_model] row operations, so it runs on the
+// CUDA-core kernels in the reference's summation order: the logits of step t
+// are bit-identical to row t of the one-shot forward in EXACT mode, which is
+// what the reference's own test asserts (src/model.rs:4991-5004).  The automata
+// use the reference's eager schedule, statement for statement (push stamps the
+// whole suffix-link chain), because the O(T log T) form needs the whole
+// sequence in advance.
+#include "generate.hpp"
+
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <string>
+
+#include "kernels.hpp"
+#include "sam_core.cuh"
+
+namespace ullis {
+namespace {
+
+inline unsigned blocks_for(size_t n, unsigned per) { return (unsigned)((n + per - 1) / per); }
+
+__device__ __forceinline__ float h2f(uint16_t b) { return __half2float(__ushort_as_half(b)); }
+
+// empty automaton per stream (src/rosa.rs:66-74: root only, fail[0] = -1, no `last`)
+template <typename Ix>
+__global__ void gen_init_kernel(uint8_t* __restrict__ blocks, size_t stride, sam::WalkerState* __restrict__ ws,
+                                size_t streams, uint32_t T) {
+    const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= streams) return;
+    sam::EagerLayout<Ix> L(T);
+    uint8_t* blk = blocks + s * stride;
+    sam::Walker<Ix> wk;
+    wk.init(reinterpret_cast<sam::Node<Ix>*>(blk + L.nodes));
+    reinterpret_cast<Ix*>(blk + L.last)[0] = 0;
+    sam::save_walker(wk, 0u, &ws[s]);
+}
+
+// time_shift_one + mixes (src/model.rs:214-228, 1331-1340, 1008-1012): xx = prev - x, or -x before the
+// first token; out_m = x + xx*mix_m, unfused; then x becomes the layer's new time-shift history
+__global__ void gen_shift_mix_kernel(const float* __restrict__ x, float* __restrict__ prev, int has_prev,
+                                     const uint16_t* __restrict__ m0, const uint16_t* __restrict__ m1,
+                                     const uint16_t* __restrict__ m2, float* __restrict__ o0, float* __restrict__ o1,
+                                     float* __restrict__ o2, size_t n, size_t C) {
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    const size_t c = e % C;
+    const float xt = x[e];
+    const float xx = has_prev ? __fsub_rn(prev[e], xt) : -xt;
+    o0[e] = __fadd_rn(xt, __fmul_rn(xx, h2f(m0[c])));
+    if (o1) o1[e] = __fadd_rn(xt, __fmul_rn(xx, h2f(m1[c])));
+    if (o2) o2[e] = __fadd_rn(xt, __fmul_rn(xx, h2f(m2[c])));
+    prev[e] = xt;
+}
+
+// one RosaSam::push per (sequence, channel) of one layer and y = (2*idx - 1)*e (src/model.rs:1344-1351)
+template <typename Ix>
+__global__ void __launch_bounds__(128)
+gen_push_kernel(uint8_t* __restrict__ blocks, size_t stride, sam::WalkerState* __restrict__ ws,
+                uint32_t* __restrict__ vhist, size_t wps, const float* __restrict__ q, const float* __restrict__ k,
+                const float* __restrict__ v, const uint16_t* __restrict__ e, float* __restrict__ y, size_t streams,
+                size_t C, uint32_t T, uint32_t* __restrict__ status) {
+    const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= streams) return;
+    sam::EagerLayout<Ix> L(T);
+    uint8_t* blk = blocks + s * stride;
+    sam::Walker<Ix> wk;
+    const uint32_t i = sam::load_walker(wk, reinterpret_cast<sam::Node<Ix>*>(blk + L.nodes), &ws[s]);
+    if (i >= T) {  // the host checks the context length first; never write past the state block
+        if (atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_SAM_CAPACITY) == ULLIS_DEV_OK) status[1] = (uint32_t)s;
+        return;
+    }
+    // src/rosa.rs:372-374: bit = activation > 0
+    const uint32_t qb = q[s] > 0.0f, kb = k[s] > 0.0f, vb = v[s] > 0.0f;
+    uint32_t* vh = vhist + s * wps;
+    const uint32_t word = (i & 31u) ? vh[i >> 5] : 0u;   // a new word starts empty
+    vh[i >> 5] = word | (vb << (i & 31u));
+    const uint32_t idx = sam::eager_step<Ix>(wk, reinterpret_cast<Ix*>(blk + L.last), vh, i, qb, kb, nullptr);
+    sam::save_walker(wk, i + 1u, &ws[s]);
+    const float ev = h2f(e[s % C]);
+    y[s] = idx ? ev : -ev;
+}
+
+}  // namespace
+}  // namespace ullis
+
+using namespace ullis;
+
+ullis_cuda_generate_state::ullis_cuda_generate_state(ullis_cuda_model* m, size_t batch_) : model(m), batch(batch_) {
+    if (batch == 0) fail(ULLIS_CUDA_ERR_SHAPE, "generate needs at least one sequence");
+    const uint32_t T = (uint32_t)m->context_len;
+    narrow = sam::node_capacity(T) <= 0xFFFFu;
+    stride = narrow ? sam::EagerLayout<uint16_t>(T).total : sam::EagerLayout<uint32_t>(T).total;
+    wps = (m->context_len + 31) / 32;
+    const size_t per_layer = batch * m->d;
+    if (per_layer / m->d != batch || m->layers > SIZE_MAX / per_layer) fail(ULLIS_CUDA_ERR_SHAPE, "generate state shape overflow");
+    streams = m->layers * per_layer;
+    if (streams > SIZE_MAX / stride) fail(ULLIS_CUDA_ERR_SHAPE, "generate state shape overflow");
+    m->rt->bind();
+    blocks.ensure(streams * stride);
+    walkers.ensure(streams * sizeof(sam::WalkerState));
+    vhist.ensure(streams * wps * 4);
+    prev.ensure(m->layers * 2 * per_layer * 4);
+    reset();
+}
+
+void ullis_cuda_generate_state::reset() {
+    ullis_cuda_runtime* rt = model->rt;
+    rt->bind();
+    const uint32_t T = (uint32_t)model->context_len;
+    auto* ws = static_cast<sam::WalkerState*>(walkers.get());
+    auto* blk = static_cast<uint8_t*>(blocks.get());
+    if (narrow) gen_init_kernel<uint16_t><<<blocks_for(streams, 256), 256, 0, rt->stream>>>(blk, stride, ws, streams, T);
+    else gen_init_kernel<uint32_t><<<blocks_for(streams, 256), 256, 0, rt->stream>>>(blk, stride, ws, streams, T);
+    rt->launched("gen_init");
+    rt->sync();
+    time = 0;
+}
+
+void ullis_cuda_generate_state::step(const uint32_t* tokens, float* logits_out) {
+    ullis_cuda_model* m = model;
+    ullis_cuda_runtime* rt = m->rt;
+    // src/model.rs:2718-2723
+    for (size_t b = 0; b < batch; ++b)
+        if (tokens[b] >= m->vocab) fail(ULLIS_CUDA_ERR_TOKEN, "token id exceeds vocabulary");
+    if (time >= m->context_len)
+        fail(ULLIS_CUDA_ERR_SHAPE, "generate exceeded context_len (" + std::to_string(m->context_len) + ")");
+    rt->bind();
+    if (rt->kernel_timing) rt->mark("(between steps)");
+    const size_t d = m->d, ffn = m->ffn, rows = batch, n = rows * d;
+    const uint32_t T = (uint32_t)m->context_len;
+    uint32_t* ids = m->ids.as<uint32_t>(rows);
+    float* X = m->x.as<float>(n);
+    float* A = m->a.as<float>(n);
+    float* Bq = m->b.as<float>(n);
+    float* Bk = m->c.as<float>(n);
+    float* Bv = m->dd.as<float>(n);
+    float* W = m->wide.as<float>(rows * std::max(ffn, 3 * d));
+    float* LG = m->logits.as<float>(rows * m->vocab);
+    rt->clear_status();
+    rt->h2d(ids, tokens, rows * 4);
+    k::embed(rt, ids, m->embedding, X, rows, d, m->vocab);
+    const int has_prev = time != 0;
+    for (size_t l = 0; l < m->layers; ++l) {
+        const LayerWeights& L = m->blocks[l];
+        float* rosa_prev = static_cast<float*>(prev.get()) + (l * 2) * n;
+        float* cmix_prev = rosa_prev + n;
+        const size_t s0 = l * n;  // first stream of this layer
+        if (l == 0) {  // ln0 REPLACES x on layer 0 (src/model.rs:2244-2248)
+            k::layer_norm(rt, X, L.ln0.weight, L.ln0.bias, A, rows, d, true);
+            ULLIS_CUDA_CHECK(cudaMemcpyAsync(X, A, n * 4, cudaMemcpyDeviceToDevice, rt->stream));
+        }
+        // ROSA (src/model.rs:1320-1352)
+        k::layer_norm(rt, X, L.ln3.weight, L.ln3.bias, A, rows, d, true);
+        gen_shift_mix_kernel<<<blocks_for(n, 256), 256, 0, rt->stream>>>(A, rosa_prev, has_prev, L.x_q, L.x_k, L.x_v, Bq, Bk,
+                                                                       Bv, n, d);
+        rt->launched("gen_shift_mix");
+        k::binary_linear_exact(rt, Bq, L.q.bits, L.q.scale, L.q.bias, W, rows, d, d, false);
+        k::binary_linear_exact(rt, Bk, L.k.bits, L.k.scale, L.k.bias, W + n, rows, d, d, false);
+        k::binary_linear_exact(rt, Bv, L.v.bits, L.v.scale, L.v.bias, W + 2 * n, rows, d, d, false);
+        {
+            auto* ws = static_cast<sam::WalkerState*>(walkers.get()) + s0;
+            uint8_t* blk = static_cast<uint8_t*>(blocks.get()) + s0 * stride;
+            uint32_t* vh = static_cast<uint32_t*>(vhist.get()) + s0 * wps;
+            if (narrow)
+                gen_push_kernel<uint16_t><<<blocks_for(n, 128), 128, 0, rt->stream>>>(blk, stride, ws, vh, wps, W, W + n, W + 2 * n,
+                                                                                     L.e, A, n, d, T, rt->dev_status);
+            else
+                gen_push_kernel<uint32_t><<<blocks_for(n, 128), 128, 0, rt->stream>>>(blk, stride, ws, vh, wps, W, W + n, W + 2 * n,
+                                                                                     L.e, A, n, d, T, rt->dev_status);
+            rt->launched("gen_push");
+        }
+        k::binary_linear_exact(rt, A, L.o.bits, L.o.scale, L.o.bias, X, rows, d, d, true);  // h += rosa out
+        // CMix (src/model.rs:1003-1016)
+        k::layer_norm(rt, X, L.ln2.weight, L.ln2.bias, A, rows, d, true);
+        gen_shift_mix_kernel<<<blocks_for(n, 256), 256, 0, rt->stream>>>(A, cmix_prev, has_prev, L.ffn_x_k, nullptr, nullptr, Bq,
+                                                                       nullptr, nullptr, n, d);
+        rt->launched("gen_shift_mix");
+        k::binary_linear_exact(rt, Bq, L.key.bits, L.key.scale, nullptr, W, rows, d, ffn, false);
+        k::relu2(rt, W, W, rows * ffn);
+        k::fp16_linear_exact(rt, W, L.value, X, rows, ffn, d, true);  // h += cmix out
+    }
+    // src/model.rs:2750-2752
+    k::layer_norm(rt, X, m->ln_out.weight, m->ln_out.bias, A, rows, d, true);
+    k::binary_linear_exact(rt, A, m->head.bits, m->head.scale, m->head.bias, LG, rows, d, m->vocab, false);
+    rt->d2h(logits_out, LG, rows * m->vocab * 4);
+    rt->check_status();  // synchronises
+    time += 1;
+}

@@ -237,13 +237,62 @@ struct Walker {
 
 // ------------------------------------------------------------------ eager
 
+// One RosaSam::push (src/rosa.rs:100-176) on a stream whose automaton lives in
+// `wk` / `last` (last stores last+1, 0 = never): step number i, bits q and k;
+// `vhist` is the stream's v history as bit words and must already hold bit i
+// (the reference appends v_t before it queries, src/rosa.rs:102).  Returns idx.
+template <typename Ix>
+SAM_HD uint32_t eager_step(Walker<Ix>& wk, Ix* last, const uint32_t* vhist, uint32_t i, uint32_t qb, uint32_t kb,
+                           Counters* cnt) {
+    constexpr uint32_t NIL = Nil<Ix>::value;
+    unsigned long long* visits = cnt ? &cnt->node_visits : nullptr;
+    const uint32_t v = wk.query(qb, visits);
+    uint32_t bit = 0;
+    if (v != NIL) {
+        const uint32_t pos = last[v];  // == last + 1 >= 1 for any non-root state
+        bit = stream_bit(vhist, pos);
+    }
+    uint32_t j, b, d;
+    wk.extend(kb, &j, &b, &d, visits);
+    if (b != NIL) last[b] = last[d];
+    last[j] = 0;
+    // src/rosa.rs:168-173: stamp the whole suffix-link chain of j
+    uint32_t c = j;
+    while (c != NIL && (uint32_t)last[c] < i + 1u) {
+        last[c] = (Ix)(i + 1u);
+        c = wk.N[c].fail;
+        if (cnt) ++cnt->chain_steps;
+    }
+    return bit;
+}
+
+// What a Walker carries from one step to the next, for automata that outlive a
+// kernel (incremental generation): 32 bytes per stream.
+struct WalkerState {
+    uint32_t u, g, w, gmax, gfail;
+    int32_t h;
+    uint32_t steps;   // pushes so far
+    uint32_t pad;
+};
+template <typename Ix>
+SAM_HD void save_walker(const Walker<Ix>& wk, uint32_t steps, WalkerState* st) {
+    st->u = wk.u; st->g = wk.g; st->w = wk.w; st->gmax = wk.gmax; st->gfail = wk.gfail; st->h = wk.h;
+    st->steps = steps; st->pad = 0;
+}
+template <typename Ix>
+SAM_HD uint32_t load_walker(Walker<Ix>& wk, Node<Ix>* nodes, const WalkerState* st) {
+    wk.N = nodes;
+    wk.u = st->u; wk.g = st->g; wk.w = st->w; wk.gmax = st->gmax; wk.gfail = st->gfail; wk.h = st->h;
+    wk.g_fresh = true;   // g is the root or the state of the last step: no children either way
+    return st->steps;
+}
+
 // scratch: EagerLayout<Ix>(T).total bytes.  qw/kw/vw: this stream's bits, bit t
 // at word t/32, bit t%32.  out: idx bits in the same layout (whole words are
 // written, tail bits zero).
 template <typename Ix>
 SAM_HD void run_eager(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw,
                       uint32_t* out, uint32_t T, Counters* cnt) {
-    constexpr uint32_t NIL = Nil<Ix>::value;
     EagerLayout<Ix> L(T);
     Node<Ix>* N = reinterpret_cast<Node<Ix>*>(scratch + L.nodes);
     Ix* last = reinterpret_cast<Ix*>(scratch + L.last);  // stores last+1, 0 = never
@@ -251,28 +300,10 @@ SAM_HD void run_eager(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, 
     wk.init(N);
     last[0] = 0;
     uint32_t acc = 0;
-    unsigned long long* visits = cnt ? &cnt->node_visits : nullptr;
     for (uint32_t i = 0; i < T; ++i) {
-        const uint32_t qb = stream_bit(qw, i), kb = stream_bit(kw, i);
-        const uint32_t v = wk.query(qb, visits);
-        uint32_t bit = 0;
-        if (v != NIL) {
-            const uint32_t pos = last[v];  // == last + 1 >= 1 for any non-root state
-            bit = stream_bit(vw, pos);
-        }
+        const uint32_t bit = eager_step<Ix>(wk, last, vw, i, stream_bit(qw, i), stream_bit(kw, i), cnt);
         acc |= bit << (i & 31);
         if ((i & 31) == 31 || i + 1 == T) { out[i >> 5] = acc; acc = 0; }
-        uint32_t j, b, d;
-        wk.extend(kb, &j, &b, &d, visits);
-        if (b != NIL) last[b] = last[d];
-        last[j] = 0;
-        // src/rosa.rs:168-173: stamp the whole suffix-link chain of j
-        uint32_t c = j;
-        while (c != NIL && (uint32_t)last[c] < i + 1u) {
-            last[c] = (Ix)(i + 1u);
-            c = N[c].fail;
-            if (cnt) ++cnt->chain_steps;
-        }
     }
 }
 

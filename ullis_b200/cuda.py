@@ -42,7 +42,9 @@ ABI_SYMBOLS = (
     "ullis_cuda_model_forward_ce", "ullis_cuda_model_upload_tokens", "ullis_cuda_model_enqueue_forward_ce",
     "ullis_cuda_model_read_loss", "ullis_cuda_model_logits", "ullis_cuda_model_hidden",
     "ullis_cuda_model_set_taps", "ullis_cuda_model_tap", "ullis_cuda_model_set_profile",
-    "ullis_cuda_model_phase_ms", "ullis_cuda_layer_norm", "ullis_cuda_time_shift_delta",
+    "ullis_cuda_model_phase_ms", "ullis_cuda_generate_state_create", "ullis_cuda_generate_state_destroy",
+    "ullis_cuda_generate_state_reset", "ullis_cuda_generate_state_time", "ullis_cuda_generate_step",
+    "ullis_cuda_layer_norm", "ullis_cuda_time_shift_delta",
     "ullis_cuda_binary_linear", "ullis_cuda_fp16_linear", "ullis_cuda_sign_pack_bits", "ullis_cuda_cmix_relu2",
     "ullis_cuda_residual_add", "ullis_cuda_rosa_qkv_1bit_fwd", "ullis_cuda_rosa_block_forward",
     "ullis_cuda_cmix_block_forward", "ullis_cuda_streamed_ce", "ullis_cuda_rosa_sam_static",
@@ -78,6 +80,10 @@ def load_library() -> C.CDLL:
         lib.ullis_cuda_runtime_destroy.argtypes = [C.c_void_p]
         lib.ullis_cuda_model_destroy.restype = None
         lib.ullis_cuda_model_destroy.argtypes = [C.c_void_p]
+        lib.ullis_cuda_generate_state_destroy.restype = None
+        lib.ullis_cuda_generate_state_destroy.argtypes = [C.c_void_p]
+        lib.ullis_cuda_generate_state_time.restype = C.c_size_t
+        lib.ullis_cuda_generate_state_time.argtypes = [C.c_void_p]
         _LIB = lib
     return _LIB
 
@@ -394,6 +400,14 @@ class CudaHeron:
         self.rt._check(self._lib.ullis_cuda_model_hidden(self._h, _ptr(t), _z(batch), _z(time), _ptr(out)))
         return out
 
+    def generate_state(self, batch: int = 1) -> "CudaGenerateState":
+        """UllisHeron::generate_state (src/model.rs:2691-2715) for `batch` independent sequences."""
+        return CudaGenerateState(self, batch)
+
+    def generate_step(self, state: "CudaGenerateState", tokens) -> np.ndarray:
+        """UllisHeron::generate_step (src/model.rs:2717-2753): logits [batch, vocab] of the new tokens."""
+        return state.step(tokens)
+
     def set_taps(self, enabled: bool):
         self.rt._check(self._lib.ullis_cuda_model_set_taps(self._h, C.c_int32(1 if enabled else 0)))
 
@@ -412,3 +426,39 @@ class CudaHeron:
         ms = (C.c_float * 6)()
         self.rt._check(self._lib.ullis_cuda_model_phase_ms(self._h, ms))
         return {name: float(ms[i]) for i, name in enumerate(PHASES)}
+
+
+class CudaGenerateState:
+    """HeronGenerateState (src/model.rs:2433-2454) on the device: one automaton per
+    (sequence, layer, channel) and the time-shift inputs; borrowed model."""
+
+    def __init__(self, model: CudaHeron, batch: int = 1):
+        self.model, self.batch = model, int(batch)
+        self._lib = model._lib
+        h = C.c_void_p()
+        model.rt._check(self._lib.ullis_cuda_generate_state_create(model._h, _z(batch), C.byref(h)))
+        self._h = h
+
+    @property
+    def time(self) -> int:
+        return int(self._lib.ullis_cuda_generate_state_time(self._h))
+
+    def reset(self) -> None:
+        self.model.rt._check(self._lib.ullis_cuda_generate_state_reset(self._h))
+
+    def step(self, tokens) -> np.ndarray:
+        t = _arr(np.atleast_1d(tokens), np.uint32, "tokens", self.batch)
+        out = np.empty((self.batch, self.model.vocab_size), np.float32)
+        self.model.rt._check(self._lib.ullis_cuda_generate_step(self._h, _ptr(t), _ptr(out)))
+        return out
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.ullis_cuda_generate_state_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass
