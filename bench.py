@@ -55,8 +55,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-run", action="store_true",
                     help="short run for a profiler: warm-up count as given, no end-to-end leg, no CPU baseline")
-    ap.add_argument("--workload", choices=["heron", "rosa", "linear"], default="heron",
-                    help="heron = the benchmark; rosa / linear = single-op loops for profiling")
+    ap.add_argument("--workload", choices=["heron", "rosa", "linear", "generate"], default="heron",
+                    help="heron = the benchmark; rosa / linear = single-op loops; generate = incremental decoding")
     ap.add_argument("--rosa-variant", choices=["iid", "periodic"], default="iid")
     ap.add_argument("--channels", type=int, default=512)
     ap.add_argument("--linear-shape", default="2048x512x512", help="MxKxN of the packed linear loop")
@@ -392,6 +392,48 @@ def run_op_loop(args, rt, stream, torch):
         rt.kernel_timing(False)
         return dt, per_kernel
 
+    if args.workload == "generate":
+        # incremental decoding: `steps` tokens for each of `batch` sequences, logits back on the host every step
+        from ullis_b200 import cuda
+        d, layers, vocab, ctx, ffn = synth.CONFIGS[args.model]
+        B = args.batch
+        data = synth.heron_checkpoint(args.model, batch_size=max(B, 1))
+        model = cuda.CudaHeron(rt, data)
+        state = model.generate_state(B)
+        n_tok = min(args.steps, ctx - args.warmup)
+        tokens = sequence_tokens(vocab, 0, B, ctx).reshape(B, ctx)
+        for t in range(args.warmup):
+            model.generate_step(state, tokens[:, t])
+        rt.kernel_timing(True)
+        t0 = time.perf_counter()
+        for t in range(args.warmup, args.warmup + n_tok):
+            model.generate_step(state, tokens[:, t])
+        dt = (time.perf_counter() - t0) / n_tok
+        per_kernel = {k: round(v[0] / n_tok, 4) for k, v in rt.kernel_times().items() if not k.startswith("(")}
+        launches = sum(v[1] for k, v in rt.kernel_times().items() if not k.startswith("(")) / n_tok
+        rt.kernel_timing(False)
+        line = {"workload": "generate", "model": args.model, "batch": B, "steps": n_tok,
+                "context_position": args.warmup + n_tok, "ms_per_step_host_timed": dt * 1e3,
+                "tokens_per_s": B / dt, "device_ms_per_step": sum(per_kernel.values()),
+                "launches_per_step": launches, "kernels_ms": per_kernel}
+        if not args.no_cpu_baseline:
+            # the oracle's generate_step (one sequence, the same first tokens) on the host
+            from oracle import oracle as O
+            O.set_threads(O.max_threads())
+            ref = O.HeronOracle(data)
+            ref_state = ref.generate_state()
+            n_ref = min(32, ctx)
+            t0 = time.perf_counter()
+            for t in range(n_ref):
+                ref.generate_step(ref_state, int(tokens[0, t]))
+            ref_dt = (time.perf_counter() - t0) / n_ref
+            line["cpu_baseline"] = {"value": 1.0 / ref_dt, "unit": "tokens/s", "cores": O.max_threads(), "kind": "port",
+                                    "sample": f"oracle generate_step, 1 sequence, first {n_ref} tokens"}
+        print(json.dumps(line))
+        state.close()
+        model.close()
+        rt.close()
+        return
     if args.workload == "rosa":
         B, T, C = args.batch, args.time or 8192, args.channels
         gen = synth.rosa_bits_iid if args.rosa_variant == "iid" else synth.rosa_bits_periodic

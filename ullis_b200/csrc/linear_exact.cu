@@ -97,12 +97,71 @@ linear_exact_kernel(const float* __restrict__ x, const uint32_t* __restrict__ bi
     }
 }
 
+// Few rows (incremental generation): one thread per output, the row of x in
+// shared memory, the same i-ascending f32 sum as above.  A thread's 32 weight
+// bits come with one load; every lane reads the same x[i] (broadcast).
+template <bool PACKED>
+__global__ void __launch_bounds__(128)
+rowvec_exact_kernel(const float* __restrict__ x, const uint32_t* __restrict__ bits,
+                    const uint16_t* __restrict__ wdense, const uint16_t* __restrict__ scale,
+                    const uint16_t* __restrict__ bias, float* __restrict__ y, size_t K, size_t N, int accumulate) {
+    extern __shared__ float xrow[];
+    const size_t r = blockIdx.y, o = (size_t)blockIdx.x * 128 + threadIdx.x;
+    for (size_t i = threadIdx.x; i < K; i += 128) xrow[i] = x[r * K + i];
+    __syncthreads();
+    if (o >= N) return;
+    float sum = 0.0f;
+    if (PACKED) {
+        if (K % 32 == 0) {
+            const uint32_t* wrow = bits + (o * K >> 5);
+            for (size_t i0 = 0; i0 < K; i0 += 32) {
+                const uint32_t w = wrow[i0 >> 5];
+#pragma unroll
+                for (int b = 0; b < 32; ++b) sum = __fmaf_rn((w >> b) & 1u ? 1.0f : -1.0f, xrow[i0 + b], sum);
+            }
+        } else {
+            for (size_t i = 0; i < K; ++i) {
+                const size_t index = o * K + i;
+                sum = __fmaf_rn((bits[index >> 5] >> (index & 31)) & 1u ? 1.0f : -1.0f, xrow[i], sum);
+            }
+        }
+        const float bv = bias ? h2f(bias[o]) : 0.0f;
+        sum = __fadd_rn(bv, __fmul_rn(h2f(scale[o]), sum));
+    } else {
+        const uint16_t* wrow = wdense + o * K;
+        if (K % 8 == 0) {
+            for (size_t i0 = 0; i0 < K; i0 += 8) {
+                const uint4 w8 = *reinterpret_cast<const uint4*>(wrow + i0);
+                const uint32_t w[4] = {w8.x, w8.y, w8.z, w8.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const uint16_t hb = (uint16_t)(e & 1 ? w[e >> 1] >> 16 : w[e >> 1] & 0xFFFFu);
+                    sum = __fadd_rn(sum, __fmul_rn(h2f(hb), xrow[i0 + e]));
+                }
+            }
+        } else {
+            for (size_t i = 0; i < K; ++i) sum = __fadd_rn(sum, __fmul_rn(h2f(wrow[i]), xrow[i]));
+        }
+    }
+    float* dst = y + r * N + o;
+    *dst = accumulate ? __fadd_rn(*dst, sum) : sum;
+}
+
+constexpr size_t ROWVEC_MAX_ROWS = 128, ROWVEC_MAX_K = 12288;   // x row within the default 48 KiB of shared memory
+
 }  // namespace
 
 void binary_linear_exact(ullis_cuda_runtime* rt, const float* x, const uint32_t* bits, const uint16_t* scale,
                          const uint16_t* bias, float* y, size_t rows, size_t in_features, size_t out_features,
                          bool accumulate) {
     if (rows == 0 || out_features == 0) return;
+    if (rows <= ROWVEC_MAX_ROWS && in_features <= ROWVEC_MAX_K) {
+        dim3 g((unsigned)((out_features + 127) / 128), (unsigned)rows);
+        rowvec_exact_kernel<true><<<g, 128, in_features * 4, rt->stream>>>(x, bits, nullptr, scale, bias, y, in_features,
+                                                                          out_features, accumulate ? 1 : 0);
+        rt->launched("binary_rowvec_exact");
+        return;
+    }
     dim3 grid((unsigned)((out_features + TN - 1) / TN), (unsigned)((rows + TM - 1) / TM));
     linear_exact_kernel<true><<<grid, 256, 0, rt->stream>>>(x, bits, nullptr, scale, bias, y, rows, in_features,
                                                            out_features, accumulate ? 1 : 0);
@@ -112,6 +171,13 @@ void binary_linear_exact(ullis_cuda_runtime* rt, const float* x, const uint32_t*
 void fp16_linear_exact(ullis_cuda_runtime* rt, const float* x, const uint16_t* w, float* y, size_t rows,
                        size_t in_features, size_t out_features, bool accumulate) {
     if (rows == 0 || out_features == 0) return;
+    if (rows <= ROWVEC_MAX_ROWS && in_features <= ROWVEC_MAX_K) {
+        dim3 g((unsigned)((out_features + 127) / 128), (unsigned)rows);
+        rowvec_exact_kernel<false><<<g, 128, in_features * 4, rt->stream>>>(x, nullptr, w, nullptr, nullptr, y, in_features,
+                                                                           out_features, accumulate ? 1 : 0);
+        rt->launched("fp16_rowvec_exact");
+        return;
+    }
     dim3 grid((unsigned)((out_features + TN - 1) / TN), (unsigned)((rows + TM - 1) / TM));
     linear_exact_kernel<false><<<grid, 256, 0, rt->stream>>>(x, nullptr, w, nullptr, nullptr, y, rows, in_features,
                                                             out_features, accumulate ? 1 : 0);
