@@ -146,6 +146,10 @@ size_t ullis_cuda_runtime::kernel_names(char* buf, size_t len) {
 void ullis_cuda_runtime::check_status() {
     d2h(host_status, dev_status, 16);
     sync();
+    throw_on_status();
+}
+
+void ullis_cuda_runtime::throw_on_status() {
     const uint32_t code = host_status[0];
     if (code == ULLIS_DEV_OK) return;
     if (code == ULLIS_DEV_BAD_TOKEN)

@@ -128,5 +128,7 @@ struct ullis_cuda_runtime {
     void clear_status() { zero(dev_status, 16); }
     // Synchronises and throws when a kernel reported a problem.
     void check_status();
+    // Throws when host_status (already copied back and synchronised) holds a kernel's report.
+    void throw_on_status();
     void launched(const char* what);  // counts a launch and checks the launch error
 };

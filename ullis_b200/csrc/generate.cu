@@ -10,11 +10,17 @@
 // use the reference's eager schedule, statement for statement (push stamps the
 // whole suffix-link chain), because the O(T log T) form needs the whole
 // sequence in advance.
+//
+// Nothing in a step depends on the host except the tokens, so after the first
+// use the ~150 small launches of a step are replayed as one CUDA graph (two
+// graphs: before and after the first token, which has no time-shift history).
 #include "generate.hpp"
 
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 #include <string>
 
 #include "kernels.hpp"
@@ -106,7 +112,21 @@ ullis_cuda_generate_state::ullis_cuda_generate_state(ullis_cuda_model* m, size_t
     walkers.ensure(streams * sizeof(sam::WalkerState));
     vhist.ensure(streams * wps * 4);
     prev.ensure(m->layers * 2 * per_layer * 4);
+    ids.ensure(batch * 4);
+    for (ullis::DeviceBuffer* buf : {&x, &a, &bq, &bk, &bv}) buf->ensure(per_layer * 4);
+    wide.ensure(batch * std::max(m->ffn, 3 * m->d) * 4);
+    logits.ensure(batch * m->vocab * 4);
+    ULLIS_CUDA_CHECK(cudaMallocHost(&h_tokens, batch * 4));
+    ULLIS_CUDA_CHECK(cudaMallocHost(&h_logits, batch * m->vocab * 4));
+    use_graph = !getenv("ULLIS_CUDA_NO_GRAPH");
     reset();
+}
+
+ullis_cuda_generate_state::~ullis_cuda_generate_state() {
+    for (cudaGraphExec_t g : graph)
+        if (g) cudaGraphExecDestroy(g);
+    if (h_tokens) cudaFreeHost(h_tokens);
+    if (h_logits) cudaFreeHost(h_logits);
 }
 
 void ullis_cuda_generate_state::reset() {
@@ -132,20 +152,56 @@ void ullis_cuda_generate_state::step(const uint32_t* tokens, float* logits_out) 
         fail(ULLIS_CUDA_ERR_SHAPE, "generate exceeded context_len (" + std::to_string(m->context_len) + ")");
     rt->bind();
     if (rt->kernel_timing) rt->mark("(between steps)");
+    std::memcpy(h_tokens, tokens, batch * 4);
+    const int has_prev = time != 0;
+    if (use_graph && !rt->kernel_timing) {
+        // Replay the step as one graph launch; per-kernel timing needs the plain launches.
+        if (!graph[has_prev]) {
+            cudaGraph_t captured = nullptr;
+            const uint64_t before = rt->launches;
+            ULLIS_CUDA_CHECK(cudaStreamBeginCapture(rt->stream, cudaStreamCaptureModeThreadLocal));
+            try {
+                enqueue(has_prev);
+            } catch (...) {
+                cudaStreamEndCapture(rt->stream, &captured);
+                if (captured) cudaGraphDestroy(captured);
+                rt->launches = before;
+                throw;
+            }
+            ULLIS_CUDA_CHECK(cudaStreamEndCapture(rt->stream, &captured));
+            graph_launches = rt->launches - before;
+            rt->launches = before;   // counted per replay below
+            const cudaError_t e = cudaGraphInstantiate(&graph[has_prev], captured, 0);
+            cudaGraphDestroy(captured);
+            ULLIS_CUDA_CHECK(e);
+        }
+        ULLIS_CUDA_CHECK(cudaGraphLaunch(graph[has_prev], rt->stream));
+        rt->launches += graph_launches;
+    } else {
+        enqueue(has_prev);
+    }
+    rt->sync();
+    rt->throw_on_status();
+    std::memcpy(logits_out, h_logits, batch * m->vocab * 4);
+    time += 1;
+}
+
+void ullis_cuda_generate_state::enqueue(int has_prev) {
+    ullis_cuda_model* m = model;
+    ullis_cuda_runtime* rt = m->rt;
     const size_t d = m->d, ffn = m->ffn, rows = batch, n = rows * d;
     const uint32_t T = (uint32_t)m->context_len;
-    uint32_t* ids = m->ids.as<uint32_t>(rows);
-    float* X = m->x.as<float>(n);
-    float* A = m->a.as<float>(n);
-    float* Bq = m->b.as<float>(n);
-    float* Bk = m->c.as<float>(n);
-    float* Bv = m->dd.as<float>(n);
-    float* W = m->wide.as<float>(rows * std::max(ffn, 3 * d));
-    float* LG = m->logits.as<float>(rows * m->vocab);
+    uint32_t* IDS = static_cast<uint32_t*>(ids.get());
+    float* X = static_cast<float*>(x.get());
+    float* A = static_cast<float*>(a.get());
+    float* Bq = static_cast<float*>(bq.get());
+    float* Bk = static_cast<float*>(bk.get());
+    float* Bv = static_cast<float*>(bv.get());
+    float* W = static_cast<float*>(wide.get());
+    float* LG = static_cast<float*>(logits.get());
     rt->clear_status();
-    rt->h2d(ids, tokens, rows * 4);
-    k::embed(rt, ids, m->embedding, X, rows, d, m->vocab);
-    const int has_prev = time != 0;
+    rt->h2d(IDS, h_tokens, rows * 4);
+    k::embed(rt, IDS, m->embedding, X, rows, d, m->vocab);
     for (size_t l = 0; l < m->layers; ++l) {
         const LayerWeights& L = m->blocks[l];
         float* rosa_prev = static_cast<float*>(prev.get()) + (l * 2) * n;
@@ -188,7 +244,6 @@ void ullis_cuda_generate_state::step(const uint32_t* tokens, float* logits_out) 
     // src/model.rs:2750-2752
     k::layer_norm(rt, X, m->ln_out.weight, m->ln_out.bias, A, rows, d, true);
     k::binary_linear_exact(rt, A, m->head.bits, m->head.scale, m->head.bias, LG, rows, d, m->vocab, false);
-    rt->d2h(logits_out, LG, rows * m->vocab * 4);
-    rt->check_status();  // synchronises
-    time += 1;
+    rt->d2h(h_logits, LG, rows * m->vocab * 4);
+    rt->d2h(rt->host_status, rt->dev_status, 16);
 }

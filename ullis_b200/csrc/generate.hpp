@@ -12,9 +12,21 @@ struct ullis_cuda_generate_state {
     size_t stride = 0, wps = 0;  // bytes of one automaton block, v-history words per stream
     size_t streams = 0;          // layers * batch * d_model
     ullis::DeviceBuffer blocks, walkers, vhist, prev;
+    // activations of one step (owned here, so that a captured graph's pointers stay valid)
+    ullis::DeviceBuffer ids, x, a, bq, bk, bv, wide, logits;
+    uint32_t* h_tokens = nullptr;   // pinned staging of the step's inputs / outputs
+    float* h_logits = nullptr;
+    // The step as a CUDA graph: [0] before the first token (no time-shift history), [1] afterwards.
+    bool use_graph = true;
+    cudaGraphExec_t graph[2] = {nullptr, nullptr};
+    uint64_t graph_launches = 0;    // kernels inside one replay
 
     ullis_cuda_generate_state(ullis_cuda_model* m, size_t batch);
+    ~ullis_cuda_generate_state();
+    ullis_cuda_generate_state(const ullis_cuda_generate_state&) = delete;
+    ullis_cuda_generate_state& operator=(const ullis_cuda_generate_state&) = delete;
     void reset();
+    void enqueue(int has_prev);   // copies in, every kernel of one step, copies out; no synchronisation
     // tokens [batch] (host) -> logits [batch, vocab] (host); advances time by one
     void step(const uint32_t* tokens, float* logits);
 };
