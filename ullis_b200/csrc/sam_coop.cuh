@@ -36,14 +36,13 @@ constexpr int COOP_THREADS = 128;
 #endif
 
 struct CoopLayout {
-    uint32_t ev, kid, parent, clone_bits, vbits, round_rank, wide, ctrl, total;
+    uint32_t ev, kid, clone_bits, vbits, round_rank, wide, ctrl, total;
     __host__ __device__ explicit CoopLayout(uint32_t T) {
         const uint32_t cap = node_capacity(T), wps = (T + 31) / 32;
         uint32_t off = 0;
         const uint32_t ev_bytes = cap * 2 * 4, tree_bytes = tree_entries(T) * 4;
         ev = off;         off += ev_bytes > tree_bytes ? ev_bytes : tree_bytes;   // events, later the max tree
         kid = off;        off += (cap * 4 + 15) & ~15u;                          // child pairs, later {lo,hi}
-        parent = off;     off += (cap * 2 + 15) & ~15u;
         clone_bits = off; off += (((cap + 31) / 32) * 4 + 15) & ~15u;
         vbits = off;      off += (wps * 4 + 15) & ~15u;
         round_rank = off; off += COOP_THREADS * 4;                                // ranks of the steps of one pass-2 round
@@ -99,7 +98,6 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     const CoopLayout L(T);
     uint32_t* ev = reinterpret_cast<uint32_t*>(smem + L.ev);
     uint32_t* kid = reinterpret_cast<uint32_t*>(smem + L.kid);
-    uint16_t* parent = reinterpret_cast<uint16_t*>(smem + L.parent);
     uint32_t* cbits = reinterpret_cast<uint32_t*>(smem + L.clone_bits);
     uint32_t* vbits = reinterpret_cast<uint32_t*>(smem + L.vbits);
     uint32_t* round_rank = reinterpret_cast<uint32_t*>(smem + L.round_rank);
@@ -121,6 +119,11 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     }
     for (uint32_t w = tid; w < (n + 31) / 32; w += COOP_THREADS) cbits[w] = B.clone_bits[w];
     for (uint32_t w = tid; w < wps; w += COOP_THREADS) vbits[w] = vw[w];
+    // the query states and new-state ids are needed much later: ask for them now, 128 bytes per thread
+    for (uint32_t i = tid * 64u; i < T; i += COOP_THREADS * 64u) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(B.vq + i));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(B.jid + i));
+    }
     uint32_t* replay_end = reinterpret_cast<uint32_t*>(smem + L.ctrl);
     if (tid == 0) *replay_end = 0;
     __syncthreads();
@@ -136,7 +139,6 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const uint32_t v = v0 + COOP_THREADS * u;
-            if (v < n) parent[v] = (uint16_t)p[u];
             if (v < n && v != 0) {
                 atomicMin(&kid_min[p[u]], v);
                 atomicMax(&kid_max[p[u]], v);
@@ -153,37 +155,33 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
 
     ULLIS_COOP_MARK(1);
     // ---- Euler tour as a list: event 2v = enter v, 2v+1 = leave v; word = successor | weight << 16
-    for (uint32_t v = tid; v < n; v += COOP_THREADS) {
-        const uint32_t k = kid[v], a = k & 0xFFFFu;
-        const uint32_t stamped = (v != 0 && !((cbits[v >> 5] >> (v & 31)) & 1u)) ? 1u : 0u;
-        const uint32_t first = a != NIL ? 2 * a : 2 * v + 1;
-        ev[2 * v] = first | (stamped << 16) | (is_splitter(first, blocks) ? LAST_OF_SUBLIST : 0u);
-        uint32_t succ = END;
-        if (v != 0) {
-            const uint32_t p = parent[v], kp = kid[p];
-            succ = ((kp & 0xFFFFu) == v && (kp >> 16) != NIL) ? 2 * (kp >> 16) : 2 * p + 1;
+    // (the suffix links come from global memory again, eight loads at a time: keeping
+    // them in shared memory would cost the fourth resident CTA per SM)
+    for (uint32_t v0 = tid; v0 < n; v0 += COOP_THREADS * 8) {
+        uint32_t par[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t v = v0 + COOP_THREADS * u;
+            par[u] = v < n ? link_words[2 * v] & 0xFFFFu : NIL;
         }
-        ev[2 * v + 1] = succ | (succ == END || is_splitter(succ, blocks) ? LAST_OF_SUBLIST : 0u);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t v = v0 + COOP_THREADS * u;
+            if (v >= n) continue;
+            const uint32_t k = kid[v], a = k & 0xFFFFu;
+            const uint32_t stamped = (v != 0 && !((cbits[v >> 5] >> (v & 31)) & 1u)) ? 1u : 0u;
+            const uint32_t first = a != NIL ? 2 * a : 2 * v + 1;
+            ev[2 * v] = first | (stamped << 16) | (is_splitter(first, blocks) ? LAST_OF_SUBLIST : 0u);
+            uint32_t succ = END;
+            if (v != 0) {
+                const uint32_t p = par[u], kp = kid[p];
+                succ = ((kp & 0xFFFFu) == v && (kp >> 16) != NIL) ? 2 * (kp >> 16) : 2 * p + 1;
+            }
+            ev[2 * v + 1] = succ | (succ == END || is_splitter(succ, blocks) ? LAST_OF_SUBLIST : 0u);
+        }
     }
     __syncthreads();
     ULLIS_COOP_MARK(2);
-    // the suffix links are dead: their space takes the query states and the new states of every step
-    uint16_t* vq_s = parent;
-    uint16_t* jid_s = parent + T;
-    for (uint32_t i0 = tid; i0 < T; i0 += COOP_THREADS * 8) {
-        uint16_t a[8], b[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const uint32_t i = i0 + COOP_THREADS * u;
-            a[u] = i < T ? B.vq[i] : (uint16_t)0;
-            b[u] = i < T ? B.jid[i] : (uint16_t)0;
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const uint32_t i = i0 + COOP_THREADS * u;
-            if (i < T) { vq_s[i] = a[u]; jid_s[i] = b[u]; }
-        }
-    }
     // List ranking in two levels.  One event in eight is a splitter.  Level 1: the
     // thread that owns a splitter walks its sublist up to the next splitter and
     // leaves in every element (weight of the sublist before it, its splitter);
@@ -273,6 +271,24 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
         lh[v] = lo | (hi << 16);
     }
     __syncthreads();
+    // The events are dead.  The front of their space becomes the max tree, the part
+    // behind it takes the query states and the new states of every step.
+    uint16_t* vq_s = reinterpret_cast<uint16_t*>(ev + ((tree_entries(T) + 3u) & ~3u));
+    uint16_t* jid_s = vq_s + T;
+    for (uint32_t i0 = tid; i0 < T; i0 += COOP_THREADS * 8) {
+        uint16_t a[8], b[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t i = i0 + COOP_THREADS * u;
+            a[u] = i < T ? B.vq[i] : (uint16_t)0;
+            b[u] = i < T ? B.jid[i] : (uint16_t)0;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t i = i0 + COOP_THREADS * u;
+            if (i < T) { vq_s[i] = a[u]; jid_s[i] = b[u]; }
+        }
+    }
 
     // ---- pass 2.  Every stamped state is stamped exactly once, by the step that
     // creates it, so level 0 of the max tree is a fixed array: stamp[rank of j_i]
