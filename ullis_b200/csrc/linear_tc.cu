@@ -203,18 +203,30 @@ sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, 
             const float* xr = x + row * C;
             const uint32_t* wbits = W.bits + (c * C >> 5);  // C % 32 == 0 on this path
             float sum = 0.0f;
-            for (size_t i4 = 0; i4 < C; i4 += 4) {
-                const float4 cur = *reinterpret_cast<const float4*>(xr + i4);
-                float4 prev = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (t != 0) prev = *reinterpret_cast<const float4*>(xr - C + i4);
-                const float xs[4] = {cur.x, cur.y, cur.z, cur.w}, ps[4] = {prev.x, prev.y, prev.z, prev.w};
-                const uint32_t wword = wbits[i4 >> 5] >> (i4 & 31);
+            // 32 inputs per round: the sixteen row loads go out together, then the sum is taken in order
+            for (size_t i0 = 0; i0 < C; i0 += 32) {
+                float4 cur[8], prev[8];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float xt = xs[k];
-                    const float xx = t == 0 ? -xt : __fsub_rn(ps[k], xt);
-                    const float in = __fadd_rn(xt, __fmul_rn(xx, h2f(mix[i4 + k])));
-                    sum = __fmaf_rn((wword >> k) & 1u ? 1.0f : -1.0f, in, sum);
+                for (int u = 0; u < 8; ++u) {
+                    cur[u] = *reinterpret_cast<const float4*>(xr + i0 + 4 * u);
+                    prev[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (t != 0) prev[u] = *reinterpret_cast<const float4*>(xr - C + i0 + 4 * u);
+                }
+                const uint32_t wword = wbits[i0 >> 5];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const float xs[4] = {cur[u].x, cur[u].y, cur[u].z, cur[u].w};
+                    const float ps[4] = {prev[u].x, prev[u].y, prev[u].z, prev[u].w};
+                    const uint2 mw = *reinterpret_cast<const uint2*>(mix + i0 + 4 * u);
+                    const uint16_t mb[4] = {(uint16_t)(mw.x & 0xFFFFu), (uint16_t)(mw.x >> 16), (uint16_t)(mw.y & 0xFFFFu),
+                                            (uint16_t)(mw.y >> 16)};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float xt = xs[k];
+                        const float xx = t == 0 ? -xt : __fsub_rn(ps[k], xt);
+                        const float in = __fadd_rn(xt, __fmul_rn(xx, h2f(mb[k])));
+                        sum = __fmaf_rn((wword >> (4 * u + k)) & 1u ? 1.0f : -1.0f, in, sum);
+                    }
                 }
             }
             const float y = __fadd_rn(W.bias ? h2f(W.bias[c]) : 0.0f, __fmul_rn(h2f(W.scale[c]), sum));
