@@ -296,6 +296,10 @@ bool usable(ullis_cuda_runtime* rt) {
             ULLIS_SET_SMEM_WS(EPI_SIGNBITS);
             ULLIS_SET_SMEM_WS(EPI_CE);
 #undef ULLIS_SET_SMEM_WS
+            ULLIS_CUDA_CHECK(cudaFuncSetAttribute(gemm_ws_kernel<EPI_STORE, false>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM_LIMIT));
+            ULLIS_CUDA_CHECK(cudaFuncSetAttribute(gemm_ws_kernel<EPI_RESIDUAL, false>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM_LIMIT));
             rt->tc_ws_kernel = !getenv("ULLIS_CUDA_NO_WS");
             ULLIS_CUDA_CHECK(cudaFuncSetAttribute(sign_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   FIX_QUEUE * 4));
@@ -328,6 +332,22 @@ void launch(ullis_cuda_runtime* rt, const GemmMaps& maps, const GemmParams& p, u
             if (members < 1) members = 1;
             if (members > m_tiles) members = m_tiles;
             gemm_ws_kernel<EPI><<<pairs * members, WS_THREADS, shape.smem, rt->stream>>>(maps, q, pairs);
+            rt->launched(what);
+            return;
+        }
+    }
+    if constexpr (!PACKED && (EPI == EPI_STORE || EPI == EPI_RESIDUAL)) {
+        // dense weights: the persistent kernel with the weight tile in the ring (large M only: a CTA needs
+        // several row tiles to amortise its set-up)
+        const uint32_t m_tiles = (p.M + BM - 1) / BM, pairs = n_prob * ((p.N + BN - 1) / BN);
+        if (rt->tc_ws_kernel && m_tiles * pairs >= 4u * (uint32_t)rt->sm_count) {
+            const WsShape shape = ws_shape(p.K, p.n_a, true, false);
+            GemmParams q = p;
+            q.stages = shape.stages;
+            uint32_t members = (uint32_t)rt->sm_count / pairs;
+            if (members < 1) members = 1;
+            if (members > m_tiles) members = m_tiles;
+            gemm_ws_kernel<EPI, false><<<pairs * members, WS_THREADS, shape.smem, rt->stream>>>(maps, q, pairs);
             rt->launched(what);
             return;
         }

@@ -33,10 +33,11 @@ struct WsShape {
 };
 
 // ring depth that fits beside the resident weight tile
-inline WsShape ws_shape(uint32_t K, uint32_t n_a, bool staged_stores) {
+inline WsShape ws_shape(uint32_t K, uint32_t n_a, bool staged_stores, bool resident_w = true) {
     const uint32_t kb = K / BK;
-    const uint32_t fixed = 1024 /*alignment slack*/ + kb * TILE_BYTES + 2 * BN * 4 + 256 +
+    const uint32_t fixed = 1024 /*alignment slack*/ + (resident_w ? kb * TILE_BYTES : 0) + 2 * BN * 4 + 256 +
                            (staged_stores ? 8 * STAGE_BYTES : 0);
+    if (!resident_w) n_a += 1;   // the weight tile travels with the activations
     uint32_t stages = (WS_SMEM_LIMIT - fixed) / (n_a * TILE_BYTES);
     if (stages > WS_MAX_STAGES) stages = WS_MAX_STAGES;
     return WsShape{stages, fixed + stages * n_a * TILE_BYTES};
@@ -54,16 +55,19 @@ __device__ __forceinline__ bool ws_wait(uint64_t* bar, uint32_t parity, volatile
     return false;
 }
 
-template <int EPI>
+// RESIDENT_W = false: dense 16-bit weights of any K, fetched by TMA into the same
+// ring stage as the activations (nothing stays resident); same roles, same
+// double-buffered accumulator.
+template <int EPI, bool RESIDENT_W = true>
 __global__ void __launch_bounds__(WS_THREADS, 1)
 gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const uint32_t pairs) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t KB = p.K / BK;
     const uint32_t STAGES = p.stages;
-    const uint32_t stage_bytes = p.n_a * TILE_BYTES;
+    const uint32_t stage_bytes = (p.n_a + (RESIDENT_W ? 0u : 1u)) * TILE_BYTES;
     uint8_t* w_tiles = smem;                               // [KB] resident weight tiles
-    uint8_t* a_ring = smem + KB * TILE_BYTES;              // [STAGES] activation stages
+    uint8_t* a_ring = smem + (RESIDENT_W ? KB * TILE_BYTES : 0u);   // [STAGES] activation (+ weight) stages
     uint4* lut = reinterpret_cast<uint4*>(a_ring);         // only until the weights are expanded
     float* s_scale = reinterpret_cast<float*>(a_ring + STAGES * stage_bytes);
     float* s_bias = s_scale + BN;
@@ -100,9 +104,10 @@ gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const 
         ptx::fence_mbar_init();
         ptx::tma_prefetch_desc(&maps.a[z][0]);
         if (p.n_a == 2) ptx::tma_prefetch_desc(&maps.a[z][1]);
+        if (!RESIDENT_W) ptx::tma_prefetch_desc(&maps.b[z]);
     }
     // 8 weight bits -> 8 FP16 values (+1.0 = 0x3C00, -1.0 = 0xBC00), bit i -> element i
-    for (int b = threadIdx.x; b < 256; b += WS_THREADS) {
+    for (int b = threadIdx.x; RESIDENT_W && b < 256; b += WS_THREADS) {
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -122,7 +127,7 @@ gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const 
     }
     __syncthreads();
     // expand this CTA's weight tile once: row r of k-block kb -> 128 bytes, 16-byte chunk j at j ^ (r % 8)
-    for (uint32_t item = threadIdx.x; item < KB * BN; item += WS_THREADS) {
+    for (uint32_t item = threadIdx.x; RESIDENT_W && item < KB * BN; item += WS_THREADS) {
         const uint32_t r = item % BN, kb = item / BN;
         const uint32_t n = n0 + r;
         uint32_t w0 = 0, w1 = 0;
@@ -163,6 +168,8 @@ gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const 
                     ptx::tma_load_2d(st, &maps.a[z][0], &full[s], (int32_t)(kb * BK), (int32_t)m0);
                     if (p.n_a == 2)
                         ptx::tma_load_2d(st + TILE_BYTES, &maps.a[z][1], &full[s], (int32_t)(kb * BK), (int32_t)m0);
+                    if (!RESIDENT_W)
+                        ptx::tma_load_2d(st + p.n_a * TILE_BYTES, &maps.b[z], &full[s], (int32_t)(kb * BK), (int32_t)n0);
                 }
             }
             if (!ok) {
@@ -195,7 +202,7 @@ gemm_ws_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const 
                     }
                     ptx::tc_fence_after_sync();
                     const uint32_t a_addr = ptx::smem_u32(a_ring + s * stage_bytes);
-                    const uint32_t b_addr = w_addr + kb * TILE_BYTES;
+                    const uint32_t b_addr = RESIDENT_W ? w_addr + kb * TILE_BYTES : a_addr + p.n_a * TILE_BYTES;
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < BK / 16; ++k4) {
                         const uint64_t db = ptx::smem_desc_sw128(b_addr + k4 * 32);
