@@ -7,7 +7,7 @@ import pytest
 
 from conftest import pack_streams
 
-ALGOS = {"eager": 0, "euler": 1, "euler_with_constant_k_shortcut": 2}
+ALGOS = {"eager": 0, "euler": 1, "euler_with_constant_k_shortcut": 2, "incremental_pushes_lazy_chain": 6}
 
 
 @pytest.mark.parametrize("T", [1, 2, 3, 4, 5])

@@ -9,7 +9,8 @@
 // what the reference's own test asserts (src/model.rs:4991-5004).  The automata
 // use the reference's eager schedule, statement for statement (push stamps the
 // whole suffix-link chain), because the O(T log T) form needs the whole
-// sequence in advance.
+// sequence in advance; a stream whose key bits have all been equal so far is
+// answered in closed form and its chain written only when that ends.
 //
 // Nothing in a step depends on the host except the tokens, so after the first
 // use the ~150 small launches of a step are replayed as one CUDA graph (two
@@ -33,18 +34,17 @@ inline unsigned blocks_for(size_t n, unsigned per) { return (unsigned)((n + per 
 
 __device__ __forceinline__ float h2f(uint16_t b) { return __half2float(__ushort_as_half(b)); }
 
-// empty automaton per stream (src/rosa.rs:66-74: root only, fail[0] = -1, no `last`)
+// empty automaton per stream (src/rosa.rs:66-74)
 template <typename Ix>
 __global__ void gen_init_kernel(uint8_t* __restrict__ blocks, size_t stride, sam::WalkerState* __restrict__ ws,
                                 size_t streams, uint32_t T) {
     const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= streams) return;
-    sam::EagerLayout<Ix> L(T);
-    uint8_t* blk = blocks + s * stride;
-    sam::Walker<Ix> wk;
-    wk.init(reinterpret_cast<sam::Node<Ix>*>(blk + L.nodes));
-    reinterpret_cast<Ix*>(blk + L.last)[0] = 0;
-    sam::save_walker(wk, 0u, &ws[s]);
+    // no pushes yet; the automaton is written lazily (sam::lazy_push), not even the root is needed
+    sam::WalkerState st;
+    st.u = 1; st.g = 0; st.w = 0; st.gmax = 0; st.gfail = 0; st.h = 0; st.steps = 0; st.pad = 0;
+    ws[s] = st;
+    (void)blocks; (void)stride; (void)T;
 }
 
 // time_shift_one + mixes (src/model.rs:214-228, 1331-1340, 1008-1012): xx = prev - x, or -x before the
@@ -75,8 +75,8 @@ gen_push_kernel(uint8_t* __restrict__ blocks, size_t stride, sam::WalkerState* _
     if (s >= streams) return;
     sam::EagerLayout<Ix> L(T);
     uint8_t* blk = blocks + s * stride;
-    sam::Walker<Ix> wk;
-    const uint32_t i = sam::load_walker(wk, reinterpret_cast<sam::Node<Ix>*>(blk + L.nodes), &ws[s]);
+    sam::WalkerState st = ws[s];
+    const uint32_t i = st.steps;
     if (i >= T) {  // the host checks the context length first; never write past the state block
         if (atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_SAM_CAPACITY) == ULLIS_DEV_OK) status[1] = (uint32_t)s;
         return;
@@ -86,8 +86,10 @@ gen_push_kernel(uint8_t* __restrict__ blocks, size_t stride, sam::WalkerState* _
     uint32_t* vh = vhist + s * wps;
     const uint32_t word = (i & 31u) ? vh[i >> 5] : 0u;   // a new word starts empty
     vh[i >> 5] = word | (vb << (i & 31u));
-    const uint32_t idx = sam::eager_step<Ix>(wk, reinterpret_cast<Ix*>(blk + L.last), vh, i, qb, kb, nullptr);
-    sam::save_walker(wk, i + 1u, &ws[s]);
+    // constant key so far: O(1); otherwise RosaSam::push statement for statement
+    const uint32_t idx = sam::lazy_push<Ix>(reinterpret_cast<sam::Node<Ix>*>(blk + L.nodes),
+                                            reinterpret_cast<Ix*>(blk + L.last), vh, &st, qb, kb);
+    ws[s] = st;
     const float ev = h2f(e[s % C]);
     y[s] = idx ? ev : -ev;
 }

@@ -287,6 +287,53 @@ SAM_HD uint32_t load_walker(Walker<Ix>& wk, Node<Ix>* nodes, const WalkerState* 
     return st->steps;
 }
 
+// Incremental pushes with a shortcut for streams whose key bits have all been
+// equal so far.  After t pushes with key c the automaton is a chain: states
+// 0..t, state m = c^m, child(m, c) = m+1, link(m) = m-1, maxlen(m) = m, every
+// `last` = t, and the query state is (w, w) with w = length of the current run
+// of q == c (not counting step 0, whose query finds an empty automaton).  So a
+// push costs O(1) instead of the O(t) chain stamping, and idx = (t >= 1 and
+// q == c) ? v : 0 (the same closed form as run_constant_k).  The chain is
+// written out only when a key bit differs for the first time; from then on the
+// stream takes eager_step.  WalkerState::pad holds the mode: 0 = chain not yet
+// written (w = run length, g = key bit c), 1 = real automaton.
+template <typename Ix>
+SAM_HD uint32_t lazy_push(Node<Ix>* nodes, Ix* last, const uint32_t* vhist, WalkerState* st, uint32_t qb,
+                          uint32_t kb) {
+    constexpr uint32_t NIL = Nil<Ix>::value;
+    const uint32_t t = st->steps;
+    if (st->pad == 0) {
+        const uint32_t c = t == 0 ? kb : st->g;
+        if (kb == c) {
+            const uint32_t run = (t >= 1 && qb == c) ? st->w + 1u : 0u;
+            st->w = run;
+            st->g = c;
+            st->steps = t + 1u;
+            return run ? stream_bit(vhist, t) : 0u;   // last[v] + 1 = t for every state: the current v bit
+        }
+        // first differing key bit: write the chain of t pushes of c, then fall through to a real push
+        for (uint32_t m = 0; m <= t; ++m) {
+            Node<Ix> n;
+            n.t0 = (Ix)((m < t && c == 0) ? m + 1u : NIL);
+            n.t1 = (Ix)((m < t && c == 1) ? m + 1u : NIL);
+            n.fail = (Ix)(m ? m - 1u : NIL);
+            n.maxlen = (Ix)m;
+            nodes[m] = n;
+            last[m] = (Ix)t;   // stored as last + 1; the root too (src/rosa.rs:168-173 walks up to it); 0 pushes: 0 = never
+        }
+        const uint32_t run = st->w;
+        st->u = t + 1u; st->g = t; st->gmax = t; st->gfail = t ? t - 1u : NIL;
+        st->w = run; st->h = (int32_t)run;
+        st->pad = 1;
+    }
+    Walker<Ix> wk;
+    const uint32_t i = load_walker(wk, nodes, st);
+    const uint32_t bit = eager_step<Ix>(wk, last, vhist, i, qb, kb, nullptr);
+    save_walker(wk, i + 1u, st);
+    st->pad = 1;
+    return bit;
+}
+
 // scratch: EagerLayout<Ix>(T).total bytes.  qw/kw/vw: this stream's bits, bit t
 // at word t/32, bit t%32.  out: idx bits in the same layout (whole words are
 // written, tail bits zero).
