@@ -158,10 +158,10 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     // The number of streams left for the automaton is only known on the device;
     // each wave is sized for the worst case and surplus threads exit at once.
     const sam::CoopLayout coop((uint32_t)time);
-    const bool use_coop = algo == ULLIS_CUDA_SAM_EULER && narrow && rt->sam_coop && coop.total <= 110 * 1024 &&
+    const bool use_coop = algo == ULLIS_CUDA_SAM_EULER && narrow && rt->sam_coop && coop.total <= 226 * 1024 &&
                           2 * sam::node_capacity((uint32_t)time) < 0xFFFFu;
     if (use_coop && !rt->sam_coop_ready) {
-        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         rt->sam_coop_ready = true;
     }
     for (size_t s0 = 0; s0 < streams; s0 += wave) {
