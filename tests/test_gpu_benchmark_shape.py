@@ -1,0 +1,74 @@
+"""The benchmark's own shape (Heron D=512 L=12 T=2048 V=8192, literal weight
+distributions) at sizes the oracle cannot cover whole: one full-depth sequence
+against the oracle, and size-independent properties on a 16-sequence batch -
+sequences are independent, so a batch must give each sequence exactly the row
+losses it gets alone, the mean is sum / count, and a repeated run is
+bit-identical."""
+import numpy as np
+import pytest
+
+from ullis_b200 import cuda, synth
+
+pytestmark = pytest.mark.gpu
+
+D, LAYERS, VOCAB, T, FFN = synth.CONFIGS["default"]
+
+
+@pytest.fixture(scope="module")
+def data():
+    return synth.heron_checkpoint("default", batch_size=16)
+
+
+def test_one_benchmark_sequence_against_the_oracle(cuda_rt, oracle, data):
+    tokens = synth.zipf_tokens(11, T, VOCAB)
+    ref = oracle.HeronOracle(data)
+    taps = {}
+    mean_ref, n_ref, row_ref, _ = ref.forward_ce(tokens, tokens, oracle.CE_NO_IGNORE, 1, T, taps=taps)
+    m = cuda.CudaHeron(cuda_rt, data)
+    m.set_taps(True)
+    mean, loss_sum, n_valid, row_loss = m.forward_ce(tokens, tokens, cuda.CE_NO_IGNORE, 1, T, want_row_loss=True)
+    assert n_valid == n_ref == T - 1
+    assert abs(mean - mean_ref) <= 1e-3                                   # mean CE: 1e-3 absolute
+    mism = total = 0
+    for l in range(LAYERS):
+        got, want = m.tap(l, "block_out", T), taps[f"{l}.block_out"]
+        err = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want.astype(np.float64))
+        assert err <= 1e-2, (l, err)                                       # activations: 1e-2 relative
+        for name in ("q_bits", "k_bits", "v_bits", "idx"):
+            mism += int((m.tap(l, name, T) != taps[f"{l}.{name}"]).sum())
+            total += T * D
+    assert mism / total <= 2e-3, f"ROSA bit mismatch rate {mism / total:.2e}"
+    m.close()
+    # validation mode: every ROSA bit and idx of every layer bit-exact, hidden bit-identical
+    cuda_rt.set_mode(cuda.MODE_EXACT)
+    try:
+        m = cuda.CudaHeron(cuda_rt, data)
+        m.set_taps(True)
+        mean_x, _, n_x = m.forward_ce(tokens, tokens, cuda.CE_NO_IGNORE, 1, T)
+        for l in range(LAYERS):
+            for name in ("q_bits", "k_bits", "v_bits", "idx"):
+                assert np.array_equal(m.tap(l, name, T), taps[f"{l}.{name}"]), (l, name)
+        assert np.array_equal(m.tap(0, "hidden", T), taps["hidden"])
+        assert n_x == n_ref and abs(mean_x - mean_ref) <= 1e-3
+        m.close()
+    finally:
+        cuda_rt.set_mode(cuda.MODE_FAST)
+
+
+def test_batch_gives_every_sequence_the_losses_it_gets_alone(cuda_rt, data):
+    B = 16
+    tokens = np.concatenate([synth.zipf_tokens(11 + b, T, VOCAB) for b in range(B)])
+    labels = tokens.copy()
+    labels[5 * T + 7] = 0          # one ignored target in sequence 5
+    m = cuda.CudaHeron(cuda_rt, data)
+    mean, loss_sum, n_valid, row_loss = m.forward_ce(tokens, labels, 0, B, T, want_row_loss=True)
+    pad_targets = int((labels.reshape(B, T)[:, 1:] == 0).sum())
+    assert n_valid == B * (T - 1) - pad_targets
+    assert abs(loss_sum - float(row_loss.astype(np.float64).sum())) <= 1e-6 * loss_sum
+    assert abs(mean - loss_sum / n_valid) <= 1e-6
+    again = m.forward_ce(tokens, labels, 0, B, T, want_row_loss=True)
+    assert np.array_equal(again[3], row_loss) and again[1] == loss_sum          # deterministic
+    for b in (0, 5, 15):
+        alone = m.forward_ce(tokens[b * T:(b + 1) * T], labels[b * T:(b + 1) * T], 0, 1, T, want_row_loss=True)
+        assert np.array_equal(alone[3], row_loss[b * T:(b + 1) * T]), b        # same kernels, same tiles per row
+    m.close()

@@ -234,3 +234,23 @@ def test_shape_errors_and_empty_inputs(cuda_rt):
                             np.array([0, 99], np.uint32), cuda.CE_NO_IGNORE, 2, 2, 4, 32)
     assert e.value.code == cuda.ERR_TOKEN
     assert cuda_rt.launch_count > 0 and cuda_rt.stream != 0
+
+
+def test_fp16_operand_range_is_reported_not_turned_into_inf(cuda_rt):
+    """The tensor-core path takes FP16 operands (65504 at most): a larger activation is an error with the
+    row in the message, never an inf in the output; the reference-order mode takes the same input."""
+    rows, K, N = 128, 64, 64
+    x = np.ones((rows, K), np.float32)
+    x[37, 5] = 1.0e5
+    w = f16(0.1 * np.random.default_rng(3).standard_normal(N * K))
+    with pytest.raises(cuda.UllisCudaError) as e:
+        cuda_rt.fp16_linear(x, w, rows, K, N)
+    assert e.value.code == cuda.ERR_DEVICE_CHECK and "FP16 range" in e.value.message and "row 37" in e.value.message
+    cuda_rt.set_mode(cuda.MODE_EXACT)
+    try:
+        y = cuda_rt.fp16_linear(x, w, rows, K, N)
+        assert np.isfinite(y).all()
+    finally:
+        cuda_rt.set_mode(cuda.MODE_FAST)
+    y = cuda_rt.fp16_linear(np.ones((rows, K), np.float32), w, rows, K, N)   # the runtime is usable afterwards
+    assert np.isfinite(y).all()

@@ -154,6 +154,10 @@ void ullis_cuda_runtime::throw_on_status() {
     if (code == ULLIS_DEV_OK) return;
     if (code == ULLIS_DEV_BAD_TOKEN)
         fail(ULLIS_CUDA_ERR_TOKEN, "token id exceeds vocabulary (row " + std::to_string(host_status[1]) + ")");
+    if (code == ULLIS_DEV_FP16_RANGE)
+        fail(ULLIS_CUDA_ERR_DEVICE_CHECK,
+             "an activation exceeds the FP16 range of the tensor-core operands (row " + std::to_string(host_status[1]) +
+                 "); use ULLIS_CUDA_MODE_EXACT for this input");
     if (code == ULLIS_DEV_WAIT_TIMEOUT)
         fail(ULLIS_CUDA_ERR_TIMEOUT, "a kernel gave up waiting (site " + std::to_string(host_status[1]) + ")");
     fail(ULLIS_CUDA_ERR_DEVICE_CHECK, "device-side check failed, code " + std::to_string(code) + " detail " +
@@ -484,9 +488,10 @@ int32_t ullis_cuda_binary_linear(ullis_cuda_runtime* rt, const float* x, const u
         uint16_t* ds = stage(rt, 2, scale, out_features);
         uint16_t* db = bias ? stage(rt, 3, bias, out_features) : nullptr;
         float* dy = rt->pool[4].as<float>(ny);
+        rt->clear_status();
         packed_linear_dev(rt, dx, dbits, ds, db, dy, rows, in_features, out_features);
         rt->d2h(y, dy, ny * 4);
-        rt->sync();
+        rt->check_status();
     });
 }
 
@@ -502,9 +507,10 @@ int32_t ullis_cuda_fp16_linear(ullis_cuda_runtime* rt, const float* x, const uin
         float* dx = stage(rt, 0, x, nx);
         uint16_t* dw = stage(rt, 1, weight, nw);
         float* dy = rt->pool[2].as<float>(ny);
+        rt->clear_status();
         dense_linear_dev(rt, dx, dw, dy, rows, in_features, out_features);
         rt->d2h(y, dy, ny * 4);
-        rt->sync();
+        rt->check_status();
     });
 }
 
@@ -666,12 +672,13 @@ int32_t ullis_cuda_cmix_block_forward(ullis_cuda_runtime* rt, const float* x, co
         float* sh = rt->pool[5].as<float>(n);
         float* key = rt->pool[6].as<float>(nf);
         float* dout = rt->pool[7].as<float>(n);
+        rt->clear_status();
         k::shift_mix(rt, dx, dm, nullptr, nullptr, sh, nullptr, nullptr, rows, time, d_model);
         packed_linear_dev(rt, sh, dkb, dks, nullptr, key, rows, d_model, dim_ffn);
         k::relu2(rt, key, key, nf);
         dense_linear_dev(rt, key, dv, dout, rows, dim_ffn, d_model);
         rt->d2h(out, dout, n * 4);
-        rt->sync();
+        rt->check_status();
     });
 }
 

@@ -75,7 +75,7 @@ void set_global_error(const char* msg);
 // that uses it): 0 = ok, otherwise a kernel-specific code; slots 1..3 hold
 // details (e.g. the offending row / stream).
 enum { ULLIS_DEV_OK = 0, ULLIS_DEV_BAD_TOKEN = 1, ULLIS_DEV_SAM_CAPACITY = 2, ULLIS_DEV_SAM_NOMATCH = 3,
-       ULLIS_DEV_WAIT_TIMEOUT = 4 };
+       ULLIS_DEV_WAIT_TIMEOUT = 4, ULLIS_DEV_FP16_RANGE = 5 };
 
 struct ullis_cuda_runtime {
     int device = 0;

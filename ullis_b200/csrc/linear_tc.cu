@@ -51,21 +51,20 @@ __device__ __forceinline__ float h2f(uint16_t b) { return __half2float(__ushort_
 
 // ------------------------------------------------------------ operand kernels
 // f32 -> f16 / bf16
-__global__ void cast16_kernel(const float* __restrict__ x, uint16_t* __restrict__ y, size_t n, int bf16) {
+// (FP16 ends at 65504: a larger finite input is reported through the status word, not turned into inf)
+__global__ void cast16_kernel(const float* __restrict__ x, uint16_t* __restrict__ y, size_t n, int bf16, size_t K,
+                              uint32_t* __restrict__ status) {
     size_t e = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (e >= n) return;
     float v[4];
     for (int k = 0; k < 4; ++k) v[k] = e + k < n ? x[e + k] : 0.0f;
     for (int k = 0; k < 4; ++k) {
         if (e + k >= n) break;
+        if (!bf16 && fabsf(v[k]) > 65504.0f && fabsf(v[k]) <= 3.4028234e38f &&
+            atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_FP16_RANGE) == ULLIS_DEV_OK)
+            status[1] = (uint32_t)((e + k) / K);
         y[e + k] = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v[k])) : __half_as_ushort(__float2half_rn(v[k]));
     }
-}
-
-// FP16 bits -> bf16 bits (the MMA takes A and B in one 16-bit format)
-__global__ void f16_to_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, size_t n) {
-    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e < n) y[e] = __bfloat16_as_ushort(__float2bfloat16_rn(h2f(x[e])));
 }
 
 // Time-shift mixes of one LayerNorm output (reference src/model.rs:1291-1298:
@@ -369,8 +368,10 @@ GemmParams base_params(ullis_cuda_runtime* rt, size_t M, size_t N, size_t K) {
     return p;
 }
 
-void cast16(ullis_cuda_runtime* rt, const float* x, uint16_t* y, size_t n, bool bf16) {
-    cast16_kernel<<<blocks_for((n + 3) / 4, 256), 256, 0, rt->stream>>>(x, y, n, bf16 ? 1 : 0);
+// x [rows, K] f32 -> 16-bit operand
+void cast16(ullis_cuda_runtime* rt, const float* x, uint16_t* y, size_t rows, size_t K, bool bf16) {
+    const size_t n = rows * K;
+    cast16_kernel<<<blocks_for((n + 3) / 4, 256), 256, 0, rt->stream>>>(x, y, n, bf16 ? 1 : 0, K, rt->dev_status);
     rt->launched("cast16");
 }
 
@@ -380,7 +381,7 @@ bool binary_linear(ullis_cuda_runtime* rt, const float* x, const uint32_t* bits,
                    const uint16_t* bias, float* y, size_t rows, size_t in_features, size_t out_features) {
     if (!usable(rt) || !shape_ok(rows, in_features, out_features) || out_features % 4) return false;
     uint16_t* a = rt->tc_ws[0].as<uint16_t>(rows * in_features);
-    cast16(rt, x, a, rows * in_features, false);
+    cast16(rt, x, a, rows, in_features, false);
     GemmMaps maps;
     memset(&maps, 0, sizeof(maps));
     maps.a[0][0] = make_map(a, rows, in_features, false);
@@ -390,27 +391,18 @@ bool binary_linear(ullis_cuda_runtime* rt, const float* x, const uint32_t* bits,
     return true;
 }
 
-void value_to_bf16(ullis_cuda_runtime* rt, const uint16_t* w, uint16_t* out, size_t n) {
-    f16_to_bf16_kernel<<<blocks_for(n, 256), 256, 0, rt->stream>>>(w, out, n);
-    rt->launched("f16_to_bf16");
-}
-
 bool fp16_linear(ullis_cuda_runtime* rt, const float* x, const uint16_t* w, float* y, size_t rows,
                  size_t in_features, size_t out_features) {
     if (!usable(rt) || !shape_ok(rows, in_features, out_features)) return false;
-    // both operands as bf16: the activations (relu^2 in the model) span the f32
-    // exponent range, and the MMA wants A and B in the same 16-bit format
+    // both operands FP16: the weights as stored (no second rounding), the activations with 11 significant
+    // bits; an activation beyond the FP16 range is reported by cast16
     uint16_t* a = rt->tc_ws[0].as<uint16_t>(rows * in_features);
-    uint16_t* wb = rt->tc_ws[8].as<uint16_t>(out_features * in_features);
-    cast16(rt, x, a, rows * in_features, true);
-    value_to_bf16(rt, w, wb, out_features * in_features);
+    cast16(rt, x, a, rows, in_features, false);
     GemmMaps maps;
     memset(&maps, 0, sizeof(maps));
-    maps.a[0][0] = make_map(a, rows, in_features, true);
-    maps.b[0] = make_map(wb, out_features, in_features, true);
+    maps.a[0][0] = make_map(a, rows, in_features, false);
+    maps.b[0] = make_map(w, out_features, in_features, false);
     GemmParams p = base_params(rt, rows, out_features, in_features);
-    p.a_fmt = 1;
-    p.b_fmt = 1;
     p.prob[0] = GemmProblem{nullptr, nullptr, nullptr, y, nullptr, nullptr};
     launch<EPI_STORE, false>(rt, maps, p, 1, "gemm_dense_store");
     return true;
@@ -472,12 +464,6 @@ bool cmix_residual(ullis_cuda_runtime* rt, const LayerWeights& L, float* x, size
                    size_t ffn) {
     const size_t rows = batch * time;
     if (!usable(rt) || !shape_ok(rows, d, ffn) || !shape_ok(rows, ffn, d) || d % 4) return false;
-    const uint16_t* value16 = L.value_bf16;
-    if (!value16) {  // weights that did not come through the model loader: convert per call
-        uint16_t* wb = rt->tc_ws[8].as<uint16_t>(ffn * d);
-        value_to_bf16(rt, L.value, wb, ffn * d);
-        value16 = wb;
-    }
     float* ln = rt->tc_ws[4].as<float>(rows * d);
     uint16_t* a16 = rt->tc_ws[0].as<uint16_t>(rows * d);
     uint16_t* k16 = rt->tc_ws[5].as<uint16_t>(rows * ffn);
@@ -489,15 +475,13 @@ bool cmix_residual(ullis_cuda_runtime* rt, const LayerWeights& L, float* x, size
     memset(&maps, 0, sizeof(maps));
     maps.a[0][0] = make_map(a16, rows, d, false);
     GemmParams p = base_params(rt, rows, ffn, d);
-    p.out_fmt = 1;  // relu^2 spans the f32 exponent range: keep it as bf16
+    p.out_fmt = 0;  // FP16: three more significant bits than bf16; the epilogue reports values past 65504
     p.prob[0] = GemmProblem{L.key.bits, L.key.scale, nullptr, k16, nullptr, nullptr};
     launch<EPI_RELU2, true>(rt, maps, p, 1, "gemm_key_relu2");
     memset(&maps, 0, sizeof(maps));
-    maps.a[0][0] = make_map(k16, rows, ffn, true);
-    maps.b[0] = make_map(value16, d, ffn, true);
+    maps.a[0][0] = make_map(k16, rows, ffn, false);
+    maps.b[0] = make_map(L.value, d, ffn, false);   // the FP16 weights as stored
     GemmParams pv = base_params(rt, rows, d, ffn);
-    pv.a_fmt = 1;
-    pv.b_fmt = 1;
     pv.prob[0] = GemmProblem{nullptr, nullptr, nullptr, x, nullptr, nullptr};
     launch<EPI_RESIDUAL, false>(rt, maps, pv, 1, "gemm_value_residual");
     return true;
@@ -511,7 +495,7 @@ bool head_ce(ullis_cuda_runtime* rt, const float* hidden, const PackedWeights& h
     uint16_t* a16 = rt->tc_ws[0].as<uint16_t>(rows * d);
     float2* part = rt->tc_ws[6].as<float2>(rows * n_tiles);
     float* tl = rt->tc_ws[7].as<float>(rows);
-    cast16(rt, hidden, a16, rows * d, false);
+    cast16(rt, hidden, a16, rows, d, false);
     GemmMaps maps;
     memset(&maps, 0, sizeof(maps));
     maps.a[0][0] = make_map(a16, rows, d, false);

@@ -14,8 +14,6 @@ bool binary_linear(ullis_cuda_runtime* rt, const float* x, const uint32_t* bits,
 // y = x . W^T, W FP16 [out,in].
 bool fp16_linear(ullis_cuda_runtime* rt, const float* x, const uint16_t* w, float* y, size_t rows,
                  size_t in_features, size_t out_features);
-// FP16 weight bits -> bf16 bits (done once per matrix at model load).
-void value_to_bf16(ullis_cuda_runtime* rt, const uint16_t* w, uint16_t* out, size_t n);
 // ln3 output -> time-shift mixes -> packed Q,K,V -> stream-major sign bits.
 bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeights& L, uint32_t* q_sw,
                    uint32_t* k_sw, uint32_t* v_sw, size_t batch, size_t time, size_t d);

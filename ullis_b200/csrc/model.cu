@@ -159,14 +159,6 @@ void ullis_cuda_model::load(const uint8_t* bytes, size_t len) {
     for (const auto& it : plan.items) rt->h2d(base + it.offset, it.src, it.bytes);
     rt->sync();  // sources (file bytes, zero_bias) may go away after return
     for (const auto& f : fixes) *f.slot = base + f.offset;
-    if (rt->cc_major == 10) {
-        uint16_t* v16 = arena_bf16.as<uint16_t>(layers * ffn * d);
-        for (size_t i = 0; i < layers; ++i) {
-            tc::value_to_bf16(rt, blocks[i].value, v16 + i * ffn * d, ffn * d);
-            blocks[i].value_bf16 = v16 + i * ffn * d;
-        }
-        rt->sync();
-    }
 }
 
 void ullis_cuda_model::check_shape(size_t batch, size_t time) const {

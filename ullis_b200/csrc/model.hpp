@@ -28,7 +28,6 @@ struct LayerWeights {  // HeronBlock, src/model.rs:2215-2221
     const uint16_t* ffn_x_k = nullptr;
     PackedWeights key;
     const uint16_t* value = nullptr;  // [d_model, dim_ffn] FP16
-    const uint16_t* value_bf16 = nullptr;  // the same matrix rounded to bf16 for the tensor-core path
 };
 
 enum Phase { PH_EMBED_LN = 0, PH_QKV, PH_SAM, PH_O, PH_CMIX, PH_HEAD_CE, PH_COUNT };
@@ -39,7 +38,6 @@ struct ullis_cuda_model {
     ullis_cuda_runtime* rt = nullptr;
     size_t d = 0, layers = 0, vocab = 0, context_len = 0, batch_size = 0, ffn = 0;
     ullis::DeviceBuffer arena;  // all weights
-    ullis::DeviceBuffer arena_bf16;  // CMix value matrices as bf16
     const uint16_t* embedding = nullptr;
     ullis::LayerNormWeights ln_out;
     ullis::PackedWeights head;

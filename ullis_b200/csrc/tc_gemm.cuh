@@ -148,7 +148,11 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
                         __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
                         w[e / 2] = *reinterpret_cast<uint32_t*>(&h);
                     } else {
-                        __half2 h = __floats2half2_rn(a, b);
+                        // FP16 keeps 11 significant bits (bf16: 8) but ends at 65504: report, do not emit inf
+                        if (row_ok && (a > 65504.0f || b > 65504.0f) &&
+                            atomicCAS(p.status, ULLIS_DEV_OK, ULLIS_DEV_FP16_RANGE) == ULLIS_DEV_OK)
+                            p.status[1] = m;
+                        __half2 h = __floats2half2_rn(fminf(a, 65504.0f), fminf(b, 65504.0f));
                         w[e / 2] = *reinterpret_cast<uint32_t*>(&h);
                     }
                 }
