@@ -26,6 +26,14 @@ static int run_batch(int algo, const uint32_t* qw, const uint32_t* kw, const uin
             run_constant_k(qw + s * wps, vw + s * wps, out + s * wps, T, c);
             continue;
         }
+        if (algo == 2 && k_is_constant(vw + s * wps, T, &c)) {   // the same test on the v words: constant v
+            if (c == 0) {
+                for (size_t w = 0; w < wps; ++w) out[s * wps + w] = 0;
+            } else {
+                run_constant_v_one<Ix>(base, qw + s * wps, kw + s * wps, out + s * wps, T, &cnt);
+            }
+            continue;
+        }
         if (algo == 0)
             run_eager<Ix>(base, qw + s * wps, kw + s * wps, vw + s * wps, out + s * wps, T, &cnt);
         else if (!run_euler<Ix>(base, qw + s * wps, kw + s * wps, vw + s * wps, out + s * wps, T, &cnt))

@@ -31,6 +31,13 @@ def _streams(kind, n, T, rng):
     if kind == "k_const":
         return [rng.integers(0, 2, (n, T), dtype=np.uint8), np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1),
                 rng.integers(0, 2, (n, T), dtype=np.uint8)]
+    if kind == "v_const":   # idx = 0 everywhere (v all 0) or "a match exists" (v all 1)
+        return [rng.integers(0, 2, (n, T), dtype=np.uint8), rng.integers(0, 2, (n, T), dtype=np.uint8),
+                np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1)]
+    if kind == "v_const_biased":
+        pr = rng.choice([0.002, 0.02, 0.98], (n, 1))
+        return [(rng.random((n, T)) < pr).astype(np.uint8), (rng.random((n, T)) < pr).astype(np.uint8),
+                np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1)]
     if kind == "biased":
         pr = rng.choice([0.001, 0.01, 0.99, 0.999], (n, 1))
         return [(rng.random((n, T)) < pr).astype(np.uint8), (rng.random((n, T)) < pr).astype(np.uint8),
@@ -48,7 +55,7 @@ def _streams(kind, n, T, rng):
     raise ValueError(kind)
 
 
-@pytest.mark.parametrize("kind,T,n", [("iid", 97, 200), ("iid", 2048, 24), ("const", 1024, 16), ("k_const", 1000, 16), ("k_const", 64, 8), ("biased", 2048, 16),
+@pytest.mark.parametrize("kind,T,n", [("v_const", 777, 32), ("v_const_biased", 2048, 16), ("iid", 97, 200), ("iid", 2048, 24), ("const", 1024, 16), ("k_const", 1000, 16), ("k_const", 64, 8), ("biased", 2048, 16),
                                       ("periodic", 1500, 16), ("periodic_clean", 2048, 8), ("qk_same", 777, 32)])
 def test_long_streams(oracle, sam_host, kind, T, n):
     rng = np.random.default_rng(hash((kind, T)) & 0xFFFF)

@@ -516,6 +516,24 @@ SAM_HD void run_constant_k(const uint32_t* qw, const uint32_t* vw, uint32_t* out
     }
 }
 
+// ---- constant v.  idx_t is a bit of the v history, so a stream whose v bits
+// are all 0 has idx = 0 everywhere, and a stream whose v bits are all 1 has
+// idx_t = 1 exactly when the query of step t finds a state to read `last` from
+// (that state was stamped when it was created, so its `last` is valid): pass 1
+// alone answers it, no tour and no pass 2.
+template <typename Ix>
+SAM_HD void run_constant_v_one(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, uint32_t* out, uint32_t T,
+                               Counters* cnt) {
+    constexpr uint32_t NIL = Nil<Ix>::value;
+    EulerBlock<Ix> B(scratch, T);
+    euler_pass1<Ix>(B, qw, kw, T, cnt);
+    uint32_t acc = 0;
+    for (uint32_t t = 0; t < T; ++t) {
+        acc |= (B.vq[t] != NIL ? 1u : 0u) << (t & 31);
+        if ((t & 31) == 31 || t + 1 == T) { out[t >> 5] = acc; acc = 0; }
+    }
+}
+
 template <typename Ix>
 SAM_HD bool run_euler(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw,
                       uint32_t* out, uint32_t T, Counters* cnt) {
