@@ -209,7 +209,10 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         if (const char* env = getenv("ULLIS_CUDA_SAM_COOP")) rt->sam_coop = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_LANES")) {
             const int v = atoi(env);
-            if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16 || v == 32) rt->sam_lanes = v;
+            if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16 || v == 32) {
+                rt->sam_lanes = v;
+                rt->sam_lanes_fixed = true;
+            }
         }
     } catch (const Error& err) {
         set_global_error(err.msg.c_str());

@@ -86,6 +86,7 @@ struct ullis_cuda_runtime {
     int sam_algo = ULLIS_CUDA_SAM_EULER;
     bool sam_coop = true;               // warp-cooperative tour / pass 2 when the stream fits shared memory
     bool sam_coop_ready = false;
+    bool sam_lanes_fixed = false;       // ULLIS_CUDA_SAM_LANES was given: no per-launch choice in pass 1
     int sam_lanes = 4;                  // streams carried per warp by the suffix-automaton kernel (1,2,4,...,32)
     uint64_t launches = 0;
     std::string last_error;

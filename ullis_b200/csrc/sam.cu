@@ -84,7 +84,12 @@ rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint
 __global__ void __launch_bounds__(128)
 rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
                   const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ list,
-                  const uint32_t* __restrict__ count, size_t first, uint32_t T, size_t wps, int lanes) {
+                  const uint32_t* __restrict__ count, size_t first, uint32_t T, size_t wps, int lanes,
+                  uint32_t dense_count) {
+    // lanes == 0: choose from the number of streams that are left, which only the device knows -
+    // many streams: four per warp (fewer issued instructions); few: two per warp (more warps to
+    // hide the pointer-chase latency).  The grid is sized for two per warp.
+    if (lanes == 0) lanes = *count > dense_count ? 4 : 2;
     const int lane = threadIdx.x & 31;
     const int spread = 32 / lanes;
     if (lane % spread != 0) return;
@@ -207,8 +212,12 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
         const size_t warps = (n + lanes - 1) / lanes;
         const unsigned grid = (unsigned)((warps * 32 + 127) / 128);
         if (use_coop) {
-            rosa_pass1_kernel<<<grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, k_sw, list, count, s0, (uint32_t)time,
-                                                             wps, lanes);
+            // sam_lanes_fixed: the caller pinned the streams per warp; otherwise the kernel picks 2 or 4
+            const int pass1_lanes = rt->sam_lanes_fixed ? lanes : 0;
+            const size_t pass1_warps = rt->sam_lanes_fixed ? warps : (n + 1) / 2;
+            rosa_pass1_kernel<<<(unsigned)((pass1_warps * 32 + 127) / 128), 128, 0, rt->stream>>>(
+                scratch, stride, q_sw, k_sw, list, count, s0, (uint32_t)time, wps, pass1_lanes,
+                96u * (uint32_t)rt->sm_count);
             rt->launched("rosa_pass1");
             rosa_coop_kernel<<<(unsigned)n, sam::COOP_THREADS, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, count, s0,
                                                                          (uint32_t)time, wps, rt->dev_status);
