@@ -17,20 +17,14 @@ namespace k {
 
 namespace {
 
-// Streams that need no (or less) automaton work are settled here with a few
-// word operations (sam_core.cuh, "constant k" and "constant v"):
-//   k bits all equal           closed form, finished here;
-//   v bits all 0               idx = 0, finished here;
-//   v bits all 1               idx_t = "the query of step t found a state": pass 1
-//                              only - listed with PASS1_ONLY set (when the caller
-//                              runs the two-kernel schedule that can use it).
+// Streams that need no automaton are settled here with a few word operations
+// (sam_core.cuh, "constant k" and "constant v"): k bits all equal, v bits all 0
+// (idx = 0) and v bits all 1 (idx_t = "q_t has occurred among the earlier keys").
 // Every other stream id is appended to `list` for the automaton kernels.
-constexpr uint32_t PASS1_ONLY = 0x80000000u, STREAM_ID = 0x7FFFFFFFu;
-
 __global__ void __launch_bounds__(128)
 rosa_classify_kernel(const uint32_t* __restrict__ q_sw, const uint32_t* __restrict__ k_sw,
                      const uint32_t* __restrict__ v_sw, uint32_t* __restrict__ idx_sw, size_t streams, uint32_t T,
-                     size_t wps, uint32_t* __restrict__ list, uint32_t* __restrict__ count, int can_flag) {
+                     size_t wps, uint32_t* __restrict__ list, uint32_t* __restrict__ count) {
     const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= streams) return;
     uint32_t c = 0;
@@ -40,7 +34,7 @@ rosa_classify_kernel(const uint32_t* __restrict__ q_sw, const uint32_t* __restri
         if (c == 0) {
             for (size_t w = 0; w < wps; ++w) idx_sw[s * wps + w] = 0u;
         } else {
-            list[atomicAdd(count, 1u)] = (uint32_t)s | (can_flag ? PASS1_ONLY : 0u);
+            sam::run_constant_v_one(q_sw + s * wps, k_sw + s * wps, idx_sw + s * wps, T);
         }
     } else {
         list[atomicAdd(count, 1u)] = (uint32_t)s;
@@ -65,7 +59,7 @@ rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint
     const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const size_t item = warp * lanes + lane / spread;
     if (first + item >= *count) return;
-    const size_t s = list[first + item] & STREAM_ID;
+    const size_t s = list[first + item];
     uint8_t* block = scratch + item * scratch_stride;
     const uint32_t* qw = q_sw + s * wps;
     const uint32_t* kw = k_sw + s * wps;
@@ -96,7 +90,7 @@ rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const ui
     const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const size_t item = warp * lanes + lane / spread;
     if (first + item >= *count) return;
-    const size_t s = list[first + item] & STREAM_ID;
+    const size_t s = list[first + item];
     sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
     sam::euler_pass1<uint16_t>(B, q_sw + s * wps, k_sw + s * wps, T, nullptr);
 }
@@ -108,30 +102,8 @@ rosa_coop_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uin
     extern __shared__ __align__(16) uint8_t coop_smem[];
     const size_t item = blockIdx.x;
     if (first + item >= *count) return;
-    const uint32_t entry = list[first + item];
-    const size_t s = entry & STREAM_ID;
+    const size_t s = list[first + item];
     sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
-    if (entry & PASS1_ONLY) {
-        // v is all ones: idx_t = 1 exactly when the query of step t found a state (sam_core.cuh, "constant v")
-        constexpr uint32_t NIL = sam::Nil<uint16_t>::value;
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        uint32_t* out = idx_sw + s * wps;
-        for (uint32_t t0 = 0; t0 < T; t0 += sam::COOP_THREADS * 8) {
-            uint16_t v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const uint32_t t = t0 + sam::COOP_THREADS * u + threadIdx.x;
-                v[u] = t < T ? B.vq[t] : (uint16_t)NIL;
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const uint32_t tw = t0 + sam::COOP_THREADS * u + warp * 32;   // first step of this warp's word
-                const uint32_t word = __ballot_sync(0xffffffffu, v[u] != NIL);
-                if (lane == 0 && tw < T) out[tw >> 5] = word;
-            }
-        }
-        return;
-    }
     if (B.meta[0] > sam::node_capacity(T)) {  // cannot happen: at most 2T states
         if (threadIdx.x == 0 && atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_SAM_CAPACITY) == ULLIS_DEV_OK)
             status[1] = (uint32_t)s;
@@ -192,14 +164,13 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     const sam::CoopLayout coop((uint32_t)time);
     const bool use_coop = algo == ULLIS_CUDA_SAM_EULER && narrow && rt->sam_coop && coop.total <= 226 * 1024 &&
                           2 * sam::node_capacity((uint32_t)time) < 0xFFFFu;
-    if (streams > STREAM_ID) fail(ULLIS_CUDA_ERR_SHAPE, "too many ROSA streams");
     if (algo == ULLIS_CUDA_SAM_EAGER) {
         rosa_list_all_kernel<<<cgrid, 128, 0, rt->stream>>>(list, count, streams);
         rt->launched("rosa_list_all");
     } else {
         rt->zero(count, 4);
         rosa_classify_kernel<<<cgrid, 128, 0, rt->stream>>>(q_sw, k_sw, v_sw, idx_sw, streams, (uint32_t)time, wps, list,
-                                                             count, use_coop ? 1 : 0);
+                                                             count);
         rt->launched("rosa_classify");
     }
     if (use_coop && !rt->sam_coop_ready) {

@@ -517,20 +517,39 @@ SAM_HD void run_constant_k(const uint32_t* qw, const uint32_t* vw, uint32_t* out
 }
 
 // ---- constant v.  idx_t is a bit of the v history, so a stream whose v bits
-// are all 0 has idx = 0 everywhere, and a stream whose v bits are all 1 has
+// are all 0 has idx = 0 everywhere.  A stream whose v bits are all 1 has
 // idx_t = 1 exactly when the query of step t finds a state to read `last` from
-// (that state was stamped when it was created, so its `last` is valid): pass 1
-// alone answers it, no tour and no pass 2.
-template <typename Ix>
-SAM_HD void run_constant_v_one(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, uint32_t* out, uint32_t T,
-                               Counters* cnt) {
-    constexpr uint32_t NIL = Nil<Ix>::value;
-    EulerBlock<Ix> B(scratch, T);
-    euler_pass1<Ix>(B, qw, kw, T, cnt);
-    uint32_t acc = 0;
-    for (uint32_t t = 0; t < T; ++t) {
-        acc |= (B.vq[t] != NIL ? 1u : 0u) << (t & 31);
-        if ((t & 31) == 31 || t + 1 == T) { out[t >> 5] = acc; acc = 0; }
+// (that state was stamped when it was created, so its `last` is valid).  The
+// query walks up the suffix links until a state has a q_t-child and fails only
+// if even the root has none - the root has a c-child as soon as c has occurred
+// among the keys - so idx_t = 1 iff q_t occurs in k_0 .. k_{t-1}: no automaton
+// at all.  With f the first step whose key differs from k_0 (f = T if none):
+// idx_t = (q_t == k_0) for 1 <= t <= f, idx_t = 1 for t > f, idx_0 = 0.
+SAM_HD void run_constant_v_one(const uint32_t* qw, const uint32_t* kw, uint32_t* out, uint32_t T) {
+    const uint32_t wps = (T + 31) >> 5;
+    const uint32_t tail = (T & 31u) ? ((1u << (T & 31u)) - 1u) : 0xFFFFFFFFu;
+    const uint32_t c0 = kw[0] & 1u, full = c0 ? 0xFFFFFFFFu : 0u;
+    uint32_t f = T;
+    for (uint32_t w = 0; w < wps && f == T; ++w) {
+        uint32_t diff = kw[w] ^ full;
+        if (w + 1 == wps) diff &= tail;
+        if (diff) {
+            uint32_t b = 0;
+            while (!((diff >> b) & 1u)) ++b;
+            f = w * 32u + b;
+        }
+    }
+    for (uint32_t w = 0; w < wps; ++w) {
+        const uint32_t same = c0 ? qw[w] : ~qw[w];   // q_t == k_0
+        // bits of this word at steps > f
+        uint32_t after;
+        if (f >= w * 32u + 31u) after = 0u;
+        else if (f < w * 32u) after = 0xFFFFFFFFu;
+        else after = ~((2u << (f - w * 32u)) - 1u);
+        uint32_t word = (same & ~after) | after;
+        if (w == 0) word &= ~1u;
+        if (w + 1 == wps) word &= tail;
+        out[w] = word;
     }
 }
 
