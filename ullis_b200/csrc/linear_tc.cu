@@ -161,6 +161,7 @@ emit_f16_kernel(const uint32_t* __restrict__ idx_sw, const uint16_t* __restrict_
 // (word, bit) pairs of its chunk into a shared queue and then spreads them
 // over all of its threads - one exact dot product per thread.
 constexpr int FIX_THREADS = 256, FIX_WORDS = 2048, FIX_QUEUE = 16384;
+static_assert(((FIX_WORDS - 1) << 5 | 31) <= 0xFFFF, "queue entries are 16 bits");
 
 __global__ void __launch_bounds__(FIX_THREADS)
 sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, const uint16_t* __restrict__ mk,
@@ -168,7 +169,7 @@ sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, 
                   uint32_t* __restrict__ bq, uint32_t* __restrict__ bk, uint32_t* __restrict__ bv,
                   const uint32_t* __restrict__ fq, const uint32_t* __restrict__ fk, const uint32_t* __restrict__ fv,
                   size_t batch, size_t T, size_t C, size_t wps) {
-    extern __shared__ uint32_t fix_queue[];  // entries: (word offset in chunk) << 5 | bit
+    extern __shared__ uint16_t fix_queue[];  // entries: (word offset in chunk, < 2048) << 5 | bit - 16 bits, so that seven CTAs fit an SM
     __shared__ uint32_t q_count;
     const int which = blockIdx.y;
     const uint32_t* flags = which == 0 ? fq : which == 1 ? fk : fv;
@@ -187,7 +188,7 @@ sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, 
             while (f) {
                 const uint32_t tt = __ffs(f) - 1;
                 f &= f - 1;
-                fix_queue[at + k++] = ((uint32_t)(sub + threadIdx.x) << 5) | tt;
+                fix_queue[at + k++] = (uint16_t)(((uint32_t)(sub + threadIdx.x) << 5) | tt);
             }
         }
         __syncthreads();
@@ -301,7 +302,7 @@ bool usable(ullis_cuda_runtime* rt) {
                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM_LIMIT));
             rt->tc_ws_kernel = !getenv("ULLIS_CUDA_NO_WS");
             ULLIS_CUDA_CHECK(cudaFuncSetAttribute(sign_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  FIX_QUEUE * 4));
+                                                  FIX_QUEUE * 2));
             rt->tc_ready = 1;
         }
     }
@@ -436,7 +437,7 @@ bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeig
         p.prob[z] = GemmProblem{W[z]->bits, W[z]->scale, W[z]->bias, outs[z], flags + z * sw, s1 + z * rows};
     launch<EPI_SIGNBITS, true>(rt, maps, p, 3, "gemm_qkv_signbits");
     dim3 grid(blocks_for(sw, FIX_WORDS), 3);
-    sign_fixup_kernel<<<grid, FIX_THREADS, FIX_QUEUE * 4, rt->stream>>>(ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, flags,
+    sign_fixup_kernel<<<grid, FIX_THREADS, FIX_QUEUE * 2, rt->stream>>>(ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, flags,
                                                    flags + sw, flags + 2 * sw, batch, time, d, wps);
     rt->launched("sign_fixup");
     return true;
