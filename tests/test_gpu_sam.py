@@ -89,3 +89,17 @@ def test_context_beyond_16_bit_state_ids(cuda_rt, oracle):
     B, T, C = 1, 32768, 4  # MAX_CONTEXT_LEN: needs the 32-bit state-id kernels
     q, k, v = synth.rosa_bits_iid(24, B, T, C)
     run_both(cuda_rt, oracle, q, k, v, B, T, C, algos=(cuda.SAM_EULER,))
+
+
+def test_streams_in_waves_when_the_scratch_budget_is_small(oracle, monkeypatch):
+    """More streams than the automaton scratch may hold at once run in waves over the same blocks."""
+    monkeypatch.setenv("ULLIS_CUDA_SAM_BUDGET_MB", "4")          # 4 MiB: 56 blocks of 74 368 B at T=2048
+    rt = cuda.CudaRuntime(0)
+    try:
+        B, T, C = 2, 2048, 96                                     # 192 streams: four waves
+        q, k, v = synth.rosa_bits_iid(31, B, T, C)
+        run_both(rt, oracle, q, k, v, B, T, C)
+        q, k, v = synth.rosa_bits_periodic(32, B, T, C)
+        run_both(rt, oracle, q, k, v, B, T, C, algos=(cuda.SAM_EULER,))
+    finally:
+        rt.close()

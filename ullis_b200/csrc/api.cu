@@ -207,6 +207,10 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
             if (a >= 2 && a <= 4 && b >= 2 && b <= 4) { rt->tc_stages = a; rt->tc_stages2 = b; }
         }
         if (const char* env = getenv("ULLIS_CUDA_SAM_COOP")) rt->sam_coop = atoi(env) != 0;
+        if (const char* env = getenv("ULLIS_CUDA_SAM_BUDGET_MB")) {
+            const long mb = atol(env);
+            if (mb > 0) rt->sam_budget_bytes = (size_t)mb << 20;
+        }
         if (const char* env = getenv("ULLIS_CUDA_SAM_LANES")) {
             const int v = atoi(env);
             if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16 || v == 32) {

@@ -93,6 +93,7 @@ struct ullis_cuda_runtime {
     uint32_t* dev_status = nullptr;     // 4 words, device
     uint32_t* host_status = nullptr;    // 4 words, pinned
     ullis::DeviceBuffer pool[24];       // op-level scratch slots
+    size_t sam_budget_bytes = (size_t)12 << 30;   // cap of sam_scratch; more streams than fit run in waves
     ullis::DeviceBuffer sam_scratch;    // suffix-automaton state blocks
     ullis::DeviceBuffer sam_list;       // ids of the streams that need the automaton + their count
     ullis::DeviceBuffer tc_ws[16];      // 16-bit operands / partials of the tensor-core stages

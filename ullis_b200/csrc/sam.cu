@@ -141,13 +141,13 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     const size_t stride = rosa_sam_scratch_bytes_per_stream(algo, time);
     const size_t wps = (time + 31) / 32;
     // wave size: all streams at once when the scratch buffer already holds them;
-    // otherwise bounded scratch (default 12 GiB, or what fits in free memory).
+    // otherwise bounded scratch (12 GiB unless ULLIS_CUDA_SAM_BUDGET_MB says otherwise, or what fits in free memory).
     // The memory query is a blocking driver call, so it is kept off the steady state.
     size_t wave = streams;
     if (rt->sam_scratch.bytes() < streams * stride) {
         size_t free_b = 0, total_b = 0;
         ULLIS_CUDA_CHECK(cudaMemGetInfo(&free_b, &total_b));
-        size_t budget = (size_t)12 << 30;
+        size_t budget = rt->sam_budget_bytes;
         const size_t avail = free_b + rt->sam_scratch.bytes();  // what the scratch buffer could grow to
         if (avail < budget + ((size_t)2 << 30)) budget = avail > ((size_t)4 << 30) ? avail - ((size_t)2 << 30) : avail / 2;
         wave = budget / stride;
