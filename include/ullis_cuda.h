@@ -38,6 +38,7 @@ extern "C" {
 typedef struct ullis_cuda_runtime ullis_cuda_runtime;
 typedef struct ullis_cuda_model ullis_cuda_model;
 typedef struct ullis_cuda_generate_state ullis_cuda_generate_state;
+typedef struct ullis_cuda_train_state ullis_cuda_train_state;
 
 enum {
     ULLIS_CUDA_OK = 0,
@@ -185,6 +186,45 @@ ULLIS_CUDA_API size_t ullis_cuda_generate_state_time(const ullis_cuda_generate_s
  * both cases the state is unchanged. */
 ULLIS_CUDA_API int32_t ullis_cuda_generate_step(ullis_cuda_generate_state* state, const uint32_t* tokens,
                                                 float* logits);
+
+/* -------------------------------------------------------------------- train
+ * One optimiser step with the weights, the BinaryConnect latents and the f32
+ * carry on the device: UllisHeron::train_step_with_labels
+ * (src/model.rs:2773-2785, train_step_on 2827-3020) in rosa_grad =
+ * stop_grad_bits mode, the only mode the reference wires.  Q/K/V, their
+ * time-shift mixes and ln3 are frozen; the head, ROSA O and e, CMix, the other
+ * LayerNorms and the embedding rows are stepped (clipped SGD with an f32 carry,
+ * BinaryConnect for the packed latents, src/precision.rs:106-134).  The loss
+ * and the flip counts are exact restatements; the gradients are FP16-operand
+ * tensor-core products with f32 accumulation, so updated tensors agree with the
+ * reference's CPU step to gradient rounding, not bit for bit. */
+
+/* Optimiser state for `model` (which it borrows and MODIFIES).  `checkpoint`
+ * (nullable) is the safetensors file the model was loaded from: its
+ * "<name>.latent" / "<name>.residual" tensors restore a resumed run's carry
+ * (src/model.rs:3461-3466); without them latents start at +/-0.01 by the sign
+ * bit (src/model.rs:640-649) and residuals at zero. */
+ULLIS_CUDA_API int32_t ullis_cuda_train_state_create(ullis_cuda_model* model, const uint8_t* checkpoint, size_t len,
+                                                     ullis_cuda_train_state** out);
+ULLIS_CUDA_API void ullis_cuda_train_state_destroy(ullis_cuda_train_state* state);
+/* CausalLoss fields the step itself produces (src/model.rs:60-83). */
+typedef struct ullis_cuda_train_result {
+    float mean_loss;      /* next_token */
+    uint64_t n_valid;     /* next_token_count */
+    uint64_t flips_head, flips_cmix, flips_rosa_o;
+} ullis_cuda_train_result;
+/* tokens, labels [batch*time] on the host.  ULLIS_CUDA_ERR_ARG unless
+ * learning_rate is finite and positive and time >= 2; ULLIS_CUDA_ERR_SHAPE
+ * for a shape or id the reference rejects (src/model.rs:2849-2861). */
+ULLIS_CUDA_API int32_t ullis_cuda_model_train_step(ullis_cuda_train_state* state, const uint32_t* tokens,
+                                                   const uint32_t* labels, uint32_t ignore_id, size_t batch,
+                                                   size_t time, float learning_rate,
+                                                   ullis_cuda_train_result* result);
+/* Copies a tensor of the trained model or of its carry to the host by its
+ * checkpoint name ("head.bits", "blocks.0.rosa.o.latent", "embedding.residual",
+ * ...; src/model.rs:3428-3466); `bytes` must be the tensor's size. */
+ULLIS_CUDA_API int32_t ullis_cuda_train_state_read(ullis_cuda_train_state* state, const char* name, void* dst,
+                                                   size_t bytes);
 
 /* ------------------------------------------------------------------ op level
  * Host pointers in, caller-allocated host buffers out; one synchronous call

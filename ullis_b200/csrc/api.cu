@@ -10,6 +10,7 @@
 #include "kernels.hpp"
 #include "linear_tc.hpp"
 #include "generate.hpp"
+#include "train.hpp"
 #include "model.hpp"
 
 using namespace ullis;
@@ -445,6 +446,44 @@ int32_t ullis_cuda_generate_step(ullis_cuda_generate_state* state, const uint32_
         need_ptr(tokens, "tokens");
         need_ptr(logits, "logits");
         state->step(tokens, logits);
+    });
+}
+
+// --------------------------------------------------------------------- train
+
+int32_t ullis_cuda_train_state_create(ullis_cuda_model* model, const uint8_t* checkpoint, size_t len,
+                                      ullis_cuda_train_state** out) {
+    return guard_model(model, [&] {
+        need_ptr(out, "out");
+        *out = nullptr;
+        *out = new ullis_cuda_train_state(model, checkpoint, len);
+    });
+}
+
+void ullis_cuda_train_state_destroy(ullis_cuda_train_state* state) {
+    if (!state) return;
+    if (state->rt) cudaSetDevice(state->rt->device);
+    delete state;
+}
+
+int32_t ullis_cuda_model_train_step(ullis_cuda_train_state* state, const uint32_t* tokens, const uint32_t* labels,
+                                    uint32_t ignore_id, size_t batch, size_t time, float learning_rate,
+                                    ullis_cuda_train_result* result) {
+    if (!state) {
+        set_global_error("train state handle is null");
+        return ULLIS_CUDA_ERR_ARG;
+    }
+    return guard_model(state->m, [&] { state->step(tokens, labels, ignore_id, batch, time, learning_rate, result); });
+}
+
+int32_t ullis_cuda_train_state_read(ullis_cuda_train_state* state, const char* name, void* dst, size_t bytes) {
+    if (!state) {
+        set_global_error("train state handle is null");
+        return ULLIS_CUDA_ERR_ARG;
+    }
+    return guard_model(state->m, [&] {
+        need_ptr(dst, "dst");
+        state->read(name, dst, bytes);
     });
 }
 

@@ -409,6 +409,19 @@ bool fp16_linear(ullis_cuda_runtime* rt, const float* x, const uint16_t* w, floa
     return true;
 }
 
+bool dense_nt(ullis_cuda_runtime* rt, const uint16_t* a16, const uint16_t* b16, float* y, size_t M, size_t K,
+              size_t N) {
+    if (!usable(rt) || !shape_ok(M, K, N)) return false;
+    GemmMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    maps.a[0][0] = make_map(a16, M, K, false);
+    maps.b[0] = make_map(b16, N, K, false);
+    GemmParams p = base_params(rt, M, N, K);
+    p.prob[0] = GemmProblem{nullptr, nullptr, nullptr, y, nullptr, nullptr};
+    launch<EPI_STORE, false>(rt, maps, p, 1, "gemm_dense_nt");
+    return true;
+}
+
 bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeights& L, uint32_t* q_sw,
                    uint32_t* k_sw, uint32_t* v_sw, size_t batch, size_t time, size_t d) {
     const size_t rows = batch * time;

@@ -14,6 +14,9 @@ bool binary_linear(ullis_cuda_runtime* rt, const float* x, const uint32_t* bits,
 // y = x . W^T, W FP16 [out,in].
 bool fp16_linear(ullis_cuda_runtime* rt, const float* x, const uint16_t* w, float* y, size_t rows,
                  size_t in_features, size_t out_features);
+// y [M,N] f32 = a . b^T with both operands already FP16: a [M,K], b [N,K] (K a multiple of 64).
+bool dense_nt(ullis_cuda_runtime* rt, const uint16_t* a16, const uint16_t* b16, float* y, size_t M, size_t K,
+              size_t N);
 // ln3 output -> time-shift mixes -> packed Q,K,V -> stream-major sign bits.
 bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeights& L, uint32_t* q_sw,
                    uint32_t* k_sw, uint32_t* v_sw, size_t batch, size_t time, size_t d);

@@ -263,6 +263,10 @@ void ullis_cuda_model::enqueue_hidden(size_t batch, size_t time) {
         if (tap_bufs.size() != layers * 8 + 1) tap_bufs = std::vector<DeviceBuffer>(layers * 8 + 1);
         tap_rows = rows;
     }
+    if (train_tape && tape_after.size() != layers) {
+        tape_after = std::vector<DeviceBuffer>(layers);
+        tape_idx = std::vector<DeviceBuffer>(layers);
+    }
     spans_used = 0;
     rt->clear_status();
 
@@ -299,6 +303,9 @@ void ullis_cuda_model::enqueue_hidden(size_t batch, size_t time) {
         begin(PH_SAM);
         k::rosa_sam(rt, QS, KS, VS, IS, batch * d, time);
         save_tap_bits((int)l, ULLIS_CUDA_TAP_IDX, IS, batch, time);
+        if (train_tape)
+            ULLIS_CUDA_CHECK(cudaMemcpyAsync(tape_idx[l].as<uint32_t>(sw_words), IS, sw_words * 4,
+                                             cudaMemcpyDeviceToDevice, rt->stream));
         end();
 
         begin(PH_O);
@@ -307,6 +314,9 @@ void ullis_cuda_model::enqueue_hidden(size_t batch, size_t time) {
             k::binary_linear_exact(rt, A, L.o.bits, L.o.scale, L.o.bias, X, rows, d, d, true);  // x += rosa out
         }
         save_tap((int)l, ULLIS_CUDA_TAP_AFTER_ROSA, X, n * 4);
+        if (train_tape)
+            ULLIS_CUDA_CHECK(cudaMemcpyAsync(tape_after[l].as<float>(n), X, n * 4, cudaMemcpyDeviceToDevice,
+                                             rt->stream));
         end();
 
         begin(PH_CMIX);

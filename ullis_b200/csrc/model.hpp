@@ -48,6 +48,10 @@ struct ullis_cuda_model {
     size_t cur_batch = 0, cur_time = 0;
     bool have_result = false;
 
+    // training tape: the residual stream after each ROSA block and the idx bits, kept per layer
+    bool train_tape = false;
+    std::vector<ullis::DeviceBuffer> tape_after, tape_idx;
+
     // taps
     bool taps_enabled = false;
     size_t tap_rows = 0;

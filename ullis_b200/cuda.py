@@ -44,6 +44,8 @@ ABI_SYMBOLS = (
     "ullis_cuda_model_set_taps", "ullis_cuda_model_tap", "ullis_cuda_model_set_profile",
     "ullis_cuda_model_phase_ms", "ullis_cuda_generate_state_create", "ullis_cuda_generate_state_destroy",
     "ullis_cuda_generate_state_reset", "ullis_cuda_generate_state_time", "ullis_cuda_generate_step",
+    "ullis_cuda_train_state_create", "ullis_cuda_train_state_destroy", "ullis_cuda_model_train_step",
+    "ullis_cuda_train_state_read",
     "ullis_cuda_layer_norm", "ullis_cuda_time_shift_delta",
     "ullis_cuda_binary_linear", "ullis_cuda_fp16_linear", "ullis_cuda_sign_pack_bits", "ullis_cuda_cmix_relu2",
     "ullis_cuda_residual_add", "ullis_cuda_rosa_qkv_1bit_fwd", "ullis_cuda_rosa_block_forward",
@@ -82,6 +84,8 @@ def load_library() -> C.CDLL:
         lib.ullis_cuda_model_destroy.argtypes = [C.c_void_p]
         lib.ullis_cuda_generate_state_destroy.restype = None
         lib.ullis_cuda_generate_state_destroy.argtypes = [C.c_void_p]
+        lib.ullis_cuda_train_state_destroy.restype = None
+        lib.ullis_cuda_train_state_destroy.argtypes = [C.c_void_p]
         lib.ullis_cuda_generate_state_time.restype = C.c_size_t
         lib.ullis_cuda_generate_state_time.argtypes = [C.c_void_p]
         _LIB = lib
@@ -408,6 +412,10 @@ class CudaHeron:
         """UllisHeron::generate_step (src/model.rs:2717-2753): logits [batch, vocab] of the new tokens."""
         return state.step(tokens)
 
+    def train_state(self, checkpoint: bytes | None = None) -> "CudaTrainState":
+        """Optimiser carry for this model (latents, f32 residuals); `checkpoint` restores a resumed run's."""
+        return CudaTrainState(self, checkpoint)
+
     def set_taps(self, enabled: bool):
         self.rt._check(self._lib.ullis_cuda_model_set_taps(self._h, C.c_int32(1 if enabled else 0)))
 
@@ -455,6 +463,54 @@ class CudaGenerateState:
     def close(self):
         if getattr(self, "_h", None):
             self._lib.ullis_cuda_generate_state_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+class _TrainResult(C.Structure):
+    _fields_ = [("mean_loss", C.c_float), ("n_valid", C.c_uint64), ("flips_head", C.c_uint64),
+                ("flips_cmix", C.c_uint64), ("flips_rosa_o", C.c_uint64)]
+
+
+class CudaTrainState:
+    """Weights, BinaryConnect latents and f32 carry of a model being trained on the device
+    (UllisHeron::train_step_with_labels, src/model.rs:2773-2785, in stop_grad_bits mode).
+    The model is borrowed and modified: its forward / generate calls see the stepped weights."""
+
+    def __init__(self, model: CudaHeron, checkpoint: bytes | None = None):
+        self.model = model
+        self._lib = model._lib
+        h = C.c_void_p()
+        buf = None if checkpoint is None else (C.c_uint8 * len(checkpoint)).from_buffer_copy(checkpoint)
+        model.rt._check(self._lib.ullis_cuda_train_state_create(model._h, buf, _z(0 if checkpoint is None else
+                                                                                  len(checkpoint)), C.byref(h)))
+        self._h = h
+
+    def train_step(self, tokens, labels, ignore_id: int, batch: int, time: int, learning_rate: float) -> dict:
+        t = _arr(tokens, np.uint32, "tokens", batch * time)
+        lab = _arr(labels, np.uint32, "labels", batch * time)
+        res = _TrainResult()
+        self.model.rt._check(self._lib.ullis_cuda_model_train_step(
+            self._h, _ptr(t), _ptr(lab), C.c_uint32(ignore_id), _z(batch), _z(time), C.c_float(learning_rate),
+            C.byref(res)))
+        return {"loss": float(res.mean_loss), "n_valid": int(res.n_valid), "flips_head": int(res.flips_head),
+                "flips_cmix": int(res.flips_cmix), "flips_rosa_o": int(res.flips_rosa_o)}
+
+    def read(self, name: str, dtype, count: int) -> np.ndarray:
+        """Tensor of the trained model or of its carry by checkpoint name (u16 = FP16 bits)."""
+        out = np.empty(count, dtype)
+        self.model.rt._check(self._lib.ullis_cuda_train_state_read(self._h, name.encode(), _ptr(out),
+                                                                   _z(out.nbytes)))
+        return out
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.ullis_cuda_train_state_destroy(self._h)
             self._h = None
 
     def __del__(self):
