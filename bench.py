@@ -55,7 +55,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-run", action="store_true",
                     help="short run for a profiler: warm-up count as given, no end-to-end leg, no CPU baseline")
-    ap.add_argument("--workload", choices=["heron", "rosa", "linear", "generate"], default="heron",
+    ap.add_argument("--workload", choices=["heron", "rosa", "linear", "generate", "train"], default="heron",
                     help="heron = the benchmark; rosa / linear = single-op loops; generate = incremental decoding")
     ap.add_argument("--rosa-variant", choices=["iid", "periodic"], default="iid")
     ap.add_argument("--channels", type=int, default=512)
@@ -432,6 +432,43 @@ def run_op_loop(args, rt, stream, torch):
             ref_dt = (time.perf_counter() - t0) / n_ref
             line["cpu_baseline"] = {"value": 1.0 / ref_dt, "unit": "tokens/s", "cores": O.max_threads(), "kind": "port",
                                     "sample": f"oracle generate_step, 1 sequence, first {n_ref} tokens"}
+        print(json.dumps(line))
+        state.close()
+        model.close()
+        rt.close()
+        return
+    if args.workload == "train":
+        # one optimiser step per step: tokens from the host, forward with the tape, backward, updates on the device
+        from ullis_b200 import cuda
+        d, layers, vocab, ctx, ffn = synth.CONFIGS[args.model]
+        B = args.batch
+        data = synth.heron_checkpoint(args.model, batch_size=max(B, 1))
+        model = cuda.CudaHeron(rt, data)
+        state = model.train_state()
+        tokens = sequence_tokens(vocab, 0, B, ctx)
+        lr = 0.005
+        losses = []
+
+        def step():
+            losses.append(state.train_step(tokens, tokens, cuda.CE_NO_IGNORE, B, ctx, lr)["loss"])
+
+        dt, per_kernel = timed(step)
+        top = dict(sorted(per_kernel.items(), key=lambda kv: -kv[1])[:12])
+        line = {"workload": "train", "model": args.model, "batch": B, "time": ctx, "steps": args.steps,
+                "learning_rate": lr, "ms_per_step_host_timed": dt * 1e3, "tokens_per_s": B * ctx / dt,
+                "device_ms_per_step": sum(per_kernel.values()), "loss_first": losses[0], "loss_last": losses[-1],
+                "kernels_ms": {k: round(v, 3) for k, v in top.items()}}
+        if not args.no_cpu_baseline:
+            # the restated CPU step on one sequence of the same tokens
+            from oracle import oracle as O
+            from oracle import train as OT
+            O.set_threads(O.max_threads())
+            ref = OT.HeronTrainer(synth.heron_checkpoint(args.model, batch_size=1))
+            t0 = time.perf_counter()
+            ref.train_step(tokens[:ctx], tokens[:ctx], O.CE_NO_IGNORE, 1, ctx, lr)
+            ref_dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": ctx / ref_dt, "unit": "tokens/s", "cores": O.max_threads(), "kind": "port",
+                                    "sample": f"restated CPU step (C forward, numpy gradients), 1 sequence of T={ctx}"}
         print(json.dumps(line))
         state.close()
         model.close()

@@ -104,3 +104,28 @@ def test_two_rank_gloo_sharding_matches_single_process(tmp_path):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs
     assert "DP_OK" in outs[0]
+
+
+def test_parent_handles_close_their_children_first():
+    """Runtime -> model -> state handles borrow one another in the C library, and a
+    garbage collection that finds the Python objects unreachable together finalises
+    them in no particular order: closing a parent destroys its children first, once each."""
+    from ullis_b200 import cuda
+    calls = []
+    rt = cuda._Handle(1, lambda h: calls.append(("runtime", h)))
+    model = cuda._Handle(2, lambda h: calls.append(("model", h)), rt)
+    train = cuda._Handle(3, lambda h: calls.append(("train", h)), model)
+    gen = cuda._Handle(4, lambda h: calls.append(("generate", h)), model)
+    gone = cuda._Handle(5, lambda h: calls.append(("generate", h)), model)
+    gone.close()                     # a state that was dropped earlier
+    assert calls == [("generate", 5)]
+    rt.close()                       # the runtime's finaliser happened to run first
+    assert calls[1:] == [("train", 3), ("generate", 4), ("model", 2), ("runtime", 1)]
+    for h in (train, gen, model, rt):   # the others' finalisers then find nothing left to do
+        h.close()
+    assert len(calls) == 5 and rt.h is None and model.h is None
+    # closed children are dropped from the parent's list when the next one registers
+    rt2 = cuda._Handle(1, lambda h: None)
+    for i in range(50):
+        cuda._Handle(10 + i, lambda h: None, rt2).close()
+    assert len(rt2.children) <= 1

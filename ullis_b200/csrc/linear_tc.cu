@@ -409,6 +409,20 @@ bool fp16_linear(ullis_cuda_runtime* rt, const float* x, const uint16_t* w, floa
     return true;
 }
 
+namespace {
+// y = sum of the split-K partials, in split order
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, float* __restrict__ y, uint32_t splits, size_t n) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;   // n % 4 == 0 (N % 8 == 0)
+    float4 acc = *reinterpret_cast<const float4*>(part + i);
+    for (uint32_t s = 1; s < splits; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(part + (size_t)s * n + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(y + i) = acc;
+}
+}  // namespace
+
 bool dense_nt(ullis_cuda_runtime* rt, const uint16_t* a16, const uint16_t* b16, float* y, size_t M, size_t K,
               size_t N) {
     if (!usable(rt) || !shape_ok(M, K, N)) return false;
@@ -418,6 +432,26 @@ bool dense_nt(ullis_cuda_runtime* rt, const uint16_t* a16, const uint16_t* b16, 
     maps.b[0] = make_map(b16, N, K, false);
     GemmParams p = base_params(rt, M, N, K);
     p.prob[0] = GemmProblem{nullptr, nullptr, nullptr, y, nullptr, nullptr};
+    // A long K under a few output tiles (a weight gradient: K = rows of the batch) is split over
+    // blockIdx.z so that the whole GPU works on it; the partials are then summed in split order.
+    const uint32_t tiles = (uint32_t)(((M + BM - 1) / BM) * ((N + BN - 1) / BN)), kb = (uint32_t)(K / BK);
+    if (tiles < (uint32_t)rt->sm_count && kb >= 32) {
+        uint32_t want = (2u * (uint32_t)rt->sm_count + tiles - 1) / tiles;
+        want = std::min(std::min(want, kb / 8), 64u);
+        const uint32_t per = (kb + want - 1) / want, splits = (kb + per - 1) / per;
+        if (splits > 1) {
+            float* part = rt->tc_ws[8].as<float>((size_t)splits * M * N);
+            p.split_k = splits;
+            p.prob[0].out = part;
+            dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), splits);
+            gemm_kernel<EPI_STORE, false><<<grid, GEMM_THREADS, gemm_smem_bytes(p.n_a, p.stages), rt->stream>>>(maps, p);
+            rt->launched("gemm_dense_nt_splitk");
+            const size_t n = M * N;
+            splitk_reduce_kernel<<<blocks_for((n + 3) / 4, 256), 256, 0, rt->stream>>>(part, y, splits, n);
+            rt->launched("splitk_reduce");
+            return true;
+        }
+    }
     launch<EPI_STORE, false>(rt, maps, p, 1, "gemm_dense_nt");
     return true;
 }

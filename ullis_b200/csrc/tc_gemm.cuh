@@ -66,6 +66,7 @@ struct GemmParams {
     const uint32_t* labels;  // EPI_CE
     uint32_t ignore_id;      // EPI_CE
     uint32_t n_tiles;        // EPI_CE: (max, sum exp) partials per row: one per vocabulary tile and epilogue warp group
+    uint32_t split_k;        // > 1 (gemm_kernel, one problem): blockIdx.z owns a K range and writes its own [M,N] partial
     uint32_t* status;
 };
 
@@ -222,10 +223,16 @@ gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     uint32_t* s_error = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t z = blockIdx.z;
-    const GemmProblem& pr = p.prob[z];
+    const uint32_t z = p.split_k > 1 ? 0u : blockIdx.z;
+    GemmProblem pr = p.prob[z];
     const uint32_t n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
-    const uint32_t KB = p.K / BK;
+    uint32_t KB = p.K / BK, kb0 = 0;
+    if (p.split_k > 1) {   // the host sizes the grid so that every split owns at least one k-block
+        const uint32_t per = (KB + p.split_k - 1) / p.split_k;
+        kb0 = blockIdx.z * per;
+        KB = min(per, KB - kb0);
+        pr.out = static_cast<float*>(pr.out) + (size_t)blockIdx.z * p.M * p.N;
+    }
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < STAGES; ++s) {
@@ -277,9 +284,10 @@ gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                 if (kb >= STAGES && !ptx::mbar_wait(&empty[s], ((kb / STAGES) & 1u) ^ 1u)) { atomicExch(s_error, 1u); break; }
                 uint8_t* st = tiles + s * stage_bytes;
                 ptx::mbar_arrive_expect_tx(&full_a[s], tx);
-                ptx::tma_load_2d(st, &maps.a[z][0], &full_a[s], (int32_t)(kb * BK), (int32_t)m0);
-                if (p.n_a == 2) ptx::tma_load_2d(st + TILE_BYTES, &maps.a[z][1], &full_a[s], (int32_t)(kb * BK), (int32_t)m0);
-                if (!PACKED) ptx::tma_load_2d(st + p.n_a * TILE_BYTES, &maps.b[z], &full_a[s], (int32_t)(kb * BK), (int32_t)n0);
+                const int32_t kx = (int32_t)((kb0 + kb) * BK);
+                ptx::tma_load_2d(st, &maps.a[z][0], &full_a[s], kx, (int32_t)m0);
+                if (p.n_a == 2) ptx::tma_load_2d(st + TILE_BYTES, &maps.a[z][1], &full_a[s], kx, (int32_t)m0);
+                if (!PACKED) ptx::tma_load_2d(st + p.n_a * TILE_BYTES, &maps.b[z], &full_a[s], kx, (int32_t)n0);
             }
             if (*s_error) {
                 // leave no copy in flight: wait (bounded) for every stage this thread filled last

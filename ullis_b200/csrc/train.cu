@@ -50,6 +50,26 @@ inline unsigned blocks_for(size_t n, unsigned per) { return (unsigned)((n + per 
 inline size_t pad64(size_t n) { return (n + 63) / 64 * 64; }
 
 // ------------------------------------------------------------ GEMM operands
+// the same for C == Cp, C % 4 == 0: four elements per thread
+__global__ void cast_rows4_kernel(const float* __restrict__ x, const uint16_t* __restrict__ colscale,
+                                  uint16_t* __restrict__ out, size_t R, size_t C, uint32_t* status) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= R * C) return;
+    const size_t r = i / C, c = i % C;
+    const float4 v = *reinterpret_cast<const float4*>(x + i);
+    float f[4] = {v.x, v.y, v.z, v.w};
+    if (colscale) {
+        const uint2 sw = *reinterpret_cast<const uint2*>(colscale + c);
+        f[0] = __fmul_rn(f[0], h2f((uint16_t)(sw.x & 0xFFFFu)));
+        f[1] = __fmul_rn(f[1], h2f((uint16_t)(sw.x >> 16)));
+        f[2] = __fmul_rn(f[2], h2f((uint16_t)(sw.y & 0xFFFFu)));
+        f[3] = __fmul_rn(f[3], h2f((uint16_t)(sw.y >> 16)));
+    }
+    const uint32_t lo = to_f16(f[0], status, r) | ((uint32_t)to_f16(f[1], status, r) << 16);
+    const uint32_t hi = to_f16(f[2], status, r) | ((uint32_t)to_f16(f[3], status, r) << 16);
+    *reinterpret_cast<uint2*>(out + i) = make_uint2(lo, hi);
+}
+
 // out [R, Cp] = FP16(x [R, C] * colscale[c]), columns C..Cp zero
 __global__ void cast_rows_kernel(const float* __restrict__ x, const uint16_t* __restrict__ colscale,
                                  uint16_t* __restrict__ out, size_t R, size_t C, size_t Cp, uint32_t* status) {
@@ -64,12 +84,14 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, const uint16_t* __
     out[i] = to_f16(v, status, r);
 }
 
-// out [C, Rp] = FP16(op(x [R, C]))^T, columns R..Rp zero.  op 1: relu(x)^2
-__global__ void transpose_cast_kernel(const float* __restrict__ x, uint16_t* __restrict__ out, size_t R, size_t C,
-                                      size_t Rp, int op, uint32_t* status) {
-    __shared__ float tile[32][33];
-    const size_t r0 = (size_t)blockIdx.x * 32, c0 = (size_t)blockIdx.y * 32;
-    for (int j = threadIdx.y; j < 32; j += 8) {
+// out [C, Rp] = FP16(op(x [R, C]))^T, columns R..Rp zero (Rp % 64 == 0).  op 1: relu(x)^2
+// A CTA moves 64 rows x 32 columns; a thread stores two consecutive rows of a column as one word.
+__global__ void __launch_bounds__(256)
+transpose_cast_kernel(const float* __restrict__ x, uint16_t* __restrict__ out, size_t R, size_t C, size_t Rp, int op,
+                      uint32_t* status) {
+    __shared__ float tile[64][33];
+    const size_t r0 = (size_t)blockIdx.x * 64, c0 = (size_t)blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 64; j += 8) {
         const size_t r = r0 + j, c = c0 + threadIdx.x;
         float v = (r < R && c < C) ? x[r * C + c] : 0.0f;
         if (op == 1) { v = fmaxf(v, 0.0f); v *= v; }
@@ -77,8 +99,12 @@ __global__ void transpose_cast_kernel(const float* __restrict__ x, uint16_t* __r
     }
     __syncthreads();
     for (int j = threadIdx.y; j < 32; j += 8) {
-        const size_t c = c0 + j, r = r0 + threadIdx.x;
-        if (c < C && r < Rp) out[c * Rp + r] = to_f16(tile[threadIdx.x][j], status, r);
+        const size_t c = c0 + j, r = r0 + 2 * threadIdx.x;
+        if (c < C) {   // r + 1 < Rp: Rp is a multiple of 64
+            const uint32_t lo = to_f16(tile[2 * threadIdx.x][j], status, r);
+            const uint32_t hi = to_f16(tile[2 * threadIdx.x + 1][j], status, r + 1);
+            *reinterpret_cast<uint32_t*>(out + c * Rp + r) = lo | (hi << 16);
+        }
     }
 }
 
@@ -247,10 +273,19 @@ ln_backward_kernel(const float* __restrict__ x, const float* __restrict__ gy, co
 // ------------------------------------------------------------ CMix pieces
 // g <- key > 0 ? 2*key*g : 0   (relu2_bwd_on, src/model.rs:1189-1204)
 __global__ void relu2_bwd_kernel(const float* __restrict__ key, float* __restrict__ g, size_t n) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= n) return;
-    const float k = key[i];
-    g[i] = k > 0.0f ? 2.0f * k * g[i] : 0.0f;
+    if (i + 4 <= n) {
+        const float4 k = *reinterpret_cast<const float4*>(key + i);
+        float4 v = *reinterpret_cast<const float4*>(g + i);
+        v.x = k.x > 0.0f ? 2.0f * k.x * v.x : 0.0f;
+        v.y = k.y > 0.0f ? 2.0f * k.y * v.y : 0.0f;
+        v.z = k.z > 0.0f ? 2.0f * k.z * v.z : 0.0f;
+        v.w = k.w > 0.0f ? 2.0f * k.w * v.w : 0.0f;
+        *reinterpret_cast<float4*>(g + i) = v;
+        return;
+    }
+    for (size_t j = i; j < n; ++j) g[j] = key[j] > 0.0f ? 2.0f * key[j] * g[j] : 0.0f;
 }
 
 // lerp_shift_backward (src/model.rs:1206-1240): out[t] = (g[t] - g[t]*mix) + g[t+1]*mix
@@ -338,18 +373,25 @@ g_scale_kernel(const float* __restrict__ G, const uint32_t* __restrict__ bits, f
 }
 
 // Embedding rows: one clipped step per ROW in row order (src/model.rs:2980-2987), so a token that
-// occurs n times is stepped n times.  A CTA per distinct token, a thread per channel.
+// occurs n times is stepped n times.  A thread per (distinct token, channel).
 __global__ void embed_sgd_kernel(uint16_t* __restrict__ emb, float* __restrict__ residual, const float* __restrict__ gx,
                                  const uint32_t* __restrict__ toks, const uint32_t* __restrict__ starts,
                                  const uint32_t* __restrict__ order, size_t d, float gmul, float lr) {
     const uint32_t tok = toks[blockIdx.x], r0 = starts[blockIdx.x], r1 = starts[blockIdx.x + 1];
-    for (size_t c = threadIdx.x; c < d; c += blockDim.x) {
-        uint16_t wb = emb[(size_t)tok * d + c];
-        float r = residual[(size_t)tok * d + c];
-        for (uint32_t k = r0; k < r1; ++k) clipped_step(wb, r, __fmul_rn(gx[(size_t)order[k] * d + c], gmul), lr);
-        emb[(size_t)tok * d + c] = wb;
-        residual[(size_t)tok * d + c] = r;
+    const size_t c = (size_t)blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= d) return;
+    uint16_t wb = emb[(size_t)tok * d + c];
+    float r = residual[(size_t)tok * d + c];
+    for (uint32_t k0 = r0; k0 < r1; k0 += 8) {
+        float g[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = k0 + j < r1 ? gx[(size_t)order[k0 + j] * d + c] : 0.0f;   // loads go out together
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (k0 + j < r1) clipped_step(wb, r, __fmul_rn(g[j], gmul), lr);                       // steps stay in row order
     }
+    emb[(size_t)tok * d + c] = wb;
+    residual[(size_t)tok * d + c] = r;
 }
 
 __global__ void init_latent_kernel(const uint32_t* __restrict__ bits, uint16_t* __restrict__ latent, size_t n) {
@@ -372,11 +414,14 @@ struct Step {
         rt->launched("gemm_nt_plain");
     }
     void cast_rows(const float* x, const uint16_t* colscale, uint16_t* out, size_t R, size_t C, size_t Cp) {
-        cast_rows_kernel<<<blocks_for(R * Cp, 256), 256, 0, rt->stream>>>(x, colscale, out, R, C, Cp, rt->dev_status);
+        if (C == Cp && C % 4 == 0 && (reinterpret_cast<uintptr_t>(colscale) & 7) == 0)
+            cast_rows4_kernel<<<blocks_for(R * C / 4, 256), 256, 0, rt->stream>>>(x, colscale, out, R, C, rt->dev_status);
+        else
+            cast_rows_kernel<<<blocks_for(R * Cp, 256), 256, 0, rt->stream>>>(x, colscale, out, R, C, Cp, rt->dev_status);
         rt->launched("cast_rows");
     }
     void transpose_cast(const float* x, uint16_t* out, size_t R, size_t C, size_t Rp, int op = 0) {
-        dim3 grid(blocks_for(Rp, 32), blocks_for(C, 32)), block(32, 8);
+        dim3 grid(blocks_for(Rp, 64), blocks_for(C, 32)), block(32, 8);
         transpose_cast_kernel<<<grid, block, 0, rt->stream>>>(x, out, R, C, Rp, op, rt->dev_status);
         rt->launched("transpose_cast");
     }
@@ -668,7 +713,7 @@ void ullis_cuda_train_state::step(const uint32_t* tokens, const uint32_t* labels
             s.gemm(A16, B16, G, d, rows_p, f);
             s.sgd(T.value, G, learning_rate);
         }
-        relu2_bwd_kernel<<<blocks_for(rows * f, 256), 256, 0, rt->stream>>>(W1, W2, rows * f);        // g_key
+        relu2_bwd_kernel<<<blocks_for((rows * f + 3) / 4, 256), 256, 0, rt->stream>>>(W1, W2, rows * f);        // g_key
         rt->launched("relu2_bwd");
         // key (src/model.rs:1141-1163)
         s.cast_rows(W2, L.key.scale, A16, rows, f, f_p);
@@ -705,7 +750,7 @@ void ullis_cuda_train_state::step(const uint32_t* tokens, const uint32_t* labels
         }
     }
     // ---- embedding rows (src/model.rs:2980-2987)
-    embed_sgd_kernel<<<(unsigned)h_toks.size(), 128, 0, rt->stream>>>(embedding.w, embedding.residual, GX,
+    embed_sgd_kernel<<<dim3((unsigned)h_toks.size(), blocks_for(d, 128)), 128, 0, rt->stream>>>(embedding.w, embedding.residual, GX,
                                                                       toks.as<uint32_t>(1), starts.as<uint32_t>(1),
                                                                       order.as<uint32_t>(1), d, s.gmul, learning_rate);
     rt->launched("embed_sgd");

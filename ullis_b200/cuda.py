@@ -92,6 +92,28 @@ def load_library() -> C.CDLL:
     return _LIB
 
 
+class _Handle:
+    """A C handle with the handles that borrow it.  Runtime -> model -> state handles must be
+    destroyed children first, but a garbage collection that finds the Python objects unreachable
+    together runs their finalisers in no particular order (and has cleared weak references by
+    then), so each parent handle keeps its children's handles and closes them before itself.
+    A child handle does not refer to its parent: no reference cycle is formed."""
+
+    def __init__(self, h, destroy, parent: "_Handle | None" = None):
+        self.h, self._destroy, self.children = h, destroy, []
+        if parent is not None:
+            parent.children[:] = [c for c in parent.children if c.h]   # drop the ones already closed
+            parent.children.append(self)
+
+    def close(self):
+        for child in self.children:
+            child.close()
+        self.children = []
+        if self.h:
+            self._destroy(self.h)
+            self.h = None
+
+
 def _ptr(a):
     return None if a is None else C.c_void_p(a.ctypes.data)
 
@@ -120,13 +142,16 @@ class CudaRuntime:
         rc = self._lib.ullis_cuda_runtime_create(C.c_int32(device), C.byref(h))
         if rc != OK:
             raise UllisCudaError(rc, self._lib.ullis_cuda_last_error(None).decode())
-        self._h = h
+        self._handle = _Handle(h, self._lib.ullis_cuda_runtime_destroy)
         self.device = device
 
+    @property
+    def _h(self):
+        return self._handle.h
+
     def close(self):
-        if getattr(self, "_h", None):
-            self._lib.ullis_cuda_runtime_destroy(self._h)
-            self._h = None
+        if getattr(self, "_handle", None):
+            self._handle.close()
 
     def __del__(self):
         try:
@@ -346,16 +371,19 @@ class CudaHeron:
         buf = np.frombuffer(checkpoint_bytes, dtype=np.uint8)
         h = C.c_void_p()
         runtime._check(self._lib.ullis_cuda_model_load_safetensors(runtime._h, _ptr(buf), _z(buf.size), C.byref(h)))
-        self._h = h
+        self._handle = _Handle(h, self._lib.ullis_cuda_model_destroy, runtime._handle)
         dims = (C.c_size_t * 6)()
         self._lib.ullis_cuda_model_dims(self._h, dims)
         self.d_model, self.n_layers, self.vocab_size, self.context_len, self.batch_size, self.dim_ffn = \
             [int(v) for v in dims]
 
+    @property
+    def _h(self):
+        return self._handle.h
+
     def close(self):
-        if getattr(self, "_h", None):
-            self._lib.ullis_cuda_model_destroy(self._h)
-            self._h = None
+        if getattr(self, "_handle", None):
+            self._handle.close()
 
     def __del__(self):
         try:
@@ -445,7 +473,11 @@ class CudaGenerateState:
         self._lib = model._lib
         h = C.c_void_p()
         model.rt._check(self._lib.ullis_cuda_generate_state_create(model._h, _z(batch), C.byref(h)))
-        self._h = h
+        self._handle = _Handle(h, self._lib.ullis_cuda_generate_state_destroy, model._handle)
+
+    @property
+    def _h(self):
+        return self._handle.h
 
     @property
     def time(self) -> int:
@@ -461,9 +493,8 @@ class CudaGenerateState:
         return out
 
     def close(self):
-        if getattr(self, "_h", None):
-            self._lib.ullis_cuda_generate_state_destroy(self._h)
-            self._h = None
+        if getattr(self, "_handle", None):
+            self._handle.close()
 
     def __del__(self):
         try:
@@ -489,7 +520,11 @@ class CudaTrainState:
         buf = None if checkpoint is None else (C.c_uint8 * len(checkpoint)).from_buffer_copy(checkpoint)
         model.rt._check(self._lib.ullis_cuda_train_state_create(model._h, buf, _z(0 if checkpoint is None else
                                                                                   len(checkpoint)), C.byref(h)))
-        self._h = h
+        self._handle = _Handle(h, self._lib.ullis_cuda_train_state_destroy, model._handle)
+
+    @property
+    def _h(self):
+        return self._handle.h
 
     def train_step(self, tokens, labels, ignore_id: int, batch: int, time: int, learning_rate: float) -> dict:
         t = _arr(tokens, np.uint32, "tokens", batch * time)
@@ -509,9 +544,8 @@ class CudaTrainState:
         return out
 
     def close(self):
-        if getattr(self, "_h", None):
-            self._lib.ullis_cuda_train_state_destroy(self._h)
-            self._h = None
+        if getattr(self, "_handle", None):
+            self._handle.close()
 
     def __del__(self):
         try:
