@@ -85,26 +85,49 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, const uint16_t* __
 }
 
 // out [C, Rp] = FP16(op(x [R, C]))^T, columns R..Rp zero (Rp % 64 == 0).  op 1: relu(x)^2
-// A CTA moves 64 rows x 32 columns; a thread stores two consecutive rows of a column as one word.
+// A CTA moves 64 rows x 64 columns: 16-byte loads along a row, 16-byte stores of eight consecutive
+// rows of one column.
 __global__ void __launch_bounds__(256)
 transpose_cast_kernel(const float* __restrict__ x, uint16_t* __restrict__ out, size_t R, size_t C, size_t Rp, int op,
                       uint32_t* status) {
-    __shared__ float tile[64][33];
-    const size_t r0 = (size_t)blockIdx.x * 64, c0 = (size_t)blockIdx.y * 32;
-    for (int j = threadIdx.y; j < 64; j += 8) {
-        const size_t r = r0 + j, c = c0 + threadIdx.x;
-        float v = (r < R && c < C) ? x[r * C + c] : 0.0f;
-        if (op == 1) { v = fmaxf(v, 0.0f); v *= v; }
-        tile[j][threadIdx.x] = v;
+    __shared__ float tile[64][65];
+    const size_t r0 = (size_t)blockIdx.x * 64, c0 = (size_t)blockIdx.y * 64;
+    const bool vec = (C & 3) == 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int slot = threadIdx.x + k * 256;      // 64 rows x 16 groups of four columns
+        const int j = slot >> 4, q = (slot & 15) * 4;
+        const size_t r = r0 + j, c = c0 + q;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (r < R) {
+            if (vec && c + 3 < C) {
+                const float4 t = *reinterpret_cast<const float4*>(x + r * C + c);
+                v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+            } else {
+                for (int e = 0; e < 4; ++e) if (c + e < C) v[e] = x[r * C + c + e];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float t = v[e];
+            if (op == 1) { t = fmaxf(t, 0.0f); t *= t; }
+            tile[j][q + e] = t;
+        }
     }
     __syncthreads();
-    for (int j = threadIdx.y; j < 32; j += 8) {
-        const size_t c = c0 + j, r = r0 + 2 * threadIdx.x;
-        if (c < C) {   // r + 1 < Rp: Rp is a multiple of 64
-            const uint32_t lo = to_f16(tile[2 * threadIdx.x][j], status, r);
-            const uint32_t hi = to_f16(tile[2 * threadIdx.x + 1][j], status, r + 1);
-            *reinterpret_cast<uint32_t*>(out + c * Rp + r) = lo | (hi << 16);
+    const int cl = threadIdx.x >> 2, seg = (threadIdx.x & 3) * 16;   // column, first of its sixteen rows
+    const size_t c = c0 + cl;
+    if (c >= C) return;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int j = seg + h * 8 + e * 2;
+            w[e] = (uint32_t)to_f16(tile[j][cl], status, r0 + j) | ((uint32_t)to_f16(tile[j + 1][cl], status, r0 + j + 1) << 16);
         }
+        // r0 + seg + 8h + 7 < Rp: Rp is a multiple of 64
+        *reinterpret_cast<uint4*>(out + c * Rp + r0 + seg + h * 8) = make_uint4(w[0], w[1], w[2], w[3]);
     }
 }
 
@@ -421,8 +444,8 @@ struct Step {
         rt->launched("cast_rows");
     }
     void transpose_cast(const float* x, uint16_t* out, size_t R, size_t C, size_t Rp, int op = 0) {
-        dim3 grid(blocks_for(Rp, 64), blocks_for(C, 32)), block(32, 8);
-        transpose_cast_kernel<<<grid, block, 0, rt->stream>>>(x, out, R, C, Rp, op, rt->dev_status);
+        dim3 grid(blocks_for(Rp, 64), blocks_for(C, 64));
+        transpose_cast_kernel<<<grid, 256, 0, rt->stream>>>(x, out, R, C, Rp, op, rt->dev_status);
         rt->launched("transpose_cast");
     }
     void unpack_transpose(const uint32_t* bits, uint16_t* out, size_t out_f, size_t in_f, size_t outp) {
