@@ -226,6 +226,22 @@ ULLIS_CUDA_API int32_t ullis_cuda_model_train_step(ullis_cuda_train_state* state
 ULLIS_CUDA_API int32_t ullis_cuda_train_state_read(ullis_cuda_train_state* state, const char* name, void* dst,
                                                    size_t bytes);
 
+/* UllisHeron::install_head_unigram_prior (src/model.rs:3034-3110): bias[v] =
+ * log((count_v + 1) / (n + V)) minus its mean over the vocabulary, from the
+ * supervised labels, and the row scales times 0.25 if their mean is still
+ * within a factor two of 1/sqrt(d_model).  Skipped (applied = 0) when mean
+ * |bias| already exceeds 0.05.  ULLIS_CUDA_ERR_ARG without any supervised label. */
+typedef struct ullis_cuda_head_unigram_install {
+    int32_t applied;
+    uint64_t n_targets;
+    float bias_rms, scale_rms;
+    int32_t shrunk_kaiming_scale;
+} ullis_cuda_head_unigram_install;
+ULLIS_CUDA_API int32_t ullis_cuda_train_state_install_head_unigram_prior(ullis_cuda_train_state* state,
+                                                                         const uint32_t* labels, size_t n,
+                                                                         uint32_t ignore_id,
+                                                                         ullis_cuda_head_unigram_install* result);
+
 /* ------------------------------------------------------------------ op level
  * Host pointers in, caller-allocated host buffers out; one synchronous call
  * each, like the MetalRuntime methods they mirror. */
@@ -254,6 +270,39 @@ ULLIS_CUDA_API int32_t ullis_cuda_cmix_relu2(ullis_cuda_runtime* rt, const float
 /* MetalRuntime::residual_add (src/metal.rs:1078): out = residual + update. */
 ULLIS_CUDA_API int32_t ullis_cuda_residual_add(ullis_cuda_runtime* rt, const float* residual, const float* update, float* out,
                                 size_t n);
+
+/* MetalRuntime::clipped_sgd_fp16 (src/metal.rs:3053): Fp16Storage::apply_clipped_sgd
+ * (src/precision.rs:106-113) on every element; FP16 bits and f32 carry in and out.
+ * Bit-identical to the reference's CPU step. */
+ULLIS_CUDA_API int32_t ullis_cuda_clipped_sgd_fp16(ullis_cuda_runtime* rt, const uint16_t* parameters,
+                                                   const float* residual, const float* gradient, float learning_rate,
+                                                   size_t n, uint16_t* next_parameters, float* next_residual);
+/* MetalRuntime::binaryconnect_sgd_fp16 (src/metal.rs:3069): apply_binaryconnect_sgd
+ * (src/precision.rs:124-134). Bit-identical to the reference's CPU step. */
+ULLIS_CUDA_API int32_t ullis_cuda_binaryconnect_sgd_fp16(ullis_cuda_runtime* rt, const uint16_t* parameters,
+                                                         const float* residual, const float* gradient,
+                                                         float learning_rate, size_t n, uint16_t* next_parameters,
+                                                         float* next_residual);
+/* MetalRuntime::apply_latent_sgd (src/metal.rs:3006): the BinaryConnect step on
+ * gradient * ste_scale, then next_bits [(n+31)/32] = latent >= 0 (rebinarize,
+ * src/model.rs:878-884). */
+ULLIS_CUDA_API int32_t ullis_cuda_apply_latent_sgd(ullis_cuda_runtime* rt, const uint16_t* latent, const float* residual,
+                                                   const float* gradient, float learning_rate, float ste_scale, size_t n,
+                                                   uint16_t* next_latent, float* next_residual, uint32_t* next_bits);
+/* MetalRuntime::rosa_qkv_1bit_bwd_e (src/metal.rs:1258); rosa_e_grad
+ * (src/model.rs:1608-1634): g_e[c] = sum over (b,t) of gy * (2*idx - 1). */
+ULLIS_CUDA_API int32_t ullis_cuda_rosa_qkv_1bit_bwd_e(ullis_cuda_runtime* rt, const float* output_gradient,
+                                                      const uint8_t* idx, size_t batch, size_t time, size_t channels,
+                                                      float* g_e);
+/* MetalRuntime::cmix_relu2_backward (src/metal.rs:1546): gx = input > 0 ? 2*input*gy : 0. */
+ULLIS_CUDA_API int32_t ullis_cuda_cmix_relu2_backward(ullis_cuda_runtime* rt, const float* input,
+                                                      const float* output_gradient, float* gx, size_t n);
+/* MetalRuntime::layer_norm_backward (src/metal.rs:1628); LayerNorm::backward
+ * (src/model.rs:270-315). weight as FP16 bits; gx [rows*channels], gw, gb [channels]. */
+ULLIS_CUDA_API int32_t ullis_cuda_layer_norm_backward(ullis_cuda_runtime* rt, const float* input,
+                                                      const float* output_gradient, const uint16_t* weight, size_t rows,
+                                                      size_t channels, float* gx, float* gw, float* gb);
+
 /* MetalRuntime::rosa_qkv_1bit_fwd (src/metal.rs:1168); rosa_qkv_batch_packed +
  * rosa_qkv_out_batched (src/rosa.rs:459-481, 585-609).  q/k/v_bits: packed
  * planes over the flat [B,T,C] index; e: FP16 bits [C]; idx u8 [B,T,C]

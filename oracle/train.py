@@ -266,3 +266,36 @@ class HeronTrainer:
         self.residual["embedding"] = res.reshape(-1)
         return {"loss": mean, "n_valid": n_valid, "flips_head": flips_head, "flips_cmix": flips_cmix,
                 "flips_rosa_o": flips_o, "embed_grad": g_x}
+
+    def install_head_unigram_prior(self, labels, ignore_id):
+        """install_head_unigram_prior + shrink_head_kaiming_scale (src/model.rs:3034-3110)."""
+        m, t = self.m, self.m.t
+        vocab = m.vocab
+        bias = O.fp16_to_f32(t["head.bias"])
+        rms = lambda bits: float(np.sqrt((O.fp16_to_f32(bits) ** 2).sum(dtype=np.float32) / np.float32(bits.size)))
+        if float(np.abs(bias).sum(dtype=np.float32) / np.float32(vocab)) > 0.05:   # HEAD_BIAS_PRIOR_ABS_EPS
+            return {"applied": False, "n_targets": 0, "bias_rms": rms(t["head.bias"]), "scale_rms": rms(t["head.scale"]),
+                    "shrunk_kaiming_scale": False}
+        labels = np.asarray(labels, np.uint32)
+        keep = labels[(labels != np.uint32(ignore_id)) & (labels < vocab)]
+        if keep.size == 0:
+            raise ValueError("head unigram prior needs at least one supervised label")
+        counts = np.bincount(keep, minlength=vocab).astype(np.float32)
+        logs = (np.log1p(counts, dtype=np.float32) - np.log(np.float32(keep.size) + np.float32(vocab), dtype=np.float32))
+        log_sum = np.float32(0)
+        for v in logs.astype(np.float32):      # sequential f32 sum, as the reference
+            log_sum = np.float32(log_sum + v)
+        t["head.bias"] = O.fp16_from_f32((logs - log_sum / np.float32(vocab)).astype(np.float32))
+        self.residual["head.bias"][:] = 0      # Fp16Storage::set clears the carry (src/precision.rs:208-211)
+        scale = O.fp16_to_f32(t["head.scale"])
+        mean = np.float32(0)
+        for v in scale:
+            mean = np.float32(mean + v)
+        mean = mean / np.float32(vocab)
+        kaiming = np.float32(1.0) / np.sqrt(np.float32(m.d))
+        shrunk = bool(kaiming * np.float32(0.5) < mean < kaiming * np.float32(2.0))
+        if shrunk:
+            t["head.scale"] = O.fp16_from_f32((scale * np.float32(0.25)).astype(np.float32))   # HEAD_KAIMING_SCALE_SHRINK
+            self.residual["head.scale"][:] = 0
+        return {"applied": True, "n_targets": int(keep.size), "bias_rms": rms(t["head.bias"]),
+                "scale_rms": rms(t["head.scale"]), "shrunk_kaiming_scale": shrunk}

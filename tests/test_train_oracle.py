@@ -193,3 +193,37 @@ def test_carry_tensors_of_a_checkpoint_are_restored():
     assert np.array_equal(tr.residual["head.latent"], tensors["head.latent.residual"])
     assert np.array_equal(tr.residual["embedding"], tensors["embedding.residual"])
     assert not tr.residual["ln_out.weight"].any()
+
+
+def _kaiming_head_checkpoint(d=16, vocab=260):
+    """Head as the reference initialises it: zero bias, row scale 1/sqrt(d) (src/model.rs:569-592)."""
+    cfg = synth.train_config(d, 1, vocab, 32, 2, 64)
+    tensors = synth.heron_tensors(cfg, seed=3, ln_gain_one=True)
+    tensors["head.bias"] = np.zeros(vocab, np.uint16)
+    tensors["head.scale"] = f16(np.full(vocab, 1.0 / np.sqrt(d)))
+    from ullis_b200 import checkpoint as ckpt
+    return ckpt.to_safetensors_bytes(tensors, cfg, step=0)
+
+
+def test_head_unigram_prior_install():
+    # unigram_prior_drops_ce_toward_batch_unigram (src/model.rs:4744-4776)
+    data = _kaiming_head_checkpoint()
+    tokens = np.array([4 + i % 8 for i in range(32)], np.uint32)
+    before = T.HeronTrainer(data).train_step(tokens, tokens, O.CE_NO_IGNORE, 1, 32, 1e-8)["loss"]
+    tr = T.HeronTrainer(data)
+    corpus = np.array([4 + i % 8 for i in range(4096)], np.uint32)
+    prior = tr.install_head_unigram_prior(corpus, O.CE_NO_IGNORE)
+    assert prior["applied"] and prior["shrunk_kaiming_scale"] and prior["n_targets"] == 4096
+    assert prior["bias_rms"] > 0.2
+    bias = O.fp16_to_f32(tr.m.t["head.bias"])
+    # log((count+1)/(n+V)) minus its mean: seen classes share one value, unseen ones another
+    seen, unseen = np.log1p(512.0) - np.log(4096 + 260.0), -np.log(4096 + 260.0)
+    mean = (8 * seen + 252 * unseen) / 260
+    assert np.allclose(bias[4:12], seen - mean, atol=2e-3) and np.allclose(bias[20:30], unseen - mean, atol=2e-3)
+    assert np.allclose(O.fp16_to_f32(tr.m.t["head.scale"]), 0.25 / 4.0, atol=1e-4)
+    after = tr.train_step(tokens, tokens, O.CE_NO_IGNORE, 1, 32, 1e-8)["loss"]
+    assert after < before - 0.5 and after < np.log(8) + 1.0
+    skipped = tr.install_head_unigram_prior(corpus, O.CE_NO_IGNORE)
+    assert not skipped["applied"] and skipped["n_targets"] == 0
+    with pytest.raises(ValueError):
+        T.HeronTrainer(data).install_head_unigram_prior(np.full(8, 3, np.uint32), 3)

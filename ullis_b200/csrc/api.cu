@@ -487,6 +487,128 @@ int32_t ullis_cuda_train_state_read(ullis_cuda_train_state* state, const char* n
     });
 }
 
+int32_t ullis_cuda_train_state_install_head_unigram_prior(ullis_cuda_train_state* state, const uint32_t* labels,
+                                                          size_t n, uint32_t ignore_id,
+                                                          ullis_cuda_head_unigram_install* result) {
+    if (!state) {
+        set_global_error("train state handle is null");
+        return ULLIS_CUDA_ERR_ARG;
+    }
+    return guard_model(state->m, [&] { state->install_head_unigram_prior(labels, n, ignore_id, result); });
+}
+
+namespace {
+// clipped (ste_scale < 0) or BinaryConnect step of n elements through pool slots 0..3
+void sgd_op(ullis_cuda_runtime* rt, const uint16_t* parameters, const float* residual, const float* gradient, float lr,
+            float ste_scale, size_t n, uint16_t* next_parameters, float* next_residual, uint32_t* next_bits,
+            const char* what) {
+    if (n == 0) return;
+    need_ptr(parameters, "parameters"); need_ptr(residual, "residual"); need_ptr(gradient, "gradient");
+    need_ptr(next_parameters, "next_parameters"); need_ptr(next_residual, "next_residual");
+    (void)what;
+    uint16_t* dw = stage(rt, 0, parameters, n);
+    float* dr = stage(rt, 1, residual, n);
+    float* dg = stage(rt, 2, gradient, n);
+    uint32_t* dbits = next_bits ? rt->pool[3].as<uint32_t>((n + 31) / 32) : nullptr;
+    if (ste_scale < 0.0f)
+        k::clipped_sgd(rt, dw, dr, dg, lr, n);
+    else
+        k::latent_sgd(rt, dw, dr, dg, lr, ste_scale, dbits, n);
+    rt->d2h(next_parameters, dw, n * 2);
+    rt->d2h(next_residual, dr, n * 4);
+    if (next_bits) rt->d2h(next_bits, dbits, (n + 31) / 32 * 4);
+    rt->sync();
+}
+}  // namespace
+
+int32_t ullis_cuda_clipped_sgd_fp16(ullis_cuda_runtime* rt, const uint16_t* parameters, const float* residual,
+                                    const float* gradient, float learning_rate, size_t n, uint16_t* next_parameters,
+                                    float* next_residual) {
+    return guard(rt, [&] {
+        sgd_op(rt, parameters, residual, gradient, learning_rate, -1.0f, n, next_parameters, next_residual, nullptr,
+               "clipped");
+    });
+}
+
+int32_t ullis_cuda_binaryconnect_sgd_fp16(ullis_cuda_runtime* rt, const uint16_t* parameters, const float* residual,
+                                          const float* gradient, float learning_rate, size_t n,
+                                          uint16_t* next_parameters, float* next_residual) {
+    return guard(rt, [&] {
+        sgd_op(rt, parameters, residual, gradient, learning_rate, 1.0f, n, next_parameters, next_residual, nullptr,
+               "binaryconnect");
+    });
+}
+
+int32_t ullis_cuda_apply_latent_sgd(ullis_cuda_runtime* rt, const uint16_t* latent, const float* residual,
+                                    const float* gradient, float learning_rate, float ste_scale, size_t n,
+                                    uint16_t* next_latent, float* next_residual, uint32_t* next_bits) {
+    return guard(rt, [&] {
+        if (n) need_ptr(next_bits, "next_bits");
+        if (!(ste_scale >= 0.0f)) fail(ULLIS_CUDA_ERR_ARG, "ste_scale must be non-negative");
+        sgd_op(rt, latent, residual, gradient, learning_rate, ste_scale, n, next_latent, next_residual, next_bits,
+               "latent");
+    });
+}
+
+int32_t ullis_cuda_rosa_qkv_1bit_bwd_e(ullis_cuda_runtime* rt, const float* output_gradient, const uint8_t* idx,
+                                       size_t batch, size_t time, size_t channels, float* g_e) {
+    return guard(rt, [&] {
+        if (channels == 0) fail(ULLIS_CUDA_ERR_SHAPE, "ROSA g_e shape mismatch");
+        const size_t rows = mul_or_fail(batch, time, "ROSA g_e"), n = mul_or_fail(rows, channels, "ROSA g_e");
+        need_ptr(g_e, "g_e");
+        float* dge = rt->pool[2].as<float>(channels);
+        if (n == 0) {
+            rt->zero(dge, channels * 4);
+        } else {
+            need_ptr(output_gradient, "output_gradient"); need_ptr(idx, "idx");
+            float* dgy = stage(rt, 0, output_gradient, n);
+            uint8_t* didx = stage(rt, 1, idx, n);
+            k::rosa_e_grad(rt, dgy, didx, dge, rows, channels, rt->pool[3]);
+        }
+        rt->d2h(g_e, dge, channels * 4);
+        rt->sync();
+    });
+}
+
+int32_t ullis_cuda_cmix_relu2_backward(ullis_cuda_runtime* rt, const float* input, const float* output_gradient,
+                                       float* gx, size_t n) {
+    return guard(rt, [&] {
+        if (n == 0) return;
+        need_ptr(input, "input"); need_ptr(output_gradient, "output_gradient"); need_ptr(gx, "gx");
+        float* din = stage(rt, 0, input, n);
+        float* dg = stage(rt, 1, output_gradient, n);
+        k::relu2_backward(rt, din, dg, n);
+        rt->d2h(gx, dg, n * 4);
+        rt->sync();
+    });
+}
+
+int32_t ullis_cuda_layer_norm_backward(ullis_cuda_runtime* rt, const float* input, const float* output_gradient,
+                                       const uint16_t* weight, size_t rows, size_t channels, float* gx, float* gw,
+                                       float* gb) {
+    return guard(rt, [&] {
+        if (channels == 0) fail(ULLIS_CUDA_ERR_SHAPE, "LayerNorm backward shape mismatch");
+        const size_t n = mul_or_fail(rows, channels, "LayerNorm backward");
+        need_ptr(weight, "weight"); need_ptr(gw, "gw"); need_ptr(gb, "gb");
+        float* dsmall = rt->pool[5].as<float>(2 * channels);
+        if (n == 0) {
+            rt->zero(dsmall, 2 * channels * 4);
+        } else {
+            need_ptr(input, "input"); need_ptr(output_gradient, "output_gradient"); need_ptr(gx, "gx");
+            float* dx = stage(rt, 0, input, n);
+            float* dgy = stage(rt, 1, output_gradient, n);
+            uint16_t* dw = stage(rt, 2, weight, channels);
+            float* dgx = rt->pool[3].as<float>(n);
+            float* dxh = rt->pool[4].as<float>(n);
+            k::layer_norm_backward(rt, dx, dgy, dw, dgx, dxh, dsmall, dsmall + channels, rows, channels, rt->pool[6]);
+            rt->d2h(gx, dgx, n * 4);
+        }
+        rt->d2h(gw, dsmall, channels * 4);
+        rt->d2h(gb, dsmall + channels, channels * 4);
+        rt->sync();
+    });
+}
+
 int32_t ullis_cuda_layer_norm(ullis_cuda_runtime* rt, const float* x, const uint16_t* weight,
                               const uint16_t* bias, float* y, size_t rows, size_t channels) {
     return guard(rt, [&] {

@@ -56,5 +56,21 @@ void ce_rows_from_logits(ullis_cuda_runtime* rt, const float* logits, const uint
 void ce_reduce(ullis_cuda_runtime* rt, const float* row_loss, const uint32_t* labels, uint32_t ignore_id,
                size_t rows, size_t time, double* loss_sum, unsigned long long* n_valid);
 
+
+// ---- train.cu  (op-level forms of the training kernels)
+// Fp16Storage::apply_clipped_sgd element by element (src/precision.rs:106-113), in place.
+void clipped_sgd(ullis_cuda_runtime* rt, uint16_t* w, float* residual, const float* g, float lr, size_t n);
+// apply_binaryconnect_sgd on g * ste_scale (src/precision.rs:124-134), in place; bits (nullable) <- latent >= 0.
+void latent_sgd(ullis_cuda_runtime* rt, uint16_t* latent, float* residual, const float* g, float lr, float ste_scale,
+                uint32_t* bits, size_t n);
+// g_e[c] = sum over rows of gy * (2*idx - 1)   (src/model.rs:1608-1634)
+void rosa_e_grad(ullis_cuda_runtime* rt, const float* gy, const uint8_t* idx, float* g_e, size_t rows, size_t channels,
+                 DeviceBuffer& scratch);
+// g <- input > 0 ? 2*input*g : 0   (src/model.rs:1189-1204)
+void relu2_backward(ullis_cuda_runtime* rt, const float* input, float* g, size_t n);
+// LayerNorm::backward (src/model.rs:270-315); xhat is scratch of the input's size.
+void layer_norm_backward(ullis_cuda_runtime* rt, const float* x, const float* gy, const uint16_t* w, float* gx,
+                         float* xhat, float* gw, float* gb, size_t rows, size_t channels, DeviceBuffer& scratch);
+
 }  // namespace k
 }  // namespace ullis

@@ -356,7 +356,7 @@ latent_sgd_kernel(uint16_t* __restrict__ latent, float* __restrict__ residual, c
     const size_t n = out_f * in_f;
     bool plus = false;
     if (i < n) {
-        const float g = __fmul_rn(__fmul_rn(__fmul_rn(h2f(scale[i / in_f]), G[i]), gmul), ste_scale);
+        const float g = __fmul_rn(__fmul_rn(__fmul_rn(scale ? h2f(scale[i / in_f]) : 1.0f, G[i]), gmul), ste_scale);
         uint16_t lb = latent[i];
         if (g != 0.0f && fabsf(g) <= 3.4028234e38f) {
             const float current = h2f(lb);
@@ -369,11 +369,11 @@ latent_sgd_kernel(uint16_t* __restrict__ latent, float* __restrict__ residual, c
         plus = h2f(lb) >= 0.0f;
     }
     const uint32_t word = __ballot_sync(0xffffffffu, plus);
-    if ((threadIdx.x & 31) == 0 && i < n) {
+    if (bits && (threadIdx.x & 31) == 0 && i < n) {
         const uint32_t old = bits[i >> 5];
         bits[i >> 5] = word;
         const uint32_t diff = __popc(old ^ word);
-        if (diff) atomicAdd(flips, (unsigned long long)diff);
+        if (diff && flips) atomicAdd(flips, (unsigned long long)diff);
     }
 }
 
@@ -423,6 +423,17 @@ __global__ void init_latent_kernel(const uint32_t* __restrict__ bits, uint16_t* 
     latent[i] = (bits[i >> 5] >> (i & 31)) & 1u ? LATENT_PLUS : (uint16_t)(LATENT_PLUS | 0x8000u);
 }
 
+void col_reduce_launch(ullis_cuda_runtime* rt, const float* a, const void* b, float* out, size_t R, size_t C, int mode,
+                       DeviceBuffer& scratch) {
+    const size_t chunks = (R + 255) / 256;
+    float* part = scratch.as<float>(chunks * C);
+    dim3 grid(blocks_for(C, 256), (unsigned)chunks);
+    col_partial_kernel<<<grid, 256, 0, rt->stream>>>(a, b, part, R, C, mode);
+    rt->launched("col_partial");
+    col_final_kernel<<<blocks_for(C, 256), 256, 0, rt->stream>>>(part, out, chunks, C);
+    rt->launched("col_final");
+}
+
 // ------------------------------------------------------------ host helpers
 struct Step {
     ullis_cuda_train_state* st;
@@ -454,13 +465,7 @@ struct Step {
     }
     // out[c] = sum_r f(a[r,c], b[r,c])
     void col_reduce(const float* a, const void* b, float* out, size_t R, size_t C, int mode) {
-        const size_t chunks = (R + 255) / 256;
-        float* part = st->part.as<float>(chunks * C);
-        dim3 grid(blocks_for(C, 256), (unsigned)chunks);
-        col_partial_kernel<<<grid, 256, 0, rt->stream>>>(a, b, part, R, C, mode);
-        rt->launched("col_partial");
-        col_final_kernel<<<blocks_for(C, 256), 256, 0, rt->stream>>>(part, out, chunks, C);
-        rt->launched("col_final");
+        col_reduce_launch(rt, a, b, out, R, C, mode, st->part);
     }
     void sgd(const Fp16Param& p, const float* g, float rate) {
         clipped_sgd_kernel<<<blocks_for(p.n, 256), 256, 0, rt->stream>>>(p.w, p.residual, g, gmul, rate, p.n);
@@ -496,6 +501,43 @@ struct Step {
 };
 
 }  // namespace
+
+// ------------------------------------------------------------ op-level launchers (kernels.hpp)
+namespace ullis {
+namespace k {
+
+void clipped_sgd(ullis_cuda_runtime* rt, uint16_t* w, float* residual, const float* g, float lr, size_t n) {
+    clipped_sgd_kernel<<<blocks_for(n, 256), 256, 0, rt->stream>>>(w, residual, g, 1.0f, lr, n);
+    rt->launched("clipped_sgd");
+}
+
+void latent_sgd(ullis_cuda_runtime* rt, uint16_t* latent, float* residual, const float* g, float lr, float ste_scale,
+                uint32_t* bits, size_t n) {
+    latent_sgd_kernel<<<blocks_for((n + 31) / 32 * 32, 256), 256, 0, rt->stream>>>(latent, residual, g, nullptr, bits, 1,
+                                                                                  n, 1.0f, ste_scale, lr, nullptr);
+    rt->launched("latent_sgd");
+}
+
+void rosa_e_grad(ullis_cuda_runtime* rt, const float* gy, const uint8_t* idx, float* g_e, size_t rows, size_t channels,
+                 DeviceBuffer& scratch) {
+    col_reduce_launch(rt, gy, idx, g_e, rows, channels, 2, scratch);
+}
+
+void relu2_backward(ullis_cuda_runtime* rt, const float* input, float* g, size_t n) {
+    relu2_bwd_kernel<<<blocks_for((n + 3) / 4, 256), 256, 0, rt->stream>>>(input, g, n);
+    rt->launched("relu2_bwd");
+}
+
+void layer_norm_backward(ullis_cuda_runtime* rt, const float* x, const float* gy, const uint16_t* w, float* gx,
+                         float* xhat, float* gw, float* gb, size_t rows, size_t channels, DeviceBuffer& scratch) {
+    ln_backward_kernel<<<blocks_for(rows, 8), 256, 0, rt->stream>>>(x, gy, w, gx, xhat, rows, channels, 0);
+    rt->launched("ln_backward");
+    col_reduce_launch(rt, gy, xhat, gw, rows, channels, 1, scratch);
+    col_reduce_launch(rt, gy, nullptr, gb, rows, channels, 0, scratch);
+}
+
+}  // namespace k
+}  // namespace ullis
 
 // ------------------------------------------------------------ state
 ullis_cuda_train_state::ullis_cuda_train_state(ullis_cuda_model* model, const uint8_t* checkpoint, size_t len)
@@ -785,4 +827,69 @@ void ullis_cuda_train_state::step(const uint32_t* tokens, const uint32_t* labels
     m->read_loss(&mean, nullptr, &n_valid, nullptr, 0);   // synchronises and checks the status word
     ++steps;
     if (out) *out = ullis_cuda_train_result{mean, n_valid, h_cnt[0], h_cnt[1], h_cnt[2]};
+}
+
+// install_head_unigram_prior (src/model.rs:3034-3085) with shrink_head_kaiming_scale (3087-3110): a
+// one-shot host computation over the labels and two vocabulary-sized tensors.
+void ullis_cuda_train_state::install_head_unigram_prior(const uint32_t* labels, size_t n, uint32_t ignore_id,
+                                                        ullis_cuda_head_unigram_install* out) {
+    if (!labels && n) fail(ULLIS_CUDA_ERR_ARG, "labels is null");
+    const size_t vocab = m->vocab, d = m->d;
+    rt->bind();
+    std::vector<uint16_t> bias(vocab), scale(vocab);
+    rt->d2h(bias.data(), head.bias.w, vocab * 2);
+    rt->d2h(scale.data(), head.scale.w, vocab * 2);
+    rt->sync();
+    auto to_f32 = [](uint16_t b) { return __half2float(__ushort_as_half(b)); };
+    auto to_f16 = [](float v) { return __half_as_ushort(__float2half_rn(v)); };
+    auto rms = [&](const std::vector<uint16_t>& v) {
+        float sum_sq = 0.0f;
+        for (uint16_t b : v) sum_sq += to_f32(b) * to_f32(b);
+        return v.empty() ? 0.0f : std::sqrt(sum_sq / (float)v.size());
+    };
+    float abs_sum = 0.0f;
+    for (uint16_t b : bias) abs_sum += std::fabs(to_f32(b));
+    ullis_cuda_head_unigram_install r{};
+    if (abs_sum / (float)vocab > 0.05f) {   // HEAD_BIAS_PRIOR_ABS_EPS: a fitted prior is left alone
+        r.bias_rms = rms(bias);
+        r.scale_rms = rms(scale);
+        if (out) *out = r;
+        return;
+    }
+    std::vector<uint64_t> counts(vocab, 0);
+    uint64_t n_targets = 0;
+    for (size_t i = 0; i < n; ++i) {
+        if (labels[i] == ignore_id || labels[i] >= vocab) continue;
+        ++counts[labels[i]];
+        ++n_targets;
+    }
+    if (n_targets == 0) fail(ULLIS_CUDA_ERR_ARG, "head unigram prior needs at least one supervised label");
+    const float log_denom = std::log((float)n_targets + (float)vocab);
+    std::vector<float> logs(vocab);
+    float log_sum = 0.0f;
+    for (size_t v = 0; v < vocab; ++v) {
+        logs[v] = std::log1p((float)counts[v]) - log_denom;
+        log_sum += logs[v];
+    }
+    const float log_mean = log_sum / (float)vocab;
+    for (size_t v = 0; v < vocab; ++v) bias[v] = to_f16(logs[v] - log_mean);
+    std::vector<float> zeros(vocab, 0.0f);
+    rt->h2d(head.bias.w, bias.data(), vocab * 2);
+    rt->h2d(head.bias.residual, zeros.data(), vocab * 4);   // Fp16Storage::set clears the carry (src/precision.rs:208-211)
+    const float kaiming = 1.0f / std::sqrt((float)d);
+    float mean = 0.0f;
+    for (uint16_t b : scale) mean += to_f32(b);
+    mean /= (float)vocab;
+    if (mean > kaiming * 0.5f && mean < kaiming * 2.0f) {
+        for (uint16_t& b : scale) b = to_f16(to_f32(b) * 0.25f);   // HEAD_KAIMING_SCALE_SHRINK
+        rt->h2d(head.scale.w, scale.data(), vocab * 2);
+        rt->h2d(head.scale.residual, zeros.data(), vocab * 4);
+        r.shrunk_kaiming_scale = 1;
+    }
+    rt->sync();
+    r.applied = 1;
+    r.n_targets = n_targets;
+    r.bias_rms = rms(bias);
+    r.scale_rms = rms(scale);
+    if (out) *out = r;
 }

@@ -50,4 +50,6 @@ struct ullis_cuda_train_state {
     void step(const uint32_t* tokens, const uint32_t* labels, uint32_t ignore_id, size_t batch, size_t time,
               float learning_rate, ullis_cuda_train_result* out);
     void read(const char* name, void* dst, size_t bytes);
+    void install_head_unigram_prior(const uint32_t* labels, size_t n, uint32_t ignore_id,
+                                    ullis_cuda_head_unigram_install* out);
 };

@@ -45,7 +45,9 @@ ABI_SYMBOLS = (
     "ullis_cuda_model_phase_ms", "ullis_cuda_generate_state_create", "ullis_cuda_generate_state_destroy",
     "ullis_cuda_generate_state_reset", "ullis_cuda_generate_state_time", "ullis_cuda_generate_step",
     "ullis_cuda_train_state_create", "ullis_cuda_train_state_destroy", "ullis_cuda_model_train_step",
-    "ullis_cuda_train_state_read",
+    "ullis_cuda_train_state_read", "ullis_cuda_train_state_install_head_unigram_prior",
+    "ullis_cuda_clipped_sgd_fp16", "ullis_cuda_binaryconnect_sgd_fp16", "ullis_cuda_apply_latent_sgd",
+    "ullis_cuda_rosa_qkv_1bit_bwd_e", "ullis_cuda_cmix_relu2_backward", "ullis_cuda_layer_norm_backward",
     "ullis_cuda_layer_norm", "ullis_cuda_time_shift_delta",
     "ullis_cuda_binary_linear", "ullis_cuda_fp16_linear", "ullis_cuda_sign_pack_bits", "ullis_cuda_cmix_relu2",
     "ullis_cuda_residual_add", "ullis_cuda_rosa_qkv_1bit_fwd", "ullis_cuda_rosa_block_forward",
@@ -246,6 +248,63 @@ class CudaRuntime:
         y = np.empty(x.size, np.float32)
         self._check(self._lib.ullis_cuda_cmix_relu2(self._h, _ptr(x), _ptr(y), _z(x.size)))
         return y
+
+    def _sgd(self, fn, parameters, residual, gradient, learning_rate, *extra):
+        w = _arr(parameters, np.uint16, "parameters")
+        r = _arr(residual, np.float32, "residual", w.size)
+        g = _arr(gradient, np.float32, "gradient", w.size)
+        nw, nr = np.empty(w.size, np.uint16), np.empty(w.size, np.float32)
+        self._check(fn(self._h, _ptr(w), _ptr(r), _ptr(g), C.c_float(learning_rate), *extra, _z(w.size), _ptr(nw),
+                       _ptr(nr)))
+        return nw, nr
+
+    def clipped_sgd_fp16(self, parameters, residual, gradient, learning_rate: float):
+        """MetalRuntime::clipped_sgd_fp16 (src/metal.rs:3053) -> (next FP16 bits, next carry)."""
+        return self._sgd(self._lib.ullis_cuda_clipped_sgd_fp16, parameters, residual, gradient, learning_rate)
+
+    def binaryconnect_sgd_fp16(self, parameters, residual, gradient, learning_rate: float):
+        """MetalRuntime::binaryconnect_sgd_fp16 (src/metal.rs:3069)."""
+        return self._sgd(self._lib.ullis_cuda_binaryconnect_sgd_fp16, parameters, residual, gradient, learning_rate)
+
+    def apply_latent_sgd(self, latent, residual, gradient, learning_rate: float, ste_scale: float):
+        """MetalRuntime::apply_latent_sgd (src/metal.rs:3006) -> (next latent, next carry, next sign bits)."""
+        w = _arr(latent, np.uint16, "latent")
+        r = _arr(residual, np.float32, "residual", w.size)
+        g = _arr(gradient, np.float32, "gradient", w.size)
+        nw, nr = np.empty(w.size, np.uint16), np.empty(w.size, np.float32)
+        bits = np.empty((w.size + 31) // 32, np.uint32)
+        self._check(self._lib.ullis_cuda_apply_latent_sgd(self._h, _ptr(w), _ptr(r), _ptr(g), C.c_float(learning_rate),
+                                                          C.c_float(ste_scale), _z(w.size), _ptr(nw), _ptr(nr),
+                                                          _ptr(bits)))
+        return nw, nr, bits
+
+    def rosa_qkv_1bit_bwd_e(self, output_gradient, idx, batch: int, time: int, channels: int) -> np.ndarray:
+        """MetalRuntime::rosa_qkv_1bit_bwd_e (src/metal.rs:1258): g_e [channels]."""
+        n = batch * time * channels
+        gy = _arr(output_gradient, np.float32, "output_gradient", n)
+        ix = _arr(idx, np.uint8, "idx", n)
+        out = np.empty(channels, np.float32)
+        self._check(self._lib.ullis_cuda_rosa_qkv_1bit_bwd_e(self._h, _ptr(gy), _ptr(ix), _z(batch), _z(time),
+                                                             _z(channels), _ptr(out)))
+        return out
+
+    def cmix_relu2_backward(self, input, output_gradient) -> np.ndarray:  # noqa: A002
+        """MetalRuntime::cmix_relu2_backward (src/metal.rs:1546)."""
+        x = _arr(input, np.float32, "input")
+        g = _arr(output_gradient, np.float32, "output_gradient", x.size)
+        out = np.empty(x.size, np.float32)
+        self._check(self._lib.ullis_cuda_cmix_relu2_backward(self._h, _ptr(x), _ptr(g), _ptr(out), _z(x.size)))
+        return out
+
+    def layer_norm_backward(self, input, output_gradient, weight_bits, rows: int, channels: int):  # noqa: A002
+        """MetalRuntime::layer_norm_backward (src/metal.rs:1628) -> (gx, gw, gb); weight as FP16 bits."""
+        x = _arr(input, np.float32, "input", rows * channels)
+        g = _arr(output_gradient, np.float32, "output_gradient", rows * channels)
+        w = _arr(weight_bits, np.uint16, "weight", channels)
+        gx, gw, gb = np.empty(x.size, np.float32), np.empty(channels, np.float32), np.empty(channels, np.float32)
+        self._check(self._lib.ullis_cuda_layer_norm_backward(self._h, _ptr(x), _ptr(g), _ptr(w), _z(rows), _z(channels),
+                                                             _ptr(gx), _ptr(gw), _ptr(gb)))
+        return gx, gw, gb
 
     def residual_add(self, residual, update) -> np.ndarray:
         a = _arr(residual, np.float32, "residual")
@@ -508,6 +567,11 @@ class _TrainResult(C.Structure):
                 ("flips_cmix", C.c_uint64), ("flips_rosa_o", C.c_uint64)]
 
 
+class _UnigramInstall(C.Structure):
+    _fields_ = [("applied", C.c_int32), ("n_targets", C.c_uint64), ("bias_rms", C.c_float), ("scale_rms", C.c_float),
+                ("shrunk_kaiming_scale", C.c_int32)]
+
+
 class CudaTrainState:
     """Weights, BinaryConnect latents and f32 carry of a model being trained on the device
     (UllisHeron::train_step_with_labels, src/model.rs:2773-2785, in stop_grad_bits mode).
@@ -535,6 +599,15 @@ class CudaTrainState:
             C.byref(res)))
         return {"loss": float(res.mean_loss), "n_valid": int(res.n_valid), "flips_head": int(res.flips_head),
                 "flips_cmix": int(res.flips_cmix), "flips_rosa_o": int(res.flips_rosa_o)}
+
+    def install_head_unigram_prior(self, labels, ignore_id: int) -> dict:
+        """UllisHeron::install_head_unigram_prior (src/model.rs:3034-3085) -> HeadUnigramInstall fields."""
+        lab = _arr(labels, np.uint32, "labels")
+        res = _UnigramInstall()
+        self.model.rt._check(self._lib.ullis_cuda_train_state_install_head_unigram_prior(
+            self._h, _ptr(lab), _z(lab.size), C.c_uint32(ignore_id), C.byref(res)))
+        return {"applied": bool(res.applied), "n_targets": int(res.n_targets), "bias_rms": float(res.bias_rms),
+                "scale_rms": float(res.scale_rms), "shrunk_kaiming_scale": bool(res.shrunk_kaiming_scale)}
 
     def read(self, name: str, dtype, count: int) -> np.ndarray:
         """Tensor of the trained model or of its carry by checkpoint name (u16 = FP16 bits)."""
