@@ -34,6 +34,10 @@ static int run_batch(int algo, const uint32_t* qw, const uint32_t* kw, const uin
             }
             continue;
         }
+        if (algo == 2 && k_is_constant(qw + s * wps, T, &c)) {   // constant q
+            run_constant_q(c, kw + s * wps, vw + s * wps, out + s * wps, T);
+            continue;
+        }
         if (algo == 0)
             run_eager<Ix>(base, qw + s * wps, kw + s * wps, vw + s * wps, out + s * wps, T, &cnt);
         else if (!run_euler<Ix>(base, qw + s * wps, kw + s * wps, vw + s * wps, out + s * wps, T, &cnt))

@@ -40,8 +40,8 @@ def test_exhaustive_t4_as_one_batch(cuda_rt, oracle):
     run_both(cuda_rt, oracle, pack_plane(bits(0)), pack_plane(bits(1)), pack_plane(bits(2)), 1, T, n)
 
 
-@pytest.mark.parametrize("kind", ["const", "k_const_mixed", "v_const_mixed", "v_const_biased", "biased", "periodic_clean",
-                                  "qk_same"])
+@pytest.mark.parametrize("kind", ["const", "k_const_mixed", "q_const_mixed", "q_const_biased", "v_const_mixed", "v_const_biased",
+                                  "biased", "periodic_clean", "qk_same"])
 def test_worst_case_streams(cuda_rt, oracle, kind):
     B, T, C = 1, 2048, 32
     rng = np.random.default_rng(len(kind))
@@ -52,9 +52,12 @@ def test_worst_case_streams(cuda_rt, oracle, kind):
         q = rng.integers(0, 2, (T, C), dtype=np.uint8)
         k = rng.integers(0, 2, (T, C), dtype=np.uint8)
         k[:, ::2] = rng.integers(0, 2, (1, C // 2), dtype=np.uint8)
-    elif kind in ("biased", "v_const_biased"):
+    elif kind in ("biased", "v_const_biased", "q_const_biased"):
         pr = rng.choice([0.001, 0.01, 0.99, 0.999], (1, C))
         q, k = (rng.random((T, C)) < pr).astype(np.uint8), (rng.random((T, C)) < pr).astype(np.uint8)
+    elif kind == "q_const_mixed":  # three quarters of the streams have constant q (scan over the key runs), keys of several densities
+        q = rng.integers(0, 2, (T, C), dtype=np.uint8)
+        k = (rng.random((T, C)) < rng.choice([0.1, 0.5, 0.9], (1, C))).astype(np.uint8)
     elif kind == "periodic_clean":
         P = rng.integers(2, 64, C)
         base = rng.integers(0, 2, (64, C), dtype=np.uint8)
@@ -64,6 +67,10 @@ def test_worst_case_streams(cuda_rt, oracle, kind):
         q = rng.integers(0, 2, (T, C), dtype=np.uint8)
         k = q.copy()
     v = rng.integers(0, 2, (T, C), dtype=np.uint8)
+    if kind.startswith("q_const"):
+        q[:, 0::4] = 0
+        q[:, 1::4] = 1
+        q[:, 2::4] = rng.integers(0, 2, (1, C // 4), dtype=np.uint8)
     if kind.startswith("v_const"):  # three quarters of the streams have constant v: all 0 (idx = 0), all 1 (pass 1 only)
         v[:, 0::4] = 0
         v[:, 1::4] = 1

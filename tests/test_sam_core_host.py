@@ -22,6 +22,21 @@ def test_exhaustive_short_streams(oracle, sam_host, T):
             assert np.array_equal(sam_host(algo, ix, q, k, v, n, T), ref)
 
 
+@pytest.mark.parametrize("T", [9, 14])
+def test_exhaustive_key_sequences_under_a_constant_query(oracle, sam_host, T):
+    """Every key sequence of length T with q constant (both values) and several v
+    sequences: the closed form for constant q against the reference's pushes."""
+    rng = np.random.default_rng(T)
+    kk = np.arange(1 << T, dtype=np.uint32)
+    m = np.uint32((1 << T) - 1)
+    for c in (0, 1):
+        q = np.full(kk.size, m if c else 0, np.uint32)
+        for v in (kk ^ np.uint32(0x2A5), rng.integers(0, 1 << T, kk.size).astype(np.uint32), np.full(kk.size, 0x1555 & int(m), np.uint32)):
+            ref = oracle.rosa_qkv_streams(q, kk, v, kk.size, T)
+            assert np.array_equal(sam_host(2, 16, q, kk, v, kk.size, T), ref), c
+            assert np.array_equal(sam_host(1, 16, q, kk, v, kk.size, T), ref), c
+
+
 def _streams(kind, n, T, rng):
     if kind == "iid":
         return [rng.integers(0, 2, (n, T), dtype=np.uint8) for _ in range(3)]
@@ -38,6 +53,16 @@ def _streams(kind, n, T, rng):
         pr = rng.choice([0.002, 0.02, 0.98], (n, 1))
         return [(rng.random((n, T)) < pr).astype(np.uint8), (rng.random((n, T)) < pr).astype(np.uint8),
                 np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1)]
+    if kind == "q_const":   # the query bits all equal: idx follows the runs of that bit among the keys
+        pr = rng.choice([0.05, 0.3, 0.5, 0.7, 0.95, 0.995], (n, 1))
+        return [np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1), (rng.random((n, T)) < pr).astype(np.uint8),
+                rng.integers(0, 2, (n, T), dtype=np.uint8)]
+    if kind == "q_const_periodic":
+        P = rng.integers(2, 40, n)
+        base = rng.integers(0, 2, (n, 64), dtype=np.uint8)
+        b = np.take_along_axis(base, np.arange(T)[None, :] % P[:, None], 1)
+        return [np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1), (b ^ (rng.random((n, T)) < 0.03)).astype(np.uint8),
+                rng.integers(0, 2, (n, T), dtype=np.uint8)]
     if kind == "biased":
         pr = rng.choice([0.001, 0.01, 0.99, 0.999], (n, 1))
         return [(rng.random((n, T)) < pr).astype(np.uint8), (rng.random((n, T)) < pr).astype(np.uint8),
@@ -55,7 +80,7 @@ def _streams(kind, n, T, rng):
     raise ValueError(kind)
 
 
-@pytest.mark.parametrize("kind,T,n", [("v_const", 777, 32), ("v_const_biased", 2048, 16), ("iid", 97, 200), ("iid", 2048, 24), ("const", 1024, 16), ("k_const", 1000, 16), ("k_const", 64, 8), ("biased", 2048, 16),
+@pytest.mark.parametrize("kind,T,n", [("q_const", 2048, 48), ("q_const", 333, 64), ("q_const_periodic", 1500, 32), ("v_const", 777, 32), ("v_const_biased", 2048, 16), ("iid", 97, 200), ("iid", 2048, 24), ("const", 1024, 16), ("k_const", 1000, 16), ("k_const", 64, 8), ("biased", 2048, 16),
                                       ("periodic", 1500, 16), ("periodic_clean", 2048, 8), ("qk_same", 777, 32)])
 def test_long_streams(oracle, sam_host, kind, T, n):
     rng = np.random.default_rng(hash((kind, T)) & 0xFFFF)

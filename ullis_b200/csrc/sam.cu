@@ -18,8 +18,9 @@ namespace k {
 namespace {
 
 // Streams that need no automaton are settled here with a few word operations
-// (sam_core.cuh, "constant k" and "constant v"): k bits all equal, v bits all 0
-// (idx = 0) and v bits all 1 (idx_t = "q_t has occurred among the earlier keys").
+// (sam_core.cuh, "constant k", "constant v" and "constant q"): k bits all equal, v bits all 0
+// (idx = 0), v bits all 1 (idx_t = "q_t has occurred among the earlier keys") and q bits all
+// equal (a scan over the key runs).
 // Every other stream id is appended to `list` for the automaton kernels.
 __global__ void __launch_bounds__(128)
 rosa_classify_kernel(const uint32_t* __restrict__ q_sw, const uint32_t* __restrict__ k_sw,
@@ -36,6 +37,8 @@ rosa_classify_kernel(const uint32_t* __restrict__ q_sw, const uint32_t* __restri
         } else {
             sam::run_constant_v_one(q_sw + s * wps, k_sw + s * wps, idx_sw + s * wps, T);
         }
+    } else if (sam::k_is_constant(q_sw + s * wps, T, &c)) {   // constant q: a scan over the runs of c among the keys
+        sam::run_constant_q(c, k_sw + s * wps, v_sw + s * wps, idx_sw + s * wps, T);
     } else {
         list[atomicAdd(count, 1u)] = (uint32_t)s;
     }
@@ -79,11 +82,11 @@ __global__ void __launch_bounds__(128)
 rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
                   const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ list,
                   const uint32_t* __restrict__ count, size_t first, uint32_t T, size_t wps, int lanes,
-                  uint32_t dense_count) {
+                  uint32_t dense_count, uint32_t sparse_count) {
     // lanes == 0: choose from the number of streams that are left, which only the device knows -
-    // many streams: four per warp (fewer issued instructions); few: two per warp (more warps to
-    // hide the pointer-chase latency).  The grid is sized for two per warp.
-    if (lanes == 0) lanes = *count > dense_count ? 4 : 2;
+    // many streams: four per warp (fewer issued instructions); fewer: two, then one per warp (more
+    // warps to hide the pointer-chase latency).  The grid is sized for one per warp.
+    if (lanes == 0) lanes = *count > dense_count ? 4 : *count > sparse_count ? 2 : 1;
     const int lane = threadIdx.x & 31;
     const int spread = 32 / lanes;
     if (lane % spread != 0) return;
@@ -185,10 +188,10 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
         if (use_coop) {
             // sam_lanes_fixed: the caller pinned the streams per warp; otherwise the kernel picks 2 or 4
             const int pass1_lanes = rt->sam_lanes_fixed ? lanes : 0;
-            const size_t pass1_warps = rt->sam_lanes_fixed ? warps : (n + 1) / 2;
+            const size_t pass1_warps = rt->sam_lanes_fixed ? warps : n;
             rosa_pass1_kernel<<<(unsigned)((pass1_warps * 32 + 127) / 128), 128, 0, rt->stream>>>(
                 scratch, stride, q_sw, k_sw, list, count, s0, (uint32_t)time, wps, pass1_lanes,
-                96u * (uint32_t)rt->sm_count);
+                96u * (uint32_t)rt->sm_count, rt->sam_sparse_per_sm * (uint32_t)rt->sm_count);
             rt->launched("rosa_pass1");
             rosa_coop_kernel<<<(unsigned)n, sam::COOP_THREADS, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, count, s0,
                                                                          (uint32_t)time, wps, rt->dev_status);

@@ -553,6 +553,36 @@ SAM_HD void run_constant_v_one(const uint32_t* qw, const uint32_t* kw, uint32_t*
     }
 }
 
+// Constant q (every query bit equals c).  The query string is c^(t+1), so only
+// the runs of c among the keys matter.  With M the longest run of c in
+// k_0 .. k_{t-1}, the automaton holds c^m alone in its own state for m < M and
+// c^M in a state Z whose shortest string is c^M; the walk reaches Z as soon as
+// the run record and the match length (both grow by at most one per step) have
+// met, and re-enters it through Z's suffix link whenever Z has no c-child.  The
+// state the reference reads is therefore Z, and last[Z] is the end of the most
+// recent run of length M:
+//   idx_t = v[p + 1],  p = max{ e < t : (length of the run of c ending at e) >= M },
+//   idx_t = 0 while no key equals c.
+// One O(T) scan, no automaton.  Checked like the other closed forms: every key
+// sequence up to T = 18 and long random / periodic ones against the eager form.
+SAM_HD void run_constant_q(uint32_t c, const uint32_t* kw, const uint32_t* vw, uint32_t* out, uint32_t T) {
+    uint32_t run = 0, best = 0, pv = 0;   // pv = v[p + 1] for the current record position p
+    uint32_t kword = 0, acc = 0;
+    for (uint32_t t = 0; t < T; ++t) {
+        if ((t & 31u) == 0) { kword = kw[t >> 5]; acc = 0; }
+        if (best) acc |= pv << (t & 31u);
+        if (((kword >> (t & 31u)) & 1u) == c) {
+            if (++run >= best) {
+                best = run;
+                pv = t + 1 < T ? stream_bit(vw, t + 1) : 0u;
+            }
+        } else {
+            run = 0;
+        }
+        if ((t & 31u) == 31u || t + 1 == T) out[t >> 5] = acc;
+    }
+}
+
 template <typename Ix>
 SAM_HD bool run_euler(uint8_t* scratch, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw,
                       uint32_t* out, uint32_t T, Counters* cnt) {
