@@ -13,6 +13,7 @@
 #include "kernels.hpp"
 #include "tc_gemm.cuh"
 #include "tc_gemm_ws.cuh"
+#include "tc_gemm_ws2.cuh"
 
 namespace ullis {
 namespace tc {
@@ -271,6 +272,29 @@ inline unsigned blocks_for(size_t n, unsigned per) { return (unsigned)((n + per 
 
 namespace {
 
+// How many CTA pairs of the pair kernel the device holds at once (0 = clusters of two cannot be placed).
+template <int EPI>
+int ws2_resident_clusters(ullis_cuda_runtime* rt) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.gridDim = dim3(2u * (unsigned)rt->sm_count);
+    cfg.blockDim = dim3(WS2_THREADS);
+    cfg.dynamicSmemBytes = WS_SMEM_LIMIT;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_ws2_kernel<EPI>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
 bool usable(ullis_cuda_runtime* rt) {
     if (rt->mode == ULLIS_CUDA_MODE_EXACT) return false;
     if (rt->tc_ready == 0) {
@@ -301,6 +325,18 @@ bool usable(ullis_cuda_runtime* rt) {
             ULLIS_CUDA_CHECK(cudaFuncSetAttribute(gemm_ws_kernel<EPI_RESIDUAL, false>,
                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM_LIMIT));
             rt->tc_ws_kernel = !getenv("ULLIS_CUDA_NO_WS");
+#define ULLIS_SET_SMEM_WS2(EPI)                                                                                    \
+    ULLIS_CUDA_CHECK(cudaFuncSetAttribute(gemm_ws2_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
+                                          (int)WS_SMEM_LIMIT));                                                    \
+    rt->tc_ws2_clusters[EPI] = ws2_resident_clusters<EPI>(rt)
+            ULLIS_SET_SMEM_WS2(EPI_STORE);
+            ULLIS_SET_SMEM_WS2(EPI_RESIDUAL);
+            ULLIS_SET_SMEM_WS2(EPI_RELU2);
+            ULLIS_SET_SMEM_WS2(EPI_SIGNBITS);
+            ULLIS_SET_SMEM_WS2(EPI_CE);
+#undef ULLIS_SET_SMEM_WS2
+            rt->tc_ws2_kernel = rt->tc_ws_kernel && !getenv("ULLIS_CUDA_NO_WS2");
+            if (const char* env = getenv("ULLIS_CUDA_WS2_MIN_ROWS")) rt->tc_ws2_min_rows = (size_t)std::max(1, atoi(env));
             ULLIS_CUDA_CHECK(cudaFuncSetAttribute(sign_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   FIX_QUEUE * 2));
             rt->tc_ready = 1;
@@ -319,8 +355,40 @@ bool takes_ws(const ullis_cuda_runtime* rt, size_t K, uint32_t n_a) {
     return rt->tc_ws_kernel && K / BK <= WS_MAX_KB && ws_shape((uint32_t)K, n_a, true).stages >= 2;
 }
 
+// ... and, with enough rows and whole 256-column tiles, to its CTA-pair form
+bool takes_ws2(const ullis_cuda_runtime* rt, int epi, size_t M, size_t K, size_t N, uint32_t n_a) {
+    return rt->tc_ws2_kernel && takes_ws(rt, K, n_a) && N % WS2_BN == 0 && M >= rt->tc_ws2_min_rows &&
+           rt->tc_ws2_clusters[epi] >= 8 && ws2_shape((uint32_t)K, n_a, epi).stages >= 2;
+}
+
 template <int EPI, bool PACKED>
 void launch(ullis_cuda_runtime* rt, const GemmMaps& maps, const GemmParams& p, unsigned n_prob, const char* what) {
+    if (PACKED && takes_ws2(rt, EPI, p.M, p.K, p.N, p.n_a)) {
+        // one (problem, 256-column tile) per CTA pair; the pairs with the same one share the 256-row tiles
+        const WsShape shape = ws2_shape(p.K, p.n_a, EPI);
+        GemmParams q = p;
+        q.stages = shape.stages;
+        const uint32_t pairs = n_prob * (p.N / WS2_BN), m_tiles = (p.M + WS2_BM - 1) / WS2_BM;
+        uint32_t members = (uint32_t)rt->tc_ws2_clusters[EPI] / pairs;
+        if (members < 1) members = 1;
+        if (members > m_tiles) members = m_tiles;
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.gridDim = dim3(2u * pairs * members);
+        cfg.blockDim = dim3(WS2_THREADS);
+        cfg.dynamicSmemBytes = shape.smem;
+        cfg.stream = rt->stream;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        ULLIS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_ws2_kernel<EPI>, maps, q, pairs));
+        rt->launched(what);
+        return;
+    }
     if (PACKED && takes_ws(rt, p.K, p.n_a)) {
         // one (problem, column tile) pair per CTA, the CTAs of a pair share the row tiles
         const WsShape shape = ws_shape(p.K, p.n_a, EPI == EPI_STORE || EPI == EPI_RESIDUAL);

@@ -76,12 +76,16 @@ inline size_t gemm_smem_bytes(uint32_t n_a, uint32_t stages) {
 
 __device__ __forceinline__ float h2f_bits(uint16_t b) { return __half2float(__ushort_as_half(b)); }
 
+// row scale / bias of the tile's columns as the kernel keeps them in shared memory: f32, or the FP16 they came from
+__device__ __forceinline__ float sb_load(const float* p, uint32_t i) { return p[i]; }
+__device__ __forceinline__ float sb_load(const __half* p, uint32_t i) { return __half2float(p[i]); }
+
 // One output row (TMEM lane) per thread, the 32-column chunks [c_begin, c_end) of the tile's 128 columns.
 // `part` = index of this call's partial among the row's p.n_tiles partials (EPI_CE).
 // The TMEM loads are warp-collective, so row / column guards only wrap stores.
-template <int EPI>
+template <int EPI, typename SB = float, bool STAGED16 = false>
 __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem& pr, uint32_t taddr, uint32_t m,
-                                         uint32_t n0, const float* s_scale, const float* s_bias, int lane, uint32_t part,
+                                         uint32_t n0, const SB* s_scale, const SB* s_bias, int lane, uint32_t part,
                                          uint32_t c_begin = 0, uint32_t c_end = BN / 32, float* stage = nullptr) {
     const bool row_ok = m < p.M;
     // EPI_SIGNBITS: the 32 rows of this warp are 32 consecutive steps of one sequence (M, time % 32 == 0)
@@ -111,10 +115,10 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
                 for (int q = 0; q < 4; ++q) {
                     const int j = h * 16 + q * 4;
                     float4 v;
-                    v.x = s_bias[c * 32 + j + 0] + s_scale[c * 32 + j + 0] * __uint_as_float(r[j + 0]);
-                    v.y = s_bias[c * 32 + j + 1] + s_scale[c * 32 + j + 1] * __uint_as_float(r[j + 1]);
-                    v.z = s_bias[c * 32 + j + 2] + s_scale[c * 32 + j + 2] * __uint_as_float(r[j + 2]);
-                    v.w = s_bias[c * 32 + j + 3] + s_scale[c * 32 + j + 3] * __uint_as_float(r[j + 3]);
+                    v.x = sb_load(s_bias, c * 32 + j + 0) + sb_load(s_scale, c * 32 + j + 0) * __uint_as_float(r[j + 0]);
+                    v.y = sb_load(s_bias, c * 32 + j + 1) + sb_load(s_scale, c * 32 + j + 1) * __uint_as_float(r[j + 1]);
+                    v.z = sb_load(s_bias, c * 32 + j + 2) + sb_load(s_scale, c * 32 + j + 2) * __uint_as_float(r[j + 2]);
+                    v.w = sb_load(s_bias, c * 32 + j + 3) + sb_load(s_scale, c * 32 + j + 3) * __uint_as_float(r[j + 3]);
                     *reinterpret_cast<float4*>(stage + lane * STAGE_STRIDE + q * 4) = v;
                 }
                 __syncwarp();
@@ -142,8 +146,8 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 8; e += 2) {
-                    float a = fmaxf(s_bias[c * 32 + j + e] + s_scale[c * 32 + j + e] * __uint_as_float(r[j + e]), 0.0f);
-                    float b = fmaxf(s_bias[c * 32 + j + e + 1] + s_scale[c * 32 + j + e + 1] * __uint_as_float(r[j + e + 1]), 0.0f);
+                    float a = fmaxf(sb_load(s_bias, c * 32 + j + e) + sb_load(s_scale, c * 32 + j + e) * __uint_as_float(r[j + e]), 0.0f);
+                    float b = fmaxf(sb_load(s_bias, c * 32 + j + e + 1) + sb_load(s_scale, c * 32 + j + e + 1) * __uint_as_float(r[j + e + 1]), 0.0f);
                     a *= a; b *= b;
                     if (p.out_fmt == 1) {
                         __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
@@ -157,13 +161,35 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
                         w[e / 2] = *reinterpret_cast<uint32_t*>(&h);
                     }
                 }
-                if (row_ok && nc + j + 7 < p.N) *reinterpret_cast<uint4*>(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                if (STAGED16) {
+                    // 16-byte granule q = j / 8 of this lane's row, at (q ^ f(row)) so that neither the
+                    // row-wise writes nor the reads below meet a bank conflict (rows are 64 bytes apart)
+                    reinterpret_cast<uint4*>(stage)[lane * 4 + ((j >> 3) ^ ((lane >> 1) & 3))] =
+                        make_uint4(w[0], w[1], w[2], w[3]);
+                } else if (row_ok && nc + j + 7 < p.N) {
+                    *reinterpret_cast<uint4*>(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            if (STAGED16) {
+                // a thread holds 64 bytes of ONE row, so direct stores touch 32 rows per instruction; through
+                // the warp's 32 x 64-byte buffer four lanes cover a row's 64 bytes and an instruction eight rows
+                __syncwarp();
+                uint16_t* base = static_cast<uint16_t*>(pr.out);
+                const uint32_t col = nc + (lane & 3) * 8;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t row = i * 8 + (lane >> 2);
+                    const uint4 v = reinterpret_cast<const uint4*>(stage)[row * 4 + ((lane & 3) ^ ((row >> 1) & 3))];
+                    const uint32_t gm = m_warp + row;
+                    if (gm < p.M && col + 7 < p.N) *reinterpret_cast<uint4*>(base + (size_t)gm * p.N + col) = v;
+                }
+                __syncwarp();
             }
         } else if (EPI == EPI_SIGNBITS) {
             uint32_t my_bits = 0, my_flags = 0;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const float sc = s_scale[c * 32 + j], bi = s_bias[c * 32 + j];
+                const float sc = sb_load(s_scale, c * 32 + j), bi = sb_load(s_bias, c * 32 + j);
                 const float t = sc * __uint_as_float(r[j]);
                 const float y = bi + t;
                 // error bound of the tensor-core sum against the reference's sequential f32 sum
@@ -183,7 +209,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
             float cmax = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const float y = s_bias[c * 32 + j] + s_scale[c * 32 + j] * __uint_as_float(r[j]);
+                const float y = sb_load(s_bias, c * 32 + j) + sb_load(s_scale, c * 32 + j) * __uint_as_float(r[j]);
                 r[j] = __float_as_uint(y);
                 if (nc + j < p.N) cmax = fmaxf(cmax, y);
                 if (nc + j == target && row_ok) static_cast<float*>(pr.out2)[m] = y;
