@@ -54,7 +54,7 @@ def _streams(kind, n, T, rng):
         return [(rng.random((n, T)) < pr).astype(np.uint8), (rng.random((n, T)) < pr).astype(np.uint8),
                 np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1)]
     if kind == "q_const":   # the query bits all equal: idx follows the runs of that bit among the keys
-        pr = rng.choice([0.05, 0.3, 0.5, 0.7, 0.95, 0.995], (n, 1))
+        pr = rng.choice([0.002, 0.05, 0.3, 0.5, 0.7, 0.95, 0.995, 0.9995], (n, 1))
         return [np.repeat(rng.integers(0, 2, (n, 1), dtype=np.uint8), T, 1), (rng.random((n, T)) < pr).astype(np.uint8),
                 rng.integers(0, 2, (n, T), dtype=np.uint8)]
     if kind == "q_const_periodic":

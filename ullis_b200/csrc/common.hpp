@@ -102,6 +102,7 @@ struct ullis_cuda_runtime {
     bool tc_ws_kernel = true;           // weight-stationary persistent kernel for packed weights with K <= 512
     bool tc_ws2_kernel = true;          // ... and its CTA-pair form (256 x 256 tiles) for large M and N % 256 == 0
     size_t tc_ws2_min_rows = 4096;      // fewer rows than this stay with the single-CTA form (more, smaller row tiles)
+    int tc_ws2_dense_clusters[2] = {0, 0};      // the same for dense weights (store, residual)
     int tc_ws2_clusters[5] = {0, 0, 0, 0, 0};   // CTA pairs of that kernel the device holds at once, per epilogue
     int tc_ready = 0;                   // 0 = not probed, 1 = usable, -1 = unusable on this device
     ullis::NcclState* nccl = nullptr;

@@ -273,7 +273,7 @@ inline unsigned blocks_for(size_t n, unsigned per) { return (unsigned)((n + per 
 namespace {
 
 // How many CTA pairs of the pair kernel the device holds at once (0 = clusters of two cannot be placed).
-template <int EPI>
+template <int EPI, bool RESIDENT_W = true>
 int ws2_resident_clusters(ullis_cuda_runtime* rt) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -288,7 +288,7 @@ int ws2_resident_clusters(ullis_cuda_runtime* rt) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_ws2_kernel<EPI>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_ws2_kernel<EPI, RESIDENT_W>, &cfg) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
@@ -335,6 +335,12 @@ bool usable(ullis_cuda_runtime* rt) {
             ULLIS_SET_SMEM_WS2(EPI_SIGNBITS);
             ULLIS_SET_SMEM_WS2(EPI_CE);
 #undef ULLIS_SET_SMEM_WS2
+            ULLIS_CUDA_CHECK(cudaFuncSetAttribute(gemm_ws2_kernel<EPI_STORE, false>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM_LIMIT));
+            ULLIS_CUDA_CHECK(cudaFuncSetAttribute(gemm_ws2_kernel<EPI_RESIDUAL, false>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM_LIMIT));
+            rt->tc_ws2_dense_clusters[0] = ws2_resident_clusters<EPI_STORE, false>(rt);
+            rt->tc_ws2_dense_clusters[1] = ws2_resident_clusters<EPI_RESIDUAL, false>(rt);
             rt->tc_ws2_kernel = rt->tc_ws_kernel && !getenv("ULLIS_CUDA_NO_WS2");
             if (const char* env = getenv("ULLIS_CUDA_WS2_MIN_ROWS")) rt->tc_ws2_min_rows = (size_t)std::max(1, atoi(env));
             ULLIS_CUDA_CHECK(cudaFuncSetAttribute(sign_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -361,32 +367,38 @@ bool takes_ws2(const ullis_cuda_runtime* rt, int epi, size_t M, size_t K, size_t
            rt->tc_ws2_clusters[epi] >= 8 && ws2_shape((uint32_t)K, n_a, epi).stages >= 2;
 }
 
+// one (problem, 256-column tile) per CTA pair; the pairs with the same one share the 256-row tiles
+template <int EPI, bool RESIDENT_W>
+void launch_ws2(ullis_cuda_runtime* rt, const GemmMaps& maps, const GemmParams& p, unsigned n_prob, int resident,
+                const char* what) {
+    const WsShape shape = ws2_shape(p.K, p.n_a, EPI, RESIDENT_W);
+    GemmParams q = p;
+    q.stages = shape.stages;
+    const uint32_t pairs = n_prob * (p.N / WS2_BN), m_tiles = (p.M + WS2_BM - 1) / WS2_BM;
+    uint32_t members = (uint32_t)resident / pairs;
+    if (members < 1) members = 1;
+    if (members > m_tiles) members = m_tiles;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.gridDim = dim3(2u * pairs * members);
+    cfg.blockDim = dim3(WS2_THREADS);
+    cfg.dynamicSmemBytes = shape.smem;
+    cfg.stream = rt->stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    ULLIS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_ws2_kernel<EPI, RESIDENT_W>, maps, q, pairs));
+    rt->launched(what);
+}
+
 template <int EPI, bool PACKED>
 void launch(ullis_cuda_runtime* rt, const GemmMaps& maps, const GemmParams& p, unsigned n_prob, const char* what) {
     if (PACKED && takes_ws2(rt, EPI, p.M, p.K, p.N, p.n_a)) {
-        // one (problem, 256-column tile) per CTA pair; the pairs with the same one share the 256-row tiles
-        const WsShape shape = ws2_shape(p.K, p.n_a, EPI);
-        GemmParams q = p;
-        q.stages = shape.stages;
-        const uint32_t pairs = n_prob * (p.N / WS2_BN), m_tiles = (p.M + WS2_BM - 1) / WS2_BM;
-        uint32_t members = (uint32_t)rt->tc_ws2_clusters[EPI] / pairs;
-        if (members < 1) members = 1;
-        if (members > m_tiles) members = m_tiles;
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof(cfg));
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2;
-        attr.val.clusterDim.y = 1;
-        attr.val.clusterDim.z = 1;
-        cfg.gridDim = dim3(2u * pairs * members);
-        cfg.blockDim = dim3(WS2_THREADS);
-        cfg.dynamicSmemBytes = shape.smem;
-        cfg.stream = rt->stream;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        ULLIS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_ws2_kernel<EPI>, maps, q, pairs));
-        rt->launched(what);
+        launch_ws2<EPI, true>(rt, maps, p, n_prob, rt->tc_ws2_clusters[EPI], what);
         return;
     }
     if (PACKED && takes_ws(rt, p.K, p.n_a)) {
@@ -408,6 +420,12 @@ void launch(ullis_cuda_runtime* rt, const GemmMaps& maps, const GemmParams& p, u
         // dense weights: the persistent kernel with the weight tile in the ring (large M only: a CTA needs
         // several row tiles to amortise its set-up)
         const uint32_t m_tiles = (p.M + BM - 1) / BM, pairs = n_prob * ((p.N + BN - 1) / BN);
+        if (rt->tc_ws2_kernel && m_tiles * pairs >= 4u * (uint32_t)rt->sm_count && p.N % WS2_BN == 0 &&
+            p.M >= rt->tc_ws2_min_rows && rt->tc_ws2_dense_clusters[EPI] >= 8 &&
+            ws2_shape(p.K, p.n_a, EPI, false).stages >= 2) {
+            launch_ws2<EPI, false>(rt, maps, p, n_prob, rt->tc_ws2_dense_clusters[EPI], what);
+            return;
+        }
         if (rt->tc_ws_kernel && m_tiles * pairs >= 4u * (uint32_t)rt->sm_count) {
             const WsShape shape = ws_shape(p.K, p.n_a, true, false);
             GemmParams q = p;

@@ -567,19 +567,42 @@ SAM_HD void run_constant_v_one(const uint32_t* qw, const uint32_t* kw, uint32_t*
 // sequence up to T = 18 and long random / periodic ones against the eager form.
 SAM_HD void run_constant_q(uint32_t c, const uint32_t* kw, const uint32_t* vw, uint32_t* out, uint32_t T) {
     uint32_t run = 0, best = 0, pv = 0;   // pv = v[p + 1] for the current record position p
-    uint32_t kword = 0, acc = 0;
-    for (uint32_t t = 0; t < T; ++t) {
-        if ((t & 31u) == 0) { kword = kw[t >> 5]; acc = 0; }
-        if (best) acc |= pv << (t & 31u);
-        if (((kword >> (t & 31u)) & 1u) == c) {
-            if (++run >= best) {
+    for (uint32_t base = 0; base < T; base += 32u) {
+        const uint32_t w = base >> 5;
+        const uint32_t n = T - base < 32u ? T - base : 32u;
+        const uint32_t kword = kw[w];
+        const uint32_t same = c ? kword : ~kword;   // bit i: k_{base+i} == c
+        uint32_t acc = 0;
+        if (n == 32u && same == 0xFFFFFFFFu && (run == best || best - run > 32u)) {
+            // 32 steps inside one run of c, taken at once: either every step sets a record (the run is the
+            // longest so far: step base + i answers with v[base + i], the first one with the old pv) or none does
+            if (run == best) {
+                acc = (vw[w] & ~1u) | (best ? pv : 0u);
+                run += 32u;
                 best = run;
-                pv = t + 1 < T ? stream_bit(vw, t + 1) : 0u;
+                pv = base + 32u < T ? stream_bit(vw, base + 32u) : 0u;
+            } else {
+                acc = pv ? 0xFFFFFFFFu : 0u;
+                run += 32u;
             }
-        } else {
+        } else if (n == 32u && same == 0u) {   // 32 steps without c: no record, the run ends
+            acc = (best && pv) ? 0xFFFFFFFFu : 0u;
             run = 0;
+        } else {
+            for (uint32_t i = 0; i < n; ++i) {
+                const uint32_t t = base + i;
+                if (best) acc |= pv << i;
+                if ((same >> i) & 1u) {
+                    if (++run >= best) {
+                        best = run;
+                        pv = t + 1 < T ? stream_bit(vw, t + 1) : 0u;
+                    }
+                } else {
+                    run = 0;
+                }
+            }
         }
-        if ((t & 31u) == 31u || t + 1 == T) out[t >> 5] = acc;
+        out[w] = acc;
     }
 }
 

@@ -31,25 +31,28 @@ inline uint32_t ws2_staging(int epi) {
     return (epi == EPI_STORE || epi == EPI_RESIDUAL) ? (uint32_t)STAGE_BYTES : epi == EPI_RELU2 ? WS2_STAGE16_BYTES : 0u;
 }
 
-inline WsShape ws2_shape(uint32_t K, uint32_t n_a, int epi) {
+inline WsShape ws2_shape(uint32_t K, uint32_t n_a, int epi, bool resident_w = true) {
     const uint32_t kb = K / BK;
-    const uint32_t fixed = 1024 /*alignment slack*/ + kb * TILE_BYTES + 2 * WS2_BN * 2 + 256 +
+    const uint32_t fixed = 1024 /*alignment slack*/ + (resident_w ? kb * TILE_BYTES : 0) + 2 * WS2_BN * 2 + 256 +
                            WS2_EPI_WARPS * ws2_staging(epi);
+    if (!resident_w) n_a += 1;   // this CTA's half of the weight tile travels with its activations
     uint32_t stages = (WS_SMEM_LIMIT - fixed) / (n_a * TILE_BYTES);
     if (stages > WS_MAX_STAGES) stages = WS_MAX_STAGES;
     return WsShape{stages, fixed + stages * n_a * TILE_BYTES};
 }
 
-template <int EPI>
+// RESIDENT_W = false: dense 16-bit weights of any K; each CTA fetches the 128 weight rows of its half of the
+// pair's 256 columns by TMA into the same ring stage as its activations (nothing stays resident).
+template <int EPI, bool RESIDENT_W = true>
 __global__ void __launch_bounds__(WS2_THREADS, 1)
 gemm_ws2_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const uint32_t pairs) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t KB = p.K / BK;
     const uint32_t STAGES = p.stages;
-    const uint32_t stage_bytes = p.n_a * TILE_BYTES;
+    const uint32_t stage_bytes = (p.n_a + (RESIDENT_W ? 0u : 1u)) * TILE_BYTES;
     uint8_t* w_tiles = smem;                               // [KB] this CTA's 128 weight rows
-    uint8_t* a_ring = smem + KB * TILE_BYTES;              // [STAGES] this CTA's 128 activation rows
+    uint8_t* a_ring = smem + (RESIDENT_W ? KB * TILE_BYTES : 0u);   // [STAGES] this CTA's 128 activation (+ weight) rows
     uint4* lut = reinterpret_cast<uint4*>(a_ring);         // only until the weights are expanded
     __half* s_scale = reinterpret_cast<__half*>(a_ring + STAGES * stage_bytes);   // [256] all columns of the pair
     __half* s_bias = s_scale + WS2_BN;
@@ -89,9 +92,10 @@ gemm_ws2_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const
         ptx::fence_mbar_init();
         ptx::tma_prefetch_desc(&maps.a[z][0]);
         if (p.n_a == 2) ptx::tma_prefetch_desc(&maps.a[z][1]);
+        if (!RESIDENT_W) ptx::tma_prefetch_desc(&maps.b[z]);
     }
     // 8 weight bits -> 8 FP16 values (+1.0 = 0x3C00, -1.0 = 0xBC00), bit i -> element i
-    for (int b = threadIdx.x; b < 256; b += WS2_THREADS) {
+    for (int b = threadIdx.x; RESIDENT_W && b < 256; b += WS2_THREADS) {
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -111,7 +115,7 @@ gemm_ws2_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const
     }
     __syncthreads();
     // expand this CTA's 128 weight rows once: row r of k-block kb -> 128 bytes, 16-byte chunk j at j ^ (r % 8)
-    for (uint32_t item = threadIdx.x; item < KB * BN; item += WS2_THREADS) {
+    for (uint32_t item = threadIdx.x; RESIDENT_W && item < KB * BN; item += WS2_THREADS) {
         const uint32_t r = item % BN, kb = item / BN;
         const uint32_t n = n0 + rank * BN + r;
         uint32_t w0 = 0, w1 = 0;
@@ -155,6 +159,9 @@ gemm_ws2_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const
                     if (p.n_a == 2)
                         ptx::tma_load_2d_pair(st + TILE_BYTES, &maps.a[z][1], full_even + 8 * s, (int32_t)(kb * BK),
                                               (int32_t)m0);
+                    if (!RESIDENT_W)
+                        ptx::tma_load_2d_pair(st + p.n_a * TILE_BYTES, &maps.b[z], full_even + 8 * s, (int32_t)(kb * BK),
+                                              (int32_t)(n0 + rank * BN));
                 }
             }
             if (!ok && rank == 0) {
@@ -187,7 +194,7 @@ gemm_ws2_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const
                     }
                     ptx::tc_fence_after_sync();
                     const uint32_t a_addr = ptx::smem_u32(a_ring + s * stage_bytes);
-                    const uint32_t b_addr = w_addr + kb * TILE_BYTES;
+                    const uint32_t b_addr = RESIDENT_W ? w_addr + kb * TILE_BYTES : a_addr + p.n_a * TILE_BYTES;
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < BK / 16; ++k4) {
                         const uint64_t db = ptx::smem_desc_sw128(b_addr + k4 * 32);
