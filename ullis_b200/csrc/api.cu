@@ -213,6 +213,7 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
             if (mb > 0) rt->sam_budget_bytes = (size_t)mb << 20;
         }
         if (const char* env = getenv("ULLIS_CUDA_SAM_SPARSE")) rt->sam_sparse_per_sm = (uint32_t)std::max(0, atoi(env));
+        if (const char* env = getenv("ULLIS_CUDA_SAM_WORDS")) rt->sam_words = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_LANES")) {
             const int v = atoi(env);
             if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16 || v == 32) {

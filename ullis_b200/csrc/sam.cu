@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(128)
 rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
                   const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ list,
                   const uint32_t* __restrict__ count, size_t first, uint32_t T, size_t wps, int lanes,
-                  uint32_t dense_count, uint32_t sparse_count) {
+                  uint32_t dense_count, uint32_t sparse_count, int words) {
     // lanes == 0: choose from the number of streams that are left, which only the device knows -
     // many streams: four per warp (fewer issued instructions); fewer: two, then one per warp (more
     // warps to hide the pointer-chase latency).  The grid is sized for one per warp.
@@ -95,7 +95,8 @@ rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const ui
     if (first + item >= *count) return;
     const size_t s = list[first + item];
     sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
-    sam::euler_pass1<uint16_t>(B, q_sw + s * wps, k_sw + s * wps, T, nullptr);
+    if (words) sam::euler_pass1_words(B, q_sw + s * wps, k_sw + s * wps, T);
+    else sam::euler_pass1<uint16_t>(B, q_sw + s * wps, k_sw + s * wps, T, nullptr);
 }
 
 __global__ void __launch_bounds__(sam::COOP_THREADS)
@@ -191,7 +192,7 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
             const size_t pass1_warps = rt->sam_lanes_fixed ? warps : n;
             rosa_pass1_kernel<<<(unsigned)((pass1_warps * 32 + 127) / 128), 128, 0, rt->stream>>>(
                 scratch, stride, q_sw, k_sw, list, count, s0, (uint32_t)time, wps, pass1_lanes,
-                96u * (uint32_t)rt->sm_count, rt->sam_sparse_per_sm * (uint32_t)rt->sm_count);
+                96u * (uint32_t)rt->sm_count, rt->sam_sparse_per_sm * (uint32_t)rt->sm_count, rt->sam_words ? 1 : 0);
             rt->launched("rosa_pass1");
             rosa_coop_kernel<<<(unsigned)n, sam::COOP_THREADS, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, count, s0,
                                                                          (uint32_t)time, wps, rt->dev_status);

@@ -79,6 +79,11 @@ __device__ __forceinline__ float h2f_bits(uint16_t b) { return __half2float(__us
 // row scale / bias of the tile's columns as the kernel keeps them in shared memory: f32, or the FP16 they came from
 __device__ __forceinline__ float sb_load(const float* p, uint32_t i) { return p[i]; }
 __device__ __forceinline__ float sb_load(const __half* p, uint32_t i) { return __half2float(p[i]); }
+// entries i and i + 1 (i even) with one shared-memory load
+__device__ __forceinline__ float2 sb_load2(const float* p, uint32_t i) { return *reinterpret_cast<const float2*>(p + i); }
+__device__ __forceinline__ float2 sb_load2(const __half* p, uint32_t i) {
+    return __half22float2(*reinterpret_cast<const __half2*>(p + i));
+}
 
 // One output row (TMEM lane) per thread, the 32-column chunks [c_begin, c_end) of the tile's 128 columns.
 // `part` = index of this call's partial among the row's p.n_tiles partials (EPI_CE).
@@ -141,22 +146,22 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
             }
         } else if (EPI == EPI_RELU2) {
             uint16_t* out = static_cast<uint16_t*>(pr.out) + (size_t)m * p.N + nc;
+            float top = 0.0f;   // largest output of this row's chunk, for the FP16 range check
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 8; e += 2) {
-                    float a = fmaxf(sb_load(s_bias, c * 32 + j + e) + sb_load(s_scale, c * 32 + j + e) * __uint_as_float(r[j + e]), 0.0f);
-                    float b = fmaxf(sb_load(s_bias, c * 32 + j + e + 1) + sb_load(s_scale, c * 32 + j + e + 1) * __uint_as_float(r[j + e + 1]), 0.0f);
+                    const float2 sc = sb_load2(s_scale, c * 32 + j + e), bi = sb_load2(s_bias, c * 32 + j + e);
+                    float a = fmaxf(bi.x + sc.x * __uint_as_float(r[j + e]), 0.0f);
+                    float b = fmaxf(bi.y + sc.y * __uint_as_float(r[j + e + 1]), 0.0f);
                     a *= a; b *= b;
                     if (p.out_fmt == 1) {
                         __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
                         w[e / 2] = *reinterpret_cast<uint32_t*>(&h);
                     } else {
                         // FP16 keeps 11 significant bits (bf16: 8) but ends at 65504: report, do not emit inf
-                        if (row_ok && (a > 65504.0f || b > 65504.0f) &&
-                            atomicCAS(p.status, ULLIS_DEV_OK, ULLIS_DEV_FP16_RANGE) == ULLIS_DEV_OK)
-                            p.status[1] = m;
+                        top = fmaxf(top, fmaxf(a, b));
                         __half2 h = __floats2half2_rn(fminf(a, 65504.0f), fminf(b, 65504.0f));
                         w[e / 2] = *reinterpret_cast<uint32_t*>(&h);
                     }
@@ -170,6 +175,8 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
                     *reinterpret_cast<uint4*>(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
+            if (row_ok && top > 65504.0f && atomicCAS(p.status, ULLIS_DEV_OK, ULLIS_DEV_FP16_RANGE) == ULLIS_DEV_OK)
+                p.status[1] = m;
             if (STAGED16) {
                 // a thread holds 64 bytes of ONE row, so direct stores touch 32 rows per instruction; through
                 // the warp's 32 x 64-byte buffer four lanes cover a row's 64 bytes and an instruction eight rows
