@@ -158,11 +158,13 @@ emit_f16_kernel(const uint32_t* __restrict__ idx_sw, const uint16_t* __restrict_
 // Sign bits whose tensor-core pre-activation fell inside the error band are
 // recomputed exactly as the reference does (src/model.rs:724-742 on the
 // time-shift mix of x): sequential f32 sum over i, then bias + scale*sum.
-// Flags are sparse (a few per thousand), so a CTA first gathers the flagged
-// (word, bit) pairs of its chunk into a shared queue and then spreads them
-// over all of its threads - one exact dot product per thread.
-constexpr int FIX_THREADS = 256, FIX_WORDS = 2048, FIX_QUEUE = 16384;
-static_assert(((FIX_WORDS - 1) << 5 | 31) <= 0xFFFF, "queue entries are 16 bits");
+// Flags are sparse (a few per thousand).  A CTA owns a window of 64 steps of
+// one sequence for ALL channels of Q, K and V, so the 65 rows of x its exact
+// dot products read stay in L1 / L2 and every row is fetched from HBM about
+// once per launch; it gathers the flagged (matrix, channel, step) triples into
+// a shared queue and spreads them over its threads, one dot product each.
+constexpr int FIX_THREADS = 256, FIX_WIN = 2 /* flag words (of 32 steps) per window */, FIX_QUEUE = 12288;
+static_assert(FIX_QUEUE >= FIX_THREADS * 32 + 1024, "one gathered slice must fit the queue");
 
 __global__ void __launch_bounds__(FIX_THREADS)
 sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, const uint16_t* __restrict__ mk,
@@ -170,39 +172,49 @@ sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, 
                   uint32_t* __restrict__ bq, uint32_t* __restrict__ bk, uint32_t* __restrict__ bv,
                   const uint32_t* __restrict__ fq, const uint32_t* __restrict__ fk, const uint32_t* __restrict__ fv,
                   size_t batch, size_t T, size_t C, size_t wps) {
-    extern __shared__ uint16_t fix_queue[];  // entries: (word offset in chunk, < 2048) << 5 | bit - 16 bits, so that seven CTAs fit an SM
+    extern __shared__ uint32_t fix_queue[];  // entries: matrix << 28 | channel << 8 | word in window << 5 | bit
     __shared__ uint32_t q_count;
-    const int which = blockIdx.y;
-    const uint32_t* flags = which == 0 ? fq : which == 1 ? fk : fv;
-    uint32_t* bits = which == 0 ? bq : which == 1 ? bk : bv;
-    const uint16_t* mix = which == 0 ? mq : which == 1 ? mk : mv;
-    const PackedWeights& W = which == 0 ? wq : which == 1 ? wk : wv;
-    const size_t total = batch * C * wps, chunk0 = (size_t)blockIdx.x * FIX_WORDS;
+    const size_t windows = (wps + FIX_WIN - 1) / FIX_WIN;
+    const size_t b = blockIdx.x / windows, w0 = (blockIdx.x % windows) * FIX_WIN;
+    const uint32_t per_matrix = (uint32_t)C * FIX_WIN, items = 3u * per_matrix;
     if (threadIdx.x == 0) q_count = 0;
     __syncthreads();
-    for (size_t sub = 0; sub < FIX_WORDS; sub += FIX_THREADS) {
-        const size_t e = chunk0 + sub + threadIdx.x;
-        uint32_t f = e < total ? flags[e] : 0u;
+    for (uint32_t base = 0; base < items; base += FIX_THREADS) {
+        const uint32_t it = base + threadIdx.x;
+        uint32_t f = 0, which = 0, c = 0, dw = 0;
+        if (it < items) {
+            which = it / per_matrix;
+            const uint32_t rem = it % per_matrix;
+            c = rem / FIX_WIN;
+            dw = rem % FIX_WIN;
+            const uint32_t* flags = which == 0 ? fq : which == 1 ? fk : fv;
+            if (w0 + dw < wps) f = flags[(b * C + c) * wps + w0 + dw];
+        }
         if (f) {
             const uint32_t at = atomicAdd(&q_count, (uint32_t)__popc(f));
             uint32_t k = 0;
             while (f) {
                 const uint32_t tt = __ffs(f) - 1;
                 f &= f - 1;
-                fix_queue[at + k++] = (uint16_t)(((uint32_t)(sub + threadIdx.x) << 5) | tt);
+                fix_queue[at + k++] = which << 28 | c << 8 | dw << 5 | tt;
             }
         }
         __syncthreads();
-        const bool last = sub + FIX_THREADS >= FIX_WORDS;
+        const bool last = base + FIX_THREADS >= items;
         if (q_count + FIX_THREADS * 32 <= FIX_QUEUE && !last) continue;  // room for another slice: keep gathering
         const uint32_t count = q_count;
         for (uint32_t i = threadIdx.x; i < count; i += FIX_THREADS) {
-            const uint32_t entry = fix_queue[i], tt = entry & 31u;
-            const size_t ew = chunk0 + (entry >> 5);
-            const size_t s = ew / wps, word = ew % wps, b = s / C, c = s % C;
+            const uint32_t entry = fix_queue[i], tt = entry & 31u, m = entry >> 28;
+            const size_t ch = (entry >> 8) & 0xFFFFFu, word = w0 + ((entry >> 5) & 7u);
+            const size_t ew = (b * C + ch) * wps + word;
             const size_t t = word * 32 + tt, row = b * T + t;
             const float* xr = x + row * C;
-            const uint32_t* wbits = W.bits + (c * C >> 5);  // C % 32 == 0 on this path
+            const uint16_t* mix = m == 0 ? mq : m == 1 ? mk : mv;
+            const uint32_t* wb = m == 0 ? wq.bits : m == 1 ? wk.bits : wv.bits;
+            const uint16_t* wscale = m == 0 ? wq.scale : m == 1 ? wk.scale : wv.scale;
+            const uint16_t* wbias = m == 0 ? wq.bias : m == 1 ? wk.bias : wv.bias;
+            uint32_t* bits = m == 0 ? bq : m == 1 ? bk : bv;
+            const uint32_t* wbits = wb + (ch * C >> 5);  // C % 32 == 0 on this path
             float sum = 0.0f;
             // 32 inputs per round: the sixteen row loads go out together, then the sum is taken in order
             for (size_t i0 = 0; i0 < C; i0 += 32) {
@@ -230,7 +242,7 @@ sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, 
                     }
                 }
             }
-            const float y = __fadd_rn(W.bias ? h2f(W.bias[c]) : 0.0f, __fmul_rn(h2f(W.scale[c]), sum));
+            const float y = __fadd_rn(wbias ? h2f(wbias[ch]) : 0.0f, __fmul_rn(h2f(wscale[ch]), sum));
             if (y > 0.0f) atomicOr(&bits[ew], 1u << tt); else atomicAnd(&bits[ew], ~(1u << tt));
         }
         __syncthreads();
@@ -344,7 +356,7 @@ bool usable(ullis_cuda_runtime* rt) {
             rt->tc_ws2_kernel = rt->tc_ws_kernel && !getenv("ULLIS_CUDA_NO_WS2");
             if (const char* env = getenv("ULLIS_CUDA_WS2_MIN_ROWS")) rt->tc_ws2_min_rows = (size_t)std::max(1, atoi(env));
             ULLIS_CUDA_CHECK(cudaFuncSetAttribute(sign_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  FIX_QUEUE * 2));
+                                                  FIX_QUEUE * 4));
             rt->tc_ready = 1;
         }
     }
@@ -569,8 +581,8 @@ bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeig
     for (int z = 0; z < 3; ++z)
         p.prob[z] = GemmProblem{W[z]->bits, W[z]->scale, W[z]->bias, outs[z], flags + z * sw, s1 + z * rows};
     launch<EPI_SIGNBITS, true>(rt, maps, p, 3, "gemm_qkv_signbits");
-    dim3 grid(blocks_for(sw, FIX_WORDS), 3);
-    sign_fixup_kernel<<<grid, FIX_THREADS, FIX_QUEUE * 2, rt->stream>>>(ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, flags,
+    const unsigned grid = (unsigned)(((wps + FIX_WIN - 1) / FIX_WIN) * batch);   // rows < 2^30, so this fits
+    sign_fixup_kernel<<<grid, FIX_THREADS, FIX_QUEUE * 4, rt->stream>>>(ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, flags,
                                                    flags + sw, flags + 2 * sw, batch, time, d, wps);
     rt->launched("sign_fixup");
     return true;
