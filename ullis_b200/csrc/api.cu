@@ -214,6 +214,10 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         }
         if (const char* env = getenv("ULLIS_CUDA_SAM_SPARSE")) rt->sam_sparse_per_sm = (uint32_t)std::max(0, atoi(env));
         if (const char* env = getenv("ULLIS_CUDA_SAM_WORDS")) rt->sam_words = atoi(env) != 0;
+        if (const char* env = getenv("ULLIS_CUDA_SAM_COOP_THREADS")) {
+            const int v = atoi(env);
+            if (v == 256 || v == 512 || v == 1024) rt->sam_coop_threads = v;
+        }
         if (const char* env = getenv("ULLIS_CUDA_SAM_LANES")) {
             const int v = atoi(env);
             if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16 || v == 32) {

@@ -88,6 +88,7 @@ struct ullis_cuda_runtime {
     bool sam_coop_ready = false;
     bool sam_lanes_fixed = false;       // ULLIS_CUDA_SAM_LANES was given: no per-launch choice in pass 1
     uint32_t sam_sparse_per_sm = 40;    // pass 1 carries one stream per warp below this many streams per SM
+    int sam_coop_threads = 0;           // threads per stream in the tour / pass 2 kernel (256, 512, 1024); 0 = from the shared memory a stream needs
     bool sam_words = true;              // pass 1 on packed state words (sam_core.cuh euler_pass1_words); false: the field-wise form
     int sam_lanes = 4;                  // streams carried per warp by the suffix-automaton kernel (1,2,4,...,32)
     uint64_t launches = 0;

@@ -99,7 +99,8 @@ rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const ui
     else sam::euler_pass1<uint16_t>(B, q_sw + s * wps, k_sw + s * wps, T, nullptr);
 }
 
-__global__ void __launch_bounds__(sam::COOP_THREADS)
+template <int NT>
+__global__ void __launch_bounds__(NT)
 rosa_coop_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ v_sw,
                  uint32_t* __restrict__ idx_sw, const uint32_t* __restrict__ list, const uint32_t* __restrict__ count,
                  size_t first, uint32_t T, size_t wps, uint32_t* __restrict__ status) {
@@ -113,7 +114,7 @@ rosa_coop_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uin
             status[1] = (uint32_t)s;
         return;
     }
-    sam::coop_tour_pass2(coop_smem, B, v_sw + s * wps, idx_sw + s * wps, T);
+    sam::coop_tour_pass2<NT>(coop_smem, B, v_sw + s * wps, idx_sw + s * wps, T);
 }
 
 // EAGER keeps the reference's schedule for every stream (no shortcut): list = all streams
@@ -178,7 +179,9 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
         rt->launched("rosa_classify");
     }
     if (use_coop && !rt->sam_coop_ready) {
-        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         rt->sam_coop_ready = true;
     }
     for (size_t s0 = 0; s0 < streams; s0 += wave) {
@@ -194,8 +197,16 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
                 scratch, stride, q_sw, k_sw, list, count, s0, (uint32_t)time, wps, pass1_lanes,
                 96u * (uint32_t)rt->sm_count, rt->sam_sparse_per_sm * (uint32_t)rt->sm_count, rt->sam_words ? 1 : 0);
             rt->launched("rosa_pass1");
-            rosa_coop_kernel<<<(unsigned)n, sam::COOP_THREADS, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, count, s0,
-                                                                         (uint32_t)time, wps, rt->dev_status);
+            // threads per stream: the fewer CTAs shared memory lets an SM hold, the more threads each one gets
+            const unsigned coop_per_sm = (unsigned)((227u * 1024u) / (coop.total + 1024u));
+            const int coop_threads = rt->sam_coop_threads ? rt->sam_coop_threads : coop_per_sm >= 3 ? 256 : coop_per_sm == 2 ? 512 : 1024;
+#define ULLIS_COOP_LAUNCH(NT)                                                                                      \
+    rosa_coop_kernel<NT><<<(unsigned)n, NT, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, count, s0, \
+                                                                      (uint32_t)time, wps, rt->dev_status)
+            if (coop_threads == 256) ULLIS_COOP_LAUNCH(256);
+            else if (coop_threads == 512) ULLIS_COOP_LAUNCH(512);
+            else ULLIS_COOP_LAUNCH(1024);
+#undef ULLIS_COOP_LAUNCH
             rt->launched("rosa_coop");
             continue;
         }

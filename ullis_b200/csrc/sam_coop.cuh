@@ -6,7 +6,7 @@
 // parallelise over states / steps, so a warp does them in far fewer issued
 // instructions and without global-memory round trips.
 //
-//  tour   (whole CTA, 128 threads) Euler tour of the link tree as a linked
+//  tour   (whole CTA, 256 to 1024 threads) Euler tour of the link tree as a linked
 //         list of 2n events (enter v, leave v); the rank of every event
 //         (number of stamped states entered before it) by two-level list
 //         ranking: serial walks of short sublists between hashed splitters,
@@ -14,8 +14,8 @@
 //  pass 2 (whole CTA) the stamp of every rank is known up front (a state is
 //         stamped once, when created), so a step with a narrow rank range scans
 //         that array directly, all steps in parallel.  Steps with wide ranges
-//         use a 16-ary max tree whose upper levels are replayed in rounds of 128
-//         steps (one shared-memory atomicMax per level and step); a stream
+//         use a 16-ary max tree whose upper levels are replayed in rounds of one step per thread
+//         (one shared-memory atomicMax per level and step); a stream
 //         without wide ranges skips the replay.
 //
 // 16-bit state ids only (2T+2 <= 65535); the caller falls back to the
@@ -27,7 +27,7 @@
 namespace ullis {
 namespace sam {
 
-constexpr int COOP_THREADS = 128;
+constexpr int COOP_MAX_THREADS = 1024;   // the kernel runs with 256, 512 or 1024 threads per stream
 
 // Optional phase timestamps for a profiling build (defined by the includer); nothing by default.
 #ifndef ULLIS_COOP_MARK
@@ -45,7 +45,7 @@ struct CoopLayout {
         kid = off;        off += (cap * 4 + 15) & ~15u;                          // child pairs, later {lo,hi}
         clone_bits = off; off += (((cap + 31) / 32) * 4 + 15) & ~15u;
         vbits = off;      off += (wps * 4 + 15) & ~15u;
-        round_rank = off; off += COOP_THREADS * 4;                                // ranks of the steps of one pass-2 round
+        round_rank = off; off += COOP_MAX_THREADS * 4;                                // ranks of the steps of one pass-2 round
         wide = off;       off += (wps * 4 + 15) & ~15u;                           // steps whose rank range is wide
         ctrl = off;       off += 16;                                              // [0] = end of the last round with a wide range
         total = off;
@@ -89,8 +89,9 @@ __device__ __forceinline__ bool is_splitter(uint32_t e, uint32_t blocks) {
 }
 constexpr uint32_t LAST_OF_SUBLIST = 0x80000000u;   // flag in an event word: the successor is a splitter or the end
 
-// One CTA of COOP_THREADS threads; `B` is the stream's global scratch block
+// One CTA of NT threads; `B` is the stream's global scratch block
 // after euler_pass1.  Every thread of the CTA must call this.
+template <int NT>
 __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<uint16_t>& B, const uint32_t* vw,
                                                 uint32_t* out, uint32_t T) {
     constexpr uint32_t NIL = 0xFFFFu, END = 0xFFFFu;
@@ -113,14 +114,14 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     // second array borrows the upper half of the event area for a moment.
     uint32_t* kid_min = kid;
     uint32_t* kid_max = ev + cap;
-    for (uint32_t v = tid; v < n; v += COOP_THREADS) {
+    for (uint32_t v = tid; v < n; v += NT) {
         kid_min[v] = 0xFFFFFFFFu;
         kid_max[v] = 0u;
     }
-    for (uint32_t w = tid; w < (n + 31) / 32; w += COOP_THREADS) cbits[w] = B.clone_bits[w];
-    for (uint32_t w = tid; w < wps; w += COOP_THREADS) vbits[w] = vw[w];
+    for (uint32_t w = tid; w < (n + 31) / 32; w += NT) cbits[w] = B.clone_bits[w];
+    for (uint32_t w = tid; w < wps; w += NT) vbits[w] = vw[w];
     // the query states and new-state ids are needed much later: ask for them now, 128 bytes per thread
-    for (uint32_t i = tid * 64u; i < T; i += COOP_THREADS * 64u) {
+    for (uint32_t i = tid * 64u; i < T; i += NT * 64u) {
         asm volatile("prefetch.global.L2 [%0];" ::"l"(B.vq + i));
         asm volatile("prefetch.global.L2 [%0];" ::"l"(B.jid + i));
     }
@@ -129,16 +130,16 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     __syncthreads();
     // global loads go out eight at a time, so that their latencies overlap
     const uint32_t* link_words = reinterpret_cast<const uint32_t*>(B.N) + 1;   // Node = {t0, t1 | fail, maxlen}
-    for (uint32_t v0 = tid; v0 < n; v0 += COOP_THREADS * 8) {
+    for (uint32_t v0 = tid; v0 < n; v0 += NT * 8) {
         uint32_t p[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const uint32_t v = v0 + COOP_THREADS * u;
+            const uint32_t v = v0 + NT * u;
             p[u] = v < n ? link_words[2 * v] & 0xFFFFu : NIL;
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const uint32_t v = v0 + COOP_THREADS * u;
+            const uint32_t v = v0 + NT * u;
             if (v < n && v != 0) {
                 atomicMin(&kid_min[p[u]], v);
                 atomicMax(&kid_max[p[u]], v);
@@ -147,7 +148,7 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     }
     __syncthreads();
     ULLIS_COOP_MARK(0);
-    for (uint32_t v = tid; v < n; v += COOP_THREADS) {
+    for (uint32_t v = tid; v < n; v += NT) {
         const uint32_t a = kid_min[v], b = kid_max[v];
         kid[v] = a == 0xFFFFFFFFu ? 0xFFFFFFFFu : (a | ((a == b ? NIL : b) << 16));
     }
@@ -157,16 +158,16 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     // ---- Euler tour as a list: event 2v = enter v, 2v+1 = leave v; word = successor | weight << 16
     // (the suffix links come from global memory again, eight loads at a time: keeping
     // them in shared memory would cost the fourth resident CTA per SM)
-    for (uint32_t v0 = tid; v0 < n; v0 += COOP_THREADS * 8) {
+    for (uint32_t v0 = tid; v0 < n; v0 += NT * 8) {
         uint32_t par[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const uint32_t v = v0 + COOP_THREADS * u;
+            const uint32_t v = v0 + NT * u;
             par[u] = v < n ? link_words[2 * v] & 0xFFFFu : NIL;
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const uint32_t v = v0 + COOP_THREADS * u;
+            const uint32_t v = v0 + NT * u;
             if (v >= n) continue;
             const uint32_t k = kid[v], a = k & 0xFFFFu;
             const uint32_t stamped = (v != 0 && !((cbits[v >> 5] >> (v & 31)) & 1u)) ? 1u : 0u;
@@ -206,7 +207,7 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
         };
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            c[u].k = tid + COOP_THREADS * u;
+            c[u].k = tid + NT * u;
             c[u].head = c[u].cur = c[u].before = 0;
             next_block(c[u]);
         }
@@ -221,7 +222,7 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
                 c[u].before += (w[u] >> 16) & 1u;
                 if (w[u] & LAST_OF_SUBLIST) {
                     ev[c[u].head] = (c[u].before << 16) | (w[u] & 0xFFFFu);
-                    c[u].k += COOP_THREADS * 2;
+                    c[u].k += NT * 2;
                     next_block(c[u]);
                 } else {
                     c[u].cur = w[u] & 0xFFFFu;
@@ -236,11 +237,11 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     for (uint32_t it = 0; it <= rounds; ++it) {
         int any = 0;
         // eight independent splitters per thread and step: their dependent loads overlap
-        for (uint32_t k0 = tid; k0 < ns; k0 += COOP_THREADS * 8) {
+        for (uint32_t k0 = tid; k0 < ns; k0 += NT * 8) {
             uint32_t sp[8], w[8], w2[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                const uint32_t k = k0 + COOP_THREADS * u;
+                const uint32_t k = k0 + NT * u;
                 sp[u] = k < ns ? splitter_of_block(k) : 0xFFFFFFFFu;
             }
 #pragma unroll
@@ -266,7 +267,7 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     // rank range of state v: stamped states entered before enter(v) / before leave(v)
     const uint32_t total = ev[0] >> 16;
     uint32_t* lh = kid;  // the splitter list is dead; same element size as the child pairs
-    for (uint32_t v = tid; v < n; v += COOP_THREADS) {
+    for (uint32_t v = tid; v < n; v += NT) {
         const uint32_t lo = total - weight_from(2 * v), hi = total - weight_from(2 * v + 1);
         lh[v] = lo | (hi << 16);
     }
@@ -275,17 +276,17 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     // behind it takes the query states and the new states of every step.
     uint16_t* vq_s = reinterpret_cast<uint16_t*>(ev + ((tree_entries(T) + 3u) & ~3u));
     uint16_t* jid_s = vq_s + T;
-    for (uint32_t i0 = tid; i0 < T; i0 += COOP_THREADS * 8) {
+    for (uint32_t i0 = tid; i0 < T; i0 += NT * 8) {
         uint16_t a[8], b[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const uint32_t i = i0 + COOP_THREADS * u;
+            const uint32_t i = i0 + NT * u;
             a[u] = i < T ? B.vq[i] : (uint16_t)0;
             b[u] = i < T ? B.jid[i] : (uint16_t)0;
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const uint32_t i = i0 + COOP_THREADS * u;
+            const uint32_t i = i0 + NT * u;
             if (i < T) { vq_s[i] = a[u]; jid_s[i] = b[u]; }
         }
     }
@@ -297,7 +298,7 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     //   narrow ranges (at most NARROW ranks; almost all of them on typical
     //     streams) are scanned directly in that array, all steps in parallel;
     //   wide ranges go through the upper tree levels (maxima of groups of 16),
-    //     which do depend on time: they are replayed in rounds of COOP_THREADS
+    //     which do depend on time: they are replayed in rounds of NT
     //     steps, and only if the stream has a wide range at all.
     constexpr uint32_t NARROW = 16;
     uint32_t* tree = ev;  // events are dead
@@ -305,12 +306,12 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     const uint32_t entries = tree_entries(T);
     const uint32_t size0 = (T + 15u) & ~15u;
     const int warp = tid >> 5;
-    for (uint32_t k = tid; k < entries; k += COOP_THREADS) tree[k] = 0;
+    for (uint32_t k = tid; k < entries; k += NT) tree[k] = 0;
     __syncthreads();
-    for (uint32_t i = tid; i < T; i += COOP_THREADS) tree[lh[jid_s[i]] & 0xFFFFu] = i + 1u;
+    for (uint32_t i = tid; i < T; i += NT) tree[lh[jid_s[i]] & 0xFFFFu] = i + 1u;
     __syncthreads();
     ULLIS_COOP_MARK(5);
-    for (uint32_t t0 = 0; t0 < T; t0 += COOP_THREADS) {
+    for (uint32_t t0 = 0; t0 < T; t0 += NT) {
         const uint32_t t = t0 + tid;
         uint32_t m = 0;
         bool is_wide = false;
@@ -335,7 +336,7 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
         if (lane == 0 && t0 + warp * 32 < T) {
             out[(t0 >> 5) + warp] = word;
             wide[(t0 >> 5) + warp] = wide_word;
-            if (wide_word) atomicMax(replay_end, t0 + COOP_THREADS);
+            if (wide_word) atomicMax(replay_end, t0 + NT);
         }
     }
     __syncthreads();
@@ -347,7 +348,7 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     // upper levels, which hold the stamps of earlier rounds; the partial groups
     // at both ends by level 0 with the `<= t` filter; stamps of earlier steps of
     // the same round by the round's published ranks, newest first.
-    for (uint32_t t0 = 0; t0 < t_end; t0 += COOP_THREADS) {
+    for (uint32_t t0 = 0; t0 < t_end; t0 += NT) {
         const uint32_t t = t0 + tid;
         const bool live = t < T;
         const uint32_t my_rank = live ? lh[jid_s[t]] & 0xFFFFu : 0xFFFFFFFFu;
