@@ -163,8 +163,8 @@ emit_f16_kernel(const uint32_t* __restrict__ idx_sw, const uint16_t* __restrict_
 // dot products read stay in L1 / L2 and every row is fetched from HBM about
 // once per launch; it gathers the flagged (matrix, channel, step) triples into
 // a shared queue and spreads them over its threads, one dot product each.
-constexpr int FIX_THREADS = 256, FIX_WIN = 2 /* flag words (of 32 steps) per window */, FIX_QUEUE = 12288;
-static_assert(FIX_QUEUE >= FIX_THREADS * 32 + 1024, "one gathered slice must fit the queue");
+constexpr int FIX_THREADS = 256, FIX_WIN = 2 /* flag words (of 32 steps) per window */, FIX_QUEUE = 12288, FIX_BATCH = 8;
+static_assert(FIX_QUEUE >= FIX_THREADS * 32, "the flag bits of one word per thread must fit the queue");
 
 __global__ void __launch_bounds__(FIX_THREADS)
 sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, const uint16_t* __restrict__ mk,
@@ -173,35 +173,16 @@ sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, 
                   const uint32_t* __restrict__ fq, const uint32_t* __restrict__ fk, const uint32_t* __restrict__ fv,
                   size_t batch, size_t T, size_t C, size_t wps) {
     extern __shared__ uint32_t fix_queue[];  // entries: matrix << 28 | channel << 8 | word in window << 5 | bit
-    __shared__ uint32_t q_count;
+    __shared__ uint32_t q_count, announced;   // entries queued; flag bits announced so far (never reset)
     const size_t windows = (wps + FIX_WIN - 1) / FIX_WIN;
     const size_t b = blockIdx.x / windows, w0 = (blockIdx.x % windows) * FIX_WIN;
     const uint32_t per_matrix = (uint32_t)C * FIX_WIN, items = 3u * per_matrix;
-    if (threadIdx.x == 0) q_count = 0;
+    if (threadIdx.x == 0) { q_count = 0; announced = 0; }
     __syncthreads();
-    for (uint32_t base = 0; base < items; base += FIX_THREADS) {
-        const uint32_t it = base + threadIdx.x;
-        uint32_t f = 0, which = 0, c = 0, dw = 0;
-        if (it < items) {
-            which = it / per_matrix;
-            const uint32_t rem = it % per_matrix;
-            c = rem / FIX_WIN;
-            dw = rem % FIX_WIN;
-            const uint32_t* flags = which == 0 ? fq : which == 1 ? fk : fv;
-            if (w0 + dw < wps) f = flags[(b * C + c) * wps + w0 + dw];
-        }
-        if (f) {
-            const uint32_t at = atomicAdd(&q_count, (uint32_t)__popc(f));
-            uint32_t k = 0;
-            while (f) {
-                const uint32_t tt = __ffs(f) - 1;
-                f &= f - 1;
-                fix_queue[at + k++] = which << 28 | c << 8 | dw << 5 | tt;
-            }
-        }
+
+    // one exact dot product per queued entry, spread over the CTA's threads; empties the queue
+    auto drain = [&]() {
         __syncthreads();
-        const bool last = base + FIX_THREADS >= items;
-        if (q_count + FIX_THREADS * 32 <= FIX_QUEUE && !last) continue;  // room for another slice: keep gathering
         const uint32_t count = q_count;
         for (uint32_t i = threadIdx.x; i < count; i += FIX_THREADS) {
             const uint32_t entry = fix_queue[i], tt = entry & 31u, m = entry >> 28;
@@ -248,7 +229,55 @@ sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, 
         __syncthreads();
         if (threadIdx.x == 0) q_count = 0;
         __syncthreads();
+    };
+    auto push = [&](uint32_t f, uint32_t it) {
+        const uint32_t which = it / per_matrix, rem = it % per_matrix;
+        const uint32_t at = atomicAdd(&q_count, (uint32_t)__popc(f));
+        uint32_t k = 0;
+        while (f) {
+            const uint32_t tt = __ffs(f) - 1;
+            f &= f - 1;
+            fix_queue[at + k++] = which << 28 | (rem / FIX_WIN) << 8 | (rem % FIX_WIN) << 5 | tt;
+        }
+    };
+
+    // Flag words are read FIX_BATCH per thread at a time, all loads in flight together; the CTA first
+    // announces how many bits the batch holds so that every thread takes the same decision about the queue.
+    uint32_t seen = 0;   // value of `announced` before this batch (the same in every thread)
+    for (uint32_t base = 0; base < items; base += FIX_THREADS * FIX_BATCH) {
+        uint32_t f[FIX_BATCH], mine = 0;
+#pragma unroll
+        for (int k = 0; k < FIX_BATCH; ++k) {
+            const uint32_t it = base + k * FIX_THREADS + threadIdx.x;
+            f[k] = 0;
+            if (it < items) {
+                const uint32_t which = it / per_matrix, rem = it % per_matrix;
+                const uint32_t* flags = which == 0 ? fq : which == 1 ? fk : fv;
+                const size_t word = w0 + rem % FIX_WIN;
+                if (word < wps) f[k] = flags[(b * C + rem / FIX_WIN) * wps + word];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < FIX_BATCH; ++k) mine += (uint32_t)__popc(f[k]);
+        if (mine) atomicAdd(&announced, mine);
+        __syncthreads();
+        const uint32_t batch_bits = announced - seen, queued = q_count;
+        seen = announced;
+        __syncthreads();   // everyone has read both counters before either moves again
+        if (queued + batch_bits > FIX_QUEUE) drain();
+        if (batch_bits <= FIX_QUEUE) {
+#pragma unroll
+            for (int k = 0; k < FIX_BATCH; ++k)
+                if (f[k]) push(f[k], base + k * FIX_THREADS + threadIdx.x);
+        } else {   // dense flags: one word per thread at a time (at most 32 * FIX_THREADS entries)
+#pragma unroll
+            for (int k = 0; k < FIX_BATCH; ++k) {
+                if (f[k]) push(f[k], base + k * FIX_THREADS + threadIdx.x);
+                drain();
+            }
+        }
     }
+    drain();
 }
 
 // Merge the per-tile (max, sum exp) partials of a row and subtract the target

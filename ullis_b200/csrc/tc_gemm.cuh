@@ -196,7 +196,8 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
             uint32_t my_bits = 0, my_flags = 0;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const float sc = sb_load(s_scale, c * 32 + j), bi = sb_load(s_bias, c * 32 + j);
+                const float2 sc2 = sb_load2(s_scale, c * 32 + (j & ~1)), bi2 = sb_load2(s_bias, c * 32 + (j & ~1));
+                const float sc = (j & 1) ? sc2.y : sc2.x, bi = (j & 1) ? bi2.y : bi2.x;
                 const float t = sc * __uint_as_float(r[j]);
                 const float y = bi + t;
                 // error bound of the tensor-core sum against the reference's sequential f32 sum
@@ -216,7 +217,8 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
             float cmax = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const float y = sb_load(s_bias, c * 32 + j) + sb_load(s_scale, c * 32 + j) * __uint_as_float(r[j]);
+                const float2 sc2 = sb_load2(s_scale, c * 32 + (j & ~1)), bi2 = sb_load2(s_bias, c * 32 + (j & ~1));
+                const float y = ((j & 1) ? bi2.y : bi2.x) + ((j & 1) ? sc2.y : sc2.x) * __uint_as_float(r[j]);
                 r[j] = __float_as_uint(y);
                 if (nc + j < p.N) cmax = fmaxf(cmax, y);
                 if (nc + j == target && row_ok) static_cast<float*>(pr.out2)[m] = y;

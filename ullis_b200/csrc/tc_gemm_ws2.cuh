@@ -216,9 +216,22 @@ gemm_ws2_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const
         const uint32_t group = (uint32_t)(warp - 2) >> 2;
         const uint32_t row_in_tile = quarter * 32 + lane;
         const uint32_t drained_even = ptx::cluster_map(tmem_empty, 0);
+        // EPI_RESIDUAL reads the f32 rows it updates: ask L2 for this lane's 256 bytes of the next tile while the
+        // current one is drained, so that the read does not pay the HBM latency inside the epilogue (packed weights
+        // only: with dense weights the ring already keeps the memory system busy and the prefetch costs time)
+        auto prefetch_rows = [&](uint32_t t) {
+            const uint32_t mp = (member + t * members) * WS2_BM + rank * BM + row_in_tile;
+            if (EPI == EPI_RESIDUAL && RESIDENT_W && t < my_tiles && mp < p.M && n0 + group * 64 < p.N) {
+                const float* q = static_cast<const float*>(pr.out) + (size_t)mp * p.N + n0 + group * 64;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(q));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(q + 32));
+            }
+        };
+        prefetch_rows(0);
         for (uint32_t t = 0; t < my_tiles; ++t) {
             const uint32_t buf = t & 1u;
             const uint32_t m = (member + t * members) * WS2_BM + rank * BM + row_in_tile;
+            prefetch_rows(t + 1);
             // the accumulator loads below are warp-collective: decide for the whole warp
             if (!__all_sync(0xffffffffu, ws_wait(&tmem_full[buf], (t >> 1) & 1u, s_error))) {
                 atomicCAS(s_error, 0u, 4u);
