@@ -433,29 +433,43 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
     store_words(N, 0, 0xFFFFFFFFu, NIL);   // root: no children, no link, length 0
     uint32_t u = 1, g = 0, gmax = 0, gfail = NIL;   // extend side
     uint32_t w = 0, h = 0;                          // query side
+    // The words of state w travel in registers from one step to the next: a hit loads them anyway (the query
+    // ends in that state), and the few stores the extend makes to an existing state are applied to the copy.
+    NodeWords nw;
+    nw.x = 0xFFFFFFFFu; nw.y = NIL;
     uint32_t qword = 0, kword = 0;
     for (uint32_t i = 0; i < T; ++i) {
         if ((i & 31u) == 0) { qword = qw[i >> 5]; kword = kw[i >> 5]; }
         const uint32_t qs = (qword & 1u) << 4, kb = kword & 1u, ks = kb << 4;
         qword >>= 1; kword >>= 1;
+        // the first state of the extend walk is known before the query runs (the query stores nothing):
+        // its load goes out now and is in flight while the query walks
+        const uint32_t e0 = gfail;
+        NodeWords ne;
+        ne.x = 0; ne.y = 0;
+        if (e0 != NIL) ne = load_words(N, e0);
         // ---- query (src/rosa.rs:104-128)
+        bool hit;
         {
             uint32_t p = w, x = h, c, v = NIL;
+            NodeWords n = nw;
             for (;;) {
-                const NodeWords n = load_words(N, p);
                 c = (n.x >> qs) & 0xFFFFu;
                 if (c != NIL) break;
                 const uint32_t ml = n.y >> 16;
                 if (x > ml) x = ml;
                 p = n.y & 0xFFFFu;
                 if (p == NIL) break;
+                n = load_words(N, p);
             }
-            if (c == NIL) {
+            hit = c != NIL;
+            if (!hit) {
                 w = 0; h = 0;
             } else {
                 x += 1;
                 v = c;
                 NodeWords nv = load_words(N, v);
+                nw = nv;                          // the state the next query starts from
                 for (;;) {
                     const uint32_t f = nv.y & 0xFFFFu;
                     if (f == NIL) break;
@@ -468,18 +482,22 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
             }
             B.vq[i] = (uint16_t)v;
         }
-        // ---- extend (src/rosa.rs:139-167)
+        // ---- extend (src/rosa.rs:139-167); every store to an existing state is mirrored into nw when it is state w
         {
             const uint32_t j = u++;
+            const uint32_t child_mask = ~(0xFFFFu << ks);
             half[4 * g + kb] = (uint16_t)j;   // g has no children yet
-            uint32_t p = gfail, d = NIL, jfail = 0, pml = 0;
+            if (g == w) nw.x = (nw.x & child_mask) | (j << ks);
+            uint32_t p = e0, d = NIL, jfail = 0, pml = 0;
+            NodeWords n = ne;
             while (p != NIL) {
-                const NodeWords n = load_words(N, p);
                 d = (n.x >> ks) & 0xFFFFu;
                 pml = n.y >> 16;
                 if (d != NIL) break;
                 half[4 * p + kb] = (uint16_t)j;
+                if (p == w) nw.x = (nw.x & child_mask) | (j << ks);
                 p = n.y & 0xFFFFu;
+                if (p != NIL) n = load_words(N, p);
             }
             if (p != NIL) {
                 const NodeWords nd = load_words(N, d);
@@ -489,13 +507,17 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
                     const uint32_t b = u++;
                     store_words(N, b, nd.x, (nd.y & 0xFFFFu) | ((pml + 1u) << 16));   // the clone copies every field of d
                     half[4 * d + 2] = (uint16_t)b;
+                    if (d == w) nw.y = (nw.y & 0xFFFF0000u) | b;
                     jfail = b;
                     B.clone_bits[b >> 5] |= 1u << (b & 31);
-                    while (p != NIL) {
-                        const NodeWords n2 = load_words(N, p);
-                        if (((n2.x >> ks) & 0xFFFFu) != d) break;
+                    // p still has d as its child (that is where the walk stopped): redirect it, then go on up
+                    for (;;) {
                         half[4 * p + kb] = (uint16_t)b;
-                        p = n2.y & 0xFFFFu;
+                        if (p == w) nw.x = (nw.x & child_mask) | (b << ks);
+                        p = n.y & 0xFFFFu;
+                        if (p == NIL) break;
+                        n = load_words(N, p);
+                        if (((n.x >> ks) & 0xFFFFu) != d) break;
                     }
                 }
             }
@@ -504,6 +526,7 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
             g = j; gfail = jfail;
             B.jid[i] = (uint16_t)j;
         }
+        if (!hit) nw = load_words(N, 0);   // a miss sends the query back to the root
     }
     B.meta[0] = u;
     return u;
