@@ -78,7 +78,7 @@ rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint
 // Two-kernel form of the O(T log T) schedule for streams whose tour / pass 2
 // working set fits shared memory: pass 1 one thread per stream (below), then
 // one warp per stream for the parallel phases (sam_coop.cuh).
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 16)
 rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
                   const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ list,
                   const uint32_t* __restrict__ count, size_t first, uint32_t T, size_t wps, int lanes,
