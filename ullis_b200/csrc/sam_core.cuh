@@ -437,17 +437,16 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
     // ends in that state), and the few stores the extend makes to an existing state are applied to the copy.
     NodeWords nw;
     nw.x = 0xFFFFFFFFu; nw.y = NIL;
+    // So do the words of state gfail, where the next extend starts: it is the state the extend read last (a
+    // solid child), the clone it just wrote, or the root it just gave a child - never a load.
+    NodeWords ne;
+    ne.x = 0xFFFFFFFFu; ne.y = NIL;
     uint32_t qword = 0, kword = 0;
     for (uint32_t i = 0; i < T; ++i) {
         if ((i & 31u) == 0) { qword = qw[i >> 5]; kword = kw[i >> 5]; }
         const uint32_t qs = (qword & 1u) << 4, kb = kword & 1u, ks = kb << 4;
         qword >>= 1; kword >>= 1;
-        // the first state of the extend walk is known before the query runs (the query stores nothing):
-        // its load goes out now and is in flight while the query walks
         const uint32_t e0 = gfail;
-        NodeWords ne;
-        ne.x = 0; ne.y = 0;
-        if (e0 != NIL) ne = load_words(N, e0);
         // ---- query (src/rosa.rs:104-128)
         bool hit;
         {
@@ -489,23 +488,28 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
             half[4 * g + kb] = (uint16_t)j;   // g has no children yet
             if (g == w) nw.x = (nw.x & child_mask) | (j << ks);
             uint32_t p = e0, d = NIL, jfail = 0, pml = 0;
-            NodeWords n = ne;
+            NodeWords n = ne;                  // e0 == NIL (first step only): the root's words, for the case below
             while (p != NIL) {
                 d = (n.x >> ks) & 0xFFFFu;
                 pml = n.y >> 16;
                 if (d != NIL) break;
                 half[4 * p + kb] = (uint16_t)j;
                 if (p == w) nw.x = (nw.x & child_mask) | (j << ks);
-                p = n.y & 0xFFFFu;
-                if (p != NIL) n = load_words(N, p);
+                const uint32_t up = n.y & 0xFFFFu;
+                if (up == NIL) break;           // p is the root and has its new child: keep its words in n
+                p = up;
+                n = load_words(N, p);
             }
-            if (p != NIL) {
+            if (d != NIL) {
                 const NodeWords nd = load_words(N, d);
                 if (pml + 1u == (nd.y >> 16)) {
                     jfail = d;
+                    ne = nd;
                 } else {
                     const uint32_t b = u++;
-                    store_words(N, b, nd.x, (nd.y & 0xFFFFu) | ((pml + 1u) << 16));   // the clone copies every field of d
+                    ne.x = nd.x;                // the clone copies every field of d
+                    ne.y = (nd.y & 0xFFFFu) | ((pml + 1u) << 16);
+                    store_words(N, b, ne.x, ne.y);
                     half[4 * d + 2] = (uint16_t)b;
                     if (d == w) nw.y = (nw.y & 0xFFFF0000u) | b;
                     jfail = b;
@@ -520,6 +524,12 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
                         if (((n.x >> ks) & 0xFFFFu) != d) break;
                     }
                 }
+            } else {
+                // the walk ran out at the root (or started there): the link of j is the root, whose words are n
+                // with the child it was just given
+                jfail = 0;
+                ne.x = (n.x & child_mask) | (j << ks);
+                ne.y = n.y;
             }
             gmax += 1;
             store_words(N, j, 0xFFFFFFFFu, jfail | (gmax << 16));
