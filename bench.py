@@ -333,7 +333,9 @@ def run_cuda(args):
         # (three FP16 inputs, one idx byte, one FP16 output), one launch per layer.
         alg_bytes = ROSA_BYTES_PER_UNIT * B * time_ * d
         achieved = alg_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
-        rosa_ms = sum(t for name, (t, _) in kernel_ms.items() if name.startswith("rosa_")) / (args.steps * layers)
+        # rosa_constq runs on the runtime's side stream beside rosa_pass1: it is listed, but adds no time to a layer
+        rosa_ms = sum(t for name, (t, _) in kernel_ms.items()
+                      if name.startswith("rosa_") and name != "rosa_constq") / (args.steps * layers)
         shares = {name: {"ms_per_step": t / args.steps, "launches_per_step": n / args.steps,
                          "share": t / sum(v[0] for v in kernel_ms.values())} for name, (t, n) in top[:10]}
         line = {

@@ -93,14 +93,32 @@ void ullis_cuda_runtime::launched(const char* what) {
     if (kernel_timing) mark(what);
 }
 
-void ullis_cuda_runtime::mark(const char* what) {
-    if (marks_used == marks.size()) {
-        LaunchMark m{what, nullptr};
+static void ensure_mark(ullis_cuda_runtime* rt) {
+    if (rt->marks_used == rt->marks.size()) {
+        ullis_cuda_runtime::LaunchMark m{"", nullptr, nullptr, false};
         ULLIS_CUDA_CHECK(cudaEventCreate(&m.done));
-        marks.push_back(m);
+        rt->marks.push_back(m);
     }
+}
+
+void ullis_cuda_runtime::mark(const char* what) {
+    ensure_mark(this);
     marks[marks_used].name = what;
+    marks[marks_used].side = false;
     ULLIS_CUDA_CHECK(cudaEventRecord(marks[marks_used].done, stream));
+    ++marks_used;
+}
+
+void ullis_cuda_runtime::side_begin() {
+    ensure_mark(this);
+    if (!marks[marks_used].begin) ULLIS_CUDA_CHECK(cudaEventCreate(&marks[marks_used].begin));
+    ULLIS_CUDA_CHECK(cudaEventRecord(marks[marks_used].begin, side_stream));
+}
+
+void ullis_cuda_runtime::side_end(const char* what) {
+    marks[marks_used].name = what;
+    marks[marks_used].side = true;
+    ULLIS_CUDA_CHECK(cudaEventRecord(marks[marks_used].done, side_stream));
     ++marks_used;
 }
 
@@ -114,10 +132,14 @@ void ullis_cuda_runtime::kernel_time(const char* name, float* total_ms, uint32_t
     sync();
     float total = 0.f;
     uint32_t n = 0;
+    if (side_stream) ULLIS_CUDA_CHECK(cudaStreamSynchronize(side_stream));
+    cudaEvent_t previous = marks_start;   // end of the last kernel on `stream`
     for (size_t i = 0; i < marks_used; ++i) {
+        const cudaEvent_t from = marks[i].side ? marks[i].begin : previous;
+        if (!marks[i].side) previous = marks[i].done;
         if (name && name[0] && std::strcmp(name, marks[i].name) != 0) continue;
         float t = 0.f;
-        ULLIS_CUDA_CHECK(cudaEventElapsedTime(&t, i ? marks[i - 1].done : marks_start, marks[i].done));
+        ULLIS_CUDA_CHECK(cudaEventElapsedTime(&t, from, marks[i].done));
         total += t;
         ++n;
     }
@@ -214,6 +236,7 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         }
         if (const char* env = getenv("ULLIS_CUDA_SAM_SPARSE")) rt->sam_sparse_per_sm = (uint32_t)std::max(0, atoi(env));
         if (const char* env = getenv("ULLIS_CUDA_SAM_WORDS")) rt->sam_words = atoi(env) != 0;
+        if (const char* env = getenv("ULLIS_CUDA_SAM_SIDE")) rt->sam_side = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_COOP_THREADS")) {
             const int v = atoi(env);
             if (v == 256 || v == 512 || v == 1024) rt->sam_coop_threads = v;
@@ -242,9 +265,18 @@ void ullis_cuda_runtime_destroy(ullis_cuda_runtime* rt) {
         cudaStreamSynchronize(rt->stream);
         cudaStreamDestroy(rt->stream);
     }
+    if (rt->side_stream) {
+        cudaStreamSynchronize(rt->side_stream);
+        cudaStreamDestroy(rt->side_stream);
+    }
+    if (rt->side_fork) cudaEventDestroy(rt->side_fork);
+    if (rt->side_join) cudaEventDestroy(rt->side_join);
     if (rt->dev_status) cudaFree(rt->dev_status);
     if (rt->host_status) cudaFreeHost(rt->host_status);
-    for (auto& m : rt->marks) cudaEventDestroy(m.done);
+    for (auto& m : rt->marks) {
+        cudaEventDestroy(m.done);
+        if (m.begin) cudaEventDestroy(m.begin);
+    }
     if (rt->marks_start) cudaEventDestroy(rt->marks_start);
     delete rt;
 }

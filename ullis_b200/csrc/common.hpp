@@ -80,6 +80,11 @@ enum { ULLIS_DEV_OK = 0, ULLIS_DEV_BAD_TOKEN = 1, ULLIS_DEV_SAM_CAPACITY = 2, UL
 struct ullis_cuda_runtime {
     int device = 0;
     cudaStream_t stream = nullptr;
+    // a second stream for a kernel that has nothing to wait for on `stream` and that a latency-bound kernel there
+    // leaves room for (the constant-q closed form beside the automaton pass); forked and joined with the two events
+    cudaStream_t side_stream = nullptr;
+    cudaEvent_t side_fork = nullptr, side_join = nullptr;
+    bool sam_side = true;               // false: everything on `stream`
     int sm_count = 0;
     int cc_major = 0, cc_minor = 0;
     int mode = ULLIS_CUDA_MODE_FAST;
@@ -112,13 +117,15 @@ struct ullis_cuda_runtime {
     // Per-kernel device times: while enabled, an event is recorded behind every
     // launch; the stream is in order, so consecutive events bracket one kernel
     // (plus any small copy queued just before it).
-    struct LaunchMark { const char* name; cudaEvent_t done; };
+    struct LaunchMark { const char* name; cudaEvent_t done; cudaEvent_t begin; bool side; };   // side: a kernel on side_stream, timed begin -> done
     bool kernel_timing = false;
     std::vector<LaunchMark> marks;
     size_t marks_used = 0;
     cudaEvent_t marks_start = nullptr;
     void kernel_timing_begin();
     void mark(const char* what);   // closes the current bracket under the name `what`
+    void side_begin();             // kernel timing on: records the start of a side-stream kernel ...
+    void side_end(const char* what);   // ... and its end, as an entry of its own in the table
     // total milliseconds and launches of the kernels recorded under `name` (all kernels when name is empty)
     void kernel_time(const char* name, float* total_ms, uint32_t* n_launches);
     size_t kernel_names(char* buf, size_t len);  // newline-separated distinct names; returns bytes needed

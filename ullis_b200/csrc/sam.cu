@@ -25,7 +25,8 @@ namespace {
 __global__ void __launch_bounds__(128)
 rosa_classify_kernel(const uint32_t* __restrict__ q_sw, const uint32_t* __restrict__ k_sw,
                      const uint32_t* __restrict__ v_sw, uint32_t* __restrict__ idx_sw, size_t streams, uint32_t T,
-                     size_t wps, uint32_t* __restrict__ list, uint32_t* __restrict__ count) {
+                     size_t wps, uint32_t* __restrict__ list, uint32_t* __restrict__ count,
+                     uint32_t* __restrict__ cq_list, uint32_t* __restrict__ cq_count) {
     const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= streams) return;
     uint32_t c = 0;
@@ -37,11 +38,23 @@ rosa_classify_kernel(const uint32_t* __restrict__ q_sw, const uint32_t* __restri
         } else {
             sam::run_constant_v_one(q_sw + s * wps, k_sw + s * wps, idx_sw + s * wps, T);
         }
-    } else if (sam::k_is_constant(q_sw + s * wps, T, &c)) {   // constant q: a scan over the runs of c among the keys
-        sam::run_constant_q(c, k_sw + s * wps, v_sw + s * wps, idx_sw + s * wps, T);
+    } else if (sam::k_is_constant(q_sw + s * wps, T, &c)) {   // constant q: a scan over the runs of c among the keys,
+        cq_list[atomicAdd(cq_count, 1u)] = (uint32_t)s;       // the one closed form with a long loop: its own kernel
     } else {
         list[atomicAdd(count, 1u)] = (uint32_t)s;
     }
+}
+
+// The constant-q streams listed by rosa_classify_kernel, one per thread: every thread of a warp runs the
+// same scan (inside rosa_classify_kernel a warp would pay for it beside each of the shorter closed forms).
+__global__ void __launch_bounds__(128)
+rosa_constq_kernel(const uint32_t* __restrict__ q_sw, const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ v_sw,
+                   uint32_t* __restrict__ idx_sw, uint32_t T, size_t wps, const uint32_t* __restrict__ cq_list,
+                   const uint32_t* __restrict__ cq_count) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= *cq_count) return;
+    const size_t s = cq_list[i];
+    sam::run_constant_q(q_sw[s * wps] & 1u, k_sw + s * wps, v_sw + s * wps, idx_sw + s * wps, T);
 }
 
 // Only `lanes` threads of each warp carry a stream (the others exit at once).
@@ -161,22 +174,49 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     }
     uint8_t* scratch = static_cast<uint8_t*>(rt->sam_scratch.ensure(wave * stride));
     if (streams > 0xFFFFFFFFull) fail(ULLIS_CUDA_ERR_SHAPE, "too many ROSA streams");
-    uint32_t* list = rt->sam_list.as<uint32_t>(streams + 1);
+    uint32_t* list = rt->sam_list.as<uint32_t>(2 * streams + 2);
     uint32_t* count = list + streams;
+    uint32_t* cq_count = count + 1;           // the constant-q streams, settled by a kernel of their own
+    uint32_t* cq_list = count + 2;
     const unsigned cgrid = (unsigned)((streams + 127) / 128);
     // The number of streams left for the automaton is only known on the device;
     // each wave is sized for the worst case and surplus threads exit at once.
     const sam::CoopLayout coop((uint32_t)time);
     const bool use_coop = algo == ULLIS_CUDA_SAM_EULER && narrow && rt->sam_coop && coop.total <= 226 * 1024 &&
                           2 * sam::node_capacity((uint32_t)time) < 0xFFFFu;
+    bool forked = false;   // the constant-q kernel is running on the side stream
     if (algo == ULLIS_CUDA_SAM_EAGER) {
         rosa_list_all_kernel<<<cgrid, 128, 0, rt->stream>>>(list, count, streams);
         rt->launched("rosa_list_all");
     } else {
-        rt->zero(count, 4);
+        rt->zero(count, 8);   // both counters
         rosa_classify_kernel<<<cgrid, 128, 0, rt->stream>>>(q_sw, k_sw, v_sw, idx_sw, streams, (uint32_t)time, wps, list,
-                                                             count);
+                                                             count, cq_list, cq_count);
         rt->launched("rosa_classify");
+        // The constant-q scan is a long serial loop for a few thousand threads; it depends on nothing but the
+        // classification and writes idx words no other kernel of this call touches, so it runs on the side stream
+        // beside the automaton pass (which is bound by latency and leaves most issue slots free).
+        if (rt->sam_side) {
+            if (!rt->side_stream) {
+                ULLIS_CUDA_CHECK(cudaStreamCreateWithFlags(&rt->side_stream, cudaStreamNonBlocking));
+                ULLIS_CUDA_CHECK(cudaEventCreateWithFlags(&rt->side_fork, cudaEventDisableTiming));
+                ULLIS_CUDA_CHECK(cudaEventCreateWithFlags(&rt->side_join, cudaEventDisableTiming));
+            }
+            ULLIS_CUDA_CHECK(cudaEventRecord(rt->side_fork, rt->stream));
+            ULLIS_CUDA_CHECK(cudaStreamWaitEvent(rt->side_stream, rt->side_fork, 0));
+            if (rt->kernel_timing) rt->side_begin();
+            rosa_constq_kernel<<<cgrid, 128, 0, rt->side_stream>>>(q_sw, k_sw, v_sw, idx_sw, (uint32_t)time, wps, cq_list,
+                                                                   cq_count);
+            const cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) fail(ULLIS_CUDA_ERR_CUDA, std::string("launch of rosa_constq: ") + cudaGetErrorString(e));
+            ++rt->launches;
+            if (rt->kernel_timing) rt->side_end("rosa_constq");
+            ULLIS_CUDA_CHECK(cudaEventRecord(rt->side_join, rt->side_stream));
+            forked = true;
+        } else {
+            rosa_constq_kernel<<<cgrid, 128, 0, rt->stream>>>(q_sw, k_sw, v_sw, idx_sw, (uint32_t)time, wps, cq_list, cq_count);
+            rt->launched("rosa_constq");
+        }
     }
     if (use_coop && !rt->sam_coop_ready) {
         ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
@@ -223,6 +263,7 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
 #undef ULLIS_SAM_LAUNCH
         rt->launched("rosa_sam");
     }
+    if (forked) ULLIS_CUDA_CHECK(cudaStreamWaitEvent(rt->stream, rt->side_join, 0));   // idx is complete on `stream` from here
 }
 
 }  // namespace k
