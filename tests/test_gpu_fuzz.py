@@ -85,3 +85,27 @@ def test_models_of_random_shapes(cuda_rt, oracle, seed):
                     assert rel <= 1e-2, (d, layers, vocab, T, ffn, B, rel)                              # logits: 1e-2 relative
     finally:
         cuda_rt.set_mode(cuda.MODE_FAST)
+
+
+@pytest.mark.parametrize("env", [{"ULLIS_CUDA_SAM_SIDE": "0"}, {"ULLIS_CUDA_SAM_WORDS": "0"},
+                                 {"ULLIS_CUDA_SAM_COOP_THREADS": "512"}, {"ULLIS_CUDA_SAM_COOP_THREADS": "1024"},
+                                 {"ULLIS_CUDA_SAM_LANES": "4"}],
+                         ids=lambda e: "-".join(f"{k[11:].lower()}={v}" for k, v in e.items()))
+def test_rosa_streams_under_every_kernel_choice(oracle, monkeypatch, env):
+    """The automaton's alternative forms (constant-q closed form on the main stream, field-wise pass 1, more threads
+    per stream in tour / pass 2, several streams per warp) give the same idx as the defaults: all equal RosaSam::push."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    rt = cuda.CudaRuntime(0)
+    try:
+        rng = np.random.default_rng(77)
+        for B, T, C in ((2, 2048, 48), (1, 1000, 33), (3, 96, 64)):
+            q, k, v = (np.stack([np.stack([_stream(rng, T, rng.integers(0, 6)) for _ in range(C)], 1) for _ in range(B)])
+                       for _ in range(3))
+            qp, kp, vp = (pack_plane(a.reshape(-1)) for a in (q, k, v))
+            ref = oracle.rosa_qkv_batch_packed(qp, kp, vp, B, T, C)
+            e = np.linspace(0.01, 0.5, C).astype(np.float16).view(np.uint16)
+            idx, _ = rt.rosa_qkv_1bit_fwd(qp, kp, vp, e, B, T, C)
+            assert np.array_equal(idx, ref), (B, T, C)
+    finally:
+        rt.close()

@@ -98,9 +98,12 @@ def test_context_beyond_16_bit_state_ids(cuda_rt, oracle):
     run_both(cuda_rt, oracle, q, k, v, B, T, C, algos=(cuda.SAM_EULER,))
 
 
-def test_streams_in_waves_when_the_scratch_budget_is_small(oracle, monkeypatch):
-    """More streams than the automaton scratch may hold at once run in waves over the same blocks."""
-    monkeypatch.setenv("ULLIS_CUDA_SAM_BUDGET_MB", "4")          # 4 MiB: 56 blocks of 74 368 B at T=2048
+@pytest.mark.parametrize("budget_mb", ["4", "5"])
+def test_streams_in_waves_when_the_scratch_budget_is_small(oracle, monkeypatch, budget_mb):
+    """More streams than the automaton scratch may hold at once run in waves over the same blocks (4 MiB: 56 blocks
+    of 74 368 B at T=2048; 5 MiB: 70, not a multiple of the streams a warp or a CTA carries, so the rounded-up grid
+    of a wave reaches past it)."""
+    monkeypatch.setenv("ULLIS_CUDA_SAM_BUDGET_MB", budget_mb)
     rt = cuda.CudaRuntime(0)
     try:
         B, T, C = 2, 2048, 96                                     # 192 streams: four waves

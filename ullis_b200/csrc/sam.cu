@@ -67,14 +67,15 @@ __global__ void __launch_bounds__(128)
 rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
                 const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ v_sw,
                 uint32_t* __restrict__ idx_sw, const uint32_t* __restrict__ list,
-                const uint32_t* __restrict__ count, size_t first, uint32_t T, size_t wps, int lanes,
+                const uint32_t* __restrict__ count, size_t first, size_t wave, uint32_t T, size_t wps, int lanes,
                 uint32_t* __restrict__ status) {
     const int lane = threadIdx.x & 31;
     const int spread = 32 / lanes;
     if (lane % spread != 0) return;
     const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const size_t item = warp * lanes + lane / spread;
-    if (first + item >= *count) return;
+    // the grid is rounded up to whole CTAs: an item past the wave has no state block (it belongs to the next wave)
+    if (item >= wave || first + item >= *count) return;
     const size_t s = list[first + item];
     uint8_t* block = scratch + item * scratch_stride;
     const uint32_t* qw = q_sw + s * wps;
@@ -94,7 +95,7 @@ rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint
 __global__ void __launch_bounds__(128, 16)
 rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
                   const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ list,
-                  const uint32_t* __restrict__ count, size_t first, uint32_t T, size_t wps, int lanes,
+                  const uint32_t* __restrict__ count, size_t first, size_t wave, uint32_t T, size_t wps, int lanes,
                   uint32_t dense_count, uint32_t sparse_count, int words) {
     // lanes == 0: choose from the number of streams that are left, which only the device knows -
     // many streams: four per warp (fewer issued instructions); fewer: two, then one per warp (more
@@ -105,7 +106,9 @@ rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const ui
     if (lane % spread != 0) return;
     const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const size_t item = warp * lanes + lane / spread;
-    if (first + item >= *count) return;
+    // the grid is sized for one stream per warp and rounded up to whole CTAs: with several streams per warp an
+    // item can lie past the wave, where it has no state block (it belongs to the next wave)
+    if (item >= wave || first + item >= *count) return;
     const size_t s = list[first + item];
     sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
     if (words) sam::euler_pass1_words(B, q_sw + s * wps, k_sw + s * wps, T);
@@ -234,7 +237,7 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
             const int pass1_lanes = rt->sam_lanes_fixed ? lanes : 0;
             const size_t pass1_warps = rt->sam_lanes_fixed ? warps : n;
             rosa_pass1_kernel<<<(unsigned)((pass1_warps * 32 + 127) / 128), 128, 0, rt->stream>>>(
-                scratch, stride, q_sw, k_sw, list, count, s0, (uint32_t)time, wps, pass1_lanes,
+                scratch, stride, q_sw, k_sw, list, count, s0, n, (uint32_t)time, wps, pass1_lanes,
                 96u * (uint32_t)rt->sm_count, rt->sam_sparse_per_sm * (uint32_t)rt->sm_count, rt->sam_words ? 1 : 0);
             rt->launched("rosa_pass1");
             // threads per stream: the fewer CTAs shared memory lets an SM hold, the more threads each one gets
@@ -252,7 +255,7 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
         }
 #define ULLIS_SAM_LAUNCH(IX, ALGO)                                                                              \
     rosa_sam_kernel<IX, ALGO><<<grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, k_sw, v_sw, idx_sw, list, count, s0, \
-                                                           (uint32_t)time, wps, lanes, rt->dev_status)
+                                                           n, (uint32_t)time, wps, lanes, rt->dev_status)
         if (narrow) {
             if (algo == ULLIS_CUDA_SAM_EAGER) ULLIS_SAM_LAUNCH(uint16_t, ULLIS_CUDA_SAM_EAGER);
             else ULLIS_SAM_LAUNCH(uint16_t, ULLIS_CUDA_SAM_EULER);
