@@ -6,16 +6,22 @@
     python bench.py --impl reference ...      # CPU arm (oracle port on the host cores)
 
 Workload (default): Heron D=512 / L=12 / T=2048 / vocab 8192, 64 sequences
-per GPU of seeded Zipf(1.1) token ids, random-init weights from a seeded v2
-checkpoint - forward + streamed CE, no backward.  Sequences are independent,
-so ranks take disjoint sequences (weak scaling: 64 per GPU) and only
-{loss_sum, n_valid} is all-reduced over NCCL.
+of seeded Zipf(1.1) token ids, random-init weights from a seeded v2 checkpoint -
+forward + streamed CE, no backward.  Sequences are independent, so ranks take
+disjoint contiguous blocks of the 64 sequences (strong scaling: rank r of W
+owns sequences [r*64/W, (r+1)*64/W)) and only {loss_sum, n_valid} is
+all-reduced over NCCL, on the device.  `--scaling weak` keeps `--batch`
+sequences on every GPU instead.
 
-A "step" is one forward+CE over the rank's batch.  `value` times K steps with
-the token ids already resident in HBM (CUDA events on the backend's stream,
-max over ranks); `e2e` times the public C-ABI call with pinned HOST buffers,
-copies and the loss read-back inside the timed region.  One JSON line is
-printed by rank 0.
+A "step" is one forward+CE over the rank's sequences.  `value` times K steps
+with the token ids already resident in HBM (CUDA events on the backend's
+stream, max over ranks, no per-kernel instrumentation); `e2e` times the public
+C-ABI call with pinned HOST buffers, copies and the loss read-back inside the
+timed region.  The per-kernel table comes from a separate pass with an event
+behind every launch.  One JSON line is printed by rank 0; at one GPU its
+`extra` object adds the other configurations of the same path (one sequence of
+the default and of the small model, the LayerNorm-gain-one weight variant, the
+three packed-linear shapes).
 """
 from __future__ import annotations
 
@@ -48,7 +54,13 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["cuda", "reference"], default="cuda")
     ap.add_argument("--model", default="default", help="checkpoint shape: default (D512 L12 T2048), small, tiny")
-    ap.add_argument("--batch", type=int, default=64, help="sequences per GPU")
+    ap.add_argument("--batch", type=int, default=64,
+                    help="sequences: in the whole job with --scaling strong (the default), per GPU with --scaling weak")
+    ap.add_argument("--scaling", choices=["strong", "weak"], default="strong")
+    ap.add_argument("--ln-gain-one", action="store_true",
+                    help="LayerNorm weights 1 + N(0, 0.02) instead of N(0, 0.02): no constant channels, every stream "
+                         "reaches the automaton")
+    ap.add_argument("--no-extras", action="store_true", help="skip the `extra` measurements of the one-GPU line")
     ap.add_argument("--time", type=int, default=0, help="steps per sequence (0 = the model's context length)")
     ap.add_argument("--mode", choices=["fast", "exact"], default="fast")
     ap.add_argument("--sam", choices=["euler", "eager"], default="euler")
@@ -147,10 +159,10 @@ def sequence_tokens(model_vocab: int, first_seq: int, n_seq: int, time_: int) ->
     return np.concatenate([synth.zipf_tokens(11 + first_seq + b, time_, model_vocab) for b in range(n_seq)])
 
 
-def cpu_baseline_sample(data: bytes, vocab: int, time_: int):
-    """Oracle port on the host cores over ONE sequence of the workload."""
+def cpu_baseline_sample(data: bytes, vocab: int, time_: int, threads: int = 0):
+    """Oracle port on the host cores (all of them unless `threads` says otherwise) over ONE sequence of the workload."""
     from oracle import oracle as O
-    threads = O.max_threads()
+    threads = threads or O.max_threads()
     O.set_threads(threads)
     m = O.HeronOracle(data)
     tokens = sequence_tokens(vocab, 0, 1, time_)
@@ -171,7 +183,7 @@ def run_reference(args):
     from ullis_b200 import synth
     shape = synth.CONFIGS[args.model]
     time_ = args.time or shape[3]
-    data = synth.heron_checkpoint(args.model, batch_size=max(args.batch, 1))
+    data = synth.heron_checkpoint(args.model, batch_size=max(args.batch, 1), ln_gain_one=args.ln_gain_one)
     threads = O.max_threads()
     O.set_threads(threads)
     m = O.HeronOracle(data)
@@ -188,7 +200,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * dt / max(args.steps, 1), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, shape, time_, world),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -197,15 +209,113 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def rank_sequences(args, rank, world):
+    """[lo, hi) of the job's sequences that `rank` owns."""
+    from ullis_b200 import dp
+    if args.scaling == "weak":
+        return rank * args.batch, (rank + 1) * args.batch
+    return dp.shard_range(args.batch, rank, world)
+
+
 def workload_config(args, shape, time_, world):
     d, layers, vocab, ctx, ffn = shape
+    total = args.batch * world if args.scaling == "weak" else args.batch
+    per_gpu = [hi - lo for lo, hi in (rank_sequences(args, r, world) for r in range(world))]
     return {"workload": f"Heron D={d} L={layers} T={time_} vocab={vocab} forward + next-token CE, "
-                        f"{args.batch} sequences per GPU (Zipf(1.1) ids)",
+                        f"{total} sequences (Zipf(1.1) ids) over {world} GPU(s)",
             "d_model": d, "n_layers": layers, "seq_len": time_, "vocab": vocab, "dim_ffn": ffn,
-            "sequences_per_gpu": args.batch, "global_sequences": args.batch * world,
-            "parallelism": f"dp{world} over independent sequences, 16-byte loss all-reduce",
+            "global_sequences": total, "sequences_per_gpu": per_gpu,
+            "parallelism": f"dp{world} over independent sequences (contiguous blocks), 16-byte loss all-reduce on the device",
+            "weights": "LayerNorm gain 1 + N(0, 0.02)" if args.ln_gain_one else "LayerNorm gain N(0, 0.02) (the literal reading of the configuration)",
             "mode": args.mode, "sam": args.sam,
-            "l2": "no flush: each step streams >2 GB of activations and automaton state per GPU, far beyond the 126 MB L2"}
+            "l2": f"no flush: a step moves at least {min(per_gpu) * time_ * d * 4 * 8 * layers / 1e9:.1f} GB of activations per GPU "
+                  "(8 f32-row-equivalents per layer), beyond the 126 MB L2"}
+
+
+def device_steps_ms(model, rt, stream, torch, B, time_, steps, warm, reduce_loss=None):
+    """ms per forward+CE step with the ids already uploaded: `warm` untimed steps, then `steps` steps between
+    two CUDA events on the backend's stream.  Every step reads its loss back (the step's result)."""
+    from ullis_b200 import cuda
+    last = None
+    for _ in range(warm):
+        model.enqueue_forward_ce(cuda.CE_NO_IGNORE, B, time_)
+        last = reduce_loss() if reduce_loss else model.read_loss()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(steps):
+        model.enqueue_forward_ce(cuda.CE_NO_IGNORE, B, time_)
+        last = reduce_loss() if reduce_loss else model.read_loss()
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    return ev0.elapsed_time(ev1) / max(steps, 1), last
+
+
+def extra_measurements(args, rt, stream, torch, peaks):
+    """The other configurations of the same path, one GPU: a single sequence of the default and of the small
+    model (latency: a step is as long as the 2048-step serial chain of one stream per layer), the
+    LayerNorm-gain-one weight variant of the benchmark (no constant channels), and the packed-linear shapes."""
+    from ullis_b200 import cuda, synth
+    out = {}
+
+    def one(model_name, B, gain_one, steps, warm, with_kernels=False):
+        d, layers, vocab, ctx, ffn = synth.CONFIGS[model_name]
+        data = synth.heron_checkpoint(model_name, batch_size=B, ln_gain_one=gain_one)
+        model = cuda.CudaHeron(rt, data)
+        tokens = sequence_tokens(vocab, 0, B, ctx)
+        model.upload_tokens(tokens, tokens, B, ctx)
+        ms, last = device_steps_ms(model, rt, stream, torch, B, ctx, steps, warm)
+        counts = rt.sam_counts()
+        res = {"model": f"D={d} L={layers} T={ctx} vocab={vocab}", "sequences": B,
+               "weights": "ln gain 1 + N(0,0.02)" if gain_one else "ln gain N(0,0.02)",
+               "ms_per_forward": ms, "tokens_per_s": B * ctx / (ms * 1e-3), "mean_ce": last[0],
+               "automaton_streams_last_layer": counts["automaton"], "constant_q_streams_last_layer": counts["constant_q"],
+               "streams_per_layer": counts["total"]}
+        if with_kernels:
+            rt.kernel_timing(True)
+            model.enqueue_forward_ce(cuda.CE_NO_IGNORE, B, ctx)
+            model.read_loss()
+            km = rt.kernel_times()
+            rt.kernel_timing(False)
+            busy = sum(t for k, (t, _) in km.items() if not k.startswith("("))
+            res["kernel_ms_sum_instrumented"] = busy
+            res["launches"] = int(sum(n for k, (_, n) in km.items() if not k.startswith("(")))
+            res["launch_gap_share"] = max(0.0, 1.0 - busy / ms) if ms > 0 else None
+        model.close()
+        return res, data
+
+    out["config3_default_batch1"], data3 = one("default", 1, args.ln_gain_one, 10, 3, with_kernels=True)
+    out["config0_small_batch1"], data0 = one("small", 1, args.ln_gain_one, 20, 3, with_kernels=True)
+    out["config4_ln_gain_one" if not args.ln_gain_one else "config4_literal_weights"], _ = one(
+        "default", args.batch, not args.ln_gain_one, 3, 2)
+    if not args.no_cpu_baseline:
+        from oracle import oracle as O
+        for key, data, name in (("config0_small_batch1", data0, "small"),):
+            d, layers, vocab, ctx, ffn = synth.CONFIGS[name]
+            for threads in (O.max_threads(), 1):
+                base, _ = cpu_baseline_sample(data, vocab, ctx, threads)
+                out[key][f"oracle_{threads}_threads_tokens_per_s" if threads > 1 else "oracle_1_thread_tokens_per_s"] = base["value"]
+    # BASELINE configuration 1: the three packed-linear shapes at M = 2048 and at the benchmark's row count
+    linear = {}
+    sustained = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    for M in (2048, 131072):
+        for K, N in ((512, 512), (512, 2048), (512, 8192)):
+            x, bits, scale, bias = synth.packed_linear_case(3, M, K, N)
+            reps = 3 if M * N > (1 << 28) else 10
+            for _ in range(2):
+                rt.binary_linear(x, bits, scale, bias, M, K, N)
+            rt.kernel_timing(True)
+            for _ in range(reps):
+                rt.binary_linear(x, bits, scale, bias, M, K, N)
+            km = rt.kernel_times()
+            rt.kernel_timing(False)
+            gemm_ms = sum(t for name, (t, _) in km.items() if name.startswith("gemm_")) / reps
+            tf = 2.0 * M * K * N / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None
+            linear[f"M{M}_{K}x{N}"] = {"gemm_ms": gemm_ms, "tflops": tf,
+                                       "frac_of_sustained_peak": tf / sustained if tf else None}
+            del x
+    out["linear_f32_out"] = linear
+    return out
 
 
 def run_cuda(args):
@@ -238,32 +348,30 @@ def run_cuda(args):
     shape = synth.CONFIGS[args.model]
     d, layers, vocab, ctx, ffn = shape
     time_ = args.time or ctx
-    B = args.batch
-    data = synth.heron_checkpoint(args.model, batch_size=B)
+    lo, hi = rank_sequences(args, rank, world)
+    B = hi - lo                                  # this rank's sequences
+    total_seqs = args.batch * world if args.scaling == "weak" else args.batch
+    if B == 0:
+        raise SystemExit("more ranks than sequences")
+    data = synth.heron_checkpoint(args.model, batch_size=max(B, 1), ln_gain_one=args.ln_gain_one)
     model = cuda.CudaHeron(rt, data)
-    tokens = sequence_tokens(vocab, rank * B, B, time_)
+    tokens = sequence_tokens(vocab, lo, B, time_)
     labels = tokens
     rows = B * time_
+    total_rows = total_seqs * time_
 
     if world > 1:
         uid = [cuda.CudaRuntime.dp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         rt.dp_init(rank, world, uid[0])
 
-    def reduce_loss(loss_sum, n_valid):
-        if world > 1:
-            return rt.dp_allreduce_loss(loss_sum, n_valid)
-        return loss_sum, n_valid
+    # the step's result: the mean over every rank's valid positions, summed on the device at N > 1
+    reduce_loss = model.read_loss_global if world > 1 else None
 
-    # ---------------- device-resident timing (`value`)
+    # ---------------- device-resident timing (`value`), no per-kernel instrumentation
     model.upload_tokens(tokens, labels, B, time_)
     n_warm = args.warmup if args.profile_run else max(args.warmup, 3)
-    for _ in range(n_warm):
-        model.enqueue_forward_ce(cuda.CE_NO_IGNORE, B, time_)
-        mean, loss_sum, n_valid = model.read_loss()
-        reduce_loss(loss_sum, n_valid)
-    model.set_profile(True)
-    rt.kernel_timing(True)
+    device_steps_ms(model, rt, stream, torch, B, time_, 0, n_warm, reduce_loss)
     sampler = ClockSampler(local)
     barrier()
     if rank == 0:
@@ -273,55 +381,80 @@ def run_cuda(args):
     ev0.record(stream)
     for _ in range(args.steps):
         model.enqueue_forward_ce(cuda.CE_NO_IGNORE, B, time_)
-        mean, loss_sum, n_valid = model.read_loss()
-        total_sum, total_n = reduce_loss(loss_sum, n_valid)
+        mean, total_sum, total_n = reduce_loss() if reduce_loss else model.read_loss()
     ev1.record(stream)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     launches = rt.launch_count - launches0
     ms_total = ev0.elapsed_time(ev1)
-    phases = model.phase_ms()  # of the last timed step
-    kernel_ms = rt.kernel_times()  # over all timed steps: {name: (total ms, launches)}
-    rt.kernel_timing(False)
-    model.set_profile(False)
     t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
-    value = world * rows * args.steps / (ms_total / 1e3)
+    value = total_rows * args.steps / (ms_total / 1e3)
 
-    # ---------------- end-to-end timing through the public call, pinned host buffers
+    # ---------------- per-kernel table and phases: a separate pass with an event behind every launch
+    model.set_profile(True)
+    rt.kernel_timing(True)
+    n_table = min(args.steps, 3)
+    for _ in range(n_table):
+        model.enqueue_forward_ce(cuda.CE_NO_IGNORE, B, time_)
+        reduce_loss() if reduce_loss else model.read_loss()
+    phases = model.phase_ms()  # of the last instrumented step
+    kernel_ms = rt.kernel_times()  # over the instrumented steps: {name: (total ms, launches)}
+    sam_counts = rt.sam_counts()
+    rt.kernel_timing(False)
+    model.set_profile(False)
+
     if args.profile_run:
         if rank == 0:
             top = sorted(((k, v) for k, v in kernel_ms.items() if not k.startswith("(")), key=lambda kv: -kv[1][0])[:8]
             print(json.dumps({"profile_run": True, "ms_per_step": ms_total / args.steps, "phases_ms": phases,
                               "gpu_launches": int(launches),
                               "kernel_ms_per_launch": {k: round(t / max(c, 1), 4) for k, (t, c) in top}}), flush=True)
+        if world > 1:
+            rt.dp_finalize()
+            dist.destroy_process_group()
         model.close()
         rt.close()
         return
+
+    # ---------------- end-to-end timing through the public call, pinned host buffers
     pin_tok = torch.from_numpy(tokens.astype(np.int64)).to(torch.int32).pin_memory()
     pin_lab = pin_tok.clone().pin_memory()
     tok_np = pin_tok.numpy().view(np.uint32)
     lab_np = pin_lab.numpy().view(np.uint32)
+
+    def e2e_step():
+        if world > 1:   # ids in, forward, loss summed over the ranks on the device, one read-back
+            model.upload_tokens(tok_np, lab_np, B, time_)
+            model.enqueue_forward_ce(cuda.CE_NO_IGNORE, B, time_)
+            return model.read_loss_global()
+        return model.forward_ce(tok_np, lab_np, cuda.CE_NO_IGNORE, B, time_)
+
     for _ in range(2):
-        model.forward_ce(tok_np, lab_np, cuda.CE_NO_IGNORE, B, time_)
+        e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
-        mean_e, loss_sum_e, n_valid_e = model.forward_ce(tok_np, lab_np, cuda.CE_NO_IGNORE, B, time_)
-        reduce_loss(loss_sum_e, n_valid_e)
+        e2e_step()
     e1.record(stream)
     barrier()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = world * rows * args.steps / (float(t.item()) / 1e3)
+    e2e_value = total_rows * args.steps / (float(t.item()) / 1e3)
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
-        # dominant kernel = the one with the largest share of device time in the timed region
+        peaks = {}
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+        except Exception:  # noqa: BLE001
+            pass
+        # dominant kernel = the one with the largest share of device time in the instrumented pass
         kernel_ms = {k: v for k, v in kernel_ms.items() if not k.startswith("(")}   # drop the between-steps bracket
         top = sorted(kernel_ms.items(), key=lambda kv: -kv[1][0])
         # (on every supported shape that is one of the suffix-automaton kernels; should a GEMM
@@ -333,19 +466,20 @@ def run_cuda(args):
         # (three FP16 inputs, one idx byte, one FP16 output), one launch per layer.
         alg_bytes = ROSA_BYTES_PER_UNIT * B * time_ * d
         achieved = alg_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
-        # rosa_constq runs on the runtime's side stream beside rosa_pass1: it is listed, but adds no time to a layer
+        # kernels on a side stream run beside the others: they are listed, but add no time to a layer
         rosa_ms = sum(t for name, (t, _) in kernel_ms.items()
-                      if name.startswith("rosa_") and name != "rosa_constq") / (args.steps * layers)
-        shares = {name: {"ms_per_step": t / args.steps, "launches_per_step": n / args.steps,
-                         "share": t / sum(v[0] for v in kernel_ms.values())} for name, (t, n) in top[:10]}
+                      if name.startswith("rosa_") and name != "rosa_constq") / (n_table * layers)
+        shares = {name: {"ms_per_step": t / n_table, "launches_per_step": n / n_table,
+                         "share": t / sum(v[0] for v in kernel_ms.values())} for name, (t, n) in top[:12]}
+        flops_per_token = layers * (4 * 2 * d * d + 2 * d * ffn + 2 * ffn * d) + 2 * d * vocab
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": n_warm, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None,
+            "scaling": args.scaling, "vs_baseline": None,
             "dtype": "f32" if args.mode == "exact" else "fp16 tensor-core operands, f32 accumulate; u16 automaton state",
             "data": "synthetic", "config": workload_config(args, shape, time_, world),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(2 * rows * 4),
-                    "d2h_bytes_per_step": 32},
+                    "d2h_bytes_per_step": 16 if world > 1 else 32},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"kernel": dominant, "bound": "hbm", "achieved": achieved, "peak": peak,
@@ -354,13 +488,25 @@ def run_cuda(args):
                          "algorithmic_bytes_per_launch": alg_bytes,
                          "rosa_kernels_ms_per_layer": rosa_ms,
                          "achieved_all_rosa_kernels": alg_bytes / (rosa_ms * 1e-3) / 1e9 if rosa_ms > 0 else 0.0},
+            "tensor_core": {"flop_per_token": flops_per_token, "tflops_whole_step": flops_per_token * value / world / 1e12,
+                            "frac_of_sustained_peak": flops_per_token * value / world / 1e12 /
+                            float(peaks.get("bf16_tflops_sustained", 1421.6))},
             "kernels": shares,
+            "kernels_note": f"per-kernel times from a separate pass of {n_table} step(s) with an event behind every launch; "
+                            "`value` and `e2e` are timed without it",
             "phases_ms_last_step": phases,
+            "automaton_streams_last_layer": sam_counts,
             "mean_ce": total_sum / total_n if total_n else 0.0,
         }
+        if world == 1 and not args.no_extras:
+            line["extra"] = extra_measurements(args, rt, stream, torch, peaks)
         if not args.no_cpu_baseline:
             base, cpu_mean = cpu_baseline_sample(data, vocab, time_)
             line["cpu_baseline"] = base
+            if world == 1:
+                one, _ = cpu_baseline_sample(data, vocab, time_, threads=1)
+                base["one_thread"] = {"value": one["value"], "unit": UNIT, "cores": 1, "sample": one["sample"],
+                                      "note": "the reference's own scheduling of this path is single-threaded"}
         print(json.dumps(line), flush=True)
     if world > 1:
         rt.dp_finalize()

@@ -108,6 +108,12 @@ ULLIS_CUDA_API int32_t ullis_cuda_runtime_kernel_timing(ullis_cuda_runtime* rt, 
 ULLIS_CUDA_API int32_t ullis_cuda_runtime_kernel_time(ullis_cuda_runtime* rt, const char* name, float* total_ms,
                                                       uint32_t* launches);
 ULLIS_CUDA_API int32_t ullis_cuda_runtime_kernel_names(ullis_cuda_runtime* rt, char* buf, size_t len, size_t* needed);
+/* How the last suffix-automaton call on `rt` (op-level or inside a model forward: the last layer's) split its
+ * streams: `automaton` streams went through the automaton kernels, `constant_q` were settled by the
+ * constant-query closed form, and the rest of `total` by the other closed forms (constant key or value bits).
+ * No counterpart in the reference, which runs every stream through RosaSam.  Synchronises. */
+ULLIS_CUDA_API int32_t ullis_cuda_runtime_sam_counts(ullis_cuda_runtime* rt, uint64_t* total, uint64_t* automaton,
+                                                     uint64_t* constant_q);
 /* Compute capability check: 1 when the device is sm_100 class. */
 ULLIS_CUDA_API int32_t ullis_cuda_runtime_is_sm100(const ullis_cuda_runtime* rt);
 
@@ -143,6 +149,13 @@ ULLIS_CUDA_API int32_t ullis_cuda_model_enqueue_forward_ce(ullis_cuda_model* mod
                                             size_t time);
 ULLIS_CUDA_API int32_t ullis_cuda_model_read_loss(ullis_cuda_model* model, float* mean_loss, double* loss_sum,
                                    uint64_t* n_valid, float* row_loss, size_t rows);
+
+/* read_loss for a rank of a data-parallel group (ullis_cuda_dp_init on the model's runtime): the
+ * {loss_sum, n_valid} pair of the last forward is summed over the ranks on the device (one 16-byte
+ * all-reduce on the runtime stream) and read back once; mean_loss = sum / count over ALL ranks, which is the
+ * reference's single-process mean over every valid position (src/model.rs:3253-3257).  One call per forward. */
+ULLIS_CUDA_API int32_t ullis_cuda_model_read_loss_global(ullis_cuda_model* model, float* mean_loss, double* loss_sum,
+                                                         uint64_t* n_valid);
 
 /* UllisHeron::logits (src/model.rs:2685-2688): logits [batch*time*vocab] host. */
 ULLIS_CUDA_API int32_t ullis_cuda_model_logits(ullis_cuda_model* model, const uint32_t* tokens, size_t batch, size_t time,
@@ -349,12 +362,15 @@ ULLIS_CUDA_API int32_t ullis_cuda_streamed_ce(ullis_cuda_runtime* rt, const floa
  * built into the library (ULLIS_CUDA_SAM_STATIC_BYTES, resident on every GPU
  * that loads it): 74368 bytes per stream at time 2048, so at most 902
  * streams there; requests beyond it fail with ULLIS_CUDA_ERR_NOMEM.  No
- * cudaMalloc / cudaFree / host allocation happens.  The first call on a
- * device resolves the array's address - make it before any stream capture.
+ * cudaMalloc / cudaFree / host allocation happens.  The call is synchronous
+ * (it returns after `cuda_stream` has drained), so never issue it on a stream
+ * that is being captured; the first call on a device also resolves the array's
+ * address and should come before any capture starts.  The caller's current
+ * device is left as it was.
  * All calls share the array (nothing needs clearing between calls, every
  * field is written before it is read), so calls that overlap on the GPU race:
  * serialise them.  The kernel is enqueued on `cuda_stream` (a cudaStream_t,
- * NULL = default stream) and the call returns after that stream has drained.
+ * NULL = default stream).
  * Failure text: ullis_cuda_last_error(NULL). */
 #define ULLIS_CUDA_SAM_STATIC_BYTES ((size_t)64 << 20)
 ULLIS_CUDA_API int32_t ullis_cuda_rosa_sam_static(int32_t device, void* cuda_stream, const uint32_t* q_sw,
@@ -366,6 +382,13 @@ ULLIS_CUDA_API int32_t ullis_cuda_rosa_sam_static(int32_t device, void* cuda_str
  * {loss_sum, n_valid} is summed across ranks (NCCL all-reduce, 16 bytes).
  * No counterpart in the reference (single process, single device). */
 ULLIS_CUDA_API int32_t ullis_cuda_dp_unique_id(uint8_t id[128]);
+/* Host-side rendezvous with a deadline, to be called before ullis_cuda_dp_init (whose NCCL bootstrap waits
+ * for every rank without one): each rank announces itself with a file `<dir>/<tag>.<rank>` in a directory all
+ * ranks of the node share and waits until all `world` files exist.  ULLIS_CUDA_ERR_TIMEOUT when a rank has not
+ * shown up within timeout_ms - no NCCL or CUDA call has been made at that point.  `tag` names the group (use a
+ * fresh one per job).  Failure text: ullis_cuda_last_error(NULL). */
+ULLIS_CUDA_API int32_t ullis_cuda_dp_rendezvous(const char* dir, const char* tag, int32_t rank, int32_t world,
+                                                uint32_t timeout_ms);
 ULLIS_CUDA_API int32_t ullis_cuda_dp_init(ullis_cuda_runtime* rt, int32_t rank, int32_t world, const uint8_t id[128]);
 ULLIS_CUDA_API int32_t ullis_cuda_dp_allreduce_loss(ullis_cuda_runtime* rt, double* loss_sum, uint64_t* n_valid);
 ULLIS_CUDA_API int32_t ullis_cuda_dp_finalize(ullis_cuda_runtime* rt);

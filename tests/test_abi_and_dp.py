@@ -129,3 +129,34 @@ def test_parent_handles_close_their_children_first():
     for i in range(50):
         cuda._Handle(10 + i, lambda h: None, rt2).close()
     assert len(rt2.children) <= 1
+
+
+def test_rendezvous_gives_up_when_a_rank_never_joins(tmp_path):
+    """The failure is made on the host: rank 1 simply never announces itself.  Rank 0 must get
+    ERR_TIMEOUT from the rendezvous - before any NCCL or CUDA call - instead of waiting in the bootstrap."""
+    import threading
+    import time
+    t0 = time.perf_counter()
+    with pytest.raises(cuda.UllisCudaError) as e:
+        cuda.CudaRuntime.dp_rendezvous(str(tmp_path), "lonely", 0, 2, timeout_s=0.3)
+    assert e.value.code == cuda.ERR_TIMEOUT and "rank 1 of 2 never arrived" in e.value.message
+    assert 0.25 <= time.perf_counter() - t0 < 5.0
+    # both ranks present (the second one late, but inside the deadline): both calls return
+    errors = []
+
+    def rank(r, delay):
+        try:
+            time.sleep(delay)
+            cuda.CudaRuntime.dp_rendezvous(str(tmp_path), "pair", r, 2, timeout_s=10.0)
+        except Exception as exc:  # noqa: BLE001
+            errors.append(exc)
+
+    threads = [threading.Thread(target=rank, args=(0, 0.0)), threading.Thread(target=rank, args=(1, 0.2))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors
+    with pytest.raises(cuda.UllisCudaError) as e:      # arguments are checked
+        cuda.CudaRuntime.dp_rendezvous(str(tmp_path), "x", 2, 2)
+    assert e.value.code == cuda.ERR_ARG

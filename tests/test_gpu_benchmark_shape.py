@@ -1,6 +1,8 @@
 """The benchmark's own shape (Heron D=512 L=12 T=2048 V=8192, literal weight
 distributions) at sizes the oracle cannot cover whole: one full-depth sequence
-against the oracle, and size-independent properties on a 16-sequence batch -
+against the oracle, and size-independent properties on batches of 16 and of 64
+sequences (the benchmark's batch, whose automaton launch carries other numbers of
+streams per warp than the small one) -
 sequences are independent, so a batch must give each sequence exactly the row
 losses it gets alone, the mean is sum / count, and a repeated run is
 bit-identical."""
@@ -29,15 +31,24 @@ def test_one_benchmark_sequence_against_the_oracle(cuda_rt, oracle, data):
     mean, loss_sum, n_valid, row_loss = m.forward_ce(tokens, tokens, cuda.CE_NO_IGNORE, 1, T, want_row_loss=True)
     assert n_valid == n_ref == T - 1
     assert abs(mean - mean_ref) <= 1e-3                                   # mean CE: 1e-3 absolute
-    mism = total = 0
+    bit_mism = bit_total = idx_mism = 0
     for l in range(LAYERS):
         got, want = m.tap(l, "block_out", T), taps[f"{l}.block_out"]
         err = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want.astype(np.float64))
         assert err <= 1e-2, (l, err)                                       # activations: 1e-2 relative
-        for name in ("q_bits", "k_bits", "v_bits", "idx"):
-            mism += int((m.tap(l, name, T) != taps[f"{l}.{name}"]).sum())
-            total += T * D
-    assert mism / total <= 2e-3, f"ROSA bit mismatch rate {mism / total:.2e}"
+        for name in ("q_bits", "k_bits", "v_bits"):
+            bit_mism += int((m.tap(l, name, T) != taps[f"{l}.{name}"]).sum())
+            bit_total += T * D
+        idx_mism += int((m.tap(l, "idx", T) != taps[f"{l}.idx"]).sum())
+    # End to end the inputs of the Q/K/V linears differ from the oracle's in the last places (another
+    # summation order in LayerNorm and in the linears before them), so a sign whose pre-activation is within
+    # that distance of zero may differ: at most one bit in 10^5, each kind counted by itself.  (Given the SAME
+    # f32 input the bits are exact: test_gpu_ops.py::test_rosa_block_forward.)
+    assert bit_mism <= 1e-5 * bit_total, f"Q/K/V sign bits: {bit_mism} of {bit_total} differ"
+    # idx is a function of the bits alone: identical bits must give identical idx, and a differing bit may
+    # only move the idx of its own stream (and what later layers make of it) - gated at the same rate
+    assert idx_mism <= (1e-5 * LAYERS * T * D if bit_mism else 0), \
+        f"idx: {idx_mism} positions differ with {bit_mism} differing sign bits"
     m.close()
     # validation mode: every ROSA bit and idx of every layer bit-exact, hidden bit-identical
     cuda_rt.set_mode(cuda.MODE_EXACT)
@@ -55,8 +66,9 @@ def test_one_benchmark_sequence_against_the_oracle(cuda_rt, oracle, data):
         cuda_rt.set_mode(cuda.MODE_FAST)
 
 
-def test_batch_gives_every_sequence_the_losses_it_gets_alone(cuda_rt, data):
-    B = 16
+@pytest.mark.parametrize("B", [16, 64])
+def test_batch_gives_every_sequence_the_losses_it_gets_alone(cuda_rt, B):
+    data = synth.heron_checkpoint("default", batch_size=B)
     tokens = np.concatenate([synth.zipf_tokens(11 + b, T, VOCAB) for b in range(B)])
     labels = tokens.copy()
     labels[5 * T + 7] = 0          # one ignored target in sequence 5
@@ -68,7 +80,7 @@ def test_batch_gives_every_sequence_the_losses_it_gets_alone(cuda_rt, data):
     assert abs(mean - loss_sum / n_valid) <= 1e-6
     again = m.forward_ce(tokens, labels, 0, B, T, want_row_loss=True)
     assert np.array_equal(again[3], row_loss) and again[1] == loss_sum          # deterministic
-    for b in (0, 5, 15):
+    for b in (0, 5, B - 1):
         alone = m.forward_ce(tokens[b * T:(b + 1) * T], labels[b * T:(b + 1) * T], 0, 1, T, want_row_loss=True)
         assert np.array_equal(alone[3], row_loss[b * T:(b + 1) * T]), b        # same kernels, same tiles per row
     m.close()

@@ -77,14 +77,18 @@ def test_exact_mode_is_bit_identical(cuda_rt, case, sam):
 def test_fast_mode_within_tolerance(cuda_rt, case):
     (mean, loss_sum, n_valid, row_loss), taps, logits, hidden = run_cuda(cuda_rt, case, cuda.MODE_FAST)
     ref = case["taps"]
-    mism = 0
-    total = 0
+    bit_mism = bit_total = idx_mism = 0
     for l in range(case["layers"]):
         assert rel_err(taps[f"{l}.block_out"], ref[f"{l}.block_out"]) <= 1e-2, l   # activations: 1e-2 relative
-        for name in ("q_bits", "k_bits", "v_bits", "idx"):
-            mism += int((taps[f"{l}.{name}"] != ref[f"{l}.{name}"]).sum())
-            total += taps[f"{l}.{name}"].size
-    assert mism / total <= 2e-3, f"ROSA bit mismatch rate {mism / total:.2e}"
+        for name in ("q_bits", "k_bits", "v_bits"):
+            bit_mism += int((taps[f"{l}.{name}"] != ref[f"{l}.{name}"]).sum())
+            bit_total += taps[f"{l}.{name}"].size
+        idx_mism += int((taps[f"{l}.idx"] != ref[f"{l}.idx"]).sum())
+    # a sign bit may differ end to end only where the pre-activation is within rounding of zero: one in 10^5
+    # (at least 2 positions allowed on the small cases), and idx only as far as those bits explain
+    assert bit_mism <= max(2, 1e-5 * bit_total), f"Q/K/V sign bits: {bit_mism} of {bit_total} differ"
+    assert idx_mism <= (max(8, 1e-4 * bit_total) if bit_mism else 0), \
+        f"idx: {idx_mism} positions differ with {bit_mism} differing sign bits"
     assert rel_err(logits, case["logits"]) <= 1e-2                                     # logits: 1e-2 relative
     assert n_valid == case["n_valid"]
     assert abs(mean - case["mean"]) <= 1e-3                                            # mean CE: 1e-3 absolute

@@ -92,6 +92,24 @@ def test_standalone_benchmark_context_length(cuda_rt, oracle):
     run_both(cuda_rt, oracle, q, k, v, B, T, C)
 
 
+def test_standalone_benchmark_at_its_full_size(cuda_rt, oracle):
+    """The standalone ROSA configuration as stated: 64 sequences x 512 channels x 8192 steps, i.i.d. bits - all
+    268 M idx positions against the oracle's pushes (rosa_qkv_batch_packed, src/rosa.rs:459-481) - and a
+    4096-stream slice (8 sequences) of the periodic variant, whose streams have long suffix matches."""
+    e = f16(np.linspace(0.01, 0.5, 512))
+    oracle.set_threads(oracle.max_threads())
+    try:
+        for gen, seed, B in ((synth.rosa_bits_iid, 21, 64), (synth.rosa_bits_periodic, 23, 8)):
+            T, C = 8192, 512
+            q, k, v = gen(seed, B, T, C)
+            idx, _ = cuda_rt.rosa_qkv_1bit_fwd(q, k, v, e, B, T, C, want_out=False)
+            ref = oracle.rosa_qkv_batch_packed(q, k, v, B, T, C)
+            assert idx.size == B * T * C and np.array_equal(idx, ref), gen.__name__
+            del idx, ref, q, k, v
+    finally:
+        oracle.set_threads(min(16, oracle.max_threads()))
+
+
 def test_context_beyond_16_bit_state_ids(cuda_rt, oracle):
     B, T, C = 1, 32768, 4  # MAX_CONTEXT_LEN: needs the 32-bit state-id kernels
     q, k, v = synth.rosa_bits_iid(24, B, T, C)

@@ -2,8 +2,9 @@
 steps against hand-derived known answers (the inputs of the reference's
 clipped_sgd_fp16_matches_cpu_residual / binaryconnect_sgd_fp16_matches_cpu_magnitude_clip,
 src/metal.rs:4006-4042), every backward piece against float64 autograd of the
-forward it differentiates, and the behaviours the reference's own train-step
-tests assert (src/model.rs:4690-4800)."""
+forward it differentiates, the straight-through vector and the latent-persistence
+behaviour the reference holds (tests/binary_linear.rs:13-66), and the behaviours
+the reference's own train-step tests assert (src/model.rs:4690-4800)."""
 import numpy as np
 import pytest
 import torch
@@ -93,6 +94,39 @@ def test_packed_backward_ste_matches_autograd_of_the_scaled_sign_product():
     assert np.allclose(g_x, xt.grad.numpy(), atol=1e-5)
     assert np.allclose(g_scale, st.grad.numpy(), atol=1e-4)
     assert np.allclose(g_bias, bt.grad.numpy(), atol=1e-5)
+
+
+def test_packed_backward_ste_reference_vector():
+    """The vector the reference holds for the straight-through gradients
+    (tests/binary_linear.rs:13-40): one output over inputs (2, 3), signs (+1, -1), row scale 0.5, gy = 1
+    => g_w = (1.0, 1.5), g_x = (0.5, -0.5), g_scale = -1, g_bias = 1."""
+    bits = np.array([0b01], np.uint32)                      # weight 0 = +1, weight 1 = -1
+    g_w, g_x, g_scale, g_bias = T.packed_backward_ste(np.array([2.0, 3.0], np.float32), np.array([1.0], np.float32),
+                                                      bits, f16([0.5]), 1, 2, 1)
+    assert np.abs(g_w.ravel() - [1.0, 1.5]).max() < 1e-6
+    assert np.abs(g_x.ravel() - [0.5, -0.5]).max() < 1e-6
+    assert abs(float(g_scale[0]) + 1.0) < 1e-6 and abs(float(g_bias[0]) - 1.0) < 1e-6
+    # the forward of the same layer (tests/binary_linear.rs:3-11): y = 0 + 0.5 * (2 - 3) = -0.5
+    y = O.binary_linear(np.array([2.0, 3.0], np.float32), bits, f16([0.5]), f16([0.0]), 1, 2, 1)
+    assert abs(float(y[0]) + 0.5) < 1e-6
+
+
+def test_latent_persists_across_steps_instead_of_reconstructing():
+    """tests/binary_linear.rs:42-66: a 1x1 layer, sign +1, scale 0.5, so the latent starts at 0.5; x = 1,
+    gy = 1 give g_w = 0.5, and a BinaryConnect step with lr 0.1 moves the latent to 0.45 - it must not snap
+    back to scale * sign = 0.5 - and a second step moves it again (to 0.40)."""
+    bits = np.array([1], np.uint32)
+    latent, residual = f16([0.5]), np.zeros(1, np.float32)
+    g_w, _, _, _ = T.packed_backward_ste(np.array([1.0], np.float32), np.array([1.0], np.float32), bits, f16([0.5]),
+                                         1, 1, 1)
+    assert abs(float(g_w.ravel()[0]) - 0.5) < 1e-6
+    latent, residual = T.binaryconnect_sgd(latent, residual, g_w.ravel(), 0.1)
+    after_one = float(O.fp16_to_f32(latent)[0])
+    assert abs(after_one - 0.5) > 1e-3 and abs(after_one + float(residual[0]) - 0.45) < 1e-6
+    latent, residual = T.binaryconnect_sgd(latent, residual, g_w.ravel(), 0.1)
+    after_two = float(O.fp16_to_f32(latent)[0])
+    assert after_two != after_one and abs(after_two + float(residual[0]) - 0.40) < 1e-6
+    assert np.array_equal(T.pack_signs(latent, 1), bits)     # still positive: the packed sign is unchanged
 
 
 def test_lerp_shift_backward_matches_autograd():

@@ -1,5 +1,6 @@
 """The allocation-free suffix-automaton entry point
-(ullis_cuda_rosa_sam_static) against the regular, pool-backed one.
+(ullis_cuda_rosa_sam_static) against the regular, pool-backed one and against
+the CPU oracle.
 
 It exists for callers that may not allocate device memory while they run - a
 process working inside a fixed device-memory budget, a latency-critical thread
@@ -50,13 +51,20 @@ def _run_pooled(cuda_rt, q, k, v):
     return idx.reshape(T, n).T
 
 
-def test_static_scratch_entry_matches_pooled_entry_twice_in_a_row(cuda_rt):
+def _run_oracle(oracle, q, k, v):
+    n, T = q.shape
+    words = oracle.rosa_qkv_streams(*(pack_streams(a) for a in (q, k, v)), n, T)
+    return np.unpackbits(words.view(np.uint8).reshape(n, -1), axis=1, bitorder="little")[:, :T]
+
+
+def test_static_scratch_entry_matches_pooled_entry_twice_in_a_row(cuda_rt, oracle):
     rng = np.random.default_rng(99)
     for n, T, biased in [(200, 300, False), (50, 64, True), (902, 2048, True)]:
         q, k, v = _case(rng, n, T, biased)
         got = _run_static(q, k, v)
         ref = _run_pooled(cuda_rt, q, k, v)
         assert np.array_equal(got, ref), (n, T)   # integer result: bit-exact
+        assert np.array_equal(got, _run_oracle(oracle, q, k, v)), (n, T)   # and equal to the reference's pushes
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit(cuda_rt):

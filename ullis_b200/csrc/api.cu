@@ -330,6 +330,21 @@ int32_t ullis_cuda_runtime_kernel_names(ullis_cuda_runtime* rt, char* buf, size_
     });
 }
 
+int32_t ullis_cuda_runtime_sam_counts(ullis_cuda_runtime* rt, uint64_t* total, uint64_t* automaton,
+                                      uint64_t* constant_q) {
+    return guard(rt, [&] {
+        uint32_t host[2] = {0, 0};
+        if (rt->sam_last_streams) {
+            // the two counters sit behind the automaton list (k::rosa_sam)
+            rt->d2h(host, rt->sam_list.as<uint32_t>(2 * rt->sam_last_streams + 2) + rt->sam_last_streams, 8);
+            rt->sync();
+        }
+        if (total) *total = rt->sam_last_streams;
+        if (automaton) *automaton = host[0];
+        if (constant_q) *constant_q = host[1];
+    });
+}
+
 int32_t ullis_cuda_runtime_is_sm100(const ullis_cuda_runtime* rt) { return rt && rt->cc_major == 10 ? 1 : 0; }
 
 // ------------------------------------------------------------------ model
@@ -389,6 +404,11 @@ int32_t ullis_cuda_model_upload_tokens(ullis_cuda_model* model, const uint32_t* 
 int32_t ullis_cuda_model_enqueue_forward_ce(ullis_cuda_model* model, uint32_t ignore_id, size_t batch,
                                             size_t time) {
     return guard_model(model, [&] { model->enqueue_forward_ce(ignore_id, batch, time); });
+}
+
+int32_t ullis_cuda_model_read_loss_global(ullis_cuda_model* model, float* mean_loss, double* loss_sum,
+                                          uint64_t* n_valid) {
+    return guard_model(model, [&] { model->read_loss_global(mean_loss, loss_sum, n_valid); });
 }
 
 int32_t ullis_cuda_model_read_loss(ullis_cuda_model* model, float* mean_loss, double* loss_sum,

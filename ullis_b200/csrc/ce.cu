@@ -51,7 +51,8 @@ ce_rows_kernel(const float* __restrict__ logits, const uint32_t* __restrict__ la
 // single CTA, fixed summation tree: deterministic for a given shape
 __global__ void __launch_bounds__(1024)
 ce_reduce_kernel(const float* __restrict__ row_loss, const uint32_t* __restrict__ labels, uint32_t ignore_id,
-                 size_t rows, size_t time, double* __restrict__ loss_sum, unsigned long long* __restrict__ n_valid) {
+                 size_t rows, size_t time, double* __restrict__ loss_sum, unsigned long long* __restrict__ n_valid,
+                 double* __restrict__ pair) {
     __shared__ double s_sum[1024];
     __shared__ unsigned long long s_cnt[1024];
     double acc = 0.0;
@@ -75,6 +76,10 @@ ce_reduce_kernel(const float* __restrict__ row_loss, const uint32_t* __restrict_
     if (threadIdx.x == 0) {
         *loss_sum = s_sum[0];
         *n_valid = s_cnt[0];
+        if (pair) {   // the same two numbers as doubles: the operand of the data-parallel all-reduce
+            pair[0] = s_sum[0];
+            pair[1] = (double)s_cnt[0];
+        }
     }
 }
 
@@ -90,8 +95,8 @@ void ce_rows_from_logits(ullis_cuda_runtime* rt, const float* logits, const uint
 }
 
 void ce_reduce(ullis_cuda_runtime* rt, const float* row_loss, const uint32_t* labels, uint32_t ignore_id,
-               size_t rows, size_t time, double* loss_sum, unsigned long long* n_valid) {
-    ce_reduce_kernel<<<1, 1024, 0, rt->stream>>>(row_loss, labels, ignore_id, rows, time, loss_sum, n_valid);
+               size_t rows, size_t time, double* loss_sum, unsigned long long* n_valid, double* pair) {
+    ce_reduce_kernel<<<1, 1024, 0, rt->stream>>>(row_loss, labels, ignore_id, rows, time, loss_sum, n_valid, pair);
     rt->launched("ce_reduce");
 }
 

@@ -9,6 +9,8 @@
 
 #include "../../include/ullis_cuda.h"
 
+struct ullis_cuda_runtime;
+
 namespace ullis {
 
 struct Error {
@@ -66,6 +68,10 @@ class DeviceBuffer {
 
 struct NcclState;  // dp.cpp
 
+// Sums `count` doubles at `dev` (device memory) over the ranks of the runtime's data-parallel group, in
+// place, on the runtime stream; no host synchronisation.  Throws without a group.  (dp.cpp)
+void dp_allreduce_device(ullis_cuda_runtime* rt, double* dev, size_t count);
+
 // Message returned by ullis_cuda_last_error(NULL); copied into a fixed buffer.
 void set_global_error(const char* msg);
 
@@ -104,6 +110,7 @@ struct ullis_cuda_runtime {
     size_t sam_budget_bytes = (size_t)12 << 30;   // cap of sam_scratch; more streams than fit run in waves
     ullis::DeviceBuffer sam_scratch;    // suffix-automaton state blocks
     ullis::DeviceBuffer sam_list;       // ids of the streams that need the automaton + their count
+    size_t sam_last_streams = 0;        // streams of the last suffix-automaton call (where its counters sit in sam_list)
     ullis::DeviceBuffer tc_ws[16];      // 16-bit operands / partials of the tensor-core stages
     int tc_stages = 2, tc_stages2 = 2;  // GEMM pipeline depth with one / two activation operands
     bool tc_ws_kernel = true;           // weight-stationary persistent kernel for packed weights with K <= 512

@@ -7,9 +7,15 @@
 // the process when PyTorch is) so the library has no link-time dependency on
 // a particular NCCL build.  The reference has no distributed layer.
 #include <dlfcn.h>
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
 
+#include <cerrno>
+#include <chrono>
 #include <cstring>
 #include <string>
+#include <thread>
 
 #include "common.hpp"
 
@@ -59,6 +65,12 @@ static void nccl_check(int rc, const char* what) {
     if (rc != 0) fail(ULLIS_CUDA_ERR_NCCL, std::string(what) + ": " + api().GetErrorString(rc));
 }
 
+void dp_allreduce_device(ullis_cuda_runtime* rt, double* dev, size_t count) {
+    if (!rt->nccl) fail(ULLIS_CUDA_ERR_NCCL, "data-parallel group is not initialised");
+    nccl_check(api().AllReduce(dev, dev, count, /*ncclDouble*/ 8, /*ncclSum*/ 0, rt->nccl->comm, rt->stream),
+               "ncclAllReduce");
+}
+
 }  // namespace ullis
 
 using namespace ullis;
@@ -76,6 +88,36 @@ int32_t ullis_cuda_dp_unique_id(uint8_t id[128]) {
         return ULLIS_CUDA_OK;
     } catch (const Error& e) {
         g_dp_error = e.msg;
+        set_global_error(e.msg.c_str());
+        return e.code;
+    }
+}
+
+int32_t ullis_cuda_dp_rendezvous(const char* dir, const char* tag, int32_t rank, int32_t world, uint32_t timeout_ms) {
+    try {
+        if (!dir || !tag || !*dir || !*tag || world < 1 || rank < 0 || rank >= world)
+            fail(ULLIS_CUDA_ERR_ARG, "bad rendezvous directory / tag / rank / world");
+        const std::string base = std::string(dir) + "/" + tag + ".";
+        const int fd = open((base + std::to_string(rank)).c_str(), O_CREAT | O_WRONLY, 0644);
+        if (fd < 0) fail(ULLIS_CUDA_ERR_ARG, "cannot create the rendezvous file of rank " + std::to_string(rank) +
+                                                 " in " + dir + ": " + strerror(errno));
+        close(fd);
+        const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+        for (;;) {
+            int missing = -1;
+            for (int r = 0; r < world && missing < 0; ++r) {
+                struct stat st;
+                if (stat((base + std::to_string(r)).c_str(), &st) != 0) missing = r;
+            }
+            if (missing < 0) return ULLIS_CUDA_OK;
+            if (std::chrono::steady_clock::now() >= deadline)
+                fail(ULLIS_CUDA_ERR_TIMEOUT, "data-parallel rendezvous timed out after " + std::to_string(timeout_ms) +
+                                                 " ms: rank " + std::to_string(missing) + " of " +
+                                                 std::to_string(world) + " never arrived");
+            std::this_thread::sleep_for(std::chrono::milliseconds(5));
+        }
+    } catch (const Error& e) {
+        set_global_error(e.msg.c_str());
         return e.code;
     }
 }

@@ -52,9 +52,10 @@ size_t rosa_sam_scratch_bytes_per_stream(int algo, size_t time);
 // or past the sequence end get 0. Targets >= vocab set the status word.
 void ce_rows_from_logits(ullis_cuda_runtime* rt, const float* logits, const uint32_t* labels, uint32_t ignore_id,
                          size_t row0, size_t rows, size_t total_rows, size_t time, size_t vocab, float* row_loss);
-// loss_sum (f64) and n_valid over row_loss / labels, fixed-order reduction.
+// loss_sum (f64) and n_valid over row_loss / labels, fixed-order reduction.  `pair` (nullable, device)
+// receives the same two numbers as doubles, the form the data-parallel all-reduce sums.
 void ce_reduce(ullis_cuda_runtime* rt, const float* row_loss, const uint32_t* labels, uint32_t ignore_id,
-               size_t rows, size_t time, double* loss_sum, unsigned long long* n_valid);
+               size_t rows, size_t time, double* loss_sum, unsigned long long* n_valid, double* pair = nullptr);
 
 
 // ---- train.cu  (op-level forms of the training kernels)

@@ -179,6 +179,7 @@ void ullis_cuda_model::upload_tokens(const uint32_t* tokens, const uint32_t* lab
     cur_batch = batch;
     cur_time = time;
     have_result = false;
+    have_pair = false;
 }
 
 void ullis_cuda_model::begin(int phase) {
@@ -343,7 +344,7 @@ void ullis_cuda_model::enqueue_forward_ce(uint32_t ignore_id, size_t batch, size
     if (!labels.get() || labels.bytes() < rows * 4) fail(ULLIS_CUDA_ERR_ARG, "labels were not uploaded");
     float* A = a.as<float>(rows * d);
     float* RL = row_loss.as<float>(rows);
-    uint8_t* res = static_cast<uint8_t*>(result.ensure(16));
+    uint8_t* res = static_cast<uint8_t*>(result.ensure(32));   // {f64 sum, u64 count} then the same as two f64
     const uint32_t* lab = labels.as<uint32_t>(rows);
     begin(PH_HEAD_CE);
     if (!tc::head_ce(rt, A, head, lab, ignore_id, rows, time, d, vocab, RL)) {
@@ -356,9 +357,10 @@ void ullis_cuda_model::enqueue_forward_ce(uint32_t ignore_id, size_t batch, size
         }
     }
     k::ce_reduce(rt, RL, lab, ignore_id, rows, time, reinterpret_cast<double*>(res),
-                 reinterpret_cast<unsigned long long*>(res + 8));
+                 reinterpret_cast<unsigned long long*>(res + 8), reinterpret_cast<double*>(res + 16));
     end();
     have_result = true;
+    have_pair = true;
 }
 
 void ullis_cuda_model::read_loss(float* mean_loss, double* loss_sum, uint64_t* n_valid, float* rl, size_t rows) {
@@ -374,6 +376,24 @@ void ullis_cuda_model::read_loss(float* mean_loss, double* loss_sum, uint64_t* n
     if (loss_sum) *loss_sum = host.sum;
     if (n_valid) *n_valid = host.n;
     if (mean_loss) *mean_loss = host.n == 0 ? 0.0f : (float)(host.sum / (double)host.n);
+}
+
+// The data-parallel form of read_loss: the {loss_sum, n_valid} pair of the last forward is summed over the
+// ranks where it lies (one all-reduce on the runtime stream) and read back once - mean = sum / count over
+// all ranks, the reference's single-process mean (src/model.rs:3253-3257).
+void ullis_cuda_model::read_loss_global(float* mean_loss, double* loss_sum, uint64_t* n_valid) {
+    if (!have_result || !have_pair) fail(ULLIS_CUDA_ERR_ARG, "no forward_ce result to read");
+    rt->bind();
+    double* pair = reinterpret_cast<double*>(static_cast<uint8_t*>(result.get()) + 16);
+    dp_allreduce_device(rt, pair, 2);
+    have_pair = false;   // the pair now holds the global sums: a second call would add them up again
+    double host[2];
+    rt->d2h(host, pair, 16);
+    rt->check_status();  // synchronises
+    const uint64_t n = (uint64_t)(host[1] + 0.5);
+    if (loss_sum) *loss_sum = host[0];
+    if (n_valid) *n_valid = n;
+    if (mean_loss) *mean_loss = n == 0 ? 0.0f : (float)(host[0] / (double)n);
 }
 
 // UllisHeron::logits (src/model.rs:2685-2688)

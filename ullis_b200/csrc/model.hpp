@@ -47,6 +47,7 @@ struct ullis_cuda_model {
     ullis::DeviceBuffer ids, labels, x, a, b, c, dd, wide, q_sw, k_sw, v_sw, idx_sw, logits, row_loss, result;
     size_t cur_batch = 0, cur_time = 0;
     bool have_result = false;
+    bool have_pair = false;   // result also holds {sum, count} as two doubles that no all-reduce has consumed yet
 
     // training tape: the residual stream after each ROSA block and the idx bits, kept per layer
     bool train_tape = false;
@@ -72,6 +73,7 @@ struct ullis_cuda_model {
     void enqueue_forward_ce(uint32_t ignore_id, size_t batch, size_t time);
     void enqueue_logits(size_t batch, size_t time, float* host_logits);
     void read_loss(float* mean_loss, double* loss_sum, uint64_t* n_valid, float* row_loss, size_t rows);
+    void read_loss_global(float* mean_loss, double* loss_sum, uint64_t* n_valid);
     void tap(int layer, int which, void* out, size_t bytes);
     void phase_ms(float ms[6]);
 

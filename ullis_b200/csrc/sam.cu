@@ -178,6 +178,7 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     uint8_t* scratch = static_cast<uint8_t*>(rt->sam_scratch.ensure(wave * stride));
     if (streams > 0xFFFFFFFFull) fail(ULLIS_CUDA_ERR_SHAPE, "too many ROSA streams");
     uint32_t* list = rt->sam_list.as<uint32_t>(2 * streams + 2);
+    rt->sam_last_streams = streams;
     uint32_t* count = list + streams;
     uint32_t* cq_count = count + 1;           // the constant-q streams, settled by a kernel of their own
     uint32_t* cq_list = count + 2;

@@ -19,8 +19,11 @@
 //  * streams * state_bytes(time) must fit the 64 MiB; larger requests are
 //    refused with ULLIS_CUDA_ERR_NOMEM, never split or spilled elsewhere.
 //  * The first call on each device looks up the array's device address
-//    (cudaGetSymbolAddress) and caches it; make that first call before any
-//    stream capture.
+//    (cudaGetSymbolAddress) and caches it.  Every call waits for `cuda_stream`
+//    to drain before it returns, so it must never be issued on a stream that
+//    is being captured - and the first call on a device, which also does the
+//    look-up, should come before any capture starts anywhere in the process.
+//  * The caller's current device is the same after the call as before it.
 //  * Every call uses the same array and leaves its last contents behind.  The
 //    kernel writes each field of a state block before reading it, so nothing
 //    has to be cleared between calls - but two calls whose kernels overlap on
@@ -55,8 +58,11 @@ rosa_sam_static_kernel(unsigned char* __restrict__ scratch, size_t stride, const
     const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const size_t s = warp * 4 + (lane >> 3);
     if (s >= streams) return;
-    ullis::sam::run_euler<Ix>(scratch + s * stride, q_sw + s * wps, k_sw + s * wps, v_sw + s * wps,
-                              idx_sw + s * wps, T, nullptr);
+    // run_euler reports "more states than 2T + 2" through its return value; an automaton over T symbols
+    // never has that many, and the host has already checked that every block fits the array, so there is
+    // nothing to report here
+    (void)ullis::sam::run_euler<Ix>(scratch + s * stride, q_sw + s * wps, k_sw + s * wps, v_sw + s * wps,
+                                    idx_sw + s * wps, T, nullptr);
 }
 
 int32_t refuse(int32_t code, const char* msg) {
@@ -67,8 +73,17 @@ int32_t refuse(int32_t code, const char* msg) {
 int32_t refuse_cuda(const char* what, cudaError_t e) {
     char buf[256];
     snprintf(buf, sizeof(buf), "%s: %s", what, cudaGetErrorString(e));
+    cudaGetLastError();   // the error is reported here: the next launch check of this thread must not see it again
     return refuse(ULLIS_CUDA_ERR_CUDA, buf);
 }
+
+// Puts the caller's current device back when the call leaves, whichever way.
+struct DeviceRestore {
+    int previous = -1;
+    ~DeviceRestore() {
+        if (previous >= 0) cudaSetDevice(previous);
+    }
+};
 
 }  // namespace
 
@@ -89,7 +104,13 @@ int32_t ullis_cuda_rosa_sam_static(int32_t device, void* cuda_stream, const uint
                  streams, stride, STATIC_SCRATCH_BYTES, STATIC_SCRATCH_BYTES / stride);
         return refuse(ULLIS_CUDA_ERR_NOMEM, buf);
     }
-    cudaError_t e = cudaSetDevice(device);
+    DeviceRestore restore;
+    cudaError_t e = cudaGetDevice(&restore.previous);
+    if (e != cudaSuccess) {
+        restore.previous = -1;
+        return refuse_cuda("cudaGetDevice", e);
+    }
+    e = cudaSetDevice(device);
     if (e != cudaSuccess) return refuse_cuda("cudaSetDevice", e);
     unsigned char* scratch = nullptr;
     {

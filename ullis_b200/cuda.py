@@ -52,6 +52,7 @@ ABI_SYMBOLS = (
     "ullis_cuda_binary_linear", "ullis_cuda_fp16_linear", "ullis_cuda_sign_pack_bits", "ullis_cuda_cmix_relu2",
     "ullis_cuda_residual_add", "ullis_cuda_rosa_qkv_1bit_fwd", "ullis_cuda_rosa_block_forward",
     "ullis_cuda_cmix_block_forward", "ullis_cuda_streamed_ce", "ullis_cuda_rosa_sam_static",
+    "ullis_cuda_runtime_sam_counts", "ullis_cuda_model_read_loss_global", "ullis_cuda_dp_rendezvous",
     "ullis_cuda_dp_unique_id", "ullis_cuda_dp_init",
     "ullis_cuda_dp_allreduce_loss", "ullis_cuda_dp_finalize",
 )
@@ -313,9 +314,10 @@ class CudaRuntime:
         self._check(self._lib.ullis_cuda_residual_add(self._h, _ptr(a), _ptr(b), _ptr(out), _z(a.size)))
         return out
 
-    def rosa_qkv_1bit_fwd(self, q_bits, k_bits, v_bits, e_bits, batch: int, time: int, channels: int):
+    def rosa_qkv_1bit_fwd(self, q_bits, k_bits, v_bits, e_bits, batch: int, time: int, channels: int,
+                          want_out: bool = True):
         """Returns (idx u8 [B,T,C], out f32 [B,T,C]) like RosaQkvForward{idx,out}
-        (src/metal.rs:253-256)."""
+        (src/metal.rs:253-256); out is None with want_out=False (the ABI's nullable output)."""
         n = batch * time * channels
         words = (n + 31) // 32
         q = _arr(q_bits, np.uint32, "q_bits", words)
@@ -323,7 +325,7 @@ class CudaRuntime:
         v = _arr(v_bits, np.uint32, "v_bits", words)
         e = _arr(e_bits, np.uint16, "e", channels)
         idx = np.empty(n, np.uint8)
-        out = np.empty(n, np.float32)
+        out = np.empty(n, np.float32) if want_out else None
         self._check(self._lib.ullis_cuda_rosa_qkv_1bit_fwd(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(e), _ptr(idx),
                                                            _ptr(out), _z(batch), _z(time), _z(channels)))
         return idx, out
@@ -390,6 +392,22 @@ class CudaRuntime:
         if rc != OK:
             raise UllisCudaError(rc, "ncclGetUniqueId failed")
         return bytes(buf)
+
+    @staticmethod
+    def dp_rendezvous(directory: str, tag: str, rank: int, world: int, timeout_s: float = 60.0) -> None:
+        """Host-side rendezvous with a deadline (ullis_cuda_dp_rendezvous): raises ERR_TIMEOUT when a rank
+        has not announced itself in `directory` in time.  Call it before dp_init."""
+        lib = load_library()
+        rc = lib.ullis_cuda_dp_rendezvous(directory.encode(), tag.encode(), C.c_int32(rank), C.c_int32(world),
+                                          C.c_uint32(int(timeout_s * 1000)))
+        if rc != OK:
+            raise UllisCudaError(rc, lib.ullis_cuda_last_error(None).decode())
+
+    def sam_counts(self) -> dict:
+        """Streams of the last suffix-automaton call: total, through the automaton, through the constant-q form."""
+        t, a, q = C.c_uint64(0), C.c_uint64(0), C.c_uint64(0)
+        self._check(self._lib.ullis_cuda_runtime_sam_counts(self._h, C.byref(t), C.byref(a), C.byref(q)))
+        return {"total": int(t.value), "automaton": int(a.value), "constant_q": int(q.value)}
 
     def dp_init(self, rank: int, world: int, unique_id: bytes):
         buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
@@ -478,6 +496,13 @@ class CudaHeron:
                                                             _ptr(rl), _z(rows)))
         out = (float(mean.value), float(s.value), int(n.value))
         return out + (rl,) if want_row_loss else out
+
+    def read_loss_global(self):
+        """read_loss summed over the ranks of the runtime's data-parallel group, on the device."""
+        mean, loss_sum, n_valid = C.c_float(0), C.c_double(0), C.c_uint64(0)
+        self.rt._check(self._lib.ullis_cuda_model_read_loss_global(self._h, C.byref(mean), C.byref(loss_sum),
+                                                                    C.byref(n_valid)))
+        return float(mean.value), float(loss_sum.value), int(n_valid.value)
 
     def logits(self, tokens, batch: int, time: int) -> np.ndarray:
         t = _arr(tokens, np.uint32, "tokens", batch * time)
