@@ -9,6 +9,7 @@ from conftest import pack_streams
 
 ALGOS = {"eager": 0, "euler": 1, "euler_with_constant_k_shortcut": 2, "incremental_pushes_lazy_chain": 6}
 PACKED_WORDS = 4   # pass 1 on packed state words: 16-bit state ids only
+SPLIT = 5          # pass 1 as extend / walk / climb against the final automaton: 16-bit state ids only
 
 
 @pytest.mark.parametrize("T", [1, 2, 3, 4, 5])
@@ -22,6 +23,7 @@ def test_exhaustive_short_streams(oracle, sam_host, T):
         for ix in (16, 32):
             assert np.array_equal(sam_host(algo, ix, q, k, v, n, T), ref)
     assert np.array_equal(sam_host(PACKED_WORDS, 16, q, k, v, n, T), ref)
+    assert np.array_equal(sam_host(SPLIT, 16, q, k, v, n, T), ref)
 
 
 @pytest.mark.parametrize("T", [9, 14])
@@ -38,6 +40,7 @@ def test_exhaustive_key_sequences_under_a_constant_query(oracle, sam_host, T):
             assert np.array_equal(sam_host(2, 16, q, kk, v, kk.size, T), ref), c
             assert np.array_equal(sam_host(1, 16, q, kk, v, kk.size, T), ref), c
             assert np.array_equal(sam_host(PACKED_WORDS, 16, q, kk, v, kk.size, T), ref), c
+            assert np.array_equal(sam_host(SPLIT, 16, q, kk, v, kk.size, T), ref), c
 
 
 def _streams(kind, n, T, rng):
@@ -89,7 +92,7 @@ def test_long_streams(oracle, sam_host, kind, T, n):
     rng = np.random.default_rng(hash((kind, T)) & 0xFFFF)
     q, k, v = (pack_streams(b) for b in _streams(kind, n, T, rng))
     ref = oracle.rosa_qkv_streams(q, k, v, n, T)
-    for algo in list(ALGOS.values()) + [PACKED_WORDS]:
+    for algo in list(ALGOS.values()) + [PACKED_WORDS, SPLIT]:
         assert np.array_equal(sam_host(algo, 16, q, k, v, n, T), ref), (kind, algo)
     assert np.array_equal(sam_host(1, 32, q, k, v, n, T), ref)
 

@@ -86,6 +86,45 @@ void set_global_error(const char* msg) {
 }
 }  // namespace ullis
 
+// Child runtime i of a lane-splitting forward: a stream, scratch and timing marks of its own; everything that
+// configures kernels is copied from the parent on every request, and the status words are the parent's.
+ullis_cuda_runtime* ullis_cuda_runtime::child(size_t i) {
+    while (children.size() <= i) {
+        ullis_cuda_runtime* c = new ullis_cuda_runtime();
+        children.push_back(c);
+        c->parent = this;
+        c->device = device;
+        c->sm_count = sm_count;
+        c->cc_major = cc_major;
+        c->cc_minor = cc_minor;
+        c->dev_status = dev_status;     // shared: a kernel of any share reports into the parent's words
+        c->host_status = host_status;
+        c->lanes = 1;
+        ULLIS_CUDA_CHECK(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        ULLIS_CUDA_CHECK(cudaEventCreateWithFlags(&c->lane_event, cudaEventDisableTiming));
+    }
+    ullis_cuda_runtime* c = children[i];
+    c->mode = mode;
+    c->sam_algo = sam_algo;
+    c->sam_coop = sam_coop;
+    c->sam_side = sam_side;
+    c->sam_lanes = sam_lanes;
+    c->sam_lanes_fixed = sam_lanes_fixed;
+    c->sam_sparse_per_sm = sam_sparse_per_sm;
+    c->sam_coop_threads = sam_coop_threads;
+    c->sam_words = sam_words;
+    c->sam_split = sam_split;
+    c->sam_budget_bytes = sam_budget_bytes / (children.size() + 1);
+    c->tc_stages = tc_stages;
+    c->tc_stages2 = tc_stages2;
+    c->tc_ws2_min_rows = tc_ws2_min_rows;
+    if (c->kernel_timing != kernel_timing) {
+        c->kernel_timing = kernel_timing;
+        if (kernel_timing) c->kernel_timing_begin();
+    }
+    return c;
+}
+
 void ullis_cuda_runtime::launched(const char* what) {
     ++launches;
     cudaError_t e = cudaGetLastError();
@@ -132,6 +171,13 @@ void ullis_cuda_runtime::kernel_time(const char* name, float* total_ms, uint32_t
     sync();
     float total = 0.f;
     uint32_t n = 0;
+    for (ullis_cuda_runtime* c : children) {   // the shares of a lane-splitting forward ran on these
+        float t = 0.f;
+        uint32_t k = 0;
+        if (c->kernel_timing) c->kernel_time(name, &t, &k);
+        total += t;
+        n += k;
+    }
     if (side_stream) ULLIS_CUDA_CHECK(cudaStreamSynchronize(side_stream));
     cudaEvent_t previous = marks_start;   // end of the last kernel on `stream`
     for (size_t i = 0; i < marks_used; ++i) {
@@ -150,14 +196,19 @@ void ullis_cuda_runtime::kernel_time(const char* name, float* total_ms, uint32_t
 size_t ullis_cuda_runtime::kernel_names(char* buf, size_t len) {
     std::vector<const char*> seen;
     std::string out;
-    for (size_t i = 0; i < marks_used; ++i) {
-        bool dup = false;
-        for (const char* s : seen) dup = dup || std::strcmp(s, marks[i].name) == 0;
-        if (dup) continue;
-        seen.push_back(marks[i].name);
-        out += marks[i].name;
-        out += '\n';
-    }
+    auto collect = [&](const ullis_cuda_runtime* r) {
+        for (size_t i = 0; i < r->marks_used; ++i) {
+            bool dup = false;
+            for (const char* s : seen) dup = dup || std::strcmp(s, r->marks[i].name) == 0;
+            if (dup) continue;
+            seen.push_back(r->marks[i].name);
+            out += r->marks[i].name;
+            out += '\n';
+        }
+    };
+    collect(this);
+    for (const ullis_cuda_runtime* c : children)
+        if (c->kernel_timing) collect(c);
     if (buf && len) {
         const size_t n = out.size() < len - 1 ? out.size() : len - 1;
         std::memcpy(buf, out.data(), n);
@@ -236,7 +287,9 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         }
         if (const char* env = getenv("ULLIS_CUDA_SAM_SPARSE")) rt->sam_sparse_per_sm = (uint32_t)std::max(0, atoi(env));
         if (const char* env = getenv("ULLIS_CUDA_SAM_WORDS")) rt->sam_words = atoi(env) != 0;
+        if (const char* env = getenv("ULLIS_CUDA_SAM_SPLIT")) rt->sam_split = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_SIDE")) rt->sam_side = atoi(env) != 0;
+        if (const char* env = getenv("ULLIS_CUDA_LANES")) rt->lanes = std::min(16, std::max(1, atoi(env)));
         if (const char* env = getenv("ULLIS_CUDA_SAM_COOP_THREADS")) {
             const int v = atoi(env);
             if (v == 256 || v == 512 || v == 1024) rt->sam_coop_threads = v;
@@ -260,6 +313,13 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
 void ullis_cuda_runtime_destroy(ullis_cuda_runtime* rt) {
     if (!rt) return;
     cudaSetDevice(rt->device);
+    for (ullis_cuda_runtime* c : rt->children) {
+        c->dev_status = nullptr;    // the parent's
+        c->host_status = nullptr;
+        ullis_cuda_runtime_destroy(c);
+    }
+    rt->children.clear();
+    if (rt->lane_event) cudaEventDestroy(rt->lane_event);
     ullis_cuda_dp_finalize(rt);
     if (rt->stream) {
         cudaStreamSynchronize(rt->stream);
@@ -306,13 +366,22 @@ int32_t ullis_cuda_runtime_synchronize(ullis_cuda_runtime* rt) {
 
 void* ullis_cuda_runtime_stream(ullis_cuda_runtime* rt) { return rt ? (void*)rt->stream : nullptr; }
 
-uint64_t ullis_cuda_runtime_launch_count(const ullis_cuda_runtime* rt) { return rt ? rt->launches : 0; }
+uint64_t ullis_cuda_runtime_launch_count(const ullis_cuda_runtime* rt) {
+    if (!rt) return 0;
+    uint64_t n = rt->launches;
+    for (const ullis_cuda_runtime* c : rt->children) n += c->launches;
+    return n;
+}
 
 int32_t ullis_cuda_runtime_kernel_timing(ullis_cuda_runtime* rt, int32_t enabled) {
     return guard(rt, [&] {
         rt->bind();
         rt->kernel_timing = enabled != 0;
         if (rt->kernel_timing) rt->kernel_timing_begin();
+        for (size_t i = 0; i < rt->children.size(); ++i) {
+            rt->children[i]->kernel_timing = false;   // re-armed (from a fresh start event) when a forward next uses it
+            rt->children[i]->marks_used = 0;
+        }
     });
 }
 
@@ -333,15 +402,22 @@ int32_t ullis_cuda_runtime_kernel_names(ullis_cuda_runtime* rt, char* buf, size_
 int32_t ullis_cuda_runtime_sam_counts(ullis_cuda_runtime* rt, uint64_t* total, uint64_t* automaton,
                                       uint64_t* constant_q) {
     return guard(rt, [&] {
-        uint32_t host[2] = {0, 0};
-        if (rt->sam_last_streams) {
-            // the two counters sit behind the automaton list (k::rosa_sam)
-            rt->d2h(host, rt->sam_list.as<uint32_t>(2 * rt->sam_last_streams + 2) + rt->sam_last_streams, 8);
-            rt->sync();
+        uint64_t sum[3] = {0, 0, 0};
+        for (size_t lane = 0; lane < rt->lanes_last; ++lane) {
+            ullis_cuda_runtime* r = lane == 0 ? rt : rt->children.at(lane - 1);
+            uint32_t host[2] = {0, 0};
+            if (r->sam_last_streams) {
+                // the two counters sit behind the automaton list (k::rosa_sam)
+                r->d2h(host, r->sam_list.as<uint32_t>(2 * r->sam_last_streams + 2) + r->sam_last_streams, 8);
+                r->sync();
+            }
+            sum[0] += r->sam_last_streams;
+            sum[1] += host[0];
+            sum[2] += host[1];
         }
-        if (total) *total = rt->sam_last_streams;
-        if (automaton) *automaton = host[0];
-        if (constant_q) *constant_q = host[1];
+        if (total) *total = sum[0];
+        if (automaton) *automaton = sum[1];
+        if (constant_q) *constant_q = sum[2];
     });
 }
 

@@ -101,6 +101,7 @@ struct ullis_cuda_runtime {
     uint32_t sam_sparse_per_sm = 40;    // pass 1 carries one stream per warp below this many streams per SM
     int sam_coop_threads = 0;           // threads per stream in the tour / pass 2 kernel (256, 512, 1024); 0 = from the shared memory a stream needs
     bool sam_words = true;              // pass 1 on packed state words (sam_core.cuh euler_pass1_words); false: the field-wise form
+    bool sam_split = true;              // pass 1 as two kernels, extend chain then query walk, and the climb inside the tour kernel
     int sam_lanes = 4;                  // streams carried per warp by the suffix-automaton kernel (1,2,4,...,32)
     uint64_t launches = 0;
     std::string last_error;
@@ -120,6 +121,18 @@ struct ullis_cuda_runtime {
     int tc_ws2_clusters[5] = {0, 0, 0, 0, 0};   // CTA pairs of that kernel the device holds at once, per epilogue
     int tc_ready = 0;                   // 0 = not probed, 1 = usable, -1 = unusable on this device
     ullis::NcclState* nccl = nullptr;
+
+    // Lanes: a model forward splits its batch into shares that run the whole pass on streams of their own, so
+    // that one share's suffix-automaton kernels (bound by the latency of a serial chain, most issue slots idle)
+    // run beside another share's GEMMs.  A share runs through a child runtime: its own stream, scratch buffers
+    // and timing marks, the parent's settings and status words.  Children are created on demand, owned by the
+    // parent and only ever used from inside a model call on the parent.
+    int lanes = 1;                                   // shares a forward may use (1 = everything on `stream`, the default: see enqueue_hidden)
+    ullis_cuda_runtime* parent = nullptr;            // set on a child
+    std::vector<ullis_cuda_runtime*> children;
+    cudaEvent_t lane_event = nullptr;                // parent: the fork point; child: the end of its share
+    ullis_cuda_runtime* child(size_t i);             // child i (0-based), created on first use with the parent's settings
+    size_t lanes_last = 1;                           // shares of the last suffix-automaton call (1 + children used)
 
     // Per-kernel device times: while enabled, an event is recorded behind every
     // launch; the stream is in order, so consecutive events bracket one kernel

@@ -663,6 +663,11 @@ bool cmix_residual(ullis_cuda_runtime* rt, const LayerWeights& L, float* x, size
     return true;
 }
 
+bool takes_model(ullis_cuda_runtime* rt, size_t rows, size_t time, size_t d, size_t ffn, size_t vocab) {
+    return usable(rt) && shape_ok(rows, d, d) && time % 32 == 0 && d % 4 == 0 && shape_ok(rows, d, ffn) &&
+           shape_ok(rows, ffn, d) && shape_ok(rows, d, vocab);
+}
+
 bool head_ce(ullis_cuda_runtime* rt, const float* hidden, const PackedWeights& head, const uint32_t* labels,
              uint32_t ignore_id, size_t rows, size_t time, size_t d, size_t vocab, float* row_loss) {
     if (!usable(rt) || !shape_ok(rows, d, vocab)) return false;

@@ -30,5 +30,9 @@ bool cmix_residual(ullis_cuda_runtime* rt, const LayerWeights& L, float* x, size
 bool head_ce(ullis_cuda_runtime* rt, const float* hidden, const PackedWeights& head, const uint32_t* labels,
              uint32_t ignore_id, size_t rows, size_t time, size_t d, size_t vocab, float* row_loss);
 
+// True when every stage above takes a model of these dimensions at `rows` rows per call (so that a forward
+// can count on none of the CUDA-core fall-backs, which share buffers, being reached).
+bool takes_model(ullis_cuda_runtime* rt, size_t rows, size_t time, size_t d, size_t ffn, size_t vocab);
+
 }  // namespace tc
 }  // namespace ullis

@@ -40,6 +40,8 @@ struct ArenaPlan {
 }  // namespace
 
 ullis_cuda_model::~ullis_cuda_model() {
+    if (rt)
+        for (ullis_cuda_runtime* c : rt->children) cudaStreamSynchronize(c->stream);   // shares may still use the buffers
     for (auto& s : spans) {
         cudaEventDestroy(s.start);
         cudaEventDestroy(s.stop);
@@ -170,6 +172,7 @@ void ullis_cuda_model::check_shape(size_t batch, size_t time) const {
 void ullis_cuda_model::upload_tokens(const uint32_t* tokens, const uint32_t* lab, size_t batch, size_t time) {
     check_shape(batch, time);
     if (!tokens) fail(ULLIS_CUDA_ERR_ARG, "tokens is null");
+    if (lanes_open) join_lanes();   // a forward that failed half way left its shares unjoined: they still read the old ids
     const size_t rows = batch * time;
     for (size_t r = 0; r < rows; ++r)
         if (tokens[r] >= vocab) fail(ULLIS_CUDA_ERR_TOKEN, "token id exceeds vocabulary");
@@ -182,7 +185,7 @@ void ullis_cuda_model::upload_tokens(const uint32_t* tokens, const uint32_t* lab
     have_pair = false;
 }
 
-void ullis_cuda_model::begin(int phase) {
+void ullis_cuda_model::begin(int phase, ullis_cuda_runtime* on) {
     if (!profile) return;
     if (spans_used == spans.size()) {
         Span s{phase, nullptr, nullptr};
@@ -191,12 +194,12 @@ void ullis_cuda_model::begin(int phase) {
         spans.push_back(s);
     }
     spans[spans_used].phase = phase;
-    ULLIS_CUDA_CHECK(cudaEventRecord(spans[spans_used].start, rt->stream));
+    ULLIS_CUDA_CHECK(cudaEventRecord(spans[spans_used].start, (on ? on : rt)->stream));
 }
 
-void ullis_cuda_model::end() {
+void ullis_cuda_model::end(ullis_cuda_runtime* on) {
     if (!profile) return;
-    ULLIS_CUDA_CHECK(cudaEventRecord(spans[spans_used].stop, rt->stream));
+    ULLIS_CUDA_CHECK(cudaEventRecord(spans[spans_used].stop, (on ? on : rt)->stream));
     ++spans_used;
 }
 
@@ -242,7 +245,13 @@ void ullis_cuda_model::tap(int layer, int which, void* out, size_t bytes) {
 // UllisHeron::hidden (src/model.rs:2644-2683) with HeronBlock::forward
 // (2224-2241), RwkvRosaQkv1Bit::forward (1284-1318), RwkvCMixX070::forward
 // (987-1001).  The residual stream `x` stays on the device for the whole pass.
-void ullis_cuda_model::enqueue_hidden(size_t batch, size_t time) {
+//
+// Sequences are independent, so the batch is cut into up to `rt->lanes` shares of whole sequences and
+// every share runs the pass on a stream of its own: the suffix-automaton kernels are serial chains that
+// leave most of an SM's issue slots and all of its tensor pipes idle, and with several shares in flight
+// one share's automata run beside another's GEMMs.  Every kernel treats rows (and streams) independently,
+// so a sequence gets the same result whichever share carries it.
+void ullis_cuda_model::enqueue_hidden(size_t batch, size_t time, bool join) {
     check_shape(batch, time);
     if (batch != cur_batch || time != cur_time) fail(ULLIS_CUDA_ERR_SHAPE, "upload_tokens was not called for this shape");
     rt->bind();
@@ -250,16 +259,12 @@ void ullis_cuda_model::enqueue_hidden(size_t batch, size_t time) {
     const size_t rows = batch * time, n = rows * d;
     const bool exact = rt->mode == ULLIS_CUDA_MODE_EXACT;
     const size_t wps = (time + 31) / 32, sw_words = batch * d * wps;
-    float* X = x.as<float>(n);
-    float* A = a.as<float>(n);
-    float* Bq = b.as<float>(n);
-    float* Bk = c.as<float>(n);
-    float* Bv = dd.as<float>(n);
-    float* W = wide.as<float>(rows * std::max(ffn, d));
-    uint32_t* QS = q_sw.as<uint32_t>(sw_words);
-    uint32_t* KS = k_sw.as<uint32_t>(sw_words);
-    uint32_t* VS = v_sw.as<uint32_t>(sw_words);
-    uint32_t* IS = idx_sw.as<uint32_t>(sw_words);
+    x.as<float>(n);
+    a.as<float>(n);
+    q_sw.as<uint32_t>(sw_words);
+    k_sw.as<uint32_t>(sw_words);
+    v_sw.as<uint32_t>(sw_words);
+    idx_sw.as<uint32_t>(sw_words);
     if (taps_enabled) {
         if (tap_bufs.size() != layers * 8 + 1) tap_bufs = std::vector<DeviceBuffer>(layers * 8 + 1);
         tap_rows = rows;
@@ -271,91 +276,171 @@ void ullis_cuda_model::enqueue_hidden(size_t batch, size_t time) {
     spans_used = 0;
     rt->clear_status();
 
-    begin(PH_EMBED_LN);
-    k::embed(rt, ids.as<uint32_t>(rows), embedding, X, rows, d, vocab);
-    end();
-    for (size_t l = 0; l < layers; ++l) {
-        const LayerWeights& L = blocks[l];
-        begin(PH_EMBED_LN);
-        if (l == 0) {  // ln0 REPLACES x on layer 0 (src/model.rs:2225-2229)
-            k::layer_norm(rt, X, L.ln0.weight, L.ln0.bias, A, rows, d, exact);
-            ULLIS_CUDA_CHECK(cudaMemcpyAsync(X, A, n * 4, cudaMemcpyDeviceToDevice, rt->stream));
-        }
-        save_tap((int)l, ULLIS_CUDA_TAP_BLOCK_IN, X, n * 4);
-        k::layer_norm(rt, X, L.ln3.weight, L.ln3.bias, A, rows, d, exact);
-        save_tap((int)l, ULLIS_CUDA_TAP_LN3_OUT, A, n * 4);
-        end();
-
-        begin(PH_QKV);
-        if (!tc::rosa_qkv_bits(rt, A, L, QS, KS, VS, batch, time, d)) {
-            k::shift_mix(rt, A, L.x_q, L.x_k, L.x_v, Bq, Bk, Bv, rows, time, d);
-            k::binary_linear_exact(rt, Bq, L.q.bits, L.q.scale, L.q.bias, W, rows, d, d, false);
-            k::sign_pack_streams(rt, W, QS, batch, time, d);
-            k::binary_linear_exact(rt, Bk, L.k.bits, L.k.scale, L.k.bias, W, rows, d, d, false);
-            k::sign_pack_streams(rt, W, KS, batch, time, d);
-            k::binary_linear_exact(rt, Bv, L.v.bits, L.v.scale, L.v.bias, W, rows, d, d, false);
-            k::sign_pack_streams(rt, W, VS, batch, time, d);
-        }
-        save_tap_bits((int)l, ULLIS_CUDA_TAP_Q_BITS, QS, batch, time);
-        save_tap_bits((int)l, ULLIS_CUDA_TAP_K_BITS, KS, batch, time);
-        save_tap_bits((int)l, ULLIS_CUDA_TAP_V_BITS, VS, batch, time);
-        end();
-
-        begin(PH_SAM);
-        k::rosa_sam(rt, QS, KS, VS, IS, batch * d, time);
-        save_tap_bits((int)l, ULLIS_CUDA_TAP_IDX, IS, batch, time);
-        if (train_tape)
-            ULLIS_CUDA_CHECK(cudaMemcpyAsync(tape_idx[l].as<uint32_t>(sw_words), IS, sw_words * 4,
-                                             cudaMemcpyDeviceToDevice, rt->stream));
-        end();
-
-        begin(PH_O);
-        if (!tc::rosa_out_residual(rt, IS, L, X, batch, time, d)) {
-            k::rosa_emit(rt, IS, L.e, nullptr, A, batch, time, d);
-            k::binary_linear_exact(rt, A, L.o.bits, L.o.scale, L.o.bias, X, rows, d, d, true);  // x += rosa out
-        }
-        save_tap((int)l, ULLIS_CUDA_TAP_AFTER_ROSA, X, n * 4);
-        if (train_tape)
-            ULLIS_CUDA_CHECK(cudaMemcpyAsync(tape_after[l].as<float>(n), X, n * 4, cudaMemcpyDeviceToDevice,
-                                             rt->stream));
-        end();
-
-        begin(PH_CMIX);
-        if (!tc::cmix_residual(rt, L, X, batch, time, d, ffn)) {
-            k::layer_norm(rt, X, L.ln2.weight, L.ln2.bias, A, rows, d, exact);
-            k::shift_mix(rt, A, L.ffn_x_k, nullptr, nullptr, Bq, nullptr, nullptr, rows, time, d);
-            k::binary_linear_exact(rt, Bq, L.key.bits, L.key.scale, nullptr, W, rows, d, ffn, false);
-            k::relu2(rt, W, W, rows * ffn);
-            k::fp16_linear_exact(rt, W, L.value, X, rows, ffn, d, true);  // x += cmix out
-        }
-        save_tap((int)l, ULLIS_CUDA_TAP_BLOCK_OUT, X, n * 4);
-        end();
+    // shares: one unless every stage runs on the tensor-core kernels (the CUDA-core fall-backs share scratch
+    // buffers of the model) and nothing wants the whole batch's intermediates in one place
+    size_t n_lanes = 1;
+    if (!exact && !taps_enabled && !train_tape && rt->lanes > 1 && batch > 1 &&
+        tc::takes_model(rt, time, time, d, ffn, vocab))
+        n_lanes = std::min<size_t>((size_t)rt->lanes, batch);
+    if (n_lanes == 1) {   // the fall-back buffers, whole batch
+        b.as<float>(n);
+        c.as<float>(n);
+        dd.as<float>(n);
+        wide.as<float>(rows * std::max(ffn, d));
     }
-    begin(PH_HEAD_CE);
-    k::layer_norm(rt, X, ln_out.weight, ln_out.bias, A, rows, d, exact);
+    lanes.clear();
+    for (size_t i = 0; i < n_lanes; ++i) {
+        const size_t lo = i * batch / n_lanes, hi = (i + 1) * batch / n_lanes;
+        lanes.push_back(Lane{i == 0 ? rt : rt->child(i - 1), lo, hi - lo});
+    }
+    if (n_lanes > 1) {
+        if (!rt->lane_event) ULLIS_CUDA_CHECK(cudaEventCreateWithFlags(&rt->lane_event, cudaEventDisableTiming));
+        ULLIS_CUDA_CHECK(cudaEventRecord(rt->lane_event, rt->stream));   // ids are in place, the status words clear
+        for (size_t i = 1; i < n_lanes; ++i) {
+            ULLIS_CUDA_CHECK(cudaStreamWaitEvent(lanes[i].rt->stream, rt->lane_event, 0));
+            if (lanes[i].rt->kernel_timing) lanes[i].rt->mark("(between steps)");
+        }
+    }
+    lanes_open = n_lanes > 1;
+
+    float* X = x.as<float>(n);
+    for (const Lane& ln : lanes) {
+        const size_t r0 = ln.seq0 * time, nr = ln.nseq * time;
+        begin(PH_EMBED_LN, ln.rt);
+        k::embed(ln.rt, ids.as<uint32_t>(rows) + r0, embedding, X + r0 * d, nr, d, vocab);
+        end(ln.rt);
+    }
+    for (size_t l = 0; l < layers; ++l)
+        for (const Lane& ln : lanes) enqueue_layer(ln, l, time);
+    float* A = a.as<float>(n);
+    for (const Lane& ln : lanes) {
+        const size_t r0 = ln.seq0 * time, nr = ln.nseq * time;
+        begin(PH_HEAD_CE, ln.rt);
+        k::layer_norm(ln.rt, X + r0 * d, ln_out.weight, ln_out.bias, A + r0 * d, nr, d, exact);
+        end(ln.rt);
+    }
     save_tap(0, ULLIS_CUDA_TAP_HIDDEN, A, n * 4);
-    end();
+    rt->lanes_last = n_lanes;
+    if (join) join_lanes();
+}
+
+void ullis_cuda_model::join_lanes() {
+    if (!lanes_open) return;
+    for (size_t i = 1; i < lanes.size(); ++i) {
+        ULLIS_CUDA_CHECK(cudaEventRecord(lanes[i].rt->lane_event, lanes[i].rt->stream));
+        ULLIS_CUDA_CHECK(cudaStreamWaitEvent(rt->stream, lanes[i].rt->lane_event, 0));
+    }
+    lanes_open = false;
+    if (rt->kernel_timing) rt->mark("(join)");   // waiting for the other shares is no kernel's time
+}
+
+// One HeronBlock (src/model.rs:2224-2241) over the sequences of one share, on that share's stream.
+void ullis_cuda_model::enqueue_layer(const Lane& ln, size_t l, size_t time) {
+    ullis_cuda_runtime* r = ln.rt;
+    const LayerWeights& L = blocks[l];
+    const bool exact = r->mode == ULLIS_CUDA_MODE_EXACT;
+    const size_t batch = ln.nseq, rows = batch * time, n = rows * d, r0 = ln.seq0 * time;
+    const size_t wps = (time + 31) / 32, sw_words = batch * d * wps, s0 = ln.seq0 * d * wps;
+    float* X = static_cast<float*>(x.get()) + r0 * d;
+    float* A = static_cast<float*>(a.get()) + r0 * d;
+    uint32_t* QS = static_cast<uint32_t*>(q_sw.get()) + s0;
+    uint32_t* KS = static_cast<uint32_t*>(k_sw.get()) + s0;
+    uint32_t* VS = static_cast<uint32_t*>(v_sw.get()) + s0;
+    uint32_t* IS = static_cast<uint32_t*>(idx_sw.get()) + s0;
+    // the CUDA-core fall-backs below are only reached with a single share (r0 == 0, whole batch)
+    float* Bq = static_cast<float*>(b.get());
+    float* Bk = static_cast<float*>(c.get());
+    float* Bv = static_cast<float*>(dd.get());
+    float* W = static_cast<float*>(wide.get());
+    const bool one = lanes.size() == 1;
+
+    begin(PH_EMBED_LN, r);
+    if (l == 0) {  // ln0 REPLACES x on layer 0 (src/model.rs:2225-2229)
+        k::layer_norm(r, X, L.ln0.weight, L.ln0.bias, A, rows, d, exact);
+        ULLIS_CUDA_CHECK(cudaMemcpyAsync(X, A, n * 4, cudaMemcpyDeviceToDevice, r->stream));
+    }
+    save_tap((int)l, ULLIS_CUDA_TAP_BLOCK_IN, X, n * 4);
+    k::layer_norm(r, X, L.ln3.weight, L.ln3.bias, A, rows, d, exact);
+    save_tap((int)l, ULLIS_CUDA_TAP_LN3_OUT, A, n * 4);
+    end(r);
+
+    begin(PH_QKV, r);
+    if (!tc::rosa_qkv_bits(r, A, L, QS, KS, VS, batch, time, d)) {
+        if (!one) fail(ULLIS_CUDA_ERR_ARG, "internal: a split forward reached a fall-back kernel");
+        k::shift_mix(r, A, L.x_q, L.x_k, L.x_v, Bq, Bk, Bv, rows, time, d);
+        k::binary_linear_exact(r, Bq, L.q.bits, L.q.scale, L.q.bias, W, rows, d, d, false);
+        k::sign_pack_streams(r, W, QS, batch, time, d);
+        k::binary_linear_exact(r, Bk, L.k.bits, L.k.scale, L.k.bias, W, rows, d, d, false);
+        k::sign_pack_streams(r, W, KS, batch, time, d);
+        k::binary_linear_exact(r, Bv, L.v.bits, L.v.scale, L.v.bias, W, rows, d, d, false);
+        k::sign_pack_streams(r, W, VS, batch, time, d);
+    }
+    save_tap_bits((int)l, ULLIS_CUDA_TAP_Q_BITS, QS, batch, time);
+    save_tap_bits((int)l, ULLIS_CUDA_TAP_K_BITS, KS, batch, time);
+    save_tap_bits((int)l, ULLIS_CUDA_TAP_V_BITS, VS, batch, time);
+    end(r);
+
+    begin(PH_SAM, r);
+    k::rosa_sam(r, QS, KS, VS, IS, batch * d, time);
+    save_tap_bits((int)l, ULLIS_CUDA_TAP_IDX, IS, batch, time);
+    if (train_tape)
+        ULLIS_CUDA_CHECK(cudaMemcpyAsync(tape_idx[l].as<uint32_t>(sw_words), IS, sw_words * 4,
+                                         cudaMemcpyDeviceToDevice, r->stream));
+    end(r);
+
+    begin(PH_O, r);
+    if (!tc::rosa_out_residual(r, IS, L, X, batch, time, d)) {
+        if (!one) fail(ULLIS_CUDA_ERR_ARG, "internal: a split forward reached a fall-back kernel");
+        k::rosa_emit(r, IS, L.e, nullptr, A, batch, time, d);
+        k::binary_linear_exact(r, A, L.o.bits, L.o.scale, L.o.bias, X, rows, d, d, true);  // x += rosa out
+    }
+    save_tap((int)l, ULLIS_CUDA_TAP_AFTER_ROSA, X, n * 4);
+    if (train_tape)
+        ULLIS_CUDA_CHECK(cudaMemcpyAsync(tape_after[l].as<float>(n), X, n * 4, cudaMemcpyDeviceToDevice,
+                                         r->stream));
+    end(r);
+
+    begin(PH_CMIX, r);
+    if (!tc::cmix_residual(r, L, X, batch, time, d, ffn)) {
+        if (!one) fail(ULLIS_CUDA_ERR_ARG, "internal: a split forward reached a fall-back kernel");
+        k::layer_norm(r, X, L.ln2.weight, L.ln2.bias, A, rows, d, exact);
+        k::shift_mix(r, A, L.ffn_x_k, nullptr, nullptr, Bq, nullptr, nullptr, rows, time, d);
+        k::binary_linear_exact(r, Bq, L.key.bits, L.key.scale, nullptr, W, rows, d, ffn, false);
+        k::relu2(r, W, W, rows * ffn);
+        k::fp16_linear_exact(r, W, L.value, X, rows, ffn, d, true);  // x += cmix out
+    }
+    save_tap((int)l, ULLIS_CUDA_TAP_BLOCK_OUT, X, n * 4);
+    end(r);
 }
 
 // CE forward of apply_head_ce (src/model.rs:3205-3228, 3253-3257).
 void ullis_cuda_model::enqueue_forward_ce(uint32_t ignore_id, size_t batch, size_t time) {
-    enqueue_hidden(batch, time);
+    enqueue_hidden(batch, time, /*join=*/false);
     const size_t rows = batch * time;
     if (!labels.get() || labels.bytes() < rows * 4) fail(ULLIS_CUDA_ERR_ARG, "labels were not uploaded");
     float* A = a.as<float>(rows * d);
     float* RL = row_loss.as<float>(rows);
     uint8_t* res = static_cast<uint8_t*>(result.ensure(32));   // {f64 sum, u64 count} then the same as two f64
     const uint32_t* lab = labels.as<uint32_t>(rows);
-    begin(PH_HEAD_CE);
-    if (!tc::head_ce(rt, A, head, lab, ignore_id, rows, time, d, vocab, RL)) {
-        const size_t chunk = std::max<size_t>(1, std::min<size_t>(rows, ((size_t)256 << 20) / (vocab * 4)));
-        float* LG = logits.as<float>(chunk * vocab);
-        for (size_t r0 = 0; r0 < rows; r0 += chunk) {
-            const size_t nr = std::min(chunk, rows - r0);
-            k::binary_linear_exact(rt, A + r0 * d, head.bits, head.scale, head.bias, LG, nr, d, vocab, false);
-            k::ce_rows_from_logits(rt, LG, lab, ignore_id, r0, nr, rows, time, vocab, RL);
+    for (const Lane& ln : lanes) {
+        // a share is made of whole sequences, so the valid-row rule (row % time, labels[row + 1]) reads the same
+        // with the share's own row numbering
+        const size_t r0 = ln.seq0 * time, nr = ln.nseq * time;
+        begin(PH_HEAD_CE, ln.rt);
+        if (!tc::head_ce(ln.rt, A + r0 * d, head, lab + r0, ignore_id, nr, time, d, vocab, RL + r0)) {
+            if (lanes.size() != 1) fail(ULLIS_CUDA_ERR_ARG, "internal: a split forward reached a fall-back kernel");
+            const size_t chunk = std::max<size_t>(1, std::min<size_t>(rows, ((size_t)256 << 20) / (vocab * 4)));
+            float* LG = logits.as<float>(chunk * vocab);
+            for (size_t c0 = 0; c0 < rows; c0 += chunk) {
+                const size_t nc = std::min(chunk, rows - c0);
+                k::binary_linear_exact(rt, A + c0 * d, head.bits, head.scale, head.bias, LG, nc, d, vocab, false);
+                k::ce_rows_from_logits(rt, LG, lab, ignore_id, c0, nc, rows, time, vocab, RL);
+            }
         }
+        end(ln.rt);
     }
+    join_lanes();
+    begin(PH_HEAD_CE);
     k::ce_reduce(rt, RL, lab, ignore_id, rows, time, reinterpret_cast<double*>(res),
                  reinterpret_cast<unsigned long long*>(res + 8), reinterpret_cast<double*>(res + 16));
     end();

@@ -68,8 +68,15 @@ struct ullis_cuda_model {
     void load(const uint8_t* bytes, size_t len);
     void upload_tokens(const uint32_t* tokens, const uint32_t* labels, size_t batch, size_t time);
     void check_shape(size_t batch, size_t time) const;
-    // x <- hidden() ; leaves ln_out output in buffer `a` as f32 [rows, d]
-    void enqueue_hidden(size_t batch, size_t time);
+    // A share of the batch (whole sequences) and the runtime - the model's own or one of its children - whose
+    // stream and scratch carry it.
+    struct Lane { ullis_cuda_runtime* rt; size_t seq0, nseq; };
+    std::vector<Lane> lanes;          // of the forward being enqueued (lane 0 runs on the model's runtime)
+    bool lanes_open = false;          // other shares may still be running: nothing on rt->stream has waited for them
+    // x <- hidden() ; leaves ln_out output in buffer `a` as f32 [rows, d].  With join = false the shares are
+    // left running on their streams (the caller appends per-share work and calls join_lanes()).
+    void enqueue_hidden(size_t batch, size_t time, bool join = true);
+    void join_lanes();                // the model's stream waits for every share
     void enqueue_forward_ce(uint32_t ignore_id, size_t batch, size_t time);
     void enqueue_logits(size_t batch, size_t time, float* host_logits);
     void read_loss(float* mean_loss, double* loss_sum, uint64_t* n_valid, float* row_loss, size_t rows);
@@ -78,8 +85,9 @@ struct ullis_cuda_model {
     void phase_ms(float ms[6]);
 
    private:
-    void begin(int phase);
-    void end();
+    void begin(int phase, ullis_cuda_runtime* on = nullptr);
+    void end(ullis_cuda_runtime* on = nullptr);
+    void enqueue_layer(const Lane& lane, size_t l, size_t time);
     void save_tap(int layer, int which, const void* src, size_t bytes);
     void save_tap_bits(int layer, int which, const uint32_t* sw, size_t batch, size_t time);
 };

@@ -115,7 +115,46 @@ rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const ui
     else sam::euler_pass1<uint16_t>(B, q_sw + s * wps, k_sw + s * wps, T, nullptr);
 }
 
-template <int NT>
+// Pass 1 in three parts (sam_core.cuh, "pass 1 in three parts"): the extend chain and the query walk as two
+// kernels with one thread per stream each, the climb inside the tour kernel.  Work items and state blocks as in
+// rosa_pass1_kernel.
+__device__ __forceinline__ bool split_item(const uint32_t* __restrict__ count, size_t first, size_t wave, int lanes,
+                                           uint32_t dense_count, uint32_t sparse_count, size_t* item_out) {
+    if (lanes == 0) lanes = *count > dense_count ? 4 : *count > sparse_count ? 2 : 1;
+    const int lane = threadIdx.x & 31;
+    const int spread = 32 / lanes;
+    if (lane % spread != 0) return false;
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const size_t item = warp * lanes + lane / spread;
+    if (item >= wave || first + item >= *count) return false;
+    *item_out = item;
+    return true;
+}
+
+__global__ void __launch_bounds__(128, 16)
+rosa_extend_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ k_sw,
+                   const uint32_t* __restrict__ list, const uint32_t* __restrict__ count, size_t first, size_t wave,
+                   uint32_t T, size_t wps, int lanes, uint32_t dense_count, uint32_t sparse_count) {
+    size_t item;
+    if (!split_item(count, first, wave, lanes, dense_count, sparse_count, &item)) return;
+    const size_t s = list[first + item];
+    sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
+    sam::euler_extend_words(B, k_sw + s * wps, T);
+}
+
+__global__ void __launch_bounds__(128, 16)
+rosa_walk_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
+                 const uint32_t* __restrict__ list, const uint32_t* __restrict__ count, size_t first, size_t wave,
+                 uint32_t T, size_t wps, int lanes, uint32_t dense_count, uint32_t sparse_count) {
+    size_t item;
+    if (!split_item(count, first, wave, lanes, dense_count, sparse_count, &item)) return;
+    const size_t s = list[first + item];
+    sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
+    uint32_t w = 0, h = 0;
+    sam::euler_walk_words(B, q_sw + s * wps, 0, T, w, h);
+}
+
+template <int NT, bool SPLIT = false>
 __global__ void __launch_bounds__(NT)
 rosa_coop_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ v_sw,
                  uint32_t* __restrict__ idx_sw, const uint32_t* __restrict__ list, const uint32_t* __restrict__ count,
@@ -130,7 +169,7 @@ rosa_coop_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uin
             status[1] = (uint32_t)s;
         return;
     }
-    sam::coop_tour_pass2<NT>(coop_smem, B, v_sw + s * wps, idx_sw + s * wps, T);
+    sam::coop_tour_pass2<NT, SPLIT>(coop_smem, B, v_sw + s * wps, idx_sw + s * wps, T);
 }
 
 // EAGER keeps the reference's schedule for every stream (no shortcut): list = all streams
@@ -179,6 +218,7 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     if (streams > 0xFFFFFFFFull) fail(ULLIS_CUDA_ERR_SHAPE, "too many ROSA streams");
     uint32_t* list = rt->sam_list.as<uint32_t>(2 * streams + 2);
     rt->sam_last_streams = streams;
+    if (!rt->parent) rt->lanes_last = 1;   // a forward that splits its batch raises this after its last layer
     uint32_t* count = list + streams;
     uint32_t* cq_count = count + 1;           // the constant-q streams, settled by a kernel of their own
     uint32_t* cq_list = count + 2;
@@ -223,9 +263,12 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
         }
     }
     if (use_coop && !rt->sam_coop_ready) {
-        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<512, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<1024, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<512, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<1024, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         rt->sam_coop_ready = true;
     }
     for (size_t s0 = 0; s0 < streams; s0 += wave) {
@@ -237,16 +280,36 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
             // sam_lanes_fixed: the caller pinned the streams per warp; otherwise the kernel picks 2 or 4
             const int pass1_lanes = rt->sam_lanes_fixed ? lanes : 0;
             const size_t pass1_warps = rt->sam_lanes_fixed ? warps : n;
-            rosa_pass1_kernel<<<(unsigned)((pass1_warps * 32 + 127) / 128), 128, 0, rt->stream>>>(
-                scratch, stride, q_sw, k_sw, list, count, s0, n, (uint32_t)time, wps, pass1_lanes,
-                96u * (uint32_t)rt->sm_count, rt->sam_sparse_per_sm * (uint32_t)rt->sm_count, rt->sam_words ? 1 : 0);
-            rt->launched("rosa_pass1");
+            const unsigned p1_grid = (unsigned)((pass1_warps * 32 + 127) / 128);
+            const uint32_t dense = 96u * (uint32_t)rt->sm_count, sparse = rt->sam_sparse_per_sm * (uint32_t)rt->sm_count;
+            const bool split = rt->sam_split && rt->sam_words;
+            if (split) {
+                rosa_extend_kernel<<<p1_grid, 128, 0, rt->stream>>>(scratch, stride, k_sw, list, count, s0, n,
+                                                                   (uint32_t)time, wps, pass1_lanes, dense, sparse);
+                rt->launched("rosa_extend");
+                rosa_walk_kernel<<<p1_grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, list, count, s0, n,
+                                                                 (uint32_t)time, wps, pass1_lanes, dense, sparse);
+                rt->launched("rosa_walk");
+            } else {
+                rosa_pass1_kernel<<<p1_grid, 128, 0, rt->stream>>>(
+                    scratch, stride, q_sw, k_sw, list, count, s0, n, (uint32_t)time, wps, pass1_lanes, dense, sparse,
+                    rt->sam_words ? 1 : 0);
+                rt->launched("rosa_pass1");
+            }
             // threads per stream: the fewer CTAs shared memory lets an SM hold, the more threads each one gets
             const unsigned coop_per_sm = (unsigned)((227u * 1024u) / (coop.total + 1024u));
             const int coop_threads = rt->sam_coop_threads ? rt->sam_coop_threads : coop_per_sm >= 3 ? 256 : coop_per_sm == 2 ? 512 : 1024;
-#define ULLIS_COOP_LAUNCH(NT)                                                                                      \
-    rosa_coop_kernel<NT><<<(unsigned)n, NT, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, count, s0, \
-                                                                      (uint32_t)time, wps, rt->dev_status)
+#define ULLIS_COOP_LAUNCH(NT)                                                                                          \
+    do {                                                                                                               \
+        if (split)                                                                                                     \
+            rosa_coop_kernel<NT, true><<<(unsigned)n, NT, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, \
+                                                                                    count, s0, (uint32_t)time, wps,    \
+                                                                                    rt->dev_status);                   \
+        else                                                                                                           \
+            rosa_coop_kernel<NT, false><<<(unsigned)n, NT, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw,    \
+                                                                                     list, count, s0, (uint32_t)time,  \
+                                                                                     wps, rt->dev_status);             \
+    } while (0)
             if (coop_threads == 256) ULLIS_COOP_LAUNCH(256);
             else if (coop_threads == 512) ULLIS_COOP_LAUNCH(512);
             else ULLIS_COOP_LAUNCH(1024);

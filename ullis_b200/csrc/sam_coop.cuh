@@ -91,7 +91,9 @@ constexpr uint32_t LAST_OF_SUBLIST = 0x80000000u;   // flag in an event word: th
 
 // One CTA of NT threads; `B` is the stream's global scratch block
 // after euler_pass1.  Every thread of the CTA must call this.
-template <int NT>
+// SPLIT: pass 1 ran in parts (sam_core.cuh) and left the walk's (w_t, h_t) in vq / head instead of v_t: the climb
+// to v_t happens here, every step by itself, while the query states are copied into shared memory.
+template <int NT, bool SPLIT = false>
 __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<uint16_t>& B, const uint32_t* vw,
                                                 uint32_t* out, uint32_t T) {
     constexpr uint32_t NIL = 0xFFFFu, END = 0xFFFFu;
@@ -277,12 +279,17 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     uint16_t* vq_s = reinterpret_cast<uint16_t*>(ev + ((tree_entries(T) + 3u) & ~3u));
     uint16_t* jid_s = vq_s + T;
     for (uint32_t i0 = tid; i0 < T; i0 += NT * 8) {
-        uint16_t a[8], b[8];
+        uint16_t a[8], b[8], hq[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const uint32_t i = i0 + NT * u;
-            a[u] = i < T ? B.vq[i] : (uint16_t)0;
+            a[u] = i < T ? B.vq[i] : (uint16_t)NIL;
             b[u] = i < T ? B.jid[i] : (uint16_t)0;
+            if (SPLIT) hq[u] = (i < T && a[u] != NIL) ? B.head[i] : (uint16_t)0;
+        }
+        if (SPLIT) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a[u] = (uint16_t)euler_climb_words(B.N, a[u], hq[u], b[u]);
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {

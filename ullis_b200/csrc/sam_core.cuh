@@ -542,6 +542,175 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
     return u;
 }
 
+// ------------------------------------------------------------------ pass 1 in three parts
+//
+// euler_pass1_words interleaves two serial chains that do not need each other step by step: the extend
+// never looks at the query, and the query only needs the automaton as it was after the extends of the
+// EARLIER steps.  The state ids say when a state was made (ids are handed out in order; step t creates
+// state jid[t], a clone right after it), so that older automaton can be read off the FINAL one:
+//   * a state exists at query time t iff its id is below lim = jid[t];
+//   * every store of the extend writes the id of a state made in that very step, so a child or link field
+//     holds either what it held at time t or the id of a younger state.  A younger child id is taken back
+//     through `orig` (a clone replaces the state it copies in the transitions it takes over, orig[clone] =
+//     that state; a state that is no clone replaces "no child", orig = NIL) until it is older than lim;
+//     a younger link is followed upwards until it is older than lim (the link tree only grows by leaves and
+//     by clones that subdivide an edge, so the nearest older ancestor is the link of time t);
+//   * lengths never change.
+// So the pass is split into
+//   extend (serial, one thread per stream): the whole automaton of the keys, jid, orig;
+//   walk   (serial, one thread per stream): the query state (w_t, h_t) of src/rosa.rs:104-119 for every step
+//          against that automaton read "as of time t" - one dependent load per step on a hit;
+//   climb  (independent per step, so it runs in parallel with the tour): the state v_t of
+//          src/rosa.rs:120-128 from (w_t, h_t), again with links as of time t.
+// Each chain is a fraction of the interleaved one, and the climb leaves the serial part altogether.
+// Scratch: h_t in the `head` array and orig in the `next` array of the block (both unused until the tour
+// of the one-thread form, which the split form does not use: its tour runs in shared memory).
+SAM_HD void euler_extend_words(EulerBlock<uint16_t>& B, const uint32_t* kw, uint32_t T) {
+    constexpr uint32_t NIL = 0xFFFFu;
+    Node<uint16_t>* N = B.N;
+    uint16_t* half = reinterpret_cast<uint16_t*>(N);   // field f of state s at half[4 * s + f]
+    uint16_t* orig = B.next;
+    const uint32_t cap = node_capacity(T);
+    for (uint32_t wd = 0; wd < (cap + 31) / 32; ++wd) B.clone_bits[wd] = 0;
+    store_words(N, 0, 0xFFFFFFFFu, NIL);   // root: no children, no link, length 0
+    orig[0] = (uint16_t)NIL;
+    uint32_t u = 1, g = 0, gmax = 0, gfail = NIL;
+    NodeWords ne;                           // the words of state gfail, where the next extend starts (never loaded)
+    ne.x = 0xFFFFFFFFu; ne.y = NIL;
+    uint32_t kword = 0;
+    for (uint32_t i = 0; i < T; ++i) {
+        if ((i & 31u) == 0) kword = kw[i >> 5];
+        const uint32_t kb = kword & 1u, ks = kb << 4;
+        kword >>= 1;
+        const uint32_t j = u++;
+        const uint32_t child_mask = ~(0xFFFFu << ks);
+        half[4 * g + kb] = (uint16_t)j;   // g has no children yet
+        orig[j] = (uint16_t)NIL;
+        uint32_t p = gfail, d = NIL, jfail = 0, pml = 0;
+        NodeWords n = ne;                  // gfail == NIL (first step only): the root's words, for the case below
+        while (p != NIL) {
+            d = (n.x >> ks) & 0xFFFFu;
+            pml = n.y >> 16;
+            if (d != NIL) break;
+            half[4 * p + kb] = (uint16_t)j;
+            const uint32_t up = n.y & 0xFFFFu;
+            if (up == NIL) break;           // p is the root and has its new child: keep its words in n
+            p = up;
+            n = load_words(N, p);
+        }
+        if (d != NIL) {
+            const NodeWords nd = load_words(N, d);
+            if (pml + 1u == (nd.y >> 16)) {
+                jfail = d;
+                ne = nd;
+            } else {
+                const uint32_t b = u++;
+                ne.x = nd.x;                // the clone copies every field of d
+                ne.y = (nd.y & 0xFFFFu) | ((pml + 1u) << 16);
+                store_words(N, b, ne.x, ne.y);
+                orig[b] = (uint16_t)d;
+                half[4 * d + 2] = (uint16_t)b;
+                jfail = b;
+                B.clone_bits[b >> 5] |= 1u << (b & 31);
+                for (;;) {                  // p still has d as its child: redirect it, then go on up
+                    half[4 * p + kb] = (uint16_t)b;
+                    p = n.y & 0xFFFFu;
+                    if (p == NIL) break;
+                    n = load_words(N, p);
+                    if (((n.x >> ks) & 0xFFFFu) != d) break;
+                }
+            }
+        } else {
+            jfail = 0;                      // the walk ran out at the root, whose words are n with its new child
+            ne.x = (n.x & child_mask) | (j << ks);
+            ne.y = n.y;
+        }
+        gmax += 1;
+        store_words(N, j, 0xFFFFFFFFu, jfail | (gmax << 16));
+        g = j; gfail = jfail;
+        B.jid[i] = (uint16_t)j;
+    }
+    B.meta[0] = u;
+}
+
+// child `c` (a raw field of the final automaton) as it was when only states below `lim` existed
+SAM_HD uint32_t child_as_of(const uint16_t* orig, uint32_t c, uint32_t lim) {
+    while (c != 0xFFFFu && c >= lim) c = orig[c];
+    return c;
+}
+// the same for a suffix link: the nearest ancestor below `lim`
+SAM_HD uint32_t link_as_of(const Node<uint16_t>* N, uint32_t f, uint32_t lim) {
+    while (f != 0xFFFFu && f >= lim) f = load_words(N, f).y & 0xFFFFu;
+    return f;
+}
+
+// The query walk of steps [t0, t1) from the state (w, h) held before step t0; writes (w_t, h_t) of a hit to
+// vq / head and NIL to vq for a miss, and returns the state after step t1 - 1 through w / h.
+SAM_HD void euler_walk_words(EulerBlock<uint16_t>& B, const uint32_t* qw, uint32_t t0, uint32_t t1, uint32_t& w,
+                             uint32_t& h) {
+    constexpr uint32_t NIL = 0xFFFFu;
+    const Node<uint16_t>* N = B.N;
+    const uint16_t* orig = B.next;
+    uint16_t* hq = B.head;
+    NodeWords nw = load_words(N, w);
+    uint32_t qword = t0 < t1 ? qw[t0 >> 5] >> (t0 & 31u) : 0u;
+    for (uint32_t i = t0; i < t1; ++i) {
+        if ((i & 31u) == 0) qword = qw[i >> 5];
+        const uint32_t qs = (qword & 1u) << 4;
+        qword >>= 1;
+        const uint32_t lim = B.jid[i];
+        uint32_t x = h, c;
+        NodeWords n = nw;
+        for (;;) {
+            c = child_as_of(orig, (n.x >> qs) & 0xFFFFu, lim);
+            if (c != NIL) break;
+            const uint32_t ml = n.y >> 16;
+            if (x > ml) x = ml;
+            const uint32_t p = link_as_of(N, n.y & 0xFFFFu, lim);
+            if (p == NIL) break;
+            n = load_words(N, p);
+        }
+        if (c == NIL) {
+            w = 0; h = 0;
+            B.vq[i] = (uint16_t)NIL;
+            nw = load_words(N, 0);
+        } else {
+            w = c; h = x + 1u;
+            B.vq[i] = (uint16_t)c;
+            hq[i] = (uint16_t)h;
+            nw = load_words(N, c);
+        }
+    }
+}
+
+// The state step t reads `last` from (src/rosa.rs:120-128), from the walk's (w_t, h_t): up the links as of
+// time t while the link's strings are still long enough; only the root has length 0 and is skipped.
+SAM_HD uint32_t euler_climb_words(const Node<uint16_t>* N, uint32_t w, uint32_t h, uint32_t lim) {
+    constexpr uint32_t NIL = 0xFFFFu;
+    if (w == NIL) return NIL;
+    uint32_t v = w;
+    NodeWords nv = load_words(N, v);
+    for (;;) {
+        const uint32_t f = link_as_of(N, nv.y & 0xFFFFu, lim);
+        if (f == NIL) break;
+        const NodeWords nf = load_words(N, f);
+        if ((nf.y >> 16) < h) break;
+        v = f; nv = nf;
+    }
+    return (nv.y >> 16) == 0 ? NIL : v;
+}
+
+// The three parts one after the other (what the split kernels compute together): same vq / jid / states as
+// euler_pass1_words.
+SAM_HD uint32_t euler_pass1_split(EulerBlock<uint16_t>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T) {
+    euler_extend_words(B, kw, T);
+    uint32_t w = 0, h = 0;
+    euler_walk_words(B, qw, 0, T, w, h);
+    for (uint32_t t = 0; t < T; ++t)
+        B.vq[t] = (uint16_t)euler_climb_words(B.N, B.vq[t], B.head[t], B.jid[t]);
+    return B.meta[0];
+}
+
 // tour: children lists, then a preorder walk; every state gets the half-open
 // rank range of the stamped (non-clone, non-root) states in its subtree
 template <typename Ix>
