@@ -114,6 +114,12 @@ ULLIS_CUDA_API int32_t ullis_cuda_runtime_kernel_names(ullis_cuda_runtime* rt, c
  * No counterpart in the reference, which runs every stream through RosaSam.  Synchronises. */
 ULLIS_CUDA_API int32_t ullis_cuda_runtime_sam_counts(ullis_cuda_runtime* rt, uint64_t* total, uint64_t* automaton,
                                                      uint64_t* constant_q);
+/* Error-path self-test: one small kernel waits - with the bounded mbarrier wait that every tensor-core kernel of
+ * the library uses, cut to `polls` polls (1..2^20) - on a barrier nothing ever arrives on, gives up, returns by
+ * itself and reports through the device status words.  The expected result is ULLIS_CUDA_ERR_TIMEOUT with
+ * "a kernel gave up waiting" as the message; the runtime stays usable.  The reference's counterpart of the path
+ * is the command-buffer error check after waitUntilCompleted (src/metal.rs:736-738). */
+ULLIS_CUDA_API int32_t ullis_cuda_runtime_wait_selftest(ullis_cuda_runtime* rt, uint32_t polls);
 /* Compute capability check: 1 when the device is sm_100 class. */
 ULLIS_CUDA_API int32_t ullis_cuda_runtime_is_sm100(const ullis_cuda_runtime* rt);
 

@@ -254,3 +254,17 @@ def test_fp16_operand_range_is_reported_not_turned_into_inf(cuda_rt):
         cuda_rt.set_mode(cuda.MODE_FAST)
     y = cuda_rt.fp16_linear(np.ones((rows, K), np.float32), w, rows, K, N)   # the runtime is usable afterwards
     assert np.isfinite(y).all()
+
+
+def test_a_device_wait_that_runs_out_is_reported_and_the_runtime_stays_usable(cuda_rt):
+    """Nothing ever arrives on the barrier the self-test kernel waits on: the bounded wait gives up after the
+    requested polls, the kernel returns by itself, the status word carries the time-out to the host as
+    ERR_TIMEOUT, and the next call on the same runtime works (no fault, no hang, no lost context)."""
+    with pytest.raises(cuda.UllisCudaError) as e:
+        cuda_rt.wait_selftest(2000)
+    assert e.value.code == cuda.ERR_TIMEOUT and "gave up waiting" in e.value.message and "99" in e.value.message
+    x = np.arange(8, dtype=np.float32)
+    assert np.array_equal(cuda_rt.residual_add(x, x), 2 * x)      # the status words were cleared; the context lives
+    with pytest.raises(cuda.UllisCudaError) as e:
+        cuda_rt.wait_selftest(0)
+    assert e.value.code == cuda.ERR_ARG

@@ -114,7 +114,9 @@ ullis_cuda_runtime* ullis_cuda_runtime::child(size_t i) {
     c->sam_coop_threads = sam_coop_threads;
     c->sam_words = sam_words;
     c->sam_split = sam_split;
+    c->sam_walk_chunked = sam_walk_chunked;
     c->sam_budget_bytes = sam_budget_bytes / (children.size() + 1);
+    c->tc_fix_list = tc_fix_list;
     c->tc_stages = tc_stages;
     c->tc_stages2 = tc_stages2;
     c->tc_ws2_min_rows = tc_ws2_min_rows;
@@ -287,6 +289,8 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         }
         if (const char* env = getenv("ULLIS_CUDA_SAM_SPARSE")) rt->sam_sparse_per_sm = (uint32_t)std::max(0, atoi(env));
         if (const char* env = getenv("ULLIS_CUDA_SAM_WORDS")) rt->sam_words = atoi(env) != 0;
+        if (const char* env = getenv("ULLIS_CUDA_FIX_LIST")) rt->tc_fix_list = atoi(env) != 0;
+        if (const char* env = getenv("ULLIS_CUDA_SAM_WALK_CHUNKED")) rt->sam_walk_chunked = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_SPLIT")) rt->sam_split = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_SIDE")) rt->sam_side = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_LANES")) rt->lanes = std::min(16, std::max(1, atoi(env)));
@@ -418,6 +422,16 @@ int32_t ullis_cuda_runtime_sam_counts(ullis_cuda_runtime* rt, uint64_t* total, u
         if (total) *total = sum[0];
         if (automaton) *automaton = sum[1];
         if (constant_q) *constant_q = sum[2];
+    });
+}
+
+int32_t ullis_cuda_runtime_wait_selftest(ullis_cuda_runtime* rt, uint32_t polls) {
+    return guard(rt, [&] {
+        if (polls == 0 || polls > (1u << 20)) fail(ULLIS_CUDA_ERR_ARG, "polls must be in 1..2^20");
+        rt->clear_status();
+        tc::wait_selftest(rt, polls);
+        rt->check_status();   // throws ULLIS_CUDA_ERR_TIMEOUT: that is the expected outcome
+        fail(ULLIS_CUDA_ERR_DEVICE_CHECK, "the wait did not time out");
     });
 }
 

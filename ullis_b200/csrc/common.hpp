@@ -102,6 +102,7 @@ struct ullis_cuda_runtime {
     int sam_coop_threads = 0;           // threads per stream in the tour / pass 2 kernel (256, 512, 1024); 0 = from the shared memory a stream needs
     bool sam_words = true;              // pass 1 on packed state words (sam_core.cuh euler_pass1_words); false: the field-wise form
     bool sam_split = true;              // pass 1 as two kernels, extend chain then query walk, and the climb inside the tour kernel
+    bool sam_walk_chunked = true;       // the query walk of the split form with eight lanes per stream (guessed pieces, then put right)
     int sam_lanes = 4;                  // streams carried per warp by the suffix-automaton kernel (1,2,4,...,32)
     uint64_t launches = 0;
     std::string last_error;
@@ -119,6 +120,7 @@ struct ullis_cuda_runtime {
     size_t tc_ws2_min_rows = 4096;      // fewer rows than this stay with the single-CTA form (more, smaller row tiles)
     int tc_ws2_dense_clusters[2] = {0, 0};      // the same for dense weights (store, residual)
     int tc_ws2_clusters[5] = {0, 0, 0, 0, 0};   // CTA pairs of that kernel the device holds at once, per epilogue
+    bool tc_fix_list = true;            // exact sign recomputation from a compact list of the flagged outputs (one thread each)
     int tc_ready = 0;                   // 0 = not probed, 1 = usable, -1 = unusable on this device
     ullis::NcclState* nccl = nullptr;
 

@@ -155,6 +155,101 @@ emit_f16_kernel(const uint32_t* __restrict__ idx_sw, const uint16_t* __restrict_
     }
 }
 
+// Exact pre-activation sign of one output of a packed linear over the time-shift mix of x, as the reference
+// computes it (src/model.rs:1291-1298 then 724-742): in_i = x_i + (x[t-1]_i - x_i) * mix_i (unfused), the sum of
+// +/- in_i for i ascending in f32, then bias + scale * sum.  R inputs per round: the 2R/4 row loads of a round go
+// out together, then the sum is taken in order.
+template <int R>
+__device__ __forceinline__ bool exact_mixed_sign(const float* __restrict__ xr, bool first_step,
+                                                 const uint16_t* __restrict__ mix, const uint32_t* __restrict__ wbits,
+                                                 float scale, float bias, size_t C) {
+    float sum = 0.0f;
+    for (size_t i0 = 0; i0 < C; i0 += R) {
+        float4 cur[R / 4], prev[R / 4];
+#pragma unroll
+        for (int u = 0; u < R / 4; ++u) {
+            cur[u] = *reinterpret_cast<const float4*>(xr + i0 + 4 * u);
+            prev[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (!first_step) prev[u] = *reinterpret_cast<const float4*>(xr - C + i0 + 4 * u);
+        }
+        const uint32_t wword = wbits[i0 >> 5] >> (i0 & 31);
+#pragma unroll
+        for (int u = 0; u < R / 4; ++u) {
+            const float xs[4] = {cur[u].x, cur[u].y, cur[u].z, cur[u].w};
+            const float ps[4] = {prev[u].x, prev[u].y, prev[u].z, prev[u].w};
+            const uint2 mw = *reinterpret_cast<const uint2*>(mix + i0 + 4 * u);
+            const uint16_t mb[4] = {(uint16_t)(mw.x & 0xFFFFu), (uint16_t)(mw.x >> 16), (uint16_t)(mw.y & 0xFFFFu),
+                                    (uint16_t)(mw.y >> 16)};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float xt = xs[k];
+                const float xx = first_step ? -xt : __fsub_rn(ps[k], xt);
+                const float in = __fadd_rn(xt, __fmul_rn(xx, h2f(mb[k])));
+                sum = __fmaf_rn((wword >> (4 * u + k)) & 1u ? 1.0f : -1.0f, in, sum);
+            }
+        }
+    }
+    return __fadd_rn(bias, __fmul_rn(scale, sum)) > 0.0f;
+}
+
+// The flagged outputs of one Q/K/V launch as a compact list, so that the exact recomputation runs with one thread
+// per flagged output over the whole device instead of a few busy threads per window.  An entry is the position of
+// the flag bit: (index of the flag word among the 3 * sw words of the launch) * 32 + bit.  More flags than the
+// list holds (never on realistic inputs: the list takes one output in 64) raise `ctrl[1]`, and the window kernel
+// below then redoes the whole launch.
+__global__ void __launch_bounds__(256)
+fix_collect_kernel(const uint32_t* __restrict__ flags, size_t words, uint32_t* __restrict__ list, uint32_t cap,
+                   uint32_t* __restrict__ ctrl) {
+    for (size_t w0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; w0 < words; w0 += (size_t)gridDim.x * blockDim.x * 4) {
+        uint32_t f[4] = {0, 0, 0, 0};
+        if (w0 + 4 <= words) {
+            const uint4 v = *reinterpret_cast<const uint4*>(flags + w0);
+            f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+        } else {
+            for (int k = 0; k < 4; ++k) f[k] = w0 + k < words ? flags[w0 + k] : 0u;
+        }
+        const uint32_t n = __popc(f[0]) + __popc(f[1]) + __popc(f[2]) + __popc(f[3]);
+        if (n == 0) continue;
+        uint32_t at = atomicAdd(&ctrl[0], n);
+        if (at + n > cap) {
+            ctrl[1] = 1u;
+            continue;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            uint32_t g = f[k];
+            while (g) {
+                const uint32_t tt = __ffs(g) - 1;
+                g &= g - 1;
+                list[at++] = (uint32_t)(w0 + k) * 32u + tt;
+            }
+        }
+    }
+}
+
+constexpr int FIXQ_THREADS = 128;
+
+__global__ void __launch_bounds__(FIXQ_THREADS, 8)
+fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, const uint16_t* __restrict__ mk,
+                 const uint16_t* __restrict__ mv, PackedWeights wq, PackedWeights wk, PackedWeights wv,
+                 uint32_t* __restrict__ bq, uint32_t* __restrict__ bk, uint32_t* __restrict__ bv,
+                 const uint32_t* __restrict__ list, uint32_t cap, const uint32_t* __restrict__ ctrl, size_t sw, size_t T,
+                 size_t C, size_t wps) {
+    if (ctrl[1]) return;   // the list overflowed: the window kernel redoes everything
+    const uint32_t count = min(ctrl[0], cap);
+    for (uint32_t i = blockIdx.x * FIXQ_THREADS + threadIdx.x; i < count; i += gridDim.x * FIXQ_THREADS) {
+        const uint32_t entry = list[i], tt = entry & 31u;
+        const size_t wi = entry >> 5, m = wi / sw, rem = wi % sw;
+        const size_t s = rem / wps, word = rem % wps, b = s / C, ch = s % C, t = word * 32 + tt;
+        const uint16_t* mix = m == 0 ? mq : m == 1 ? mk : mv;
+        const PackedWeights& W = m == 0 ? wq : m == 1 ? wk : wv;
+        uint32_t* bits = m == 0 ? bq : m == 1 ? bk : bv;
+        const bool plus = exact_mixed_sign<16>(x + (b * T + t) * C, t == 0, mix, W.bits + (ch * C >> 5), h2f(W.scale[ch]),
+                                               W.bias ? h2f(W.bias[ch]) : 0.0f, C);
+        if (plus) atomicOr(&bits[rem], 1u << tt); else atomicAnd(&bits[rem], ~(1u << tt));
+    }
+}
+
 // Sign bits whose tensor-core pre-activation fell inside the error band are
 // recomputed exactly as the reference does (src/model.rs:724-742 on the
 // time-shift mix of x): sequential f32 sum over i, then bias + scale*sum.
@@ -171,7 +266,8 @@ sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, 
                   const uint16_t* __restrict__ mv, PackedWeights wq, PackedWeights wk, PackedWeights wv,
                   uint32_t* __restrict__ bq, uint32_t* __restrict__ bk, uint32_t* __restrict__ bv,
                   const uint32_t* __restrict__ fq, const uint32_t* __restrict__ fk, const uint32_t* __restrict__ fv,
-                  size_t batch, size_t T, size_t C, size_t wps) {
+                  size_t batch, size_t T, size_t C, size_t wps, const uint32_t* __restrict__ only_if) {
+    if (only_if && *only_if == 0u) return;   // the compact list took every flag: nothing left for the windows
     extern __shared__ uint32_t fix_queue[];  // entries: matrix << 28 | channel << 8 | word in window << 5 | bit
     __shared__ uint32_t q_count, announced;   // entries queued; flag bits announced so far (never reset)
     const size_t windows = (wps + FIX_WIN - 1) / FIX_WIN;
@@ -196,35 +292,8 @@ sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, 
             const uint16_t* wbias = m == 0 ? wq.bias : m == 1 ? wk.bias : wv.bias;
             uint32_t* bits = m == 0 ? bq : m == 1 ? bk : bv;
             const uint32_t* wbits = wb + (ch * C >> 5);  // C % 32 == 0 on this path
-            float sum = 0.0f;
-            // 32 inputs per round: the sixteen row loads go out together, then the sum is taken in order
-            for (size_t i0 = 0; i0 < C; i0 += 32) {
-                float4 cur[8], prev[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    cur[u] = *reinterpret_cast<const float4*>(xr + i0 + 4 * u);
-                    prev[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (t != 0) prev[u] = *reinterpret_cast<const float4*>(xr - C + i0 + 4 * u);
-                }
-                const uint32_t wword = wbits[i0 >> 5];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const float xs[4] = {cur[u].x, cur[u].y, cur[u].z, cur[u].w};
-                    const float ps[4] = {prev[u].x, prev[u].y, prev[u].z, prev[u].w};
-                    const uint2 mw = *reinterpret_cast<const uint2*>(mix + i0 + 4 * u);
-                    const uint16_t mb[4] = {(uint16_t)(mw.x & 0xFFFFu), (uint16_t)(mw.x >> 16), (uint16_t)(mw.y & 0xFFFFu),
-                                            (uint16_t)(mw.y >> 16)};
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const float xt = xs[k];
-                        const float xx = t == 0 ? -xt : __fsub_rn(ps[k], xt);
-                        const float in = __fadd_rn(xt, __fmul_rn(xx, h2f(mb[k])));
-                        sum = __fmaf_rn((wword >> (4 * u + k)) & 1u ? 1.0f : -1.0f, in, sum);
-                    }
-                }
-            }
-            const float y = __fadd_rn(wbias ? h2f(wbias[ch]) : 0.0f, __fmul_rn(h2f(wscale[ch]), sum));
-            if (y > 0.0f) atomicOr(&bits[ew], 1u << tt); else atomicAnd(&bits[ew], ~(1u << tt));
+            const bool plus = exact_mixed_sign<32>(xr, t == 0, mix, wbits, h2f(wscale[ch]), wbias ? h2f(wbias[ch]) : 0.0f, C);
+            if (plus) atomicOr(&bits[ew], 1u << tt); else atomicAnd(&bits[ew], ~(1u << tt));
         }
         __syncthreads();
         if (threadIdx.x == 0) q_count = 0;
@@ -612,8 +681,22 @@ bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeig
         p.prob[z] = GemmProblem{W[z]->bits, W[z]->scale, W[z]->bias, outs[z], flags + z * sw, s1 + z * rows};
     launch<EPI_SIGNBITS, true>(rt, maps, p, 3, "gemm_qkv_signbits");
     const unsigned grid = (unsigned)(((wps + FIX_WIN - 1) / FIX_WIN) * batch);   // rows < 2^30, so this fits
+    const uint32_t* only_if = nullptr;
+    if (rt->tc_fix_list && 3 * sw < ((size_t)1 << 27)) {
+        // one thread per flagged output, from a compact list; room for one output in 64
+        const size_t cap = std::max<size_t>(65536, 3 * sw * 32 / 64);
+        uint32_t* ctrl = rt->tc_ws[9].as<uint32_t>(2 + cap);
+        uint32_t* list = ctrl + 2;
+        rt->zero(ctrl, 8);
+        fix_collect_kernel<<<2 * (unsigned)rt->sm_count, 256, 0, rt->stream>>>(flags, 3 * sw, list, (uint32_t)cap, ctrl);
+        rt->launched("fix_collect");
+        fix_apply_kernel<<<8 * (unsigned)rt->sm_count, FIXQ_THREADS, 0, rt->stream>>>(
+            ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, list, (uint32_t)cap, ctrl, sw, time, d, wps);
+        rt->launched("fix_apply");
+        only_if = ctrl + 1;
+    }
     sign_fixup_kernel<<<grid, FIX_THREADS, FIX_QUEUE * 4, rt->stream>>>(ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, flags,
-                                                   flags + sw, flags + 2 * sw, batch, time, d, wps);
+                                                   flags + sw, flags + 2 * sw, batch, time, d, wps, only_if);
     rt->launched("sign_fixup");
     return true;
 }
@@ -661,6 +744,27 @@ bool cmix_residual(ullis_cuda_runtime* rt, const LayerWeights& L, float* x, size
     pv.prob[0] = GemmProblem{nullptr, nullptr, nullptr, x, nullptr, nullptr};
     launch<EPI_RESIDUAL, false>(rt, maps, pv, 1, "gemm_value_residual");
     return true;
+}
+
+namespace {
+// One CTA waits, with the bounded mbarrier wait every tensor-core kernel here uses, on a barrier that nothing
+// ever arrives on, and reports the give-up through the runtime's status words like those kernels do.
+__global__ void wait_selftest_kernel(uint32_t polls, uint32_t* status) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1);
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !ptx::mbar_wait(&bar, 0, polls)) {
+        if (atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_WAIT_TIMEOUT) == ULLIS_DEV_OK) status[1] = 99u;   // site: self-test
+    }
+}
+}  // namespace
+
+void wait_selftest(ullis_cuda_runtime* rt, uint32_t polls) {
+    wait_selftest_kernel<<<1, 32, 0, rt->stream>>>(polls, rt->dev_status);
+    rt->launched("wait_selftest");
 }
 
 bool takes_model(ullis_cuda_runtime* rt, size_t rows, size_t time, size_t d, size_t ffn, size_t vocab) {

@@ -30,6 +30,10 @@ bool cmix_residual(ullis_cuda_runtime* rt, const LayerWeights& L, float* x, size
 bool head_ce(ullis_cuda_runtime* rt, const float* hidden, const PackedWeights& head, const uint32_t* labels,
              uint32_t ignore_id, size_t rows, size_t time, size_t d, size_t vocab, float* row_loss);
 
+// Makes a bounded device wait run out on purpose (a barrier nothing arrives on, `polls` polls): the kernel
+// returns by itself and leaves ULLIS_DEV_WAIT_TIMEOUT in the runtime's status words.
+void wait_selftest(ullis_cuda_runtime* rt, uint32_t polls);
+
 // True when every stage above takes a model of these dimensions at `rows` rows per call (so that a forward
 // can count on none of the CUDA-core fall-backs, which share buffers, being reached).
 bool takes_model(ullis_cuda_runtime* rt, size_t rows, size_t time, size_t d, size_t ffn, size_t vocab);

@@ -151,7 +151,39 @@ rosa_walk_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uin
     const size_t s = list[first + item];
     sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
     uint32_t w = 0, h = 0;
-    sam::euler_walk_words(B, q_sw + s * wps, 0, T, w, h);
+    sam::euler_walk_words<false>(B, q_sw + s * wps, 0, T, w, h);
+}
+
+// The query walk with eight lanes per stream (sam_core.cuh euler_walk_chunked): each lane first walks an eighth of
+// the steps from the guessed state "no match", all at once; then the pieces are put right one after the other,
+// each from the true end state of the piece before it, which takes a few steps where matches are short.  Four
+// streams per warp.  A lane only ever reads the records it wrote itself.
+__global__ void __launch_bounds__(128, 16)
+rosa_walk_chunked_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
+                         const uint32_t* __restrict__ list, const uint32_t* __restrict__ count, size_t first, size_t wave,
+                         uint32_t T, size_t wps) {
+    const int lane = threadIdx.x & 31, group = lane >> 3, c = lane & 7;
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const size_t item = warp * 4 + group;
+    if (item >= wave || first + item >= *count) return;   // the eight lanes of a group leave together
+    const size_t s = list[first + item];
+    sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
+    const uint32_t* qw = q_sw + s * wps;
+    const uint32_t piece = (((T + 7u) >> 3) + 31u) & ~31u;
+    const uint32_t t0 = min((uint32_t)c * piece, T), t1 = min(t0 + piece, T);
+    uint32_t w = 0, h = 0;
+    sam::euler_walk_words<false>(B, qw, t0, t1, w, h);
+    const unsigned mask = 0xFFu << (8 * group);
+    for (int k = 1; k < 8; ++k) {
+        const uint32_t pw = __shfl_sync(mask, w, (lane & ~7) + k - 1), ph = __shfl_sync(mask, h, (lane & ~7) + k - 1);
+        if (c != k) continue;
+        if (t0 >= t1) {           // an empty piece hands the state on
+            w = pw; h = ph;
+        } else {
+            uint32_t tw = pw, th = ph;
+            if (sam::euler_walk_words<true>(B, qw, t0, t1, tw, th) == t1) { w = tw; h = th; }   // never met: its own end state
+        }
+    }
 }
 
 template <int NT, bool SPLIT = false>
@@ -287,8 +319,13 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
                 rosa_extend_kernel<<<p1_grid, 128, 0, rt->stream>>>(scratch, stride, k_sw, list, count, s0, n,
                                                                    (uint32_t)time, wps, pass1_lanes, dense, sparse);
                 rt->launched("rosa_extend");
-                rosa_walk_kernel<<<p1_grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, list, count, s0, n,
-                                                                 (uint32_t)time, wps, pass1_lanes, dense, sparse);
+                if (rt->sam_walk_chunked) {
+                    rosa_walk_chunked_kernel<<<(unsigned)(((n + 3) / 4 * 32 + 127) / 128), 128, 0, rt->stream>>>(
+                        scratch, stride, q_sw, list, count, s0, n, (uint32_t)time, wps);
+                } else {
+                    rosa_walk_kernel<<<p1_grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, list, count, s0, n,
+                                                                     (uint32_t)time, wps, pass1_lanes, dense, sparse);
+                }
                 rt->launched("rosa_walk");
             } else {
                 rosa_pass1_kernel<<<p1_grid, 128, 0, rt->stream>>>(

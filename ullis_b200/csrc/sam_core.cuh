@@ -645,9 +645,14 @@ SAM_HD uint32_t link_as_of(const Node<uint16_t>* N, uint32_t f, uint32_t lim) {
 }
 
 // The query walk of steps [t0, t1) from the state (w, h) held before step t0; writes (w_t, h_t) of a hit to
-// vq / head and NIL to vq for a miss, and returns the state after step t1 - 1 through w / h.
-SAM_HD void euler_walk_words(EulerBlock<uint16_t>& B, const uint32_t* qw, uint32_t t0, uint32_t t1, uint32_t& w,
-                             uint32_t& h) {
+// vq / head and NIL to vq for a miss, and returns the state after its last step through w / h.
+// UNTIL_SAME: the records of these steps already hold a walk from a GUESSED start state; this walk, from the
+// true one, stops at the first step whose state equals the recorded one - from there on the two walks are the
+// same walk (the next state is a function of the state, the bit and the step alone) - and returns that step
+// (t1 if the walks never met).  Without it the return value is t1.
+template <bool UNTIL_SAME>
+SAM_HD uint32_t euler_walk_words(EulerBlock<uint16_t>& B, const uint32_t* qw, uint32_t t0, uint32_t t1, uint32_t& w,
+                                 uint32_t& h) {
     constexpr uint32_t NIL = 0xFFFFu;
     const Node<uint16_t>* N = B.N;
     const uint16_t* orig = B.next;
@@ -672,14 +677,40 @@ SAM_HD void euler_walk_words(EulerBlock<uint16_t>& B, const uint32_t* qw, uint32
         }
         if (c == NIL) {
             w = 0; h = 0;
+            if (UNTIL_SAME && B.vq[i] == NIL) return i;
             B.vq[i] = (uint16_t)NIL;
             nw = load_words(N, 0);
         } else {
             w = c; h = x + 1u;
+            if (UNTIL_SAME && B.vq[i] == c && hq[i] == h) return i;
             B.vq[i] = (uint16_t)c;
             hq[i] = (uint16_t)h;
             nw = load_words(N, c);
         }
+    }
+    return t1;
+}
+
+// The whole walk in `chunks` pieces, the way a group of lanes runs it: every piece first walks from the guessed
+// state "no match" (the true one for piece 0), all pieces at once; then piece after piece is redone from the true
+// end state of the piece before it until it meets its guessed walk - after a few steps on streams whose matches
+// are short, after the whole piece at worst.  `piece` = steps per piece (a multiple of 32 keeps whole bit words).
+SAM_HD void euler_walk_chunked(EulerBlock<uint16_t>& B, const uint32_t* qw, uint32_t T, uint32_t piece) {
+    const uint32_t chunks = (T + piece - 1) / piece;
+    uint32_t w = 0, h = 0;              // true state at the end of the piece before the current one
+    for (uint32_t c = 0; c < chunks; ++c) {   // on the device: all pieces at once, one lane each
+        uint32_t gw = 0, gh = 0;
+        const uint32_t t0 = c * piece, t1 = t0 + piece < T ? t0 + piece : T;
+        euler_walk_words<false>(B, qw, t0, t1, gw, gh);
+        if (c == 0) { w = gw; h = gh; }
+    }
+    for (uint32_t c = 1; c < chunks; ++c) {
+        const uint32_t t0 = c * piece, t1 = t0 + piece < T ? t0 + piece : T;
+        // the guessed walk's end state: its last record
+        uint32_t ew = B.vq[t1 - 1] == 0xFFFFu ? 0u : B.vq[t1 - 1], eh = B.vq[t1 - 1] == 0xFFFFu ? 0u : B.head[t1 - 1];
+        uint32_t tw = w, th = h;
+        const uint32_t met = euler_walk_words<true>(B, qw, t0, t1, tw, th);
+        if (met < t1) { w = ew; h = eh; } else { w = tw; h = th; }
     }
 }
 
@@ -705,7 +736,17 @@ SAM_HD uint32_t euler_climb_words(const Node<uint16_t>* N, uint32_t w, uint32_t 
 SAM_HD uint32_t euler_pass1_split(EulerBlock<uint16_t>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T) {
     euler_extend_words(B, kw, T);
     uint32_t w = 0, h = 0;
-    euler_walk_words(B, qw, 0, T, w, h);
+    euler_walk_words<false>(B, qw, 0, T, w, h);
+    for (uint32_t t = 0; t < T; ++t)
+        B.vq[t] = (uint16_t)euler_climb_words(B.N, B.vq[t], B.head[t], B.jid[t]);
+    return B.meta[0];
+}
+
+// The same with the walk in pieces of `piece` steps (euler_walk_chunked).
+SAM_HD uint32_t euler_pass1_split_chunked(EulerBlock<uint16_t>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T,
+                                          uint32_t piece) {
+    euler_extend_words(B, kw, T);
+    euler_walk_chunked(B, qw, T, piece);
     for (uint32_t t = 0; t < T; ++t)
         B.vq[t] = (uint16_t)euler_climb_words(B.N, B.vq[t], B.head[t], B.jid[t]);
     return B.meta[0];

@@ -165,9 +165,17 @@ gemm_ws2_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p, const
                 }
             }
             if (!ok && rank == 0) {
-                // leave no copy in flight: wait (bounded) for every stage this thread filled last
+                // leave no copy in flight: wait (bounded) for every stage this thread filled last (both CTAs'
+                // bytes of a stage are counted on these barriers)
                 const uint32_t first = it > STAGES ? it - STAGES : 0;
                 for (uint32_t k = first; k < it; ++k) ptx::mbar_wait(&full[k % STAGES], (k / STAGES) & 1u);
+            }
+            if (!ok && rank == 1) {
+                // The odd CTA's copies complete on the even CTA's barriers, which it cannot poll.  A copy it
+                // issued goes into a stage the MMAs had released and lands within microseconds; the wait that
+                // failed just before took about a second.  Give the last ones far longer than they need
+                // before this CTA may leave (the cluster barrier below comes after).
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
             }
         }
     } else if (warp == 1) {

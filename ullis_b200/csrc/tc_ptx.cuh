@@ -54,9 +54,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait (~ a second at worst); false = gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+// Bounded wait (~ a second at worst with the default number of polls); false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t polls = 1u << 24) {
+    for (uint32_t spin = 0; spin < polls; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
         if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
     }

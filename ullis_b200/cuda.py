@@ -52,7 +52,7 @@ ABI_SYMBOLS = (
     "ullis_cuda_binary_linear", "ullis_cuda_fp16_linear", "ullis_cuda_sign_pack_bits", "ullis_cuda_cmix_relu2",
     "ullis_cuda_residual_add", "ullis_cuda_rosa_qkv_1bit_fwd", "ullis_cuda_rosa_block_forward",
     "ullis_cuda_cmix_block_forward", "ullis_cuda_streamed_ce", "ullis_cuda_rosa_sam_static",
-    "ullis_cuda_runtime_sam_counts", "ullis_cuda_model_read_loss_global", "ullis_cuda_dp_rendezvous",
+    "ullis_cuda_runtime_sam_counts", "ullis_cuda_runtime_wait_selftest", "ullis_cuda_model_read_loss_global", "ullis_cuda_dp_rendezvous",
     "ullis_cuda_dp_unique_id", "ullis_cuda_dp_init",
     "ullis_cuda_dp_allreduce_loss", "ullis_cuda_dp_finalize",
 )
@@ -402,6 +402,11 @@ class CudaRuntime:
                                           C.c_uint32(int(timeout_s * 1000)))
         if rc != OK:
             raise UllisCudaError(rc, lib.ullis_cuda_last_error(None).decode())
+
+    def wait_selftest(self, polls: int = 2000) -> None:
+        """Makes a bounded device wait run out (ullis_cuda_runtime_wait_selftest): always raises, ERR_TIMEOUT
+        when the error path works."""
+        self._check(self._lib.ullis_cuda_runtime_wait_selftest(self._h, C.c_uint32(polls)))
 
     def sam_counts(self) -> dict:
         """Streams of the last suffix-automaton call: total, through the automaton, through the constant-q form."""
