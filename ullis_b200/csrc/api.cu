@@ -117,6 +117,7 @@ ullis_cuda_runtime* ullis_cuda_runtime::child(size_t i) {
     c->sam_walk_chunked = sam_walk_chunked;
     c->sam_budget_bytes = sam_budget_bytes / (children.size() + 1);
     c->tc_fix_list = tc_fix_list;
+    c->tc_fuse_ln = tc_fuse_ln;
     c->tc_stages = tc_stages;
     c->tc_stages2 = tc_stages2;
     c->tc_ws2_min_rows = tc_ws2_min_rows;
@@ -289,6 +290,7 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         }
         if (const char* env = getenv("ULLIS_CUDA_SAM_SPARSE")) rt->sam_sparse_per_sm = (uint32_t)std::max(0, atoi(env));
         if (const char* env = getenv("ULLIS_CUDA_SAM_WORDS")) rt->sam_words = atoi(env) != 0;
+        if (const char* env = getenv("ULLIS_CUDA_FUSE_LN")) rt->tc_fuse_ln = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_FIX_LIST")) rt->tc_fix_list = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_WALK_CHUNKED")) rt->sam_walk_chunked = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_SPLIT")) rt->sam_split = atoi(env) != 0;

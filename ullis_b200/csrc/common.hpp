@@ -120,6 +120,7 @@ struct ullis_cuda_runtime {
     size_t tc_ws2_min_rows = 4096;      // fewer rows than this stay with the single-CTA form (more, smaller row tiles)
     int tc_ws2_dense_clusters[2] = {0, 0};      // the same for dense weights (store, residual)
     int tc_ws2_clusters[5] = {0, 0, 0, 0, 0};   // CTA pairs of that kernel the device holds at once, per epilogue
+    bool tc_fuse_ln = true;             // LayerNorm folded into the kernel that writes the 16-bit operands of the next GEMM
     bool tc_fix_list = true;            // exact sign recomputation from a compact list of the flagged outputs (one thread each)
     int tc_ready = 0;                   // 0 = not probed, 1 = usable, -1 = unusable on this device
     ullis::NcclState* nccl = nullptr;

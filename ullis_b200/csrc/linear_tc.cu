@@ -126,6 +126,108 @@ mix_split_kernel(const float* __restrict__ x, const uint16_t* __restrict__ m0, c
     }
 }
 
+// LayerNorm and mix_split_kernel in one pass over the residual stream: a warp normalises its row and the row
+// before it (the same arithmetic as the stand-alone warp LayerNorm, so both warps that need a row get the same
+// values), forms the mixes and writes the 16-bit operands; the LayerNorm output itself is only written when
+// something downstream reads it as f32 (`ln_out`: the exact sign fix-up).  Saves the round trip of the
+// LayerNorm output through HBM.  C = 128 * VEC channels, VEC <= 8.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+ln_mix_split_kernel(const float* __restrict__ x, const uint16_t* __restrict__ lw, const uint16_t* __restrict__ lb,
+                    float* __restrict__ ln_out, const uint16_t* __restrict__ m0, const uint16_t* __restrict__ m1,
+                    const uint16_t* __restrict__ m2, uint16_t* __restrict__ hi0, uint16_t* __restrict__ lo0,
+                    uint16_t* __restrict__ hi1, uint16_t* __restrict__ lo1, uint16_t* __restrict__ hi2,
+                    uint16_t* __restrict__ lo2, float* __restrict__ s1, size_t rows, size_t time) {
+    constexpr int C = 128 * VEC;
+    const int lane = threadIdx.x & 31;
+    const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const bool first = row % time == 0;
+    const uint2* w4 = reinterpret_cast<const uint2*>(lw);
+    const uint2* b4 = reinterpret_cast<const uint2*>(lb);
+    // normalised values of one row, in place
+    auto layer_norm_row = [&](float4 (&v)[VEC]) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mean = sum / (float)C;
+        float sq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            float a = v[i].x - mean, bb = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+            sq += (a * a + bb * bb) + (c * c + d * d);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        const float inv = 1.0f / sqrtf(sq / (float)C + 1e-5f);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const uint2 wb = w4[lane + 32 * i], bb = b4[lane + 32 * i];
+            v[i].x = (v[i].x - mean) * inv * h2f((uint16_t)(wb.x & 0xffff)) + h2f((uint16_t)(bb.x & 0xffff));
+            v[i].y = (v[i].y - mean) * inv * h2f((uint16_t)(wb.x >> 16)) + h2f((uint16_t)(bb.x >> 16));
+            v[i].z = (v[i].z - mean) * inv * h2f((uint16_t)(wb.y & 0xffff)) + h2f((uint16_t)(bb.y & 0xffff));
+            v[i].w = (v[i].w - mean) * inv * h2f((uint16_t)(wb.y >> 16)) + h2f((uint16_t)(bb.y >> 16));
+        }
+    };
+    float4 cur[VEC], prev[VEC];
+    const float4* src = reinterpret_cast<const float4*>(x + row * C);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        cur[i] = src[lane + 32 * i];
+        prev[i] = first ? make_float4(0.f, 0.f, 0.f, 0.f) : (src - C / 4)[lane + 32 * i];
+    }
+    layer_norm_row(cur);
+    if (!first) layer_norm_row(prev);   // `first` is the same for the whole warp
+    if (ln_out) {
+        float4* dst = reinterpret_cast<float4*>(ln_out + row * C);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) dst[lane + 32 * i] = cur[i];
+    }
+    const uint16_t* mix[3] = {m0, m1, m2};
+    uint16_t* hi[3] = {hi0, hi1, hi2};
+    uint16_t* lo[3] = {lo0, lo1, lo2};
+    float sum[3] = {0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        const size_t c = (size_t)(lane + 32 * i) * 4;
+        const float xt[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w}, pt[4] = {prev[i].x, prev[i].y, prev[i].z, prev[i].w};
+        float xx[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) xx[e] = first ? -xt[e] : __fsub_rn(pt[e], xt[e]);
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            if (!mix[k]) continue;
+            const uint2 mw = *reinterpret_cast<const uint2*>(mix[k] + c);
+            const uint16_t mb[4] = {(uint16_t)(mw.x & 0xFFFFu), (uint16_t)(mw.x >> 16), (uint16_t)(mw.y & 0xFFFFu),
+                                    (uint16_t)(mw.y >> 16)};
+            uint16_t hb[4], lbt[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float v = __fadd_rn(xt[e], __fmul_rn(xx[e], h2f(mb[e])));
+                const __half h = __float2half_rn(v);
+                hb[e] = __half_as_ushort(h);
+                lbt[e] = __half_as_ushort(__float2half_rn(v - __half2float(h)));
+                sum[k] += fabsf(v);
+            }
+            *reinterpret_cast<uint2*>(hi[k] + row * C + c) =
+                make_uint2(hb[0] | ((uint32_t)hb[1] << 16), hb[2] | ((uint32_t)hb[3] << 16));
+            if (lo[k])
+                *reinterpret_cast<uint2*>(lo[k] + row * C + c) =
+                    make_uint2(lbt[0] | ((uint32_t)lbt[1] << 16), lbt[2] | ((uint32_t)lbt[3] << 16));
+        }
+    }
+    if (s1) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            float s = sum[k];
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0 && mix[k]) s1[k * rows + row] = s;
+        }
+    }
+}
+
 // idx bits (stream-major) -> y = +/-e as FP16 [B*T, C] (reference src/model.rs:1313)
 // One CTA: 32 steps x 256 channels; a thread writes eight channels (16 bytes) of four steps.
 __global__ void __launch_bounds__(256)
@@ -194,34 +296,45 @@ __device__ __forceinline__ bool exact_mixed_sign(const float* __restrict__ xr, b
 
 // The flagged outputs of one Q/K/V launch as a compact list, so that the exact recomputation runs with one thread
 // per flagged output over the whole device instead of a few busy threads per window.  An entry is the position of
-// the flag bit: (index of the flag word among the 3 * sw words of the launch) * 32 + bit.  More flags than the
-// list holds (never on realistic inputs: the list takes one output in 64) raise `ctrl[1]`, and the window kernel
-// below then redoes the whole launch.
+// the flag bit: (index of the flag word among the 3 * sw words of the launch) * 32 + bit.  The list is built in
+// the order (sequence, block of 32 steps, matrix, channel), so that entries next to each other read the same few
+// rows of x: a warp takes one (sequence, block of steps, matrix) at a time and sweeps the channels, 32 flag words
+// per round, one append per round.  More flags than the list holds (never on realistic inputs: the list takes
+// one output in 64) raise `ctrl[1]`, and the window kernel below then redoes the whole launch.
 __global__ void __launch_bounds__(256)
-fix_collect_kernel(const uint32_t* __restrict__ flags, size_t words, uint32_t* __restrict__ list, uint32_t cap,
-                   uint32_t* __restrict__ ctrl) {
-    for (size_t w0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; w0 < words; w0 += (size_t)gridDim.x * blockDim.x * 4) {
-        uint32_t f[4] = {0, 0, 0, 0};
-        if (w0 + 4 <= words) {
-            const uint4 v = *reinterpret_cast<const uint4*>(flags + w0);
-            f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
-        } else {
-            for (int k = 0; k < 4; ++k) f[k] = w0 + k < words ? flags[w0 + k] : 0u;
-        }
-        const uint32_t n = __popc(f[0]) + __popc(f[1]) + __popc(f[2]) + __popc(f[3]);
-        if (n == 0) continue;
-        uint32_t at = atomicAdd(&ctrl[0], n);
-        if (at + n > cap) {
-            ctrl[1] = 1u;
-            continue;
-        }
+fix_collect_kernel(const uint32_t* __restrict__ flags, size_t sw, size_t batch, size_t C, size_t wps,
+                   uint32_t* __restrict__ list, uint32_t cap, uint32_t* __restrict__ ctrl) {
+    const int lane = threadIdx.x & 31;
+    const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const size_t buckets = batch * wps * 3;
+    for (size_t bk = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; bk < buckets; bk += warps) {
+        const size_t m = bk % 3, word = (bk / 3) % wps, b = bk / (3 * wps);
+        const size_t base = m * sw + b * C * wps + word;     // flag word of channel ch: base + ch * wps
+        for (size_t c0 = 0; c0 < C; c0 += 32) {
+            const size_t ch = c0 + lane;
+            const uint32_t f = ch < C ? flags[base + ch * wps] : 0u;
+            const uint32_t n = __popc(f);
+            uint32_t incl = n;                                 // inclusive prefix sum over the lanes
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            uint32_t g = f[k];
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+            if (total == 0) continue;
+            uint32_t at = 0;
+            if (lane == 31) at = atomicAdd(&ctrl[0], total);
+            at = __shfl_sync(0xffffffffu, at, 31);
+            if (at + total > cap) {
+                if (lane == 0) ctrl[1] = 1u;
+                continue;
+            }
+            at += incl - n;
+            uint32_t g = f;
             while (g) {
                 const uint32_t tt = __ffs(g) - 1;
                 g &= g - 1;
-                list[at++] = (uint32_t)(w0 + k) * 32u + tt;
+                list[at++] = (uint32_t)(base + ch * wps) * 32u + tt;
             }
         }
     }
@@ -229,6 +342,7 @@ fix_collect_kernel(const uint32_t* __restrict__ flags, size_t words, uint32_t* _
 
 constexpr int FIXQ_THREADS = 128;
 
+// One exact recomputation per thread; a CTA takes a contiguous piece of the list (its entries share rows of x).
 __global__ void __launch_bounds__(FIXQ_THREADS, 8)
 fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, const uint16_t* __restrict__ mk,
                  const uint16_t* __restrict__ mv, PackedWeights wq, PackedWeights wk, PackedWeights wv,
@@ -237,7 +351,9 @@ fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, c
                  size_t C, size_t wps) {
     if (ctrl[1]) return;   // the list overflowed: the window kernel redoes everything
     const uint32_t count = min(ctrl[0], cap);
-    for (uint32_t i = blockIdx.x * FIXQ_THREADS + threadIdx.x; i < count; i += gridDim.x * FIXQ_THREADS) {
+    const uint32_t per_cta = (count + gridDim.x - 1) / gridDim.x;
+    const uint32_t begin = blockIdx.x * per_cta, end = min(begin + per_cta, count);
+    for (uint32_t i = begin + threadIdx.x; i < end; i += FIXQ_THREADS) {
         const uint32_t entry = list[i], tt = entry & 31u;
         const size_t wi = entry >> 5, m = wi / sw, rem = wi % sw;
         const size_t s = rem / wps, word = rem % wps, b = s / C, ch = s % C, t = word * 32 + tt;
@@ -566,6 +682,32 @@ GemmParams base_params(ullis_cuda_runtime* rt, size_t M, size_t N, size_t K) {
     return p;
 }
 
+// LayerNorm + mixes + 16-bit operands in one kernel when the width allows (a multiple of 128 up to 1024 channels);
+// returns false when it does not, and the caller runs the two kernels one after the other.
+bool launch_ln_mix_split(ullis_cuda_runtime* rt, const float* x, const LayerNormWeights& ln, float* ln_out,
+                         const uint16_t* m0, const uint16_t* m1, const uint16_t* m2, uint16_t* hi0, uint16_t* lo0,
+                         uint16_t* hi1, uint16_t* lo1, uint16_t* hi2, uint16_t* lo2, float* s1, size_t rows, size_t time,
+                         size_t d, const char* what) {
+    if (!rt->tc_fuse_ln || d % 128 != 0 || d > 1024) return false;
+    const unsigned grid = blocks_for(rows, 8);
+#define ULLIS_LN_MIX(V)                                                                                              \
+    ln_mix_split_kernel<V><<<grid, 256, 0, rt->stream>>>(x, ln.weight, ln.bias, ln_out, m0, m1, m2, hi0, lo0, hi1, lo1, \
+                                                         hi2, lo2, s1, rows, time)
+    switch (d / 128) {
+        case 1: ULLIS_LN_MIX(1); break;
+        case 2: ULLIS_LN_MIX(2); break;
+        case 3: ULLIS_LN_MIX(3); break;
+        case 4: ULLIS_LN_MIX(4); break;
+        case 5: ULLIS_LN_MIX(5); break;
+        case 6: ULLIS_LN_MIX(6); break;
+        case 7: ULLIS_LN_MIX(7); break;
+        default: ULLIS_LN_MIX(8); break;
+    }
+#undef ULLIS_LN_MIX
+    rt->launched(what);
+    return true;
+}
+
 // x [rows, K] f32 -> 16-bit operand
 void cast16(ullis_cuda_runtime* rt, const float* x, uint16_t* y, size_t rows, size_t K, bool bf16) {
     const size_t n = rows * K;
@@ -654,16 +796,23 @@ bool dense_nt(ullis_cuda_runtime* rt, const uint16_t* a16, const uint16_t* b16, 
 }
 
 bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeights& L, uint32_t* q_sw,
-                   uint32_t* k_sw, uint32_t* v_sw, size_t batch, size_t time, size_t d) {
+                   uint32_t* k_sw, uint32_t* v_sw, size_t batch, size_t time, size_t d, const float* x_before_ln,
+                   float* ln3_write) {
     const size_t rows = batch * time;
     if (!usable(rt) || !shape_ok(rows, d, d) || time % 32) return false;
     const size_t n = rows * d, wps = time / 32, sw = batch * d * wps;
     uint16_t* op = rt->tc_ws[1].as<uint16_t>(6 * n);   // q/k/v hi, then q/k/v lo
     float* s1 = rt->tc_ws[2].as<float>(3 * rows);
     uint32_t* flags = rt->tc_ws[3].as<uint32_t>(3 * sw);
-    mix_split_kernel<<<blocks_for(rows, 8), 256, 0, rt->stream>>>(ln3_out, L.x_q, L.x_k, L.x_v, op, op + 3 * n, op + n,
-                                                                 op + 4 * n, op + 2 * n, op + 5 * n, s1, rows, time, d);
-    rt->launched("mix_split");
+    // x_before_ln: ln3 has not run yet - it is folded into the operand kernel, which leaves its output in ln3_write
+    // (= ln3_out) for the exact fix-up below
+    if (!(x_before_ln && launch_ln_mix_split(rt, x_before_ln, L.ln3, ln3_write, L.x_q, L.x_k, L.x_v, op, op + 3 * n, op + n,
+                                             op + 4 * n, op + 2 * n, op + 5 * n, s1, rows, time, d, "ln_mix_split"))) {
+        if (x_before_ln) k::layer_norm(rt, x_before_ln, L.ln3.weight, L.ln3.bias, ln3_write, rows, d, false);
+        mix_split_kernel<<<blocks_for(rows, 8), 256, 0, rt->stream>>>(ln3_out, L.x_q, L.x_k, L.x_v, op, op + 3 * n, op + n,
+                                                                     op + 4 * n, op + 2 * n, op + 5 * n, s1, rows, time, d);
+        rt->launched("mix_split");
+    }
     GemmMaps maps;
     memset(&maps, 0, sizeof(maps));
     for (int z = 0; z < 3; ++z) {
@@ -688,9 +837,9 @@ bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeig
         uint32_t* ctrl = rt->tc_ws[9].as<uint32_t>(2 + cap);
         uint32_t* list = ctrl + 2;
         rt->zero(ctrl, 8);
-        fix_collect_kernel<<<2 * (unsigned)rt->sm_count, 256, 0, rt->stream>>>(flags, 3 * sw, list, (uint32_t)cap, ctrl);
+        fix_collect_kernel<<<4 * (unsigned)rt->sm_count, 256, 0, rt->stream>>>(flags, sw, batch, d, wps, list, (uint32_t)cap, ctrl);
         rt->launched("fix_collect");
-        fix_apply_kernel<<<8 * (unsigned)rt->sm_count, FIXQ_THREADS, 0, rt->stream>>>(
+        fix_apply_kernel<<<16 * (unsigned)rt->sm_count, FIXQ_THREADS, 0, rt->stream>>>(
             ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, list, (uint32_t)cap, ctrl, sw, time, d, wps);
         rt->launched("fix_apply");
         only_if = ctrl + 1;
@@ -726,10 +875,13 @@ bool cmix_residual(ullis_cuda_runtime* rt, const LayerWeights& L, float* x, size
     float* ln = rt->tc_ws[4].as<float>(rows * d);
     uint16_t* a16 = rt->tc_ws[0].as<uint16_t>(rows * d);
     uint16_t* k16 = rt->tc_ws[5].as<uint16_t>(rows * ffn);
-    k::layer_norm(rt, x, L.ln2.weight, L.ln2.bias, ln, rows, d, false);
-    mix_split_kernel<<<blocks_for(rows, 8), 256, 0, rt->stream>>>(ln, L.ffn_x_k, nullptr, nullptr, a16, nullptr, nullptr,
-                                                                 nullptr, nullptr, nullptr, nullptr, rows, time, d);
-    rt->launched("mix_f16");
+    if (!launch_ln_mix_split(rt, x, L.ln2, nullptr, L.ffn_x_k, nullptr, nullptr, a16, nullptr, nullptr, nullptr, nullptr,
+                             nullptr, nullptr, rows, time, d, "ln_mix_f16")) {
+        k::layer_norm(rt, x, L.ln2.weight, L.ln2.bias, ln, rows, d, false);
+        mix_split_kernel<<<blocks_for(rows, 8), 256, 0, rt->stream>>>(ln, L.ffn_x_k, nullptr, nullptr, a16, nullptr,
+                                                                     nullptr, nullptr, nullptr, nullptr, nullptr, rows, time, d);
+        rt->launched("mix_f16");
+    }
     GemmMaps maps;
     memset(&maps, 0, sizeof(maps));
     maps.a[0][0] = make_map(a16, rows, d, false);

@@ -17,9 +17,12 @@ bool fp16_linear(ullis_cuda_runtime* rt, const float* x, const uint16_t* w, floa
 // y [M,N] f32 = a . b^T with both operands already FP16: a [M,K], b [N,K] (K a multiple of 64).
 bool dense_nt(ullis_cuda_runtime* rt, const uint16_t* a16, const uint16_t* b16, float* y, size_t M, size_t K,
               size_t N);
-// ln3 output -> time-shift mixes -> packed Q,K,V -> stream-major sign bits.
+// ln3 output -> time-shift mixes -> packed Q,K,V -> stream-major sign bits.  With `x_before_ln` the LayerNorm
+// itself is part of the call (L.ln3 over x_before_ln, folded into the operand kernel where the width allows) and
+// its output is left in `ln3_write`, which must be the buffer `ln3_out` names.
 bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeights& L, uint32_t* q_sw,
-                   uint32_t* k_sw, uint32_t* v_sw, size_t batch, size_t time, size_t d);
+                   uint32_t* k_sw, uint32_t* v_sw, size_t batch, size_t time, size_t d,
+                   const float* x_before_ln = nullptr, float* ln3_write = nullptr);
 // x += O((2*idx-1)*e)
 bool rosa_out_residual(ullis_cuda_runtime* rt, const uint32_t* idx_sw, const LayerWeights& L, float* x,
                        size_t batch, size_t time, size_t d);

@@ -360,12 +360,12 @@ void ullis_cuda_model::enqueue_layer(const Lane& ln, size_t l, size_t time) {
         ULLIS_CUDA_CHECK(cudaMemcpyAsync(X, A, n * 4, cudaMemcpyDeviceToDevice, r->stream));
     }
     save_tap((int)l, ULLIS_CUDA_TAP_BLOCK_IN, X, n * 4);
-    k::layer_norm(r, X, L.ln3.weight, L.ln3.bias, A, rows, d, exact);
-    save_tap((int)l, ULLIS_CUDA_TAP_LN3_OUT, A, n * 4);
     end(r);
 
     begin(PH_QKV, r);
-    if (!tc::rosa_qkv_bits(r, A, L, QS, KS, VS, batch, time, d)) {
+    // ln3 belongs to the Q/K/V stage: the tensor-core path folds it into its operand kernel (output left in A)
+    if (!tc::rosa_qkv_bits(r, A, L, QS, KS, VS, batch, time, d, X, A)) {
+        k::layer_norm(r, X, L.ln3.weight, L.ln3.bias, A, rows, d, exact);
         if (!one) fail(ULLIS_CUDA_ERR_ARG, "internal: a split forward reached a fall-back kernel");
         k::shift_mix(r, A, L.x_q, L.x_k, L.x_v, Bq, Bk, Bv, rows, time, d);
         k::binary_linear_exact(r, Bq, L.q.bits, L.q.scale, L.q.bias, W, rows, d, d, false);
@@ -375,6 +375,7 @@ void ullis_cuda_model::enqueue_layer(const Lane& ln, size_t l, size_t time) {
         k::binary_linear_exact(r, Bv, L.v.bits, L.v.scale, L.v.bias, W, rows, d, d, false);
         k::sign_pack_streams(r, W, VS, batch, time, d);
     }
+    save_tap((int)l, ULLIS_CUDA_TAP_LN3_OUT, A, n * 4);
     save_tap_bits((int)l, ULLIS_CUDA_TAP_Q_BITS, QS, batch, time);
     save_tap_bits((int)l, ULLIS_CUDA_TAP_K_BITS, KS, batch, time);
     save_tap_bits((int)l, ULLIS_CUDA_TAP_V_BITS, VS, batch, time);

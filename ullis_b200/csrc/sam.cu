@@ -135,8 +135,21 @@ __global__ void __launch_bounds__(128, 16)
 rosa_extend_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ k_sw,
                    const uint32_t* __restrict__ list, const uint32_t* __restrict__ count, size_t first, size_t wave,
                    uint32_t T, size_t wps, int lanes, uint32_t dense_count, uint32_t sparse_count) {
-    size_t item;
-    if (!split_item(count, first, wave, lanes, dense_count, sparse_count, &item)) return;
+    // All lanes of the group that belongs to a stream first fill the stream's `orig` array with NIL (16-byte
+    // stores, the lanes side by side); then one lane of the group runs the chain and the others leave.
+    if (lanes == 0) lanes = *count > dense_count ? 4 : *count > sparse_count ? 2 : 1;
+    const int lane = threadIdx.x & 31, spread = 32 / lanes;
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const size_t item = warp * lanes + lane / spread;
+    const bool live = item < wave && first + item < *count;
+    if (live) {
+        sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
+        uint4* o = reinterpret_cast<uint4*>(B.next);                       // 16-byte aligned by the layout
+        const uint32_t vecs = (sam::node_capacity(T) * 2u + 15u) / 16u;    // the array's room is a multiple of 16 bytes
+        for (uint32_t k = lane % spread; k < vecs; k += spread) o[k] = make_uint4(~0u, ~0u, ~0u, ~0u);
+    }
+    __syncwarp();
+    if (!live || lane % spread != 0) return;
     const size_t s = list[first + item];
     sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
     sam::euler_extend_words(B, k_sw + s * wps, T);

@@ -120,7 +120,14 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
         kid_min[v] = 0xFFFFFFFFu;
         kid_max[v] = 0u;
     }
-    for (uint32_t w = tid; w < (n + 31) / 32; w += NT) cbits[w] = B.clone_bits[w];
+    if (SPLIT) {   // a clone is a state with an `orig` entry (the split extend keeps no bitmap)
+        for (uint32_t v = tid; v < ((n + 31u) & ~31u); v += NT) {
+            const uint32_t word = __ballot_sync(0xffffffffu, v < n && B.next[v] != NIL);
+            if (lane == 0) cbits[v >> 5] = word;
+        }
+    } else {
+        for (uint32_t w = tid; w < (n + 31) / 32; w += NT) cbits[w] = B.clone_bits[w];
+    }
     for (uint32_t w = tid; w < wps; w += NT) vbits[w] = vw[w];
     // the query states and new-state ids are needed much later: ask for them now, 128 bytes per thread
     for (uint32_t i = tid * 64u; i < T; i += NT * 64u) {

@@ -564,16 +564,15 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
 //          src/rosa.rs:120-128 from (w_t, h_t), again with links as of time t.
 // Each chain is a fraction of the interleaved one, and the climb leaves the serial part altogether.
 // Scratch: h_t in the `head` array and orig in the `next` array of the block (both unused until the tour
-// of the one-thread form, which the split form does not use: its tour runs in shared memory).
+// of the one-thread form, which the split form does not use: its tour runs in shared memory).  The caller
+// fills orig with NIL beforehand; the extend only writes the entries of the clones, and those entries are
+// also what tells the tour which states are clones (no stamp of their own).
 SAM_HD void euler_extend_words(EulerBlock<uint16_t>& B, const uint32_t* kw, uint32_t T) {
     constexpr uint32_t NIL = 0xFFFFu;
     Node<uint16_t>* N = B.N;
     uint16_t* half = reinterpret_cast<uint16_t*>(N);   // field f of state s at half[4 * s + f]
-    uint16_t* orig = B.next;
-    const uint32_t cap = node_capacity(T);
-    for (uint32_t wd = 0; wd < (cap + 31) / 32; ++wd) B.clone_bits[wd] = 0;
+    uint16_t* orig = B.next;               // the caller has filled it with NIL (0xFFFF): only clones get an entry
     store_words(N, 0, 0xFFFFFFFFu, NIL);   // root: no children, no link, length 0
-    orig[0] = (uint16_t)NIL;
     uint32_t u = 1, g = 0, gmax = 0, gfail = NIL;
     NodeWords ne;                           // the words of state gfail, where the next extend starts (never loaded)
     ne.x = 0xFFFFFFFFu; ne.y = NIL;
@@ -585,7 +584,6 @@ SAM_HD void euler_extend_words(EulerBlock<uint16_t>& B, const uint32_t* kw, uint
         const uint32_t j = u++;
         const uint32_t child_mask = ~(0xFFFFu << ks);
         half[4 * g + kb] = (uint16_t)j;   // g has no children yet
-        orig[j] = (uint16_t)NIL;
         uint32_t p = gfail, d = NIL, jfail = 0, pml = 0;
         NodeWords n = ne;                  // gfail == NIL (first step only): the root's words, for the case below
         while (p != NIL) {
@@ -608,10 +606,9 @@ SAM_HD void euler_extend_words(EulerBlock<uint16_t>& B, const uint32_t* kw, uint
                 ne.x = nd.x;                // the clone copies every field of d
                 ne.y = (nd.y & 0xFFFFu) | ((pml + 1u) << 16);
                 store_words(N, b, ne.x, ne.y);
-                orig[b] = (uint16_t)d;
+                orig[b] = (uint16_t)d;      // also what marks b as a clone for the tour
                 half[4 * d + 2] = (uint16_t)b;
                 jfail = b;
-                B.clone_bits[b >> 5] |= 1u << (b & 31);
                 for (;;) {                  // p still has d as its child: redirect it, then go on up
                     half[4 * p + kb] = (uint16_t)b;
                     p = n.y & 0xFFFFu;
@@ -733,8 +730,22 @@ SAM_HD uint32_t euler_climb_words(const Node<uint16_t>* N, uint32_t w, uint32_t 
 
 // The three parts one after the other (what the split kernels compute together): same vq / jid / states as
 // euler_pass1_words.
+// orig <- NIL for every state (before the extend), clone bitmap <- "has an orig" (after it): the pieces the
+// kernels do with a fill of the scratch blocks and inside the tour kernel.
+SAM_HD void split_fill_orig(EulerBlock<uint16_t>& B, uint32_t T) {
+    for (uint32_t v = 0; v < node_capacity(T); ++v) B.next[v] = (uint16_t)0xFFFFu;
+}
+SAM_HD void split_clone_bits(EulerBlock<uint16_t>& B, uint32_t T) {
+    const uint32_t cap = node_capacity(T);
+    for (uint32_t wd = 0; wd < (cap + 31) / 32; ++wd) B.clone_bits[wd] = 0;
+    for (uint32_t v = 0; v < B.meta[0]; ++v)
+        if (B.next[v] != 0xFFFFu) B.clone_bits[v >> 5] |= 1u << (v & 31);
+}
+
 SAM_HD uint32_t euler_pass1_split(EulerBlock<uint16_t>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T) {
+    split_fill_orig(B, T);
     euler_extend_words(B, kw, T);
+    split_clone_bits(B, T);
     uint32_t w = 0, h = 0;
     euler_walk_words<false>(B, qw, 0, T, w, h);
     for (uint32_t t = 0; t < T; ++t)
@@ -745,7 +756,9 @@ SAM_HD uint32_t euler_pass1_split(EulerBlock<uint16_t>& B, const uint32_t* qw, c
 // The same with the walk in pieces of `piece` steps (euler_walk_chunked).
 SAM_HD uint32_t euler_pass1_split_chunked(EulerBlock<uint16_t>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T,
                                           uint32_t piece) {
+    split_fill_orig(B, T);
     euler_extend_words(B, kw, T);
+    split_clone_bits(B, T);
     euler_walk_chunked(B, qw, T, piece);
     for (uint32_t t = 0; t < T; ++t)
         B.vq[t] = (uint16_t)euler_climb_words(B.N, B.vq[t], B.head[t], B.jid[t]);

@@ -214,21 +214,37 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
                 static_cast<uint32_t*>(pr.out2)[o] = my_flags;
             }
         } else if (EPI == EPI_CE) {
+            // whole chunks (the usual case: the vocabulary is a multiple of 32) skip the per-column range test,
+            // and the target's logit is picked out only in the one chunk of the row that holds it
+            const bool whole = nc + 32u <= p.N;
             float cmax = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const float2 sc2 = sb_load2(s_scale, c * 32 + (j & ~1)), bi2 = sb_load2(s_bias, c * 32 + (j & ~1));
-                const float y = ((j & 1) ? bi2.y : bi2.x) + ((j & 1) ? sc2.y : sc2.x) * __uint_as_float(r[j]);
-                r[j] = __float_as_uint(y);
-                if (nc + j < p.N) cmax = fmaxf(cmax, y);
-                if (nc + j == target && row_ok) static_cast<float*>(pr.out2)[m] = y;
+            for (int j = 0; j < 32; j += 2) {
+                const float2 sc2 = sb_load2(s_scale, c * 32 + j), bi2 = sb_load2(s_bias, c * 32 + j);
+                const float y0 = bi2.x + sc2.x * __uint_as_float(r[j]);
+                const float y1 = bi2.y + sc2.y * __uint_as_float(r[j + 1]);
+                r[j] = __float_as_uint(y0);
+                r[j + 1] = __float_as_uint(y1);
+                if (whole || nc + j < p.N) cmax = fmaxf(cmax, y0);
+                if (whole || nc + j + 1 < p.N) cmax = fmaxf(cmax, y1);
+            }
+            if (row_ok && target - nc < 32u) {
+                const uint32_t tj = target - nc;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if ((uint32_t)j == tj) static_cast<float*>(pr.out2)[m] = __uint_as_float(r[j]);
             }
             if (cmax > -INFINITY) {
                 const float nmax = fmaxf(run_max, cmax);
                 float add = 0.0f;
+                if (whole) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (nc + j < p.N) add += __expf(__uint_as_float(r[j]) - nmax);
+                    for (int j = 0; j < 32; ++j) add += __expf(__uint_as_float(r[j]) - nmax);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (nc + j < p.N) add += __expf(__uint_as_float(r[j]) - nmax);
+                }
                 run_sum = run_sum * __expf(run_max - nmax) + add;
                 run_max = nmax;
             }
