@@ -89,3 +89,33 @@ def test_generate_error_cases_leave_the_state_unchanged(cuda_rt, oracle):  # src
     assert e.value.code == cuda.ERR_SHAPE and "context_len" in str(e.value) and state.time == 6
     state.close()
     m.close()
+
+
+def test_a_step_that_fails_after_its_kernels_ran_poisons_the_state_until_reset(cuda_rt, monkeypatch):
+    """The failure is injected on the host (no GPU fault): step 3 raises after its kernels have advanced the
+    device-side automata.  `time` has not moved, so a retry would push position 2 twice; the state must refuse
+    further steps until it is reset, and after the reset it must generate exactly what a fresh state does."""
+    data = synth.heron_checkpoint("tiny", batch_size=1)
+    m = cuda.CudaHeron(cuda_rt, data)
+    tokens = synth.zipf_tokens(5, 8, 512)
+    fresh = m.generate_state(1)
+    want = [fresh.step(tokens[t:t + 1]).copy() for t in range(6)]
+    fresh.close()
+    monkeypatch.setenv("ULLIS_CUDA_INJECT_GENERATE_FAILURE", "3")
+    state = m.generate_state(1)
+    monkeypatch.delenv("ULLIS_CUDA_INJECT_GENERATE_FAILURE")
+    for t in range(2):
+        assert np.array_equal(state.step(tokens[t:t + 1]), want[t])
+    with pytest.raises(cuda.UllisCudaError) as e:
+        state.step(tokens[2:3])
+    assert e.value.code == cuda.ERR_CUDA and "injected" in e.value.message
+    assert state.time == 2
+    with pytest.raises(cuda.UllisCudaError) as e:      # no silent retry on a state that is out of step with itself
+        state.step(tokens[2:3])
+    assert e.value.code == cuda.ERR_ARG and "reset" in e.value.message
+    state.reset()
+    assert state.time == 0
+    for t in range(6):
+        assert np.array_equal(state.step(tokens[t:t + 1]), want[t]), t
+    state.close()
+    m.close()

@@ -121,6 +121,7 @@ ullis_cuda_generate_state::ullis_cuda_generate_state(ullis_cuda_model* m, size_t
     ULLIS_CUDA_CHECK(cudaMallocHost(&h_tokens, batch * 4));
     ULLIS_CUDA_CHECK(cudaMallocHost(&h_logits, batch * m->vocab * 4));
     use_graph = !getenv("ULLIS_CUDA_NO_GRAPH");
+    if (const char* env = getenv("ULLIS_CUDA_INJECT_GENERATE_FAILURE")) inject_failure_at = (size_t)std::max(0, atoi(env));
     reset();
 }
 
@@ -142,6 +143,7 @@ void ullis_cuda_generate_state::reset() {
     rt->launched("gen_init");
     rt->sync();
     time = 0;
+    poisoned = false;
 }
 
 void ullis_cuda_generate_state::step(const uint32_t* tokens, float* logits_out) {
@@ -152,10 +154,21 @@ void ullis_cuda_generate_state::step(const uint32_t* tokens, float* logits_out) 
         if (tokens[b] >= m->vocab) fail(ULLIS_CUDA_ERR_TOKEN, "token id exceeds vocabulary");
     if (time >= m->context_len)
         fail(ULLIS_CUDA_ERR_SHAPE, "generate exceeded context_len (" + std::to_string(m->context_len) + ")");
+    if (poisoned)
+        fail(ULLIS_CUDA_ERR_ARG, "generate state is unusable after a failed step: reset it (ullis_cuda_generate_state_reset)");
     rt->bind();
     if (rt->kernel_timing) rt->mark("(between steps)");
     std::memcpy(h_tokens, tokens, batch * 4);
     const int has_prev = time != 0;
+    // From here on the device-side automata, v history and time-shift inputs may have moved on by one position
+    // while `time` has not: a failure below leaves the state out of step with itself, and a retry would push the
+    // same position twice.  The state stays refused until reset() (which rebuilds it from scratch).
+    struct Poison {
+        bool* flag;
+        bool armed = true;
+        ~Poison() { if (armed) *flag = true; }
+    } poison{&poisoned};
+
     if (use_graph && !rt->kernel_timing) {
         // Replay the step as one graph launch; per-kernel timing needs the plain launches.
         if (!graph[has_prev]) {
@@ -184,8 +197,13 @@ void ullis_cuda_generate_state::step(const uint32_t* tokens, float* logits_out) 
     }
     rt->sync();
     rt->throw_on_status();
+    if (inject_failure_at && time + 1 == inject_failure_at) {   // host-injected: what a CUDA error after the launches does
+        inject_failure_at = 0;
+        fail(ULLIS_CUDA_ERR_CUDA, "injected failure after the step's kernels ran");
+    }
     std::memcpy(logits_out, h_logits, batch * m->vocab * 4);
     time += 1;
+    poison.armed = false;
 }
 
 void ullis_cuda_generate_state::enqueue(int has_prev) {

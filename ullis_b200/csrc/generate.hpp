@@ -20,6 +20,12 @@ struct ullis_cuda_generate_state {
     bool use_graph = true;
     cudaGraphExec_t graph[2] = {nullptr, nullptr};
     uint64_t graph_launches = 0;    // kernels inside one replay
+    // A step that fails after its kernels were enqueued leaves the device-side automata one position ahead of
+    // `time`; the state then refuses further steps until reset().
+    bool poisoned = false;
+    // Test hook (ULLIS_CUDA_INJECT_GENERATE_FAILURE=n when the state is created): step n fails on the host after
+    // its kernels have run, the way a CUDA error reported at the synchronisation would.
+    size_t inject_failure_at = 0;
 
     ullis_cuda_generate_state(ullis_cuda_model* m, size_t batch);
     ~ullis_cuda_generate_state();

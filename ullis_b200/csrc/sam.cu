@@ -273,7 +273,16 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     const sam::CoopLayout coop((uint32_t)time);
     const bool use_coop = algo == ULLIS_CUDA_SAM_EULER && narrow && rt->sam_coop && coop.total <= 226 * 1024 &&
                           2 * sam::node_capacity((uint32_t)time) < 0xFFFFu;
-    bool forked = false;   // the constant-q kernel is running on the side stream
+    // The constant-q kernel runs on the side stream from the fork below until `stream` has waited for side_join.
+    // Whichever way this function leaves in between (a launch error throws), the wait is issued: the next call
+    // clears the counters and lists that kernel still reads.
+    struct SideJoin {
+        ullis_cuda_runtime* rt;
+        bool forked = false;
+        ~SideJoin() {
+            if (forked) cudaStreamWaitEvent(rt->stream, rt->side_join, 0);
+        }
+    } side{rt};
     if (algo == ULLIS_CUDA_SAM_EAGER) {
         rosa_list_all_kernel<<<cgrid, 128, 0, rt->stream>>>(list, count, streams);
         rt->launched("rosa_list_all");
@@ -293,6 +302,15 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
             }
             ULLIS_CUDA_CHECK(cudaEventRecord(rt->side_fork, rt->stream));
             ULLIS_CUDA_CHECK(cudaStreamWaitEvent(rt->side_stream, rt->side_fork, 0));
+            // side_join must be recorded behind whatever reached the side stream, also when a step below throws
+            struct Recorder {
+                ullis_cuda_runtime* rt;
+                SideJoin* side;
+                ~Recorder() {
+                    if (cudaEventRecord(rt->side_join, rt->side_stream) == cudaSuccess) side->forked = true;
+                }
+            };
+            Recorder recorder{rt, &side};
             if (rt->kernel_timing) rt->side_begin();
             rosa_constq_kernel<<<cgrid, 128, 0, rt->side_stream>>>(q_sw, k_sw, v_sw, idx_sw, (uint32_t)time, wps, cq_list,
                                                                    cq_count);
@@ -300,8 +318,6 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
             if (e != cudaSuccess) fail(ULLIS_CUDA_ERR_CUDA, std::string("launch of rosa_constq: ") + cudaGetErrorString(e));
             ++rt->launches;
             if (rt->kernel_timing) rt->side_end("rosa_constq");
-            ULLIS_CUDA_CHECK(cudaEventRecord(rt->side_join, rt->side_stream));
-            forked = true;
         } else {
             rosa_constq_kernel<<<cgrid, 128, 0, rt->stream>>>(q_sw, k_sw, v_sw, idx_sw, (uint32_t)time, wps, cq_list, cq_count);
             rt->launched("rosa_constq");
@@ -380,7 +396,7 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
 #undef ULLIS_SAM_LAUNCH
         rt->launched("rosa_sam");
     }
-    if (forked) ULLIS_CUDA_CHECK(cudaStreamWaitEvent(rt->stream, rt->side_join, 0));   // idx is complete on `stream` from here
+    // `side` goes out of scope here: `stream` waits for the side kernel, idx is complete on `stream` from then on
 }
 
 }  // namespace k
