@@ -56,6 +56,15 @@ static int run_batch(int algo, const uint32_t* qw, const uint32_t* kw, const uin
             euler_pass2<uint16_t>(B, vw + s * wps, out + s * wps, T);
             continue;
         }
+        if (algo == 7) {   // interleaved pass 1 with the climb taken out of the serial loop (16-bit state ids only)
+            if (sizeof(Ix) != 2) return 3;
+            EulerBlock<uint16_t> B(base, T);
+            const uint32_t n = euler_pass1_deferred(B, qw + s * wps, kw + s * wps, T);
+            if (n > node_capacity(T)) return 2;
+            euler_tour<uint16_t>(B, n);
+            euler_pass2<uint16_t>(B, vw + s * wps, out + s * wps, T);
+            continue;
+        }
         if (algo >= 100) {   // the split form with the query walk in pieces of (algo - 100) steps
             if (sizeof(Ix) != 2) return 3;
             EulerBlock<uint16_t> B(base, T);

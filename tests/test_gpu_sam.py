@@ -131,3 +131,26 @@ def test_streams_in_waves_when_the_scratch_budget_is_small(oracle, monkeypatch, 
         run_both(rt, oracle, q, k, v, B, T, C, algos=(cuda.SAM_EULER,))
     finally:
         rt.close()
+
+
+@pytest.mark.parametrize("chunked", ["0", "1"])
+def test_pass_one_in_parts_gives_the_same_idx(oracle, monkeypatch, chunked):
+    """The optional form of pass 1 - extend chain and query walk as two kernels against the final automaton read
+    as of each step, the climb inside the tour kernel; the walk either serial or in eight guessed pieces per stream -
+    is off by default (it measured slower than the interleaved form) but stays bit-exact."""
+    monkeypatch.setenv("ULLIS_CUDA_SAM_SPLIT", "1")
+    monkeypatch.setenv("ULLIS_CUDA_SAM_WALK_CHUNKED", chunked)
+    rt = cuda.CudaRuntime(0)
+    try:
+        B, T, C = 2, 2048, 64
+        q, k, v = synth.rosa_bits_iid(41, B, T, C)
+        run_both(rt, oracle, q, k, v, B, T, C, algos=(cuda.SAM_EULER,))
+        q, k, v = synth.rosa_bits_periodic(42, B, T, C)
+        run_both(rt, oracle, q, k, v, B, T, C, algos=(cuda.SAM_EULER,))
+        rng = np.random.default_rng(43)
+        T, C = 777, 96                                       # a ragged length, biased streams
+        pr = rng.choice([0.01, 0.1, 0.5, 0.9, 0.99], (1, C))
+        q, k, v = (pack_plane((rng.random((T, C)) < pr).astype(np.uint8)) for _ in range(3))
+        run_both(rt, oracle, q, k, v, 1, T, C, algos=(cuda.SAM_EULER,))
+    finally:
+        rt.close()

@@ -9,6 +9,7 @@ from conftest import pack_streams
 
 ALGOS = {"eager": 0, "euler": 1, "euler_with_constant_k_shortcut": 2, "incremental_pushes_lazy_chain": 6}
 PACKED_WORDS = 4   # pass 1 on packed state words: 16-bit state ids only
+DEFERRED_CLIMB = 7 # interleaved pass 1 that records (w_t, h_t); the climb to v_t afterwards, links read as of step t
 SPLIT = 5          # pass 1 as extend / walk / climb against the final automaton: 16-bit state ids only
 SPLIT_PIECES = [100 + p for p in (1, 3, 32, 256)]   # the same with the query walk in pieces of p steps, guessed and put right
 
@@ -25,6 +26,7 @@ def test_exhaustive_short_streams(oracle, sam_host, T):
             assert np.array_equal(sam_host(algo, ix, q, k, v, n, T), ref)
     assert np.array_equal(sam_host(PACKED_WORDS, 16, q, k, v, n, T), ref)
     assert np.array_equal(sam_host(SPLIT, 16, q, k, v, n, T), ref)
+    assert np.array_equal(sam_host(DEFERRED_CLIMB, 16, q, k, v, n, T), ref)
     for algo in SPLIT_PIECES[:2]:
         assert np.array_equal(sam_host(algo, 16, q, k, v, n, T), ref)
 
@@ -44,6 +46,7 @@ def test_exhaustive_key_sequences_under_a_constant_query(oracle, sam_host, T):
             assert np.array_equal(sam_host(1, 16, q, kk, v, kk.size, T), ref), c
             assert np.array_equal(sam_host(PACKED_WORDS, 16, q, kk, v, kk.size, T), ref), c
             assert np.array_equal(sam_host(SPLIT, 16, q, kk, v, kk.size, T), ref), c
+            assert np.array_equal(sam_host(DEFERRED_CLIMB, 16, q, kk, v, kk.size, T), ref), c
 
 
 def _streams(kind, n, T, rng):
@@ -95,7 +98,7 @@ def test_long_streams(oracle, sam_host, kind, T, n):
     rng = np.random.default_rng(hash((kind, T)) & 0xFFFF)
     q, k, v = (pack_streams(b) for b in _streams(kind, n, T, rng))
     ref = oracle.rosa_qkv_streams(q, k, v, n, T)
-    for algo in list(ALGOS.values()) + [PACKED_WORDS, SPLIT] + SPLIT_PIECES:
+    for algo in list(ALGOS.values()) + [PACKED_WORDS, SPLIT, DEFERRED_CLIMB] + SPLIT_PIECES:
         assert np.array_equal(sam_host(algo, 16, q, k, v, n, T), ref), (kind, algo)
     assert np.array_equal(sam_host(1, 32, q, k, v, n, T), ref)
 

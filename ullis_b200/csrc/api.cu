@@ -114,6 +114,7 @@ ullis_cuda_runtime* ullis_cuda_runtime::child(size_t i) {
     c->sam_coop_threads = sam_coop_threads;
     c->sam_words = sam_words;
     c->sam_split = sam_split;
+    c->sam_defer_climb = sam_defer_climb;
     c->sam_walk_chunked = sam_walk_chunked;
     c->sam_budget_bytes = sam_budget_bytes / (children.size() + 1);
     c->tc_fix_list = tc_fix_list;
@@ -293,6 +294,7 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         if (const char* env = getenv("ULLIS_CUDA_FUSE_LN")) rt->tc_fuse_ln = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_FIX_LIST")) rt->tc_fix_list = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_WALK_CHUNKED")) rt->sam_walk_chunked = atoi(env) != 0;
+        if (const char* env = getenv("ULLIS_CUDA_SAM_DEFER_CLIMB")) rt->sam_defer_climb = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_SPLIT")) rt->sam_split = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_SIDE")) rt->sam_side = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_LANES")) rt->lanes = std::min(16, std::max(1, atoi(env)));

@@ -101,8 +101,10 @@ struct ullis_cuda_runtime {
     uint32_t sam_sparse_per_sm = 40;    // pass 1 carries one stream per warp below this many streams per SM
     int sam_coop_threads = 0;           // threads per stream in the tour / pass 2 kernel (256, 512, 1024); 0 = from the shared memory a stream needs
     bool sam_words = true;              // pass 1 on packed state words (sam_core.cuh euler_pass1_words); false: the field-wise form
-    bool sam_split = true;              // pass 1 as two kernels, extend chain then query walk, and the climb inside the tour kernel
-    bool sam_walk_chunked = true;       // the query walk of the split form with eight lanes per stream (guessed pieces, then put right)
+    bool sam_split = false;             // pass 1 as two kernels, extend chain then query walk, and the climb inside the tour kernel
+                                        // (off: measured slower than the interleaved single-thread form at every stream count)
+    bool sam_defer_climb = true;        // interleaved pass 1 records where each query walk ended; the climb to the state it reads runs in the tour kernel
+    bool sam_walk_chunked = false;      // the query walk of the split form with eight lanes per stream (guessed pieces, then put right)
     int sam_lanes = 4;                  // streams carried per warp by the suffix-automaton kernel (1,2,4,...,32)
     uint64_t launches = 0;
     std::string last_error;

@@ -294,75 +294,143 @@ __device__ __forceinline__ bool exact_mixed_sign(const float* __restrict__ xr, b
     return __fadd_rn(bias, __fmul_rn(scale, sum)) > 0.0f;
 }
 
-// The flagged outputs of one Q/K/V launch as a compact list, so that the exact recomputation runs with one thread
-// per flagged output over the whole device instead of a few busy threads per window.  An entry is the position of
-// the flag bit: (index of the flag word among the 3 * sw words of the launch) * 32 + bit.  The list is built in
-// the order (sequence, block of 32 steps, matrix, channel), so that entries next to each other read the same few
-// rows of x: a warp takes one (sequence, block of steps, matrix) at a time and sweeps the channels, 32 flag words
-// per round, one append per round.  More flags than the list holds (never on realistic inputs: the list takes
-// one output in 64) raise `ctrl[1]`, and the window kernel below then redoes the whole launch.
+// The flagged outputs of one Q/K/V launch as a compact list, so that the exact recomputation runs over the whole
+// device instead of a few busy threads per window.  An entry is the position of the flag bit: (index of the flag
+// word among the 3 * sw words of the launch) * 32 + bit.  A warp takes one (sequence, block of 32 steps, matrix) at
+// a time, reads that block's flag word of every channel and appends all the bits it found with ONE addition to the
+// list's counter (an addition per word would queue a hundred thousand of them on one address).  Entries of a
+// block lie together in the list and read the same 33 rows of x.  More flags than the list holds (never on
+// realistic inputs: the list takes one output in 64) raise `ctrl[1]`, and the window kernel below then redoes the
+// whole launch.  C <= 32 * FIXQ_MAX_WORDS channels.
+constexpr int FIXQ_MAX_WORDS = 32;
 __global__ void __launch_bounds__(256)
 fix_collect_kernel(const uint32_t* __restrict__ flags, size_t sw, size_t batch, size_t C, size_t wps,
                    uint32_t* __restrict__ list, uint32_t cap, uint32_t* __restrict__ ctrl) {
     const int lane = threadIdx.x & 31;
     const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
     const size_t buckets = batch * wps * 3;
+    const int rounds = (int)((C + 31) / 32);
     for (size_t bk = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; bk < buckets; bk += warps) {
         const size_t m = bk % 3, word = (bk / 3) % wps, b = bk / (3 * wps);
         const size_t base = m * sw + b * C * wps + word;     // flag word of channel ch: base + ch * wps
-        for (size_t c0 = 0; c0 < C; c0 += 32) {
-            const size_t ch = c0 + lane;
-            const uint32_t f = ch < C ? flags[base + ch * wps] : 0u;
-            const uint32_t n = __popc(f);
-            uint32_t incl = n;                                 // inclusive prefix sum over the lanes
+        uint32_t f[FIXQ_MAX_WORDS];
+        uint32_t mine = 0;
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += up;
-            }
-            const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-            if (total == 0) continue;
-            uint32_t at = 0;
-            if (lane == 31) at = atomicAdd(&ctrl[0], total);
-            at = __shfl_sync(0xffffffffu, at, 31);
-            if (at + total > cap) {
-                if (lane == 0) ctrl[1] = 1u;
-                continue;
-            }
-            at += incl - n;
-            uint32_t g = f;
+        for (int r = 0; r < FIXQ_MAX_WORDS; ++r) {
+            const size_t ch = (size_t)r * 32 + lane;
+            f[r] = (r < rounds && ch < C) ? flags[base + ch * wps] : 0u;
+            mine += __popc(f[r]);
+        }
+        uint32_t incl = mine;                                  // inclusive prefix sum over the lanes
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+        if (total == 0) continue;
+        uint32_t at = 0;
+        if (lane == 31) at = atomicAdd(&ctrl[0], total);
+        at = __shfl_sync(0xffffffffu, at, 31);
+        if (at + total > cap) {
+            if (lane == 0) ctrl[1] = 1u;
+            continue;
+        }
+        at += incl - mine;
+#pragma unroll
+        for (int r = 0; r < FIXQ_MAX_WORDS; ++r) {
+            uint32_t g = f[r];
             while (g) {
                 const uint32_t tt = __ffs(g) - 1;
                 g &= g - 1;
-                list[at++] = (uint32_t)(base + ch * wps) * 32u + tt;
+                list[at++] = (uint32_t)(base + ((size_t)r * 32 + lane) * wps) * 32u + tt;
             }
         }
     }
 }
 
-constexpr int FIXQ_THREADS = 128;
+// The exact recomputation of the listed outputs, a warp for 32 entries at a time.  The terms +/- in_i of an
+// output have to be added one after the other in f32 (that order is what makes the sign exact), which only a
+// single thread can do; everything before it is shared: for 64 input columns at a time the whole warp loads the
+// rows of one entry after the other side by side (256 bytes per request instead of 32 requests into 32 rows),
+// forms the signed terms and leaves them in shared memory, and then lane e adds up the 64 terms of entry e.
+constexpr int FIXQ_WARPS = 4, FIXQ_COLS = 64, FIXQ_PITCH = FIXQ_COLS + 1;
 
-// One exact recomputation per thread; a CTA takes a contiguous piece of the list (its entries share rows of x).
-__global__ void __launch_bounds__(FIXQ_THREADS, 8)
+__global__ void __launch_bounds__(FIXQ_WARPS * 32)
 fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, const uint16_t* __restrict__ mk,
                  const uint16_t* __restrict__ mv, PackedWeights wq, PackedWeights wk, PackedWeights wv,
                  uint32_t* __restrict__ bq, uint32_t* __restrict__ bk, uint32_t* __restrict__ bv,
                  const uint32_t* __restrict__ list, uint32_t cap, const uint32_t* __restrict__ ctrl, size_t sw, size_t T,
                  size_t C, size_t wps) {
+    __shared__ float terms[FIXQ_WARPS][32 * FIXQ_PITCH];
     if (ctrl[1]) return;   // the list overflowed: the window kernel redoes everything
     const uint32_t count = min(ctrl[0], cap);
-    const uint32_t per_cta = (count + gridDim.x - 1) / gridDim.x;
-    const uint32_t begin = blockIdx.x * per_cta, end = min(begin + per_cta, count);
-    for (uint32_t i = begin + threadIdx.x; i < end; i += FIXQ_THREADS) {
-        const uint32_t entry = list[i], tt = entry & 31u;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* mine = terms[warp];
+    const uint32_t tasks = (count + 31u) / 32u;
+    for (uint32_t task = blockIdx.x * FIXQ_WARPS + warp; task < tasks; task += gridDim.x * FIXQ_WARPS) {
+        // lane e owns entry e of the task
+        const uint32_t i = task * 32u + lane;
+        const bool live = i < count;
+        const uint32_t entry = live ? list[i] : 0u, tt = entry & 31u;
         const size_t wi = entry >> 5, m = wi / sw, rem = wi % sw;
         const size_t s = rem / wps, word = rem % wps, b = s / C, ch = s % C, t = word * 32 + tt;
-        const uint16_t* mix = m == 0 ? mq : m == 1 ? mk : mv;
+        const float* my_row = x + (b * T + t) * C;
         const PackedWeights& W = m == 0 ? wq : m == 1 ? wk : wv;
-        uint32_t* bits = m == 0 ? bq : m == 1 ? bk : bv;
-        const bool plus = exact_mixed_sign<16>(x + (b * T + t) * C, t == 0, mix, W.bits + (ch * C >> 5), h2f(W.scale[ch]),
-                                               W.bias ? h2f(W.bias[ch]) : 0.0f, C);
-        if (plus) atomicOr(&bits[rem], 1u << tt); else atomicAnd(&bits[rem], ~(1u << tt));
+        const uint32_t* my_w = W.bits + (ch * C >> 5);            // C % 32 == 0 on this path
+        const uint32_t my_flags = (uint32_t)m | (t == 0 ? 4u : 0u) | (live ? 8u : 0u);
+        float sum = 0.0f;
+        for (size_t i0 = 0; i0 < C; i0 += FIXQ_COLS) {
+            // eight entries at a time: first every load of the eight (they do not depend on each other and the
+            // compiler cannot move a load above a store to shared memory by itself), then the arithmetic
+            for (int e0 = 0; e0 < 32; e0 += 8) {
+                float2 cur[8], prev[8];
+                uint32_t mw[8], ww[8], fl[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int e = e0 + u;
+                    fl[u] = __shfl_sync(0xffffffffu, my_flags, e);
+                    const float* row = reinterpret_cast<const float*>(
+                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_row), e));
+                    const uint32_t* wrow = reinterpret_cast<const uint32_t*>(
+                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_w), e));
+                    const uint16_t* mix = (fl[u] & 3u) == 0 ? mq : (fl[u] & 3u) == 1 ? mk : mv;
+                    const size_t c = i0 + 2 * lane;
+                    cur[u] = make_float2(0.f, 0.f);
+                    prev[u] = make_float2(0.f, 0.f);
+                    mw[u] = 0u;
+                    ww[u] = 0u;
+                    if (fl[u] & 8u) {                              // uniform over the warp
+                        cur[u] = *reinterpret_cast<const float2*>(row + c);
+                        if (!(fl[u] & 4u)) prev[u] = *reinterpret_cast<const float2*>(row - C + c);
+                        mw[u] = *reinterpret_cast<const uint32_t*>(mix + c);
+                        ww[u] = wrow[c >> 5] >> (c & 31);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int e = e0 + u;
+                    const bool first_step = (fl[u] & 4u) != 0;
+                    const float xx0 = first_step ? -cur[u].x : __fsub_rn(prev[u].x, cur[u].x);
+                    const float xx1 = first_step ? -cur[u].y : __fsub_rn(prev[u].y, cur[u].y);
+                    const float in0 = __fadd_rn(cur[u].x, __fmul_rn(xx0, h2f((uint16_t)(mw[u] & 0xFFFFu))));
+                    const float in1 = __fadd_rn(cur[u].y, __fmul_rn(xx1, h2f((uint16_t)(mw[u] >> 16))));
+                    mine[e * FIXQ_PITCH + 2 * lane] = (ww[u] & 1u) ? in0 : -in0;
+                    mine[e * FIXQ_PITCH + 2 * lane + 1] = (ww[u] & 2u) ? in1 : -in1;
+                }
+            }
+            __syncwarp();
+            if (live) {
+#pragma unroll 8
+                for (int k = 0; k < FIXQ_COLS; ++k) sum = __fadd_rn(sum, mine[lane * FIXQ_PITCH + k]);   // i ascending
+            }
+            __syncwarp();
+        }
+        if (live) {
+            const float y = __fadd_rn(W.bias ? h2f(W.bias[ch]) : 0.0f, __fmul_rn(h2f(W.scale[ch]), sum));
+            uint32_t* bits = m == 0 ? bq : m == 1 ? bk : bv;
+            if (y > 0.0f) atomicOr(&bits[rem], 1u << tt); else atomicAnd(&bits[rem], ~(1u << tt));
+        }
     }
 }
 
@@ -831,7 +899,7 @@ bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeig
     launch<EPI_SIGNBITS, true>(rt, maps, p, 3, "gemm_qkv_signbits");
     const unsigned grid = (unsigned)(((wps + FIX_WIN - 1) / FIX_WIN) * batch);   // rows < 2^30, so this fits
     const uint32_t* only_if = nullptr;
-    if (rt->tc_fix_list && 3 * sw < ((size_t)1 << 27)) {
+    if (rt->tc_fix_list && 3 * sw < ((size_t)1 << 27) && d % FIXQ_COLS == 0 && d <= 32 * FIXQ_MAX_WORDS) {
         // one thread per flagged output, from a compact list; room for one output in 64
         const size_t cap = std::max<size_t>(65536, 3 * sw * 32 / 64);
         uint32_t* ctrl = rt->tc_ws[9].as<uint32_t>(2 + cap);
@@ -839,7 +907,7 @@ bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeig
         rt->zero(ctrl, 8);
         fix_collect_kernel<<<4 * (unsigned)rt->sm_count, 256, 0, rt->stream>>>(flags, sw, batch, d, wps, list, (uint32_t)cap, ctrl);
         rt->launched("fix_collect");
-        fix_apply_kernel<<<16 * (unsigned)rt->sm_count, FIXQ_THREADS, 0, rt->stream>>>(
+        fix_apply_kernel<<<8 * (unsigned)rt->sm_count, FIXQ_WARPS * 32, 0, rt->stream>>>(
             ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, list, (uint32_t)cap, ctrl, sw, time, d, wps);
         rt->launched("fix_apply");
         only_if = ctrl + 1;

@@ -97,6 +97,7 @@ rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const ui
                   const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ list,
                   const uint32_t* __restrict__ count, size_t first, size_t wave, uint32_t T, size_t wps, int lanes,
                   uint32_t dense_count, uint32_t sparse_count, int words) {
+    // words: 0 = field-wise state layout, 1 = packed words, 2 = packed words with the climb left to the tour kernel
     // lanes == 0: choose from the number of streams that are left, which only the device knows -
     // many streams: four per warp (fewer issued instructions); fewer: two, then one per warp (more
     // warps to hide the pointer-chase latency).  The grid is sized for one per warp.
@@ -111,7 +112,8 @@ rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const ui
     if (item >= wave || first + item >= *count) return;
     const size_t s = list[first + item];
     sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
-    if (words) sam::euler_pass1_words(B, q_sw + s * wps, k_sw + s * wps, T);
+    if (words == 2) sam::euler_pass1_words<true>(B, q_sw + s * wps, k_sw + s * wps, T);
+    else if (words) sam::euler_pass1_words<false>(B, q_sw + s * wps, k_sw + s * wps, T);
     else sam::euler_pass1<uint16_t>(B, q_sw + s * wps, k_sw + s * wps, T, nullptr);
 }
 
@@ -199,7 +201,7 @@ rosa_walk_chunked_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, c
     }
 }
 
-template <int NT, bool SPLIT = false>
+template <int NT, int MODE = 0>   // 0: pass 1 left v_t; 1: split form (climb here, clones from orig); 2: deferred climb
 __global__ void __launch_bounds__(NT)
 rosa_coop_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ v_sw,
                  uint32_t* __restrict__ idx_sw, const uint32_t* __restrict__ list, const uint32_t* __restrict__ count,
@@ -214,7 +216,7 @@ rosa_coop_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uin
             status[1] = (uint32_t)s;
         return;
     }
-    sam::coop_tour_pass2<NT, SPLIT>(coop_smem, B, v_sw + s * wps, idx_sw + s * wps, T);
+    sam::coop_tour_pass2<NT, MODE != 0, MODE == 1>(coop_smem, B, v_sw + s * wps, idx_sw + s * wps, T);
 }
 
 // EAGER keeps the reference's schedule for every stream (no shortcut): list = all streams
@@ -324,12 +326,12 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
         }
     }
     if (use_coop && !rt->sam_coop_ready) {
-        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<512, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<1024, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<512, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<1024, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+#define ULLIS_COOP_SMEM(NT, MODE) \
+    ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_coop_kernel<NT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024))
+        ULLIS_COOP_SMEM(256, 0); ULLIS_COOP_SMEM(512, 0); ULLIS_COOP_SMEM(1024, 0);
+        ULLIS_COOP_SMEM(256, 1); ULLIS_COOP_SMEM(512, 1); ULLIS_COOP_SMEM(1024, 1);
+        ULLIS_COOP_SMEM(256, 2); ULLIS_COOP_SMEM(512, 2); ULLIS_COOP_SMEM(1024, 2);
+#undef ULLIS_COOP_SMEM
         rt->sam_coop_ready = true;
     }
     for (size_t s0 = 0; s0 < streams; s0 += wave) {
@@ -344,6 +346,8 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
             const unsigned p1_grid = (unsigned)((pass1_warps * 32 + 127) / 128);
             const uint32_t dense = 96u * (uint32_t)rt->sm_count, sparse = rt->sam_sparse_per_sm * (uint32_t)rt->sm_count;
             const bool split = rt->sam_split && rt->sam_words;
+            const bool defer = !split && rt->sam_words && rt->sam_defer_climb;
+            const int coop_mode = split ? 1 : defer ? 2 : 0;
             if (split) {
                 rosa_extend_kernel<<<p1_grid, 128, 0, rt->stream>>>(scratch, stride, k_sw, list, count, s0, n,
                                                                    (uint32_t)time, wps, pass1_lanes, dense, sparse);
@@ -359,26 +363,25 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
             } else {
                 rosa_pass1_kernel<<<p1_grid, 128, 0, rt->stream>>>(
                     scratch, stride, q_sw, k_sw, list, count, s0, n, (uint32_t)time, wps, pass1_lanes, dense, sparse,
-                    rt->sam_words ? 1 : 0);
+                    rt->sam_words ? (defer ? 2 : 1) : 0);
                 rt->launched("rosa_pass1");
             }
             // threads per stream: the fewer CTAs shared memory lets an SM hold, the more threads each one gets
             const unsigned coop_per_sm = (unsigned)((227u * 1024u) / (coop.total + 1024u));
             const int coop_threads = rt->sam_coop_threads ? rt->sam_coop_threads : coop_per_sm >= 3 ? 256 : coop_per_sm == 2 ? 512 : 1024;
-#define ULLIS_COOP_LAUNCH(NT)                                                                                          \
-    do {                                                                                                               \
-        if (split)                                                                                                     \
-            rosa_coop_kernel<NT, true><<<(unsigned)n, NT, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, \
-                                                                                    count, s0, (uint32_t)time, wps,    \
-                                                                                    rt->dev_status);                   \
-        else                                                                                                           \
-            rosa_coop_kernel<NT, false><<<(unsigned)n, NT, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw,    \
-                                                                                     list, count, s0, (uint32_t)time,  \
-                                                                                     wps, rt->dev_status);             \
+#define ULLIS_COOP_LAUNCH_MODE(NT, MODE)                                                                                 \
+    rosa_coop_kernel<NT, MODE><<<(unsigned)n, NT, coop.total, rt->stream>>>(scratch, stride, v_sw, idx_sw, list, count, s0, \
+                                                                            (uint32_t)time, wps, rt->dev_status)
+#define ULLIS_COOP_LAUNCH(NT)                                 \
+    do {                                                      \
+        if (coop_mode == 1) ULLIS_COOP_LAUNCH_MODE(NT, 1);    \
+        else if (coop_mode == 2) ULLIS_COOP_LAUNCH_MODE(NT, 2); \
+        else ULLIS_COOP_LAUNCH_MODE(NT, 0);                   \
     } while (0)
             if (coop_threads == 256) ULLIS_COOP_LAUNCH(256);
             else if (coop_threads == 512) ULLIS_COOP_LAUNCH(512);
             else ULLIS_COOP_LAUNCH(1024);
+#undef ULLIS_COOP_LAUNCH_MODE
 #undef ULLIS_COOP_LAUNCH
             rt->launched("rosa_coop");
             continue;

@@ -91,9 +91,11 @@ constexpr uint32_t LAST_OF_SUBLIST = 0x80000000u;   // flag in an event word: th
 
 // One CTA of NT threads; `B` is the stream's global scratch block
 // after euler_pass1.  Every thread of the CTA must call this.
-// SPLIT: pass 1 ran in parts (sam_core.cuh) and left the walk's (w_t, h_t) in vq / head instead of v_t: the climb
-// to v_t happens here, every step by itself, while the query states are copied into shared memory.
-template <int NT, bool SPLIT = false>
+// CLIMB: pass 1 left the walk's (w_t, h_t) in vq / head instead of v_t (sam_core.cuh: the split form, or the
+// interleaved form with the deferred climb): the climb to v_t happens here, every step by itself, while the query
+// states are copied into shared memory.  ORIG: the clones are the states with an `orig` entry (split form) instead
+// of the ones in the clone bitmap.
+template <int NT, bool CLIMB = false, bool ORIG = false>
 __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<uint16_t>& B, const uint32_t* vw,
                                                 uint32_t* out, uint32_t T) {
     constexpr uint32_t NIL = 0xFFFFu, END = 0xFFFFu;
@@ -120,7 +122,7 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
         kid_min[v] = 0xFFFFFFFFu;
         kid_max[v] = 0u;
     }
-    if (SPLIT) {   // a clone is a state with an `orig` entry (the split extend keeps no bitmap)
+    if (ORIG) {   // a clone is a state with an `orig` entry (the split extend keeps no bitmap)
         for (uint32_t v = tid; v < ((n + 31u) & ~31u); v += NT) {
             const uint32_t word = __ballot_sync(0xffffffffu, v < n && B.next[v] != NIL);
             if (lane == 0) cbits[v >> 5] = word;
@@ -292,9 +294,9 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
             const uint32_t i = i0 + NT * u;
             a[u] = i < T ? B.vq[i] : (uint16_t)NIL;
             b[u] = i < T ? B.jid[i] : (uint16_t)0;
-            if (SPLIT) hq[u] = (i < T && a[u] != NIL) ? B.head[i] : (uint16_t)0;
+            if (CLIMB) hq[u] = (i < T && a[u] != NIL) ? B.head[i] : (uint16_t)0;
         }
-        if (SPLIT) {
+        if (CLIMB) {
 #pragma unroll
             for (int u = 0; u < 8; ++u) a[u] = (uint16_t)euler_climb_words(B.N, a[u], hq[u], b[u]);
         }

@@ -424,6 +424,11 @@ SAM_HD void store_words(Node<uint16_t>* N, uint32_t id, uint32_t x, uint32_t y) 
     *reinterpret_cast<unsigned long long*>(N + id) = (unsigned long long)x | ((unsigned long long)y << 32);
 }
 
+// DEFER_CLIMB: the walk up the links to the state whose `last` the step reads (src/rosa.rs:120-128) does not feed
+// the next step, so it need not sit in this serial loop: the step then only records where the walk ended, (w_t, h_t)
+// in vq / head, and euler_climb_words finds v_t later, every step by itself, with the links read as of step t (a
+// link that points to a state younger than jid[t] is followed on to the first older one).
+template <bool DEFER_CLIMB = false>
 SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T) {
     constexpr uint32_t NIL = 0xFFFFu;
     Node<uint16_t>* N = B.N;
@@ -469,14 +474,18 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
                 v = c;
                 NodeWords nv = load_words(N, v);
                 nw = nv;                          // the state the next query starts from
-                for (;;) {
-                    const uint32_t f = nv.y & 0xFFFFu;
-                    if (f == NIL) break;
-                    const NodeWords nf = load_words(N, f);
-                    if ((nf.y >> 16) < x) break;
-                    v = f; nv = nf;
+                if (DEFER_CLIMB) {
+                    B.head[i] = (uint16_t)x;      // v stays c: the climb happens later
+                } else {
+                    for (;;) {
+                        const uint32_t f = nv.y & 0xFFFFu;
+                        if (f == NIL) break;
+                        const NodeWords nf = load_words(N, f);
+                        if ((nf.y >> 16) < x) break;
+                        v = f; nv = nf;
+                    }
+                    if ((nv.y >> 16) == 0) v = NIL;   // only the root has length 0
                 }
-                if ((nv.y >> 16) == 0) v = NIL;   // only the root has length 0
                 w = c; h = x;
             }
             B.vq[i] = (uint16_t)v;
@@ -726,6 +735,15 @@ SAM_HD uint32_t euler_climb_words(const Node<uint16_t>* N, uint32_t w, uint32_t 
         v = f; nv = nf;
     }
     return (nv.y >> 16) == 0 ? NIL : v;
+}
+
+// Interleaved pass 1 without the climb, then the climb of every step (what rosa_pass1_kernel with the deferred
+// climb and the tour kernel compute together).
+SAM_HD uint32_t euler_pass1_deferred(EulerBlock<uint16_t>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T) {
+    const uint32_t n = euler_pass1_words<true>(B, qw, kw, T);
+    for (uint32_t t = 0; t < T; ++t)
+        B.vq[t] = (uint16_t)euler_climb_words(B.N, B.vq[t], B.head[t], B.jid[t]);
+    return n;
 }
 
 // The three parts one after the other (what the split kernels compute together): same vq / jid / states as
