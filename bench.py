@@ -272,15 +272,24 @@ def extra_measurements(args, rt, stream, torch, peaks):
                "automaton_streams_last_layer": counts["automaton"], "constant_q_streams_last_layer": counts["constant_q"],
                "streams_per_layer": counts["total"]}
         if with_kernels:
+            # one more forward with an event behind every launch, itself between two events: what share of that
+            # forward no kernel accounts for (launch gaps: at one sequence a kernel is often shorter than a launch)
             rt.kernel_timing(True)
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(stream)
             model.enqueue_forward_ce(cuda.CE_NO_IGNORE, B, ctx)
+            a1.record(stream)
             model.read_loss()
             km = rt.kernel_times()
             rt.kernel_timing(False)
-            busy = sum(t for k, (t, _) in km.items() if not k.startswith("("))
+            inst_ms = a0.elapsed_time(a1)
+            busy = sum(t for k, (t, _) in km.items() if not k.startswith("(") and k != "rosa_constq")   # side stream: overlaps
+            res["instrumented_forward_ms"] = inst_ms
             res["kernel_ms_sum_instrumented"] = busy
             res["launches"] = int(sum(n for k, (_, n) in km.items() if not k.startswith("(")))
-            res["launch_gap_share"] = max(0.0, 1.0 - busy / ms) if ms > 0 else None
+            res["launch_gap_share"] = max(0.0, 1.0 - busy / inst_ms) if inst_ms > 0 else None
+            top = sorted(((k, t) for k, (t, _) in km.items() if not k.startswith("(")), key=lambda kv: -kv[1])[:4]
+            res["top_kernels_ms"] = {k: round(t, 3) for k, t in top}
         model.close()
         return res, data
 

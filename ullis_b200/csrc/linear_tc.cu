@@ -351,10 +351,10 @@ fix_collect_kernel(const uint32_t* __restrict__ flags, size_t sw, size_t batch, 
 
 // The exact recomputation of the listed outputs, a warp for 32 entries at a time.  The terms +/- in_i of an
 // output have to be added one after the other in f32 (that order is what makes the sign exact), which only a
-// single thread can do; everything before it is shared: for 64 input columns at a time the whole warp loads the
-// rows of one entry after the other side by side (256 bytes per request instead of 32 requests into 32 rows),
-// forms the signed terms and leaves them in shared memory, and then lane e adds up the 64 terms of entry e.
-constexpr int FIXQ_WARPS = 4, FIXQ_COLS = 64, FIXQ_PITCH = FIXQ_COLS + 1;
+// single thread can do; everything before it is shared: for 128 input columns at a time the whole warp loads the
+// rows of one entry after the other side by side (512 bytes per request instead of 32 requests into 32 rows),
+// forms the signed terms and leaves them in shared memory, and then lane e adds up the 128 terms of entry e.
+constexpr int FIXQ_WARPS = 2, FIXQ_COLS = 128, FIXQ_PITCH = FIXQ_COLS + 1;
 
 __global__ void __launch_bounds__(FIXQ_WARPS * 32)
 fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, const uint16_t* __restrict__ mk,
@@ -363,66 +363,76 @@ fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, c
                  const uint32_t* __restrict__ list, uint32_t cap, const uint32_t* __restrict__ ctrl, size_t sw, size_t T,
                  size_t C, size_t wps) {
     __shared__ float terms[FIXQ_WARPS][32 * FIXQ_PITCH];
+    // what the whole warp needs to know about entry e, written by lane e once per task
+    __shared__ const float* e_row[FIXQ_WARPS][32];
+    __shared__ const uint32_t* e_w[FIXQ_WARPS][32];
+    __shared__ const uint16_t* e_mix[FIXQ_WARPS][32];
+    __shared__ uint32_t e_flags[FIXQ_WARPS][32];   // 1: first step of its sequence (no row before it), 2: entry exists
     if (ctrl[1]) return;   // the list overflowed: the window kernel redoes everything
     const uint32_t count = min(ctrl[0], cap);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* mine = terms[warp];
     const uint32_t tasks = (count + 31u) / 32u;
     for (uint32_t task = blockIdx.x * FIXQ_WARPS + warp; task < tasks; task += gridDim.x * FIXQ_WARPS) {
-        // lane e owns entry e of the task
         const uint32_t i = task * 32u + lane;
         const bool live = i < count;
         const uint32_t entry = live ? list[i] : 0u, tt = entry & 31u;
         const size_t wi = entry >> 5, m = wi / sw, rem = wi % sw;
         const size_t s = rem / wps, word = rem % wps, b = s / C, ch = s % C, t = word * 32 + tt;
-        const float* my_row = x + (b * T + t) * C;
         const PackedWeights& W = m == 0 ? wq : m == 1 ? wk : wv;
-        const uint32_t* my_w = W.bits + (ch * C >> 5);            // C % 32 == 0 on this path
-        const uint32_t my_flags = (uint32_t)m | (t == 0 ? 4u : 0u) | (live ? 8u : 0u);
+        e_row[warp][lane] = x + (b * T + t) * C;
+        e_w[warp][lane] = W.bits + (ch * C >> 5);               // C % 32 == 0 on this path
+        e_mix[warp][lane] = m == 0 ? mq : m == 1 ? mk : mv;
+        e_flags[warp][lane] = (t == 0 ? 1u : 0u) | (live ? 2u : 0u);
+        __syncwarp();
         float sum = 0.0f;
         for (size_t i0 = 0; i0 < C; i0 += FIXQ_COLS) {
-            // eight entries at a time: first every load of the eight (they do not depend on each other and the
-            // compiler cannot move a load above a store to shared memory by itself), then the arithmetic
-            for (int e0 = 0; e0 < 32; e0 += 8) {
-                float2 cur[8], prev[8];
-                uint32_t mw[8], ww[8], fl[8];
+            const size_t c = i0 + 4 * lane;
+            // four entries at a time: first every load of the four (they do not depend on each other, and the
+            // compiler will not move a load above a store to shared memory by itself), then the arithmetic
+            for (int e0 = 0; e0 < 32; e0 += 4) {
+                float4 cur[4], prev[4];
+                uint2 mw[4];
+                uint32_t ww[4], fl[4];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < 4; ++u) {
                     const int e = e0 + u;
-                    fl[u] = __shfl_sync(0xffffffffu, my_flags, e);
-                    const float* row = reinterpret_cast<const float*>(
-                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_row), e));
-                    const uint32_t* wrow = reinterpret_cast<const uint32_t*>(
-                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_w), e));
-                    const uint16_t* mix = (fl[u] & 3u) == 0 ? mq : (fl[u] & 3u) == 1 ? mk : mv;
-                    const size_t c = i0 + 2 * lane;
-                    cur[u] = make_float2(0.f, 0.f);
-                    prev[u] = make_float2(0.f, 0.f);
-                    mw[u] = 0u;
+                    fl[u] = e_flags[warp][e];
+                    cur[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    prev[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    mw[u] = make_uint2(0u, 0u);
                     ww[u] = 0u;
-                    if (fl[u] & 8u) {                              // uniform over the warp
-                        cur[u] = *reinterpret_cast<const float2*>(row + c);
-                        if (!(fl[u] & 4u)) prev[u] = *reinterpret_cast<const float2*>(row - C + c);
-                        mw[u] = *reinterpret_cast<const uint32_t*>(mix + c);
-                        ww[u] = wrow[c >> 5] >> (c & 31);
+                    if (fl[u] & 2u) {                              // uniform over the warp
+                        const float* row = e_row[warp][e];
+                        cur[u] = *reinterpret_cast<const float4*>(row + c);
+                        if (!(fl[u] & 1u)) prev[u] = *reinterpret_cast<const float4*>(row - C + c);
+                        mw[u] = *reinterpret_cast<const uint2*>(e_mix[warp][e] + c);
+                        ww[u] = e_w[warp][e][c >> 5] >> (c & 31);
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < 4; ++u) {
                     const int e = e0 + u;
-                    const bool first_step = (fl[u] & 4u) != 0;
-                    const float xx0 = first_step ? -cur[u].x : __fsub_rn(prev[u].x, cur[u].x);
-                    const float xx1 = first_step ? -cur[u].y : __fsub_rn(prev[u].y, cur[u].y);
-                    const float in0 = __fadd_rn(cur[u].x, __fmul_rn(xx0, h2f((uint16_t)(mw[u] & 0xFFFFu))));
-                    const float in1 = __fadd_rn(cur[u].y, __fmul_rn(xx1, h2f((uint16_t)(mw[u] >> 16))));
-                    mine[e * FIXQ_PITCH + 2 * lane] = (ww[u] & 1u) ? in0 : -in0;
-                    mine[e * FIXQ_PITCH + 2 * lane + 1] = (ww[u] & 2u) ? in1 : -in1;
+                    const bool first_step = (fl[u] & 1u) != 0;
+                    const float xs[4] = {cur[u].x, cur[u].y, cur[u].z, cur[u].w};
+                    const float ps[4] = {prev[u].x, prev[u].y, prev[u].z, prev[u].w};
+                    const uint16_t mb[4] = {(uint16_t)(mw[u].x & 0xFFFFu), (uint16_t)(mw[u].x >> 16),
+                                            (uint16_t)(mw[u].y & 0xFFFFu), (uint16_t)(mw[u].y >> 16)};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float xx = first_step ? -xs[k] : __fsub_rn(ps[k], xs[k]);
+                        const float in = __fadd_rn(xs[k], __fmul_rn(xx, h2f(mb[k])));
+                        // column 4 * lane + k of the chunk is kept at k * 32 + lane: no bank conflict here (lanes side
+                        // by side) nor in the sums below (rows 129 words apart)
+                        mine[e * FIXQ_PITCH + k * 32 + lane] = ((ww[u] >> k) & 1u) ? in : -in;
+                    }
                 }
             }
             __syncwarp();
             if (live) {
 #pragma unroll 8
-                for (int k = 0; k < FIXQ_COLS; ++k) sum = __fadd_rn(sum, mine[lane * FIXQ_PITCH + k]);   // i ascending
+                for (int k = 0; k < FIXQ_COLS; ++k)   // i ascending
+                    sum = __fadd_rn(sum, mine[lane * FIXQ_PITCH + (k & 3) * 32 + (k >> 2)]);
             }
             __syncwarp();
         }
@@ -431,6 +441,7 @@ fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, c
             uint32_t* bits = m == 0 ? bq : m == 1 ? bk : bv;
             if (y > 0.0f) atomicOr(&bits[rem], 1u << tt); else atomicAnd(&bits[rem], ~(1u << tt));
         }
+        __syncwarp();   // the entry table is rewritten by the next task
     }
 }
 
@@ -907,7 +918,7 @@ bool rosa_qkv_bits(ullis_cuda_runtime* rt, const float* ln3_out, const LayerWeig
         rt->zero(ctrl, 8);
         fix_collect_kernel<<<4 * (unsigned)rt->sm_count, 256, 0, rt->stream>>>(flags, sw, batch, d, wps, list, (uint32_t)cap, ctrl);
         rt->launched("fix_collect");
-        fix_apply_kernel<<<8 * (unsigned)rt->sm_count, FIXQ_WARPS * 32, 0, rt->stream>>>(
+        fix_apply_kernel<<<12 * (unsigned)rt->sm_count, FIXQ_WARPS * 32, 0, rt->stream>>>(
             ln3_out, L.x_q, L.x_k, L.x_v, L.q, L.k, L.v, q_sw, k_sw, v_sw, list, (uint32_t)cap, ctrl, sw, time, d, wps);
         rt->launched("fix_apply");
         only_if = ctrl + 1;
