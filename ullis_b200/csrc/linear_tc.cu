@@ -367,7 +367,7 @@ fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, c
     __shared__ const float* e_row[FIXQ_WARPS][32];
     __shared__ const uint32_t* e_w[FIXQ_WARPS][32];
     __shared__ const uint16_t* e_mix[FIXQ_WARPS][32];
-    __shared__ uint32_t e_flags[FIXQ_WARPS][32];   // 1: first step of its sequence (no row before it), 2: entry exists
+    __shared__ uint32_t e_flags[FIXQ_WARPS][32];   // 1: first step of its sequence (no row before it)
     if (ctrl[1]) return;   // the list overflowed: the window kernel redoes everything
     const uint32_t count = min(ctrl[0], cap);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -380,10 +380,12 @@ fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, c
         const size_t wi = entry >> 5, m = wi / sw, rem = wi % sw;
         const size_t s = rem / wps, word = rem % wps, b = s / C, ch = s % C, t = word * 32 + tt;
         const PackedWeights& W = m == 0 ? wq : m == 1 ? wk : wv;
-        e_row[warp][lane] = x + (b * T + t) * C;
+        // a lane without an entry (the tail of the list) stands in with row 0 of x: every load below is then
+        // unconditional, and only the final write looks at `live`
+        e_row[warp][lane] = live ? x + (b * T + t) * C : x;
         e_w[warp][lane] = W.bits + (ch * C >> 5);               // C % 32 == 0 on this path
         e_mix[warp][lane] = m == 0 ? mq : m == 1 ? mk : mv;
-        e_flags[warp][lane] = (t == 0 ? 1u : 0u) | (live ? 2u : 0u);
+        e_flags[warp][lane] = (t == 0 || !live) ? 1u : 0u;     // 1: no row before it
         __syncwarp();
         float sum = 0.0f;
         for (size_t i0 = 0; i0 < C; i0 += FIXQ_COLS) {
@@ -398,17 +400,12 @@ fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, c
                 for (int u = 0; u < 4; ++u) {
                     const int e = e0 + u;
                     fl[u] = e_flags[warp][e];
-                    cur[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    prev[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    mw[u] = make_uint2(0u, 0u);
-                    ww[u] = 0u;
-                    if (fl[u] & 2u) {                              // uniform over the warp
-                        const float* row = e_row[warp][e];
-                        cur[u] = *reinterpret_cast<const float4*>(row + c);
-                        if (!(fl[u] & 1u)) prev[u] = *reinterpret_cast<const float4*>(row - C + c);
-                        mw[u] = *reinterpret_cast<const uint2*>(e_mix[warp][e] + c);
-                        ww[u] = e_w[warp][e][c >> 5] >> (c & 31);
-                    }
+                    const float* row = e_row[warp][e];
+                    cur[u] = *reinterpret_cast<const float4*>(row + c);
+                    // the row before it, or (first step of a sequence) the row itself: its value is not used then
+                    prev[u] = *reinterpret_cast<const float4*>((fl[u] & 1u) ? row + c : row - C + c);
+                    mw[u] = *reinterpret_cast<const uint2*>(e_mix[warp][e] + c);
+                    ww[u] = e_w[warp][e][c >> 5] >> (c & 31);
                 }
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {

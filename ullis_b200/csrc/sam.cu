@@ -92,12 +92,14 @@ rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint
 // Two-kernel form of the O(T log T) schedule for streams whose tour / pass 2
 // working set fits shared memory: pass 1 one thread per stream (below), then
 // one warp per stream for the parallel phases (sam_coop.cuh).
+// WORDS: 0 = field-wise state layout, 1 = packed words, 2 = packed words with the climb left to the tour kernel
+// (a kernel each, so that the form that runs gets the registers to itself)
+template <int WORDS>
 __global__ void __launch_bounds__(128, 16)
 rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
                   const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ list,
                   const uint32_t* __restrict__ count, size_t first, size_t wave, uint32_t T, size_t wps, int lanes,
-                  uint32_t dense_count, uint32_t sparse_count, int words) {
-    // words: 0 = field-wise state layout, 1 = packed words, 2 = packed words with the climb left to the tour kernel
+                  uint32_t dense_count, uint32_t sparse_count) {
     // lanes == 0: choose from the number of streams that are left, which only the device knows -
     // many streams: four per warp (fewer issued instructions); fewer: two, then one per warp (more
     // warps to hide the pointer-chase latency).  The grid is sized for one per warp.
@@ -112,8 +114,8 @@ rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const ui
     if (item >= wave || first + item >= *count) return;
     const size_t s = list[first + item];
     sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
-    if (words == 2) sam::euler_pass1_words<true>(B, q_sw + s * wps, k_sw + s * wps, T);
-    else if (words) sam::euler_pass1_words<false>(B, q_sw + s * wps, k_sw + s * wps, T);
+    if (WORDS == 2) sam::euler_pass1_words<true>(B, q_sw + s * wps, k_sw + s * wps, T);
+    else if (WORDS == 1) sam::euler_pass1_words<false>(B, q_sw + s * wps, k_sw + s * wps, T);
     else sam::euler_pass1<uint16_t>(B, q_sw + s * wps, k_sw + s * wps, T, nullptr);
 }
 
@@ -361,9 +363,13 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
                 }
                 rt->launched("rosa_walk");
             } else {
-                rosa_pass1_kernel<<<p1_grid, 128, 0, rt->stream>>>(
-                    scratch, stride, q_sw, k_sw, list, count, s0, n, (uint32_t)time, wps, pass1_lanes, dense, sparse,
-                    rt->sam_words ? (defer ? 2 : 1) : 0);
+#define ULLIS_PASS1(W) \
+    rosa_pass1_kernel<W><<<p1_grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, k_sw, list, count, s0, n, (uint32_t)time, \
+                                                          wps, pass1_lanes, dense, sparse)
+                if (!rt->sam_words) ULLIS_PASS1(0);
+                else if (defer) ULLIS_PASS1(2);
+                else ULLIS_PASS1(1);
+#undef ULLIS_PASS1
                 rt->launched("rosa_pass1");
             }
             // threads per stream: the fewer CTAs shared memory lets an SM hold, the more threads each one gets

@@ -91,10 +91,10 @@ constexpr uint32_t LAST_OF_SUBLIST = 0x80000000u;   // flag in an event word: th
 
 // One CTA of NT threads; `B` is the stream's global scratch block
 // after euler_pass1.  Every thread of the CTA must call this.
-// CLIMB: pass 1 left the walk's (w_t, h_t) in vq / head instead of v_t (sam_core.cuh: the split form, or the
-// interleaved form with the deferred climb): the climb to v_t happens here, every step by itself, while the query
-// states are copied into shared memory.  ORIG: the clones are the states with an `orig` entry (split form) instead
-// of the ones in the clone bitmap.
+// CLIMB: pass 1 left the walk's (w_t, h_t) instead of v_t (sam_core.cuh): the climb to v_t happens here, every step
+// by itself, while the query states are copied into shared memory.  ORIG (the split form): (w_t, h_t) lie in vq /
+// head and the clones are the states with an `orig` entry.  CLIMB without ORIG (the interleaved form with the
+// deferred climb): (w_t, h_t) lie packed in `rec` and the clones are the states whose id is no jid[t].
 template <int NT, bool CLIMB = false, bool ORIG = false>
 __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<uint16_t>& B, const uint32_t* vw,
                                                 uint32_t* out, uint32_t T) {
@@ -106,6 +106,12 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
     uint32_t* cbits = reinterpret_cast<uint32_t*>(smem + L.clone_bits);
     uint32_t* vbits = reinterpret_cast<uint32_t*>(smem + L.vbits);
     uint32_t* round_rank = reinterpret_cast<uint32_t*>(smem + L.round_rank);
+    // the deferred-climb form of pass 1: clone flags per step and their prefix counts (2 * wps <= 1024 words)
+    uint32_t* step_words = round_rank;
+    uint32_t* step_prefix = round_rank + ((T + 31) / 32);
+    auto step_state = [&](uint32_t i) {
+        return 1u + i + step_prefix[i >> 5] + (uint32_t)__popc(step_words[i >> 5] & ((1u << (i & 31u)) - 1u));
+    };
     const uint32_t n = B.meta[0], wps = (T + 31) / 32;
     const uint32_t cap = node_capacity(T);
     const uint32_t blocks = (2 * n) >> 3;       // whole blocks of eight events: one list-ranking splitter each
@@ -127,14 +133,43 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
             const uint32_t word = __ballot_sync(0xffffffffu, v < n && B.next[v] != NIL);
             if (lane == 0) cbits[v >> 5] = word;
         }
+    } else if (CLIMB) {
+        // Pass 1 kept one bit per step ("this step made a clone").  Ids are handed out in order, so the state of
+        // step i is 1 + i + (clones before step i): a prefix count over the flag words (kept, with the words, in
+        // the buffer the pass-2 rounds use much later); the clones are the states no step created.
+        for (uint32_t w = tid; w < wps; w += NT) step_words[w] = B.clone_bits[w];
+        for (uint32_t w = tid; w < (n + 31) / 32; w += NT) cbits[w] = 0u;
+        __syncthreads();
+        if (tid < 32) {
+            uint32_t carry = 0;
+            for (uint32_t base = 0; base < wps; base += 32) {
+                const uint32_t c = base + lane < wps ? __popc(step_words[base + lane]) : 0u;
+                uint32_t incl = c;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += up;
+                }
+                if (base + lane < wps) step_prefix[base + lane] = carry + incl - c;
+                carry += __shfl_sync(0xffffffffu, incl, 31);
+            }
+        }
+        __syncthreads();
+        for (uint32_t i = tid; i < T; i += NT) {
+            const uint32_t j = step_state(i);
+            atomicOr(&cbits[j >> 5], 1u << (j & 31));
+        }
+        __syncthreads();
+        for (uint32_t w = tid; w < (n + 31) / 32; w += NT) cbits[w] = ~cbits[w];
     } else {
         for (uint32_t w = tid; w < (n + 31) / 32; w += NT) cbits[w] = B.clone_bits[w];
     }
     for (uint32_t w = tid; w < wps; w += NT) vbits[w] = vw[w];
     // the query states and new-state ids are needed much later: ask for them now, 128 bytes per thread
     for (uint32_t i = tid * 64u; i < T; i += NT * 64u) {
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(B.vq + i));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(B.jid + i));
+        if (CLIMB && !ORIG) asm volatile("prefetch.global.L2 [%0];" ::"l"(B.rec + i));
+        else asm volatile("prefetch.global.L2 [%0];" ::"l"(B.vq + i));
+        if (!(CLIMB && !ORIG)) asm volatile("prefetch.global.L2 [%0];" ::"l"(B.jid + i));
     }
     uint32_t* replay_end = reinterpret_cast<uint32_t*>(smem + L.ctrl);
     if (tid == 0) *replay_end = 0;
@@ -292,9 +327,16 @@ __device__ __forceinline__ void coop_tour_pass2(uint8_t* smem, const EulerBlock<
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const uint32_t i = i0 + NT * u;
-            a[u] = i < T ? B.vq[i] : (uint16_t)NIL;
-            b[u] = i < T ? B.jid[i] : (uint16_t)0;
-            if (CLIMB) hq[u] = (i < T && a[u] != NIL) ? B.head[i] : (uint16_t)0;
+            if (CLIMB && !ORIG) {
+                const uint32_t r = i < T ? B.rec[i] : NIL;
+                a[u] = (uint16_t)(r & 0xFFFFu);
+                hq[u] = (uint16_t)(r >> 16);
+            } else {
+                a[u] = i < T ? B.vq[i] : (uint16_t)NIL;
+                if (CLIMB) hq[u] = (i < T && a[u] != NIL) ? B.head[i] : (uint16_t)0;
+            }
+            if (CLIMB && !ORIG) b[u] = i < T ? (uint16_t)step_state(i) : (uint16_t)0;
+            else b[u] = i < T ? B.jid[i] : (uint16_t)0;
         }
         if (CLIMB) {
 #pragma unroll

@@ -366,6 +366,7 @@ struct EulerBlock {
     Node<Ix>* N;
     Ix *vq, *jid, *head, *next;
     Pair<Ix>* lh;    // rank range [a, b) of the stamped states below each state
+    uint32_t* rec;   // 16-bit ids only, same memory as lh: w_t | h_t << 16 of the pass 1 that leaves the climb for later
     uint32_t* clone_bits;
     uint32_t* meta;
     SAM_HD EulerBlock(uint8_t* scratch, uint32_t T) {
@@ -376,6 +377,7 @@ struct EulerBlock {
         head = reinterpret_cast<Ix*>(scratch + L.head);
         next = reinterpret_cast<Ix*>(scratch + L.next);
         lh = reinterpret_cast<Pair<Ix>*>(scratch + L.lh);
+        rec = reinterpret_cast<uint32_t*>(scratch + L.lh);
         clone_bits = reinterpret_cast<uint32_t*>(scratch + L.clone_bits);
         meta = reinterpret_cast<uint32_t*>(scratch + L.meta);
     }
@@ -425,16 +427,23 @@ SAM_HD void store_words(Node<uint16_t>* N, uint32_t id, uint32_t x, uint32_t y) 
 }
 
 // DEFER_CLIMB: the walk up the links to the state whose `last` the step reads (src/rosa.rs:120-128) does not feed
-// the next step, so it need not sit in this serial loop: the step then only records where the walk ended, (w_t, h_t)
-// in vq / head, and euler_climb_words finds v_t later, every step by itself, with the links read as of step t (a
-// link that points to a state younger than jid[t] is followed on to the first older one).
+// the next step, so it need not sit in this serial loop: the step then only records where the walk ended, as one
+// word w_t | h_t << 16 in `rec` (NIL for a miss), and euler_climb_words finds v_t later, every step by itself, with
+// the links read as of step t (a link that points to a state younger than jid[t] is followed on to the first older
+// one).  This form keeps neither a clone bitmap over the states (a read-modify-write of global memory in seven
+// steps out of ten on biased streams) nor the jid array: it leaves one bit per STEP, "this step made a clone", in
+// the words of clone_bits (word t / 32, bit t % 32).  Ids are handed out in order, one per step plus one per
+// clone, so jid[t] = 1 + t + (clones of the steps before t), and the clones are the states whose id is no jid[t];
+// the tour works both out by itself.  Every store taken out of this loop shortens the serial chain.
 template <bool DEFER_CLIMB = false>
 SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T) {
     constexpr uint32_t NIL = 0xFFFFu;
     Node<uint16_t>* N = B.N;
     uint16_t* half = reinterpret_cast<uint16_t*>(N);   // field f of state s at half[4 * s + f]
-    const uint32_t cap = node_capacity(T);
-    for (uint32_t wd = 0; wd < (cap + 31) / 32; ++wd) B.clone_bits[wd] = 0;
+    if (!DEFER_CLIMB) {
+        const uint32_t cap = node_capacity(T);
+        for (uint32_t wd = 0; wd < (cap + 31) / 32; ++wd) B.clone_bits[wd] = 0;
+    }
     store_words(N, 0, 0xFFFFFFFFu, NIL);   // root: no children, no link, length 0
     uint32_t u = 1, g = 0, gmax = 0, gfail = NIL;   // extend side
     uint32_t w = 0, h = 0;                          // query side
@@ -447,8 +456,12 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
     NodeWords ne;
     ne.x = 0xFFFFFFFFu; ne.y = NIL;
     uint32_t qword = 0, kword = 0;
+    uint32_t cloned = 0;   // DEFER_CLIMB: bit (i % 32) = step i made a clone; one word per 32 steps goes to clone_bits
     for (uint32_t i = 0; i < T; ++i) {
-        if ((i & 31u) == 0) { qword = qw[i >> 5]; kword = kw[i >> 5]; }
+        if ((i & 31u) == 0) {
+            qword = qw[i >> 5]; kword = kw[i >> 5];
+            if (DEFER_CLIMB && i) { B.clone_bits[(i >> 5) - 1u] = cloned; cloned = 0; }
+        }
         const uint32_t qs = (qword & 1u) << 4, kb = kword & 1u, ks = kb << 4;
         qword >>= 1; kword >>= 1;
         const uint32_t e0 = gfail;
@@ -475,7 +488,7 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
                 NodeWords nv = load_words(N, v);
                 nw = nv;                          // the state the next query starts from
                 if (DEFER_CLIMB) {
-                    B.head[i] = (uint16_t)x;      // v stays c: the climb happens later
+                    v = c | (x << 16);            // the record of this step: the climb happens later
                 } else {
                     for (;;) {
                         const uint32_t f = nv.y & 0xFFFFu;
@@ -488,7 +501,8 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
                 }
                 w = c; h = x;
             }
-            B.vq[i] = (uint16_t)v;
+            if (DEFER_CLIMB) B.rec[i] = v;   // NIL (0xFFFF) for a miss
+            else B.vq[i] = (uint16_t)v;
         }
         // ---- extend (src/rosa.rs:139-167); every store to an existing state is mirrored into nw when it is state w
         {
@@ -522,7 +536,8 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
                     half[4 * d + 2] = (uint16_t)b;
                     if (d == w) nw.y = (nw.y & 0xFFFF0000u) | b;
                     jfail = b;
-                    B.clone_bits[b >> 5] |= 1u << (b & 31);
+                    if (DEFER_CLIMB) cloned |= 1u << (i & 31u);
+                    else B.clone_bits[b >> 5] |= 1u << (b & 31);
                     // p still has d as its child (that is where the walk stopped): redirect it, then go on up
                     for (;;) {
                         half[4 * p + kb] = (uint16_t)b;
@@ -543,10 +558,11 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
             gmax += 1;
             store_words(N, j, 0xFFFFFFFFu, jfail | (gmax << 16));
             g = j; gfail = jfail;
-            B.jid[i] = (uint16_t)j;
+            if (!DEFER_CLIMB) B.jid[i] = (uint16_t)j;   // otherwise j_i = 1 + i + (clones of the steps before i)
         }
         if (!hit) nw = load_words(N, 0);   // a miss sends the query back to the root
     }
+    if (DEFER_CLIMB && T) B.clone_bits[(T - 1u) >> 5] = cloned;
     B.meta[0] = u;
     return u;
 }
@@ -741,8 +757,18 @@ SAM_HD uint32_t euler_climb_words(const Node<uint16_t>* N, uint32_t w, uint32_t 
 // climb and the tour kernel compute together).
 SAM_HD uint32_t euler_pass1_deferred(EulerBlock<uint16_t>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T) {
     const uint32_t n = euler_pass1_words<true>(B, qw, kw, T);
-    for (uint32_t t = 0; t < T; ++t)
-        B.vq[t] = (uint16_t)euler_climb_words(B.N, B.vq[t], B.head[t], B.jid[t]);
+    for (uint32_t t = 0, clones = 0; t < T; ++t) {   // the new-state ids from the per-step clone flags
+        B.jid[t] = (uint16_t)(1u + t + clones);
+        clones += (B.clone_bits[t >> 5] >> (t & 31u)) & 1u;
+    }
+    for (uint32_t t = 0; t < T; ++t) {
+        const uint32_t r = B.rec[t];
+        B.vq[t] = (uint16_t)euler_climb_words(B.N, r & 0xFFFFu, r >> 16, B.jid[t]);
+    }
+    // clones = the states that no step created as its new state
+    const uint32_t cap = node_capacity(T);
+    for (uint32_t wd = 0; wd < (cap + 31) / 32; ++wd) B.clone_bits[wd] = 0xFFFFFFFFu;
+    for (uint32_t t = 0; t < T; ++t) B.clone_bits[B.jid[t] >> 5] &= ~(1u << (B.jid[t] & 31));
     return n;
 }
 
