@@ -38,6 +38,7 @@ extern "C" {
 typedef struct ullis_cuda_runtime ullis_cuda_runtime;
 typedef struct ullis_cuda_model ullis_cuda_model;
 typedef struct ullis_cuda_generate_state ullis_cuda_generate_state;
+typedef struct ullis_cuda_rosa_pushers ullis_cuda_rosa_pushers;
 typedef struct ullis_cuda_train_state ullis_cuda_train_state;
 
 enum {
@@ -205,6 +206,22 @@ ULLIS_CUDA_API size_t ullis_cuda_generate_state_time(const ullis_cuda_generate_s
  * both cases the state is unchanged. */
 ULLIS_CUDA_API int32_t ullis_cuda_generate_step(ullis_cuda_generate_state* state, const uint32_t* tokens,
                                                 float* logits);
+
+/* RosaSam (src/rosa.rs:55-176) for `streams` independent 1-bit streams, kept on
+ * the device between calls: what a generate state holds per layer, at op
+ * level.  `capacity` is the number of pushes a stream can take (RosaSam grows
+ * without bound; here the memory is sized once).  RosaSam::push
+ * (src/rosa.rs:100-176) for every stream, `steps` times: q, k, v and idx are
+ * host arrays [steps, streams] of 0 / 1 bytes; idx[s, c] is what the
+ * reference's push returns for stream c at its position time + s.
+ * ULLIS_CUDA_ERR_SHAPE (nothing pushed) when time + steps > capacity. */
+ULLIS_CUDA_API int32_t ullis_cuda_rosa_pushers_create(ullis_cuda_runtime* rt, size_t streams, size_t capacity,
+                                                      ullis_cuda_rosa_pushers** out);
+ULLIS_CUDA_API void ullis_cuda_rosa_pushers_destroy(ullis_cuda_rosa_pushers* pushers);
+/* RosaSam::reset (src/rosa.rs:66-74). */
+ULLIS_CUDA_API int32_t ullis_cuda_rosa_pushers_reset(ullis_cuda_rosa_pushers* pushers);
+ULLIS_CUDA_API int32_t ullis_cuda_rosa_pushers_push(ullis_cuda_rosa_pushers* pushers, const uint8_t* q, const uint8_t* k,
+                                                    const uint8_t* v, size_t steps, uint8_t* idx);
 
 /* -------------------------------------------------------------------- train
  * One optimiser step with the weights, the BinaryConnect latents and the f32

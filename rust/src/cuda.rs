@@ -922,6 +922,53 @@ impl Drop for CudaGenerateState<'_, '_> {
     }
 }
 
+/// `streams` independent `RosaSam` automata (`src/rosa.rs:55-176`) kept on the device between calls: the
+/// per-layer state of a generate state at op level.
+#[derive(Debug)]
+pub struct CudaRosaPushers<'rt> {
+    raw: *mut sys::ullis_cuda_rosa_pushers,
+    rt: &'rt CudaRuntime,
+    streams: usize,
+}
+
+impl<'rt> CudaRosaPushers<'rt> {
+    /// `RosaSam::new` for every stream; `capacity` pushes fit (the reference's vectors grow instead).
+    pub fn new(rt: &'rt CudaRuntime, streams: usize, capacity: usize) -> Result<Self> {
+        let mut raw = std::ptr::null_mut();
+        // SAFETY: `raw` receives a fresh handle or stays null.
+        rt.check(unsafe { sys::ullis_cuda_rosa_pushers_create(rt.raw, streams, capacity, &mut raw) })?;
+        Ok(Self { raw, rt, streams })
+    }
+
+    /// `RosaSam::reset` (`src/rosa.rs:66-74`).
+    pub fn reset(&mut self) -> Result<()> {
+        // SAFETY: live handle.
+        self.rt.check(unsafe { sys::ullis_cuda_rosa_pushers_reset(self.raw) })
+    }
+
+    /// `RosaSam::push` (`src/rosa.rs:100-176`) for every stream, once per row: `q`, `k`, `v` are
+    /// `[steps, streams]` of 0 / 1; returns idx in the same layout.
+    pub fn push(&mut self, q: &[u8], k: &[u8], v: &[u8]) -> Result<Vec<u8>> {
+        if self.streams == 0 || q.len() % self.streams != 0 || k.len() != q.len() || v.len() != q.len() {
+            bail!("ROSA pushers take [steps, streams] bits for q, k and v");
+        }
+        let steps = q.len() / self.streams;
+        let mut idx = vec![0_u8; q.len()];
+        // SAFETY: the four slices hold steps * streams bytes.
+        self.rt.check(unsafe {
+            sys::ullis_cuda_rosa_pushers_push(self.raw, q.as_ptr(), k.as_ptr(), v.as_ptr(), steps, idx.as_mut_ptr())
+        })?;
+        Ok(idx)
+    }
+}
+
+impl Drop for CudaRosaPushers<'_> {
+    fn drop(&mut self) {
+        // SAFETY: destroyed exactly once, before the runtime it borrows.
+        unsafe { sys::ullis_cuda_rosa_pushers_destroy(self.raw) };
+    }
+}
+
 /// The fields of `CausalLoss` a device step produces (`src/model.rs:60-83`).
 #[derive(Clone, Copy, Debug, Default, PartialEq)]
 pub struct CudaTrainStep {

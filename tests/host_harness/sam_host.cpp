@@ -14,7 +14,7 @@ template <typename Ix>
 static int run_batch(int algo, const uint32_t* qw, const uint32_t* kw, const uint32_t* vw, size_t n_streams,
                      uint32_t T, uint32_t* out, unsigned long long* visits, unsigned long long* chain) {
     const size_t wps = (T + 31) / 32;
-    const size_t bytes = algo == 0 ? EagerLayout<Ix>(T).total : EulerLayout<Ix>(T).total;
+    const size_t bytes = algo == 0 ? EagerLayout<Ix>(T).total : algo == 6 ? GenLayout<Ix>(T).total : EulerLayout<Ix>(T).total;
     std::vector<uint8_t> scratch(bytes + 64);
     uint8_t* base = scratch.data();
     base += (64 - reinterpret_cast<uintptr_t>(base) % 64) % 64;
@@ -54,6 +54,19 @@ static int run_batch(int algo, const uint32_t* qw, const uint32_t* kw, const uin
             if (n > node_capacity(T)) return 2;
             euler_tour<uint16_t>(B, n);
             euler_pass2<uint16_t>(B, vw + s * wps, out + s * wps, T);
+            continue;
+        }
+        if (algo == 6) {   // incremental pushes of an automaton that is kept between calls (what generation does)
+            GenLayout<Ix> L(T);
+            WalkerState st;
+            st.u = 1; st.g = 0; st.w = 0; st.gmax = 0; st.gfail = 0; st.h = 0; st.steps = 0; st.pad = 0;
+            for (uint32_t w = 0; w < wps; ++w) out[s * wps + w] = 0;
+            for (uint32_t i = 0; i < T; ++i) {
+                const uint32_t bit = gen_push<Ix>(reinterpret_cast<Node<Ix>*>(base + L.nodes), reinterpret_cast<Ix*>(base + L.last),
+                                                  reinterpret_cast<Ix*>(base + L.path), vw + s * wps, &st,
+                                                  stream_bit(qw + s * wps, i), stream_bit(kw + s * wps, i));
+                out[s * wps + (i >> 5)] |= bit << (i & 31);
+            }
             continue;
         }
         if (algo == 7) {   // interleaved pass 1 with the climb taken out of the serial loop (16-bit state ids only)

@@ -64,6 +64,28 @@ def test_generate_equals_device_one_shot_in_exact_mode(cuda_rt, gen_case):
         cuda_rt.set_mode(cuda.MODE_FAST)
 
 
+def test_late_context_of_the_benchmark_model(cuda_rt):
+    """The whole 2 048-token context of the benchmark model, two sequences: by the end the suffix-link chains of the
+    biased channels are as long as the context, which is where the chain stamping (src/rosa.rs:168-173) is done
+    by a warp per stream from the chain kept as an array.  Every step against the device's one-shot forward in
+    EXACT mode (itself held to the oracle bit for bit in test_gpu_benchmark_shape)."""
+    d, layers, vocab, T, ffn = synth.CONFIGS["default"]
+    B = 2
+    data = synth.heron_checkpoint("default", batch_size=B)
+    tokens = synth.zipf_tokens(23, B * T, vocab).reshape(B, T)
+    cuda_rt.set_mode(cuda.MODE_EXACT)
+    try:
+        m = cuda.CudaHeron(cuda_rt, data)
+        one = m.logits(tokens.reshape(-1), B, T).reshape(B, T, vocab)
+        state = m.generate_state(B)
+        for t in range(T):
+            assert np.array_equal(m.generate_step(state, tokens[:, t]), one[:, t, :]), t
+        state.close()
+        m.close()
+    finally:
+        cuda_rt.set_mode(cuda.MODE_FAST)
+
+
 def test_generate_error_cases_leave_the_state_unchanged(cuda_rt, oracle):  # src/model.rs:2718-2723, 5044-5056
     data = synth.heron_checkpoint("tiny", batch_size=2, context_len=6)
     ref = oracle.HeronOracle(data)

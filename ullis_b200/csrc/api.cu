@@ -115,6 +115,7 @@ ullis_cuda_runtime* ullis_cuda_runtime::child(size_t i) {
     c->sam_words = sam_words;
     c->sam_split = sam_split;
     c->sam_defer_climb = sam_defer_climb;
+    c->sam_reload_w = sam_reload_w;
     c->sam_walk_chunked = sam_walk_chunked;
     c->sam_budget_bytes = sam_budget_bytes / (children.size() + 1);
     c->tc_fix_list = tc_fix_list;
@@ -294,6 +295,7 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         if (const char* env = getenv("ULLIS_CUDA_FUSE_LN")) rt->tc_fuse_ln = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_FIX_LIST")) rt->tc_fix_list = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_WALK_CHUNKED")) rt->sam_walk_chunked = atoi(env) != 0;
+        if (const char* env = getenv("ULLIS_CUDA_SAM_RELOAD_W")) rt->sam_reload_w = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_DEFER_CLIMB")) rt->sam_defer_climb = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_SPLIT")) rt->sam_split = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_SIDE")) rt->sam_side = atoi(env) != 0;
@@ -598,6 +600,41 @@ int32_t ullis_cuda_generate_step(ullis_cuda_generate_state* state, const uint32_
         need_ptr(tokens, "tokens");
         need_ptr(logits, "logits");
         state->step(tokens, logits);
+    });
+}
+
+int32_t ullis_cuda_rosa_pushers_create(ullis_cuda_runtime* rt, size_t streams, size_t capacity,
+                                       ullis_cuda_rosa_pushers** out) {
+    return guard(rt, [&] {
+        need_ptr(out, "out");
+        *out = nullptr;
+        *out = new ullis_cuda_rosa_pushers(rt, streams, capacity);
+    });
+}
+
+void ullis_cuda_rosa_pushers_destroy(ullis_cuda_rosa_pushers* pushers) {
+    if (!pushers) return;
+    if (pushers->rt) cudaSetDevice(pushers->rt->device);
+    delete pushers;
+}
+
+int32_t ullis_cuda_rosa_pushers_reset(ullis_cuda_rosa_pushers* pushers) {
+    if (!pushers) {
+        set_global_error("ROSA pushers handle is null");
+        return ULLIS_CUDA_ERR_ARG;
+    }
+    return guard(pushers->rt, [&] { pushers->reset(); });
+}
+
+int32_t ullis_cuda_rosa_pushers_push(ullis_cuda_rosa_pushers* pushers, const uint8_t* q, const uint8_t* k,
+                                     const uint8_t* v, size_t steps, uint8_t* idx) {
+    if (!pushers) {
+        set_global_error("ROSA pushers handle is null");
+        return ULLIS_CUDA_ERR_ARG;
+    }
+    return guard(pushers->rt, [&] {
+        need_ptr(q, "q"); need_ptr(k, "k"); need_ptr(v, "v"); need_ptr(idx, "idx");
+        pushers->push(q, k, v, steps, idx);
     });
 }
 

@@ -103,6 +103,7 @@ struct ullis_cuda_runtime {
     bool sam_words = true;              // pass 1 on packed state words (sam_core.cuh euler_pass1_words); false: the field-wise form
     bool sam_split = false;             // pass 1 as two kernels, extend chain then query walk, and the climb inside the tour kernel
                                         // (off: measured slower than the interleaved single-thread form at every stream count)
+    bool sam_reload_w = true;           // serial pass: load the query state's words once per step instead of carrying a patched copy
     bool sam_defer_climb = true;        // interleaved pass 1 records where each query walk ended; the climb to the state it reads runs in the tour kernel
     bool sam_walk_chunked = false;      // the query walk of the split form with eight lanes per stream (guessed pieces, then put right)
     int sam_lanes = 4;                  // streams carried per warp by the suffix-automaton kernel (1,2,4,...,32)

@@ -7,10 +7,12 @@
 // CUDA-core kernels in the reference's summation order: the logits of step t
 // are bit-identical to row t of the one-shot forward in EXACT mode, which is
 // what the reference's own test asserts (src/model.rs:4991-5004).  The automata
-// use the reference's eager schedule, statement for statement (push stamps the
-// whole suffix-link chain), because the O(T log T) form needs the whole
-// sequence in advance; a stream whose key bits have all been equal so far is
-// answered in closed form and its chain written only when that ends.
+// follow the reference's eager schedule (push stamps the whole suffix-link chain
+// of the new state), because the O(T log T) form needs the whole sequence in
+// advance; the chain is kept as an array and stamped by a warp, 32 states per
+// round, instead of one dependent load per state.  A stream whose key bits have
+// all been equal so far is answered in closed form and its automaton written
+// only when that ends.
 //
 // Nothing in a step depends on the host except the tokens, so after the first
 // use the ~150 small launches of a step are replayed as one CUDA graph (two
@@ -23,6 +25,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "kernels.hpp"
 #include "sam_core.cuh"
@@ -40,7 +43,7 @@ __global__ void gen_init_kernel(uint8_t* __restrict__ blocks, size_t stride, sam
                                 size_t streams, uint32_t T) {
     const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= streams) return;
-    // no pushes yet; the automaton is written lazily (sam::lazy_push), not even the root is needed
+    // no pushes yet; the automaton is written lazily (sam::gen_push), not even the root is needed
     sam::WalkerState st;
     st.u = 1; st.g = 0; st.w = 0; st.gmax = 0; st.gfail = 0; st.h = 0; st.steps = 0; st.pad = 0;
     ws[s] = st;
@@ -64,34 +67,41 @@ __global__ void gen_shift_mix_kernel(const float* __restrict__ x, float* __restr
     prev[e] = xt;
 }
 
-// one RosaSam::push per (sequence, channel) of one layer and y = (2*idx - 1)*e (src/model.rs:1344-1351)
+// one RosaSam::push per (sequence, channel) of one layer and y = (2*idx - 1)*e (src/model.rs:1344-1351).
+// One warp per stream: lane 0 runs the query and the extend, all lanes the stamping of the suffix-link chain
+// (sam::gen_push), which is what a late position costs.
 template <typename Ix>
 __global__ void __launch_bounds__(128)
 gen_push_kernel(uint8_t* __restrict__ blocks, size_t stride, sam::WalkerState* __restrict__ ws,
                 uint32_t* __restrict__ vhist, size_t wps, const float* __restrict__ q, const float* __restrict__ k,
                 const float* __restrict__ v, const uint16_t* __restrict__ e, float* __restrict__ y, size_t streams,
                 size_t C, uint32_t T, uint32_t* __restrict__ status) {
-    const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= streams) return;
-    sam::EagerLayout<Ix> L(T);
+    const size_t s = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t lane = threadIdx.x & 31u;
+    if (s >= streams) return;   // the whole warp
+    sam::GenLayout<Ix> L(T);
     uint8_t* blk = blocks + s * stride;
     sam::WalkerState st = ws[s];
     const uint32_t i = st.steps;
     if (i >= T) {  // the host checks the context length first; never write past the state block
-        if (atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_SAM_CAPACITY) == ULLIS_DEV_OK) status[1] = (uint32_t)s;
+        if (lane == 0 && atomicCAS(status, ULLIS_DEV_OK, ULLIS_DEV_SAM_CAPACITY) == ULLIS_DEV_OK) status[1] = (uint32_t)s;
         return;
     }
     // src/rosa.rs:372-374: bit = activation > 0
     const uint32_t qb = q[s] > 0.0f, kb = k[s] > 0.0f, vb = v[s] > 0.0f;
     uint32_t* vh = vhist + s * wps;
-    const uint32_t word = (i & 31u) ? vh[i >> 5] : 0u;   // a new word starts empty
-    vh[i >> 5] = word | (vb << (i & 31u));
-    // constant key so far: O(1); otherwise RosaSam::push statement for statement
-    const uint32_t idx = sam::lazy_push<Ix>(reinterpret_cast<sam::Node<Ix>*>(blk + L.nodes),
-                                            reinterpret_cast<Ix*>(blk + L.last), vh, &st, qb, kb);
-    ws[s] = st;
-    const float ev = h2f(e[s % C]);
-    y[s] = idx ? ev : -ev;
+    if (lane == 0) {   // only lane 0 reads the v history
+        const uint32_t word = (i & 31u) ? vh[i >> 5] : 0u;   // a new word starts empty
+        vh[i >> 5] = word | (vb << (i & 31u));
+    }
+    // constant key so far: O(1); otherwise RosaSam::push with the chain stamped by the warp
+    const uint32_t idx = sam::gen_push<Ix>(reinterpret_cast<sam::Node<Ix>*>(blk + L.nodes), reinterpret_cast<Ix*>(blk + L.last),
+                                           reinterpret_cast<Ix*>(blk + L.path), vh, &st, qb, kb);
+    if (lane == 0) {
+        ws[s] = st;
+        const float ev = h2f(e[s % C]);
+        y[s] = idx ? ev : -ev;
+    }
 }
 
 }  // namespace
@@ -103,7 +113,7 @@ ullis_cuda_generate_state::ullis_cuda_generate_state(ullis_cuda_model* m, size_t
     if (batch == 0) fail(ULLIS_CUDA_ERR_SHAPE, "generate needs at least one sequence");
     const uint32_t T = (uint32_t)m->context_len;
     narrow = sam::node_capacity(T) <= 0xFFFFu;
-    stride = narrow ? sam::EagerLayout<uint16_t>(T).total : sam::EagerLayout<uint32_t>(T).total;
+    stride = narrow ? sam::GenLayout<uint16_t>(T).total : sam::GenLayout<uint32_t>(T).total;
     wps = (m->context_len + 31) / 32;
     const size_t per_layer = batch * m->d;
     if (per_layer / m->d != batch || m->layers > SIZE_MAX / per_layer) fail(ULLIS_CUDA_ERR_SHAPE, "generate state shape overflow");
@@ -244,10 +254,10 @@ void ullis_cuda_generate_state::enqueue(int has_prev) {
             uint8_t* blk = static_cast<uint8_t*>(blocks.get()) + s0 * stride;
             uint32_t* vh = static_cast<uint32_t*>(vhist.get()) + s0 * wps;
             if (narrow)
-                gen_push_kernel<uint16_t><<<blocks_for(n, 128), 128, 0, rt->stream>>>(blk, stride, ws, vh, wps, W, W + n, W + 2 * n,
+                gen_push_kernel<uint16_t><<<blocks_for(n * 32, 128), 128, 0, rt->stream>>>(blk, stride, ws, vh, wps, W, W + n, W + 2 * n,
                                                                                      L.e, A, n, d, T, rt->dev_status);
             else
-                gen_push_kernel<uint32_t><<<blocks_for(n, 128), 128, 0, rt->stream>>>(blk, stride, ws, vh, wps, W, W + n, W + 2 * n,
+                gen_push_kernel<uint32_t><<<blocks_for(n * 32, 128), 128, 0, rt->stream>>>(blk, stride, ws, vh, wps, W, W + n, W + 2 * n,
                                                                                      L.e, A, n, d, T, rt->dev_status);
             rt->launched("gen_push");
         }
@@ -266,4 +276,77 @@ void ullis_cuda_generate_state::enqueue(int has_prev) {
     k::binary_linear_exact(rt, A, m->head.bits, m->head.scale, m->head.bias, LG, rows, d, m->vocab, false);
     rt->d2h(h_logits, LG, rows * m->vocab * 4);
     rt->d2h(rt->host_status, rt->dev_status, 16);
+}
+
+// ------------------------------------------------------------------ op level: RosaSam::push for many streams
+
+ullis_cuda_rosa_pushers::ullis_cuda_rosa_pushers(ullis_cuda_runtime* rt_, size_t streams_, size_t capacity_)
+    : rt(rt_), streams(streams_), capacity(capacity_) {
+    if (streams == 0 || capacity == 0) fail(ULLIS_CUDA_ERR_SHAPE, "ROSA pushers need at least one stream and one position");
+    if (capacity > 0x7FFFFFF0u) fail(ULLIS_CUDA_ERR_SHAPE, "ROSA pushers: capacity too large");
+    const uint32_t T = (uint32_t)capacity;
+    narrow = sam::node_capacity(T) <= 0xFFFFu;
+    stride = narrow ? sam::GenLayout<uint16_t>(T).total : sam::GenLayout<uint32_t>(T).total;
+    wps = (capacity + 31) / 32;
+    if (streams > SIZE_MAX / stride) fail(ULLIS_CUDA_ERR_SHAPE, "ROSA pushers: shape overflow");
+    rt->bind();
+    blocks.ensure(streams * stride);
+    walkers.ensure(streams * sizeof(sam::WalkerState));
+    vhist.ensure(streams * wps * 4);
+    reset();
+}
+
+void ullis_cuda_rosa_pushers::reset() {
+    rt->bind();
+    auto* ws = static_cast<sam::WalkerState*>(walkers.get());
+    auto* blk = static_cast<uint8_t*>(blocks.get());
+    gen_init_kernel<uint16_t><<<blocks_for(streams, 256), 256, 0, rt->stream>>>(blk, stride, ws, streams, (uint32_t)capacity);
+    rt->launched("gen_init");
+    rt->sync();
+    time = 0;
+}
+
+void ullis_cuda_rosa_pushers::push(const uint8_t* q, const uint8_t* k, const uint8_t* v, size_t steps, uint8_t* idx) {
+    // RosaSam has no capacity (src/rosa.rs:55-64 grows its vectors); here it is fixed when the state is made
+    if (steps > capacity - time) fail(ULLIS_CUDA_ERR_SHAPE, "ROSA pushers: more pushes than the capacity given at creation");
+    if (steps == 0) return;
+    if (steps > SIZE_MAX / streams / 20) fail(ULLIS_CUDA_ERR_SHAPE, "ROSA pushers: shape overflow");
+    rt->bind();
+    const size_t n = steps * streams;
+    // the generation kernel takes activations (bit = x > 0) and writes (2*idx - 1)*e: feed it +-1 and e = 1
+    std::vector<float> h(3 * n);
+    for (size_t i = 0; i < n; ++i) {
+        h[i] = q[i] ? 1.0f : -1.0f;
+        h[n + i] = k[i] ? 1.0f : -1.0f;
+        h[2 * n + i] = v[i] ? 1.0f : -1.0f;
+    }
+    io.ensure(4 * n * 4 + 16);
+    float* d = static_cast<float*>(io.get());
+    uint16_t* one = reinterpret_cast<uint16_t*>(d + 4 * n);
+    const uint16_t h_one = 0x3C00u;   // FP16 1.0
+    rt->clear_status();
+    rt->h2d(d, h.data(), 3 * n * 4);
+    rt->h2d(one, &h_one, 2);
+    auto* ws = static_cast<sam::WalkerState*>(walkers.get());
+    auto* blk = static_cast<uint8_t*>(blocks.get());
+    uint32_t* vh = static_cast<uint32_t*>(vhist.get());
+    for (size_t t = 0; t < steps; ++t) {
+        const float* row = d + t * streams;
+        if (narrow)
+            gen_push_kernel<uint16_t><<<blocks_for(streams * 32, 128), 128, 0, rt->stream>>>(
+                blk, stride, ws, vh, wps, row, row + n, row + 2 * n, one, d + 3 * n + t * streams, streams, 1, (uint32_t)capacity,
+                rt->dev_status);
+        else
+            gen_push_kernel<uint32_t><<<blocks_for(streams * 32, 128), 128, 0, rt->stream>>>(
+                blk, stride, ws, vh, wps, row, row + n, row + 2 * n, one, d + 3 * n + t * streams, streams, 1, (uint32_t)capacity,
+                rt->dev_status);
+        rt->launched("gen_push");
+    }
+    std::vector<float> y(n);
+    rt->d2h(y.data(), d + 3 * n, n * 4);
+    rt->d2h(rt->host_status, rt->dev_status, 16);
+    rt->sync();
+    time += steps;   // the automata have moved on whatever the status says
+    rt->throw_on_status();
+    for (size_t i = 0; i < n; ++i) idx[i] = y[i] > 0.0f;
 }

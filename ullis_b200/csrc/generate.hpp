@@ -36,3 +36,18 @@ struct ullis_cuda_generate_state {
     // tokens [batch] (host) -> logits [batch, vocab] (host); advances time by one
     void step(const uint32_t* tokens, float* logits);
 };
+
+// `streams` independent RosaSam automata (src/rosa.rs:55-176) kept on the device between calls: the op-level form
+// of what a generate state holds per layer.  push() advances every stream by `steps` positions.
+struct ullis_cuda_rosa_pushers {
+    ullis_cuda_runtime* rt = nullptr;
+    size_t streams = 0, capacity = 0, time = 0;
+    bool narrow = true;
+    size_t stride = 0, wps = 0;
+    ullis::DeviceBuffer blocks, walkers, vhist, io;
+
+    ullis_cuda_rosa_pushers(ullis_cuda_runtime* rt, size_t streams, size_t capacity);
+    void reset();
+    // q, k, v, idx: [steps, streams] bytes of 0 / 1 on the host
+    void push(const uint8_t* q, const uint8_t* k, const uint8_t* v, size_t steps, uint8_t* idx);
+};

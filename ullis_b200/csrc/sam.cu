@@ -92,7 +92,8 @@ rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint
 // Two-kernel form of the O(T log T) schedule for streams whose tour / pass 2
 // working set fits shared memory: pass 1 one thread per stream (below), then
 // one warp per stream for the parallel phases (sam_coop.cuh).
-// WORDS: 0 = field-wise state layout, 1 = packed words, 2 = packed words with the climb left to the tour kernel
+// WORDS: 0 = field-wise state layout, 1 = packed words, 2 = packed words with the climb left to the tour kernel,
+// 3 = the same without the register copy of the query state's words (one load per step instead of the patches)
 // (a kernel each, so that the form that runs gets the registers to itself)
 // (16 CTAs per SM = 32 registers: with 40 registers the same loop ran 4 % slower at 64 sequences and 40 % slower at 8)
 template <int WORDS>
@@ -115,7 +116,8 @@ rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const ui
     if (item >= wave || first + item >= *count) return;
     const size_t s = list[first + item];
     sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
-    if (WORDS == 2) sam::euler_pass1_words<true>(B, q_sw + s * wps, k_sw + s * wps, T);
+    if (WORDS == 3) sam::euler_pass1_words<true, true>(B, q_sw + s * wps, k_sw + s * wps, T);
+    else if (WORDS == 2) sam::euler_pass1_words<true, false>(B, q_sw + s * wps, k_sw + s * wps, T);
     else if (WORDS == 1) sam::euler_pass1_words<false>(B, q_sw + s * wps, k_sw + s * wps, T);
     else sam::euler_pass1<uint16_t>(B, q_sw + s * wps, k_sw + s * wps, T, nullptr);
 }
@@ -368,6 +370,7 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
     rosa_pass1_kernel<W><<<p1_grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, k_sw, list, count, s0, n, (uint32_t)time, \
                                                           wps, pass1_lanes, dense, sparse)
                 if (!rt->sam_words) ULLIS_PASS1(0);
+                else if (defer && rt->sam_reload_w) ULLIS_PASS1(3);
                 else if (defer) ULLIS_PASS1(2);
                 else ULLIS_PASS1(1);
 #undef ULLIS_PASS1

@@ -287,22 +287,121 @@ SAM_HD uint32_t load_walker(Walker<Ix>& wk, Node<Ix>* nodes, const WalkerState* 
     return st->steps;
 }
 
-// Incremental pushes with a shortcut for streams whose key bits have all been
-// equal so far.  After t pushes with key c the automaton is a chain: states
-// 0..t, state m = c^m, child(m, c) = m+1, link(m) = m-1, maxlen(m) = m, every
-// `last` = t, and the query state is (w, w) with w = length of the current run
-// of q == c (not counting step 0, whose query finds an empty automaton).  So a
-// push costs O(1) instead of the O(t) chain stamping, and idx = (t >= 1 and
-// q == c) ? v : 0 (the same closed form as run_constant_k).  The chain is
-// written out only when a key bit differs for the first time; from then on the
-// stream takes eager_step.  WalkerState::pad holds the mode: 0 = chain not yet
-// written (w = run length, g = key bit c), 1 = real automaton.
+// ------------------------------------------------------------------ incremental pushes, chain kept as an array
+//
+// src/rosa.rs:168-173 stamps `last = i` on every state of the suffix-link chain of the step's new state j_i; the
+// loop never stops early (every older stamp is < i), so it costs the length of the chain, which is the length of
+// the key's current run on a biased stream.  Following the links is a chain of dependent loads.  The chain need
+// not be followed: its states are the states of all suffixes of the keys so far, and a suffix of keys[0..i] is
+// a suffix of keys[0..i-1] followed by k_i.  So
+//
+//     chain(j_i) = dedupe( child(c, k_i) for c in chain(j_{i-1}) ) ++ [root]
+//
+// with the children read after step i's extend (which gave every state of the old chain a child on k_i: j_i
+// itself below the state the extend's walk stopped at, the old child or its clone from there on; equal children
+// are neighbours because a state's strings are contiguous in length).  With chain(j_{i-1}) kept as an array the
+// new chain is a map over independent loads, a compaction, and the stamps: one warp per stream does 32 entries
+// per round, in place (the compacted position of an entry is never ahead of the entry).  The `last` array holds
+// exactly what the reference's holds after every step.
+//
+// A stream whose key bits have all been equal so far needs no automaton yet.  After t pushes with key c it is a
+// chain: states 0..t, state m = c^m, child(m, c) = m+1, link(m) = m-1, maxlen(m) = m, every `last` = t, and the
+// query state is (w, w) with w = length of the current run of q == c (not counting step 0, whose query finds an
+// empty automaton).  So a push costs O(1), idx = (t >= 1 and q == c) ? v : 0 (the same closed form as
+// run_constant_k), and the automaton is written out only when a key bit differs for the first time.
+//
+// Lanes: inside a CUDA kernel all 32 lanes of a warp call gen_push together with equal arguments; on the host
+// one caller stands for a warp of one lane.
+namespace lanes {
+#if defined(__CUDA_ARCH__)
+SAM_HD uint32_t count() { return 32u; }
+SAM_HD uint32_t id() { return threadIdx.x & 31u; }
+SAM_HD uint32_t ballot(bool p) { return __ballot_sync(0xFFFFFFFFu, p); }
+SAM_HD uint32_t from_below(uint32_t v) { return __shfl_up_sync(0xFFFFFFFFu, v, 1); }
+SAM_HD uint32_t from_last(uint32_t v) { return __shfl_sync(0xFFFFFFFFu, v, 31); }
+SAM_HD void sync() { __syncwarp(); }
+#else
+SAM_HD uint32_t count() { return 1u; }
+SAM_HD uint32_t id() { return 0u; }
+SAM_HD uint32_t ballot(bool p) { return p ? 1u : 0u; }
+SAM_HD uint32_t from_below(uint32_t v) { return v; }
+SAM_HD uint32_t from_last(uint32_t v) { return v; }
+SAM_HD void sync() {}
+#endif
+SAM_HD uint32_t popc(uint32_t m) {
+#if defined(__CUDA_ARCH__)
+    return (uint32_t)__popc(m);
+#else
+    uint32_t n = 0;
+    for (; m; m &= m - 1u) ++n;
+    return n;
+#endif
+}
+}  // namespace lanes
+
+// Byte layout of one stream's block for incremental pushes: the eager layout plus the chain array.
 template <typename Ix>
-SAM_HD uint32_t lazy_push(Node<Ix>* nodes, Ix* last, const uint32_t* vhist, WalkerState* st, uint32_t qb,
-                          uint32_t kb) {
+struct GenLayout {
+    size_t nodes, last, path, total;
+    SAM_HD explicit GenLayout(uint32_t T) {
+        const size_t cap = node_capacity(T);
+        size_t off = 0;
+        nodes = off; off = align_up(off + cap * sizeof(Node<Ix>), 16);
+        last = off;  off = align_up(off + cap * sizeof(Ix), 16);
+        path = off;  off = align_up(off + ((size_t)T + 2) * sizeof(Ix), 16);   // chain(j_i) has at most i + 2 states
+        total = align_up(off, 128);
+    }
+};
+
+// chain(j_{i-1}) in path[0..len) -> chain(j_i), every state of it stamped; returns the new length.
+template <typename Ix>
+SAM_HD uint32_t chain_advance(const Node<Ix>* N, Ix* last, Ix* path, uint32_t len, uint32_t kb, uint32_t stamp) {
     constexpr uint32_t NIL = Nil<Ix>::value;
+    const uint32_t W = lanes::count(), lane = lanes::id();
+    uint32_t cnt = 0, carry = NIL;
+    uint32_t t = NIL;
+    if (lane < len) {
+        const Node<Ix> n = N[path[lane]];
+        t = kb ? n.t1 : n.t0;
+    }
+    for (uint32_t base = 0; base < len; base += W) {
+        // the next round's loads are issued before this round's stores (which land at or below base + lane)
+        uint32_t t_next = NIL;
+        if (base + W + lane < len) {
+            const Node<Ix> n = N[path[base + W + lane]];
+            t_next = kb ? n.t1 : n.t0;
+        }
+        uint32_t below = lanes::from_below(t);
+        if (lane == 0) below = carry;
+        const bool keep = base + lane < len && t != below;
+        const uint32_t mask = lanes::ballot(keep);
+        if (keep) {
+            path[cnt + lanes::popc(mask & ((1u << lane) - 1u))] = (Ix)t;
+            last[t] = (Ix)stamp;
+        }
+        cnt += lanes::popc(mask);
+        carry = lanes::from_last(t);   // only read while a further round follows: then lane W-1 held an entry
+        t = t_next;
+    }
+    if (lane == 0) {
+        path[cnt] = 0;        // the root ends every chain and is stamped too (src/rosa.rs:168-173 walks up to it)
+        last[0] = (Ix)stamp;
+    }
+    return cnt + 1u;
+}
+
+// One RosaSam::push (src/rosa.rs:100-176) of an automaton that outlives the call.  `st` is the caller's copy of the
+// stream's WalkerState (every lane holds one; lane 0's is the one to store back).  WalkerState::pad: bit 0 = the
+// automaton has been written (see lazy_push: while every key bit so far was equal a push is O(1) and nothing is
+// written), bits 1.. = length of the chain array.  `vhist` must already hold bit `steps`.  Returns idx on lane 0.
+template <typename Ix>
+SAM_HD uint32_t gen_push(Node<Ix>* nodes, Ix* last, Ix* path, const uint32_t* vhist, WalkerState* st, uint32_t qb,
+                         uint32_t kb) {
+    constexpr uint32_t NIL = Nil<Ix>::value;
+    const uint32_t W = lanes::count(), lane = lanes::id();
     const uint32_t t = st->steps;
-    if (st->pad == 0) {
+    uint32_t len = st->pad >> 1;
+    if ((st->pad & 1u) == 0) {
         const uint32_t c = t == 0 ? kb : st->g;
         if (kb == c) {
             const uint32_t run = (t >= 1 && qb == c) ? st->w + 1u : 0u;
@@ -311,26 +410,38 @@ SAM_HD uint32_t lazy_push(Node<Ix>* nodes, Ix* last, const uint32_t* vhist, Walk
             st->steps = t + 1u;
             return run ? stream_bit(vhist, t) : 0u;   // last[v] + 1 = t for every state: the current v bit
         }
-        // first differing key bit: write the chain of t pushes of c, then fall through to a real push
-        for (uint32_t m = 0; m <= t; ++m) {
+        // first differing key bit: write the automaton of t pushes of c (a chain of t + 1 states) and its chain array
+        for (uint32_t m = lane; m <= t; m += W) {
             Node<Ix> n;
             n.t0 = (Ix)((m < t && c == 0) ? m + 1u : NIL);
             n.t1 = (Ix)((m < t && c == 1) ? m + 1u : NIL);
             n.fail = (Ix)(m ? m - 1u : NIL);
             n.maxlen = (Ix)m;
             nodes[m] = n;
-            last[m] = (Ix)t;   // stored as last + 1; the root too (src/rosa.rs:168-173 walks up to it); 0 pushes: 0 = never
+            last[m] = (Ix)t;   // stored as last + 1 (0 = never); the root too
+            path[m] = (Ix)(t - m);
         }
+        len = t + 1u;
         const uint32_t run = st->w;
         st->u = t + 1u; st->g = t; st->gmax = t; st->gfail = t ? t - 1u : NIL;
         st->w = run; st->h = (int32_t)run;
-        st->pad = 1;
+        lanes::sync();
     }
     Walker<Ix> wk;
     const uint32_t i = load_walker(wk, nodes, st);
-    const uint32_t bit = eager_step<Ix>(wk, last, vhist, i, qb, kb, nullptr);
+    uint32_t bit = 0;
+    if (lane == 0) {
+        const uint32_t v = wk.query(qb, nullptr);
+        if (v != NIL) bit = stream_bit(vhist, last[v]);   // stored last + 1 >= 1 for any non-root state
+        uint32_t j, b, d;
+        wk.extend(kb, &j, &b, &d, nullptr);
+        // the reference's last[b] = last[d] and last[j] = -1 are both overwritten by the stamps of this very step
+    }
+    lanes::sync();
+    len = chain_advance<Ix>(nodes, last, path, len, kb, i + 1u);
+    lanes::sync();
     save_walker(wk, i + 1u, st);
-    st->pad = 1;
+    st->pad = 1u | (len << 1);
     return bit;
 }
 
@@ -435,8 +546,14 @@ SAM_HD void store_words(Node<uint16_t>* N, uint32_t id, uint32_t x, uint32_t y) 
 // the words of clone_bits (word t / 32, bit t % 32).  Ids are handed out in order, one per step plus one per
 // clone, so jid[t] = 1 + t + (clones of the steps before t), and the clones are the states whose id is no jid[t];
 // the tour works both out by itself.  Every store taken out of this loop shortens the serial chain.
-template <bool DEFER_CLIMB = false>
+// RELOAD_W (with DEFER_CLIMB only): the words of the state the next query starts from are not carried along and
+// patched whenever the extend stores into that state ("mirrored"); they are loaded once per step, after the last
+// store of the extend that can touch an existing state and before the step's remaining bookkeeping, which hides
+// the load.  With the climb gone nothing else in the step needs those words, so the query's hit path has no load
+// at all and four compare-and-patch sites leave the loop.
+template <bool DEFER_CLIMB = false, bool RELOAD_W = false>
 SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T) {
+    static_assert(DEFER_CLIMB || !RELOAD_W, "the climb inside the loop needs the words of the state it starts from");
     constexpr uint32_t NIL = 0xFFFFu;
     Node<uint16_t>* N = B.N;
     uint16_t* half = reinterpret_cast<uint16_t*>(N);   // field f of state s at half[4 * s + f]
@@ -485,8 +602,12 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
             } else {
                 x += 1;
                 v = c;
-                NodeWords nv = load_words(N, v);
-                nw = nv;                          // the state the next query starts from
+                NodeWords nv;
+                nv.x = 0; nv.y = 0;
+                if (!RELOAD_W) {
+                    nv = load_words(N, v);
+                    nw = nv;                      // the state the next query starts from
+                }
                 if (DEFER_CLIMB) {
                     v = c | (x << 16);            // the record of this step: the climb happens later
                 } else {
@@ -509,7 +630,7 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
             const uint32_t j = u++;
             const uint32_t child_mask = ~(0xFFFFu << ks);
             half[4 * g + kb] = (uint16_t)j;   // g has no children yet
-            if (g == w) nw.x = (nw.x & child_mask) | (j << ks);
+            if (!RELOAD_W && g == w) nw.x = (nw.x & child_mask) | (j << ks);
             uint32_t p = e0, d = NIL, jfail = 0, pml = 0;
             NodeWords n = ne;                  // e0 == NIL (first step only): the root's words, for the case below
             while (p != NIL) {
@@ -517,7 +638,7 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
                 pml = n.y >> 16;
                 if (d != NIL) break;
                 half[4 * p + kb] = (uint16_t)j;
-                if (p == w) nw.x = (nw.x & child_mask) | (j << ks);
+                if (!RELOAD_W && p == w) nw.x = (nw.x & child_mask) | (j << ks);
                 const uint32_t up = n.y & 0xFFFFu;
                 if (up == NIL) break;           // p is the root and has its new child: keep its words in n
                 p = up;
@@ -534,14 +655,14 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
                     ne.y = (nd.y & 0xFFFFu) | ((pml + 1u) << 16);
                     store_words(N, b, ne.x, ne.y);
                     half[4 * d + 2] = (uint16_t)b;
-                    if (d == w) nw.y = (nw.y & 0xFFFF0000u) | b;
+                    if (!RELOAD_W && d == w) nw.y = (nw.y & 0xFFFF0000u) | b;
                     jfail = b;
                     if (DEFER_CLIMB) cloned |= 1u << (i & 31u);
                     else B.clone_bits[b >> 5] |= 1u << (b & 31);
                     // p still has d as its child (that is where the walk stopped): redirect it, then go on up
                     for (;;) {
                         half[4 * p + kb] = (uint16_t)b;
-                        if (p == w) nw.x = (nw.x & child_mask) | (b << ks);
+                        if (!RELOAD_W && p == w) nw.x = (nw.x & child_mask) | (b << ks);
                         p = n.y & 0xFFFFu;
                         if (p == NIL) break;
                         n = load_words(N, p);
@@ -555,12 +676,15 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
                 ne.x = (n.x & child_mask) | (j << ks);
                 ne.y = n.y;
             }
+            // every store into an existing state has been issued: the state the next query starts from (the root
+            // after a miss) is read now, and the rest of the step runs while the load is under way
+            if (RELOAD_W) nw = load_words(N, w);
             gmax += 1;
             store_words(N, j, 0xFFFFFFFFu, jfail | (gmax << 16));
             g = j; gfail = jfail;
             if (!DEFER_CLIMB) B.jid[i] = (uint16_t)j;   // otherwise j_i = 1 + i + (clones of the steps before i)
         }
-        if (!hit) nw = load_words(N, 0);   // a miss sends the query back to the root
+        if (!RELOAD_W && !hit) nw = load_words(N, 0);   // a miss sends the query back to the root
     }
     if (DEFER_CLIMB && T) B.clone_bits[(T - 1u) >> 5] = cloned;
     B.meta[0] = u;
@@ -756,7 +880,7 @@ SAM_HD uint32_t euler_climb_words(const Node<uint16_t>* N, uint32_t w, uint32_t 
 // Interleaved pass 1 without the climb, then the climb of every step (what rosa_pass1_kernel with the deferred
 // climb and the tour kernel compute together).
 SAM_HD uint32_t euler_pass1_deferred(EulerBlock<uint16_t>& B, const uint32_t* qw, const uint32_t* kw, uint32_t T) {
-    const uint32_t n = euler_pass1_words<true>(B, qw, kw, T);
+    const uint32_t n = euler_pass1_words<true, true>(B, qw, kw, T);
     for (uint32_t t = 0, clones = 0; t < T; ++t) {   // the new-state ids from the per-step clone flags
         B.jid[t] = (uint16_t)(1u + t + clones);
         clones += (B.clone_bits[t >> 5] >> (t & 31u)) & 1u;

@@ -44,6 +44,8 @@ ABI_SYMBOLS = (
     "ullis_cuda_model_set_taps", "ullis_cuda_model_tap", "ullis_cuda_model_set_profile",
     "ullis_cuda_model_phase_ms", "ullis_cuda_generate_state_create", "ullis_cuda_generate_state_destroy",
     "ullis_cuda_generate_state_reset", "ullis_cuda_generate_state_time", "ullis_cuda_generate_step",
+    "ullis_cuda_rosa_pushers_create", "ullis_cuda_rosa_pushers_destroy", "ullis_cuda_rosa_pushers_reset",
+    "ullis_cuda_rosa_pushers_push",
     "ullis_cuda_train_state_create", "ullis_cuda_train_state_destroy", "ullis_cuda_model_train_step",
     "ullis_cuda_train_state_read", "ullis_cuda_train_state_install_head_unigram_prior",
     "ullis_cuda_clipped_sgd_fp16", "ullis_cuda_binaryconnect_sgd_fp16", "ullis_cuda_apply_latent_sgd",
@@ -87,6 +89,8 @@ def load_library() -> C.CDLL:
         lib.ullis_cuda_model_destroy.argtypes = [C.c_void_p]
         lib.ullis_cuda_generate_state_destroy.restype = None
         lib.ullis_cuda_generate_state_destroy.argtypes = [C.c_void_p]
+        lib.ullis_cuda_rosa_pushers_destroy.restype = None
+        lib.ullis_cuda_rosa_pushers_destroy.argtypes = [C.c_void_p]
         lib.ullis_cuda_train_state_destroy.restype = None
         lib.ullis_cuda_train_state_destroy.argtypes = [C.c_void_p]
         lib.ullis_cuda_generate_state_time.restype = C.c_size_t
@@ -580,6 +584,39 @@ class CudaGenerateState:
         out = np.empty((self.batch, self.model.vocab_size), np.float32)
         self.model.rt._check(self._lib.ullis_cuda_generate_step(self._h, _ptr(t), _ptr(out)))
         return out
+
+    def close(self):
+        if getattr(self, "_handle", None):
+            self._handle.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+class CudaRosaPushers:
+    """`streams` RosaSam automata (src/rosa.rs:55-176) on the device; push() is RosaSam::push for every stream,
+    once per row of q / k / v ([steps, streams] of 0 / 1), and returns idx in the same shape."""
+
+    def __init__(self, rt: CudaRuntime, streams: int, capacity: int):
+        self.rt, self.streams, self.capacity = rt, int(streams), int(capacity)
+        self._lib = rt._lib
+        h = C.c_void_p()
+        rt._check(self._lib.ullis_cuda_rosa_pushers_create(rt._h, _z(streams), _z(capacity), C.byref(h)))
+        self._handle = _Handle(h, self._lib.ullis_cuda_rosa_pushers_destroy, rt._handle)
+
+    def reset(self) -> None:
+        self.rt._check(self._lib.ullis_cuda_rosa_pushers_reset(self._handle.h))
+
+    def push(self, q, k, v) -> np.ndarray:
+        q = np.ascontiguousarray(np.atleast_2d(q), np.uint8)
+        steps = q.shape[0]
+        q, k, v = (_arr(np.atleast_2d(a), np.uint8, n, steps * self.streams) for a, n in ((q, "q"), (k, "k"), (v, "v")))
+        idx = np.empty((steps, self.streams), np.uint8)
+        self.rt._check(self._lib.ullis_cuda_rosa_pushers_push(self._handle.h, _ptr(q), _ptr(k), _ptr(v), _z(steps), _ptr(idx)))
+        return idx
 
     def close(self):
         if getattr(self, "_handle", None):
