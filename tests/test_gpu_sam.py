@@ -154,3 +154,35 @@ def test_pass_one_in_parts_gives_the_same_idx(oracle, monkeypatch, chunked):
         run_both(rt, oracle, q, k, v, 1, T, C, algos=(cuda.SAM_EULER,))
     finally:
         rt.close()
+
+
+@pytest.mark.parametrize("waves", ["0", "1", "1000"])
+def test_both_forms_of_the_serial_pass_give_the_same_idx(oracle, monkeypatch, waves):
+    """Pass 1 keeps a stream's state array in shared memory (one one-warp CTA per stream) when it expects few
+    enough streams for all of them to be resident at once, and in global memory otherwise.  The expectation is
+    the number of streams the same call site sent to the automaton the last time, so a first call takes the
+    global-memory kernel and a repeated one may take the other.  Forced here in turn: 0 = never shared memory,
+    1000 = always (also when the streams need several rounds of resident CTAs), 1 = the default rule; every input
+    runs twice."""
+    monkeypatch.setenv("ULLIS_CUDA_SAM_SMEM_WAVES", waves)
+    rt = cuda.CudaRuntime(0)
+    try:
+        rt.kernel_timing(True)
+        rng = np.random.default_rng(53)
+        cases = []
+        B, T, C = 2, 2048, 64
+        cases.append((synth.rosa_bits_iid(51, B, T, C), B, T, C))
+        B, T, C = 6, 2048, 256      # 1 536 streams, more than one round of resident CTAs at this length
+        cases.append((synth.rosa_bits_periodic(52, B, T, C), B, T, C))
+        T, C = 333, 96                                       # a ragged length, biased streams
+        pr = rng.choice([0.01, 0.1, 0.5, 0.9, 0.99], (1, C))
+        cases.append((tuple(pack_plane((rng.random((T, C)) < pr).astype(np.uint8)) for _ in range(3)), 1, T, C))
+        T, C = 5000, 40                                      # 80 KB of states per stream: two CTAs per SM
+        cases.append((tuple(pack_plane(rng.integers(0, 2, (T, C), dtype=np.uint8)) for _ in range(3)), 1, T, C))
+        for (q, k, v), B, T, C in cases:
+            for _ in range(2):
+                run_both(rt, oracle, q, k, v, B, T, C, algos=(cuda.SAM_EULER,))
+        ran = rt.kernel_times()
+        assert ("rosa_pass1_smem" in ran) == (waves != "0") and ("rosa_pass1" in ran) == (waves != "1000")
+    finally:
+        rt.close()

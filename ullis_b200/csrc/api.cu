@@ -116,6 +116,8 @@ ullis_cuda_runtime* ullis_cuda_runtime::child(size_t i) {
     c->sam_split = sam_split;
     c->sam_defer_climb = sam_defer_climb;
     c->sam_reload_w = sam_reload_w;
+    c->sam_smem_waves = sam_smem_waves;
+    c->tc_ln_rows = tc_ln_rows;
     c->sam_walk_chunked = sam_walk_chunked;
     c->sam_budget_bytes = sam_budget_bytes / (children.size() + 1);
     c->tc_fix_list = tc_fix_list;
@@ -279,6 +281,18 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         ULLIS_CUDA_CHECK(cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking));
         ULLIS_CUDA_CHECK(cudaMalloc(&rt->dev_status, 16));
         ULLIS_CUDA_CHECK(cudaMallocHost(&rt->host_status, 16));
+        {   // mapped pinned memory: the kernels store into it, the host reads it without a copy or a wait
+            void* hints = nullptr;
+            ULLIS_CUDA_CHECK(cudaHostAlloc(&hints, ullis_cuda_runtime::SAM_HINT_SLOTS * sizeof(uint32_t), cudaHostAllocMapped));
+            rt->sam_hints = static_cast<uint32_t*>(hints);
+            for (int i = 0; i < ullis_cuda_runtime::SAM_HINT_SLOTS; ++i) rt->sam_hints[i] = 0xFFFFFFFFu;
+            void* dev_view = nullptr;
+            ULLIS_CUDA_CHECK(cudaHostGetDevicePointer(&dev_view, hints, 0));
+            if (dev_view != hints) {   // no unified addressing of host memory: the kernels cannot be handed the host pointer
+                cudaFreeHost(hints);
+                rt->sam_hints = nullptr;
+            }
+        }
         rt->clear_status();
         rt->sync();
         if (const char* env = getenv("ULLIS_CUDA_TC_STAGES")) {
@@ -295,6 +309,8 @@ int32_t ullis_cuda_runtime_create(int32_t device, ullis_cuda_runtime** out) {
         if (const char* env = getenv("ULLIS_CUDA_FUSE_LN")) rt->tc_fuse_ln = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_FIX_LIST")) rt->tc_fix_list = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_WALK_CHUNKED")) rt->sam_walk_chunked = atoi(env) != 0;
+        if (const char* env = getenv("ULLIS_CUDA_LN_ROWS")) rt->tc_ln_rows = atoi(env);
+        if (const char* env = getenv("ULLIS_CUDA_SAM_SMEM_WAVES")) rt->sam_smem_waves = std::max(0, atoi(env));
         if (const char* env = getenv("ULLIS_CUDA_SAM_RELOAD_W")) rt->sam_reload_w = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_DEFER_CLIMB")) rt->sam_defer_climb = atoi(env) != 0;
         if (const char* env = getenv("ULLIS_CUDA_SAM_SPLIT")) rt->sam_split = atoi(env) != 0;
@@ -343,6 +359,7 @@ void ullis_cuda_runtime_destroy(ullis_cuda_runtime* rt) {
     if (rt->side_join) cudaEventDestroy(rt->side_join);
     if (rt->dev_status) cudaFree(rt->dev_status);
     if (rt->host_status) cudaFreeHost(rt->host_status);
+    if (rt->sam_hints) cudaFreeHost(rt->sam_hints);
     for (auto& m : rt->marks) {
         cudaEventDestroy(m.done);
         if (m.begin) cudaEventDestroy(m.begin);

@@ -103,6 +103,18 @@ struct ullis_cuda_runtime {
     bool sam_words = true;              // pass 1 on packed state words (sam_core.cuh euler_pass1_words); false: the field-wise form
     bool sam_split = false;             // pass 1 as two kernels, extend chain then query walk, and the climb inside the tour kernel
                                         // (off: measured slower than the interleaved single-thread form at every stream count)
+    int tc_ln_rows = 0;                 // rows per warp (1, 2, 4) in the LayerNorm + mix + operand kernel; 0 = by the number of rows
+    int sam_smem_waves = 1;             // serial pass with the states in shared memory when the streams are expected to fit in this many rounds of resident CTAs; 0 = never, >= 1000 = always
+    bool sam_smem_ready = false;        // that kernel has been allowed its dynamic shared memory
+    // Streams that reached the automaton at each call site's last call, written by the serial-pass kernels straight
+    // into pinned host memory (slot 0: callers without a site); 0xFFFFFFFF = no call yet.  Children share the parent's.
+    static constexpr int SAM_HINT_SLOTS = 257;
+    uint32_t* sam_hints = nullptr;
+    uint32_t* sam_hint_slot(int site) {
+        ullis_cuda_runtime* owner = parent ? parent : this;
+        if (!owner->sam_hints) return nullptr;
+        return owner->sam_hints + ((site >= 0 && site < SAM_HINT_SLOTS - 1) ? site + 1 : 0);
+    }
     bool sam_reload_w = true;           // serial pass: load the query state's words once per step instead of carrying a patched copy
     bool sam_defer_climb = true;        // interleaved pass 1 records where each query walk ended; the climb to the state it reads runs in the tour kernel
     bool sam_walk_chunked = false;      // the query walk of the split form with eight lanes per stream (guessed pieces, then put right)

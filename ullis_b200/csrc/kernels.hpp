@@ -42,9 +42,11 @@ void fp16_linear_exact(ullis_cuda_runtime* rt, const float* x, const uint16_t* w
                        size_t in_features, size_t out_features, bool accumulate);
 
 // ---- sam.cu
-// idx_sw <- suffix-automaton match of each stream; uses rt->sam_scratch.
+// idx_sw <- suffix-automaton match of each stream; uses rt->sam_scratch.  `site` names the caller's call site (a
+// model passes its layer): calls of one site are expected to send a similar number of streams to the automaton,
+// which picks the kernel of the serial pass; -1 = a site shared by every other caller.
 void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw, const uint32_t* v_sw,
-              uint32_t* idx_sw, size_t streams, size_t time);
+              uint32_t* idx_sw, size_t streams, size_t time, int site = -1);
 size_t rosa_sam_scratch_bytes_per_stream(int algo, size_t time);
 
 // ---- ce.cu

@@ -131,7 +131,7 @@ mix_split_kernel(const float* __restrict__ x, const uint16_t* __restrict__ m0, c
 // values), forms the mixes and writes the 16-bit operands; the LayerNorm output itself is only written when
 // something downstream reads it as f32 (`ln_out`: the exact sign fix-up).  Saves the round trip of the
 // LayerNorm output through HBM.  C = 128 * VEC channels, VEC <= 8.
-template <int VEC>
+template <int VEC, int ROWS>
 __global__ void __launch_bounds__(256)
 ln_mix_split_kernel(const float* __restrict__ x, const uint16_t* __restrict__ lw, const uint16_t* __restrict__ lb,
                     float* __restrict__ ln_out, const uint16_t* __restrict__ m0, const uint16_t* __restrict__ m1,
@@ -140,9 +140,10 @@ ln_mix_split_kernel(const float* __restrict__ x, const uint16_t* __restrict__ lw
                     uint16_t* __restrict__ lo2, float* __restrict__ s1, size_t rows, size_t time) {
     constexpr int C = 128 * VEC;
     const int lane = threadIdx.x & 31;
-    const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const bool first = row % time == 0;
+    // a warp takes ROWS consecutive rows: the LayerNorm of a row is then computed once and handed on as the next
+    // row's "row before" (with ROWS = 1 every row is normalised twice, by its own warp and by its successor's)
+    const size_t row0 = ((size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * ROWS;
+    if (row0 >= rows) return;
     const uint2* w4 = reinterpret_cast<const uint2*>(lw);
     const uint2* b4 = reinterpret_cast<const uint2*>(lb);
     // normalised values of one row, in place
@@ -172,22 +173,30 @@ ln_mix_split_kernel(const float* __restrict__ x, const uint16_t* __restrict__ lw
         }
     };
     float4 cur[VEC], prev[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) prev[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const uint16_t* mix[3] = {m0, m1, m2};
+    uint16_t* hi[3] = {hi0, hi1, hi2};
+    uint16_t* lo[3] = {lo0, lo1, lo2};
+#pragma unroll 1
+    for (int r = 0; r < ROWS; ++r) {
+    const size_t row = row0 + r;
+    if (row >= rows) break;
+    const bool first = row % time == 0;   // the same for the whole warp
     const float4* src = reinterpret_cast<const float4*>(x + row * C);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-        cur[i] = src[lane + 32 * i];
-        prev[i] = first ? make_float4(0.f, 0.f, 0.f, 0.f) : (src - C / 4)[lane + 32 * i];
+    for (int i = 0; i < VEC; ++i) cur[i] = src[lane + 32 * i];
+    if (r == 0 && !first) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) prev[i] = (src - C / 4)[lane + 32 * i];
+        layer_norm_row(prev);
     }
     layer_norm_row(cur);
-    if (!first) layer_norm_row(prev);   // `first` is the same for the whole warp
     if (ln_out) {
         float4* dst = reinterpret_cast<float4*>(ln_out + row * C);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) dst[lane + 32 * i] = cur[i];
     }
-    const uint16_t* mix[3] = {m0, m1, m2};
-    uint16_t* hi[3] = {hi0, hi1, hi2};
-    uint16_t* lo[3] = {lo0, lo1, lo2};
     float sum[3] = {0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
@@ -225,6 +234,9 @@ ln_mix_split_kernel(const float* __restrict__ x, const uint16_t* __restrict__ lw
             for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
             if (lane == 0 && mix[k]) s1[k * rows + row] = s;
         }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) prev[i] = cur[i];
     }
 }
 
@@ -765,10 +777,23 @@ bool launch_ln_mix_split(ullis_cuda_runtime* rt, const float* x, const LayerNorm
                          uint16_t* hi1, uint16_t* lo1, uint16_t* hi2, uint16_t* lo2, float* s1, size_t rows, size_t time,
                          size_t d, const char* what) {
     if (!rt->tc_fuse_ln || d % 128 != 0 || d > 1024) return false;
-    const unsigned grid = blocks_for(rows, 8);
-#define ULLIS_LN_MIX(V)                                                                                              \
-    ln_mix_split_kernel<V><<<grid, 256, 0, rt->stream>>>(x, ln.weight, ln.bias, ln_out, m0, m1, m2, hi0, lo0, hi1, lo1, \
-                                                         hi2, lo2, s1, rows, time)
+    // rows per warp: several once there are enough rows to fill the device with warps anyway
+    // (measured at 131 072 rows: the Q/K/V form, bound by its 0.8 GB of stores, is best with two; the one-operand
+    // form, bound by instruction issue, with four)
+    const int per_warp = rt->tc_ln_rows > 0 ? rt->tc_ln_rows : rows < 32768 ? 1 : m1 ? 2 : 4;
+    const unsigned grid = blocks_for(rows, 8 * (per_warp == 4 ? 4 : per_warp == 2 ? 2 : 1));
+#define ULLIS_LN_MIX(V)                                                                                                  \
+    do {                                                                                                                 \
+        if (per_warp == 4)                                                                                               \
+            ln_mix_split_kernel<V, 4><<<grid, 256, 0, rt->stream>>>(x, ln.weight, ln.bias, ln_out, m0, m1, m2, hi0, lo0, \
+                                                                    hi1, lo1, hi2, lo2, s1, rows, time);                 \
+        else if (per_warp == 2)                                                                                          \
+            ln_mix_split_kernel<V, 2><<<grid, 256, 0, rt->stream>>>(x, ln.weight, ln.bias, ln_out, m0, m1, m2, hi0, lo0, \
+                                                                    hi1, lo1, hi2, lo2, s1, rows, time);                 \
+        else                                                                                                             \
+            ln_mix_split_kernel<V, 1><<<grid, 256, 0, rt->stream>>>(x, ln.weight, ln.bias, ln_out, m0, m1, m2, hi0, lo0, \
+                                                                    hi1, lo1, hi2, lo2, s1, rows, time);                 \
+    } while (0)
     switch (d / 128) {
         case 1: ULLIS_LN_MIX(1); break;
         case 2: ULLIS_LN_MIX(2); break;

@@ -382,7 +382,7 @@ void ullis_cuda_model::enqueue_layer(const Lane& ln, size_t l, size_t time) {
     end(r);
 
     begin(PH_SAM, r);
-    k::rosa_sam(r, QS, KS, VS, IS, batch * d, time);
+    k::rosa_sam(r, QS, KS, VS, IS, batch * d, time, (int)l);
     save_tap_bits((int)l, ULLIS_CUDA_TAP_IDX, IS, batch, time);
     if (train_tape)
         ULLIS_CUDA_CHECK(cudaMemcpyAsync(tape_idx[l].as<uint32_t>(sw_words), IS, sw_words * 4,

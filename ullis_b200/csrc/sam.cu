@@ -8,6 +8,8 @@
 // Streams with constant k bits are finished by a closed form first; the rest
 // are processed in waves sized to the scratch budget, so any batch works; all
 // waves are enqueued back to back on the runtime stream.
+#include <algorithm>
+
 #include "kernels.hpp"
 #include "sam_coop.cuh"
 #include "sam_core.cuh"
@@ -20,28 +22,90 @@ namespace {
 // Streams that need no automaton are settled here with a few word operations
 // (sam_core.cuh, "constant k", "constant v" and "constant q"): k bits all equal, v bits all 0
 // (idx = 0), v bits all 1 (idx_t = "q_t has occurred among the earlier keys") and q bits all
-// equal (a scan over the key runs).
+// equal (a scan over the key runs, in a kernel of its own).
 // Every other stream id is appended to `list` for the automaton kernels.
+// Eight lanes share a stream: each takes every eighth word of its three bit streams (a group reads 32
+// consecutive bytes per request), the group combines by shuffle, and the closed forms - all of them word by
+// word - are written the same way.  One thread per stream spent its time in 3 x 64 dependent strided loads.
+constexpr int CLASSIFY_LANES = 8;
 __global__ void __launch_bounds__(128)
 rosa_classify_kernel(const uint32_t* __restrict__ q_sw, const uint32_t* __restrict__ k_sw,
                      const uint32_t* __restrict__ v_sw, uint32_t* __restrict__ idx_sw, size_t streams, uint32_t T,
                      size_t wps, uint32_t* __restrict__ list, uint32_t* __restrict__ count,
                      uint32_t* __restrict__ cq_list, uint32_t* __restrict__ cq_count) {
-    const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= streams) return;
-    uint32_t c = 0;
-    if (sam::k_is_constant(k_sw + s * wps, T, &c)) {
-        sam::run_constant_k(q_sw + s * wps, v_sw + s * wps, idx_sw + s * wps, T, c);
-    } else if (sam::k_is_constant(v_sw + s * wps, T, &c)) {   // the same test on the v words
-        if (c == 0) {
-            for (size_t w = 0; w < wps; ++w) idx_sw[s * wps + w] = 0u;
-        } else {
-            sam::run_constant_v_one(q_sw + s * wps, k_sw + s * wps, idx_sw + s * wps, T);
+    constexpr uint32_t G = CLASSIFY_LANES;
+    const size_t s = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    if (s >= streams) return;   // a whole group
+    const uint32_t sub = threadIdx.x % G, lane = threadIdx.x & 31u;
+    const uint32_t group = ((1u << G) - 1u) << (lane & ~(G - 1u));
+    const uint32_t* qw = q_sw + s * wps;
+    const uint32_t* kw = k_sw + s * wps;
+    const uint32_t* vw = v_sw + s * wps;
+    uint32_t* out = idx_sw + s * wps;
+    const uint32_t last = (uint32_t)wps - 1u;
+    const uint32_t tail = (T & 31u) ? ((1u << (T & 31u)) - 1u) : 0xFFFFFFFFu;
+    // AND and OR of the three streams over steps 0 .. T-1 (the bits past T in the last word count for neither)
+    uint32_t all[3] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu}, any[3] = {0u, 0u, 0u};
+    for (uint32_t w = sub; w <= last; w += G) {
+        const uint32_t m = w == last ? tail : 0xFFFFFFFFu;
+        const uint32_t x[3] = {kw[w], vw[w], qw[w]};
+#pragma unroll
+        for (int a = 0; a < 3; ++a) {
+            all[a] &= x[a] | ~m;
+            any[a] |= x[a] & m;
         }
-    } else if (sam::k_is_constant(q_sw + s * wps, T, &c)) {   // constant q: a scan over the runs of c among the keys,
-        cq_list[atomicAdd(cq_count, 1u)] = (uint32_t)s;       // the one closed form with a long loop: its own kernel
-    } else {
-        list[atomicAdd(count, 1u)] = (uint32_t)s;
+    }
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+#pragma unroll
+        for (uint32_t o = 1; o < G; o <<= 1) {
+            all[a] &= __shfl_xor_sync(group, all[a], o);
+            any[a] |= __shfl_xor_sync(group, any[a], o);
+        }
+    }
+    auto constant = [&](int a, uint32_t* c) {
+        if (all[a] == 0xFFFFFFFFu) { *c = 1u; return true; }
+        if (any[a] == 0u) { *c = 0u; return true; }
+        return false;
+    };
+    uint32_t c = 0;
+    if (constant(0, &c)) {
+        // sam::run_constant_k, a word per lane
+        for (uint32_t w = sub; w <= last; w += G) {
+            uint32_t word = (c ? qw[w] : ~qw[w]) & vw[w];
+            if (w == 0) word &= ~1u;
+            if (w == last) word &= tail;
+            out[w] = word;
+        }
+    } else if (constant(1, &c)) {
+        if (c == 0) {
+            for (uint32_t w = sub; w <= last; w += G) out[w] = 0u;
+        } else {
+            // sam::run_constant_v_one: f = the first step whose key differs from k_0 (it exists: k is not constant)
+            const uint32_t c0 = kw[0] & 1u, full = c0 ? 0xFFFFFFFFu : 0u;
+            uint32_t f = T;
+            for (uint32_t w = sub; w <= last && f == T; w += G) {
+                uint32_t diff = kw[w] ^ full;
+                if (w == last) diff &= tail;
+                if (diff) f = w * 32u + (uint32_t)__ffs((int)diff) - 1u;
+            }
+#pragma unroll
+            for (uint32_t o = 1; o < G; o <<= 1) f = min(f, __shfl_xor_sync(group, f, o));
+            for (uint32_t w = sub; w <= last; w += G) {
+                const uint32_t same = c0 ? qw[w] : ~qw[w];   // q_t == k_0
+                uint32_t after;                               // bits of this word at steps > f
+                if (f >= w * 32u + 31u) after = 0u;
+                else if (f < w * 32u) after = 0xFFFFFFFFu;
+                else after = ~((2u << (f - w * 32u)) - 1u);
+                uint32_t word = (same & ~after) | after;
+                if (w == 0) word &= ~1u;
+                if (w == last) word &= tail;
+                out[w] = word;
+            }
+        }
+    } else if (sub == 0) {
+        if (constant(2, &c)) cq_list[atomicAdd(cq_count, 1u)] = (uint32_t)s;   // constant q: a long scan, its own kernel
+        else list[atomicAdd(count, 1u)] = (uint32_t)s;
     }
 }
 
@@ -89,6 +153,13 @@ rosa_sam_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint
     }
 }
 
+// streams of the wave [first, first + wave) that reached the automaton
+__device__ __forceinline__ uint32_t wave_items(uint32_t total, size_t first, size_t wave) {
+    if (first >= total) return 0u;
+    const size_t left = total - first;
+    return (uint32_t)(left < wave ? left : wave);
+}
+
 // Two-kernel form of the O(T log T) schedule for streams whose tour / pass 2
 // working set fits shared memory: pass 1 one thread per stream (below), then
 // one warp per stream for the parallel phases (sam_coop.cuh).
@@ -101,7 +172,9 @@ __global__ void __launch_bounds__(128, 16)
 rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
                   const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ list,
                   const uint32_t* __restrict__ count, size_t first, size_t wave, uint32_t T, size_t wps, int lanes,
-                  uint32_t dense_count, uint32_t sparse_count) {
+                  uint32_t dense_count, uint32_t sparse_count, uint32_t* __restrict__ hint) {
+    // how many streams reached the automaton, for the host's choice of kernel the next time round (see rosa_sam)
+    if (hint && blockIdx.x == 0 && threadIdx.x == 0) *hint = *count;
     // lanes == 0: choose from the number of streams that are left, which only the device knows -
     // many streams: four per warp (fewer issued instructions); fewer: two, then one per warp (more
     // warps to hide the pointer-chase latency).  The grid is sized for one per warp.
@@ -120,6 +193,35 @@ rosa_pass1_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const ui
     else if (WORDS == 2) sam::euler_pass1_words<true, false>(B, q_sw + s * wps, k_sw + s * wps, T);
     else if (WORDS == 1) sam::euler_pass1_words<false>(B, q_sw + s * wps, k_sw + s * wps, T);
     else sam::euler_pass1<uint16_t>(B, q_sw + s * wps, k_sw + s * wps, T, nullptr);
+}
+
+// The same serial pass with the state array of the stream in shared memory, for calls with so few streams that
+// every one of them gets its own one-warp CTA at once (six per SM at T = 2048): lane 0 runs the loop - a state
+// visit is then a shared-memory access instead of a trip through L1, whose lines the step's own stores keep
+// displacing - and the whole warp copies the states out for the tour kernel.  The grid covers every stream of
+// the wave, so any number of them is handled (in rounds of resident CTAs); the host launches this form only
+// when it expects one round.
+__global__ void __launch_bounds__(32)
+rosa_pass1_smem_kernel(uint8_t* __restrict__ scratch, size_t scratch_stride, const uint32_t* __restrict__ q_sw,
+                       const uint32_t* __restrict__ k_sw, const uint32_t* __restrict__ list,
+                       const uint32_t* __restrict__ count, size_t first, size_t wave, uint32_t T, size_t wps,
+                       uint32_t* __restrict__ hint) {
+    extern __shared__ __align__(16) uint8_t pass1_states[];
+    if (hint && blockIdx.x == 0 && threadIdx.x == 0) *hint = *count;
+    const size_t item = blockIdx.x;
+    if (item >= wave_items(*count, first, wave)) return;
+    const size_t s = list[first + item];
+    sam::EulerBlock<uint16_t> B(scratch + item * scratch_stride, T);
+    if (threadIdx.x == 0) {
+        sam::EulerBlock<uint16_t> S = B;
+        S.N = reinterpret_cast<sam::Node<uint16_t>*>(pass1_states);
+        sam::euler_pass1_words<true, true>(S, q_sw + s * wps, k_sw + s * wps, T);
+    }
+    __syncwarp();
+    const uint32_t n = B.meta[0];   // written by lane 0 just now
+    const uint4* src = reinterpret_cast<const uint4*>(pass1_states);
+    uint4* dst = reinterpret_cast<uint4*>(B.N);
+    for (uint32_t i = threadIdx.x; i < (n + 1u) / 2u; i += 32u) dst[i] = src[i];
 }
 
 // Pass 1 in three parts (sam_core.cuh, "pass 1 in three parts"): the extend chain and the query walk as two
@@ -245,7 +347,7 @@ size_t rosa_sam_scratch_bytes_per_stream(int algo, size_t time) {
 }
 
 void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw, const uint32_t* v_sw,
-              uint32_t* idx_sw, size_t streams, size_t time) {
+              uint32_t* idx_sw, size_t streams, size_t time, int site) {
     if (streams == 0 || time == 0) return;
     if (time > 0x3FFFFFFFu) fail(ULLIS_CUDA_ERR_SHAPE, "ROSA time does not fit 32-bit state ids");
     const int algo = rt->sam_algo;
@@ -295,7 +397,8 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
         rt->launched("rosa_list_all");
     } else {
         rt->zero(count, 8);   // both counters
-        rosa_classify_kernel<<<cgrid, 128, 0, rt->stream>>>(q_sw, k_sw, v_sw, idx_sw, streams, (uint32_t)time, wps, list,
+        const unsigned classify_grid = (unsigned)((streams * CLASSIFY_LANES + 127) / 128);
+        rosa_classify_kernel<<<classify_grid, 128, 0, rt->stream>>>(q_sw, k_sw, v_sw, idx_sw, streams, (uint32_t)time, wps, list,
                                                              count, cq_list, cq_count);
         rt->launched("rosa_classify");
         // The constant-q scan is a long serial loop for a few thousand threads; it depends on nothing but the
@@ -366,15 +469,41 @@ void rosa_sam(ullis_cuda_runtime* rt, const uint32_t* q_sw, const uint32_t* k_sw
                 }
                 rt->launched("rosa_walk");
             } else {
+                // Few streams: the state arrays in shared memory, one one-warp CTA per stream, all resident at once.
+                // How many streams reach the automaton is known on the device only, so the choice goes by what the
+                // same call site (`site`: the model's layer) saw the last time its kernel ran - the kernels leave
+                // that number in pinned host memory - and only when it was well inside one round of resident CTAs.
+                // Either kernel is correct for any number of streams; a wrong guess costs time, not results.
+                const size_t state_bytes = (size_t)sam::node_capacity((uint32_t)time) * sizeof(sam::Node<uint16_t>);
+                uint32_t* hint = rt->sam_hint_slot(site);
+                bool in_smem = false;
+                if (defer && rt->sam_reload_w && rt->sam_smem_waves > 0 && hint && wave == streams &&
+                    state_bytes <= 226 * 1024) {
+                    const size_t per_sm = std::min<size_t>(32, (227 * 1024) / (state_bytes + 1024));
+                    const size_t resident = per_sm * (size_t)rt->sm_count * (size_t)rt->sam_smem_waves;
+                    const uint32_t expected = *static_cast<volatile uint32_t*>(hint);
+                    in_smem = rt->sam_smem_waves >= 1000 || (expected != 0xFFFFFFFFu && (size_t)expected + expected / 8 <= resident);
+                }
+                if (in_smem) {
+                    if (!rt->sam_smem_ready) {   // the attribute belongs to the function, not to this runtime: always the same value
+                        ULLIS_CUDA_CHECK(cudaFuncSetAttribute(rosa_pass1_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                              226 * 1024));
+                        rt->sam_smem_ready = true;
+                    }
+                    rosa_pass1_smem_kernel<<<(unsigned)n, 32, state_bytes, rt->stream>>>(scratch, stride, q_sw, k_sw, list, count,
+                                                                                        s0, n, (uint32_t)time, wps, hint);
+                    rt->launched("rosa_pass1_smem");
+                } else {
 #define ULLIS_PASS1(W) \
     rosa_pass1_kernel<W><<<p1_grid, 128, 0, rt->stream>>>(scratch, stride, q_sw, k_sw, list, count, s0, n, (uint32_t)time, \
-                                                          wps, pass1_lanes, dense, sparse)
+                                                          wps, pass1_lanes, dense, sparse, hint)
                 if (!rt->sam_words) ULLIS_PASS1(0);
                 else if (defer && rt->sam_reload_w) ULLIS_PASS1(3);
                 else if (defer) ULLIS_PASS1(2);
                 else ULLIS_PASS1(1);
 #undef ULLIS_PASS1
                 rt->launched("rosa_pass1");
+                }
             }
             // threads per stream: the fewer CTAs shared memory lets an SM hold, the more threads each one gets
             const unsigned coop_per_sm = (unsigned)((227u * 1024u) / (coop.total + 1024u));
