@@ -67,8 +67,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-run", action="store_true",
                     help="short run for a profiler: warm-up count as given, no end-to-end leg, no CPU baseline")
-    ap.add_argument("--workload", choices=["heron", "rosa", "linear", "generate", "train"], default="heron",
-                    help="heron = the benchmark; rosa / linear = single-op loops; generate = incremental decoding")
+    ap.add_argument("--workload", choices=["heron", "rosa", "linear", "generate", "train", "pushers"], default="heron",
+                    help="heron = the benchmark; rosa / linear = single-op loops; generate = incremental decoding; "
+                         "pushers = RosaSam::push for many streams at a late position")
     ap.add_argument("--rosa-variant", choices=["iid", "periodic"], default="iid")
     ap.add_argument("--channels", type=int, default=512)
     ap.add_argument("--linear-shape", default="2048x512x512", help="MxKxN of the packed linear loop")
@@ -631,7 +632,31 @@ def run_op_loop(args, rt, stream, torch):
         model.close()
         rt.close()
         return
-    if args.workload == "rosa":
+    if args.workload == "pushers":
+        # RosaSam::push at op level: batch x channels streams with the benchmark's kind of bias (a flip every ~50
+        # steps on a third of the streams, i.i.d. bits on the rest), pushed up to position T - steps untimed,
+        # then `steps` pushes timed: what a step of incremental decoding pays per layer late in the context.
+        from ullis_b200 import cuda
+        import numpy as np
+        B, T, C = args.batch, args.time or 2048, args.channels
+        n, steps = B * C, min(args.steps, (args.time or 2048) // 2)
+        rng = np.random.default_rng(33)
+        pr = rng.choice([0.02, 0.5, 0.98], (1, n))
+        q, k, v = ((rng.random((T, n)) < pr).astype(np.uint8) for _ in range(3))
+        pushers = cuda.CudaRosaPushers(rt, n, T)
+        pushers.push(q[:T - steps], k[:T - steps], v[:T - steps])
+        rt.kernel_timing(True)
+        t0 = time.perf_counter()
+        pushers.push(q[T - steps:], k[T - steps:], v[T - steps:])
+        dt = time.perf_counter() - t0
+        ms, launches = rt.kernel_times().get("gen_push", (0.0, 0))
+        rt.kernel_timing(False)
+        print(json.dumps({"workload": "pushers", "streams": n, "position": T - steps, "pushes_timed": steps,
+                          "gen_push_ms_per_push": ms / max(launches, 1), "launches": launches,
+                          "stream_pushes_per_s": n * launches / (ms * 1e-3) if ms else None,
+                          "ms_per_call_host_timed": dt * 1e3}))
+        pushers.close()
+    elif args.workload == "rosa":
         B, T, C = args.batch, args.time or 8192, args.channels
         gen = synth.rosa_bits_iid if args.rosa_variant == "iid" else synth.rosa_bits_periodic
         q, k, v = gen(21, B, T, C)

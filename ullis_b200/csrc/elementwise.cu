@@ -222,6 +222,38 @@ __global__ void planes_to_streams_kernel(const uint32_t* __restrict__ plane, uin
     sw[e] = word;
 }
 
+// The same for C % 32 == 0, where a step's channels are whole words: a warp takes one word column (32 channels)
+// of one sequence and eight blocks of 32 steps.  Lane l reads the word of step l; 32 ballots turn the 32 x 32 bit
+// block (lane i keeps the word of channel i), and after eight blocks lane i writes eight consecutive words of its
+// stream.  The warps of a CTA take neighbouring word columns of the same steps, so the 4-byte reads of a row
+// share their sectors in L1.
+constexpr int P2S_BLOCKS = 8;
+__global__ void __launch_bounds__(512)
+planes_to_streams_words_kernel(const uint32_t* __restrict__ plane, uint32_t* __restrict__ sw, size_t T, size_t C,
+                               size_t wps) {
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, cwords = (uint32_t)(C >> 5);
+    const size_t b = blockIdx.z, tb0 = (size_t)blockIdx.x * P2S_BLOCKS;
+    const uint32_t cw = blockIdx.y * (blockDim.x >> 5) + warp;
+    if (cw >= cwords) return;
+    uint32_t mine[P2S_BLOCKS];
+#pragma unroll
+    for (int k = 0; k < P2S_BLOCKS; ++k) {
+        const size_t t = (tb0 + k) * 32 + lane;
+        const uint32_t x = t < T ? plane[(b * T + t) * cwords + cw] : 0u;
+        uint32_t keep = 0;
+#pragma unroll
+        for (uint32_t i = 0; i < 32; ++i) {
+            const uint32_t word = __ballot_sync(0xffffffffu, (x >> i) & 1u);
+            if (lane == i) keep = word;
+        }
+        mine[k] = keep;
+    }
+    uint32_t* dst = sw + (b * C + (size_t)cw * 32 + lane) * wps + tb0;
+#pragma unroll
+    for (int k = 0; k < P2S_BLOCKS; ++k)
+        if (tb0 + k < wps) dst[k] = mine[k];
+}
+
 __global__ void streams_to_planes_kernel(const uint32_t* __restrict__ sw, uint32_t* __restrict__ plane, size_t B,
                                          size_t T, size_t C, size_t wps) {
     size_t wd = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -343,6 +375,13 @@ void planes_to_streams(ullis_cuda_runtime* rt, const uint32_t* plane, uint32_t* 
                        size_t channels) {
     const size_t wps = (time + 31) / 32, n = batch * channels * wps;
     if (!n) return;
+    if (channels % 32 == 0 && batch <= 65535) {
+        const unsigned cwords = (unsigned)(channels / 32), warps = cwords < 16 ? cwords : 16;
+        dim3 grid((unsigned)((wps + P2S_BLOCKS - 1) / P2S_BLOCKS), (cwords + warps - 1) / warps, (unsigned)batch);
+        planes_to_streams_words_kernel<<<grid, warps * 32, 0, rt->stream>>>(plane, sw, time, channels, wps);
+        rt->launched("planes_to_streams");
+        return;
+    }
     planes_to_streams_kernel<<<blocks_for(n, 256), 256, 0, rt->stream>>>(plane, sw, batch, time, channels, wps);
     rt->launched("planes_to_streams");
 }
