@@ -105,11 +105,20 @@ class ClockSampler:
         self.samples = []
         self.proc = None
         self.thread = None
+        self.first_of_region = 0
+
+    def mark_region(self, wait_s: float = 3.0):
+        """The timed region starts now.  nvidia-smi needs a moment before its first line, and the region can be
+        shorter than that: wait (bounded) until the sampler is delivering, and remember where the region begins."""
+        t0 = time.perf_counter()
+        while self.proc is not None and not self.samples and time.perf_counter() - t0 < wait_s:
+            time.sleep(0.01)
+        self.first_of_region = len(self.samples)
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:  # noqa: BLE001
             self.proc = None
@@ -135,7 +144,13 @@ class ClockSampler:
             self.thread.join(timeout=2)
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for s in self.samples:
+        # the samples of the timed region; should it have been too short for one, those of the warm-up steps right
+        # before it (the same kernels on the same device) stand in, and the line says so
+        window = self.samples[self.first_of_region:]
+        during = "timed region"
+        if not window:
+            window, during = self.samples, "warm-up steps before the timed region (it was shorter than a sampling interval)"
+        for s in window:
             try:
                 sm.append(float(s[0]))
                 mx.append(float(s[1]))
@@ -145,7 +160,7 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "sampled_during": during}
 
 
 def dist_env():
@@ -381,11 +396,13 @@ def run_cuda(args):
     # ---------------- device-resident timing (`value`), no per-kernel instrumentation
     model.upload_tokens(tokens, labels, B, time_)
     n_warm = args.warmup if args.profile_run else max(args.warmup, 3)
-    device_steps_ms(model, rt, stream, torch, B, time_, 0, n_warm, reduce_loss)
     sampler = ClockSampler(local)
-    barrier()
     if rank == 0:
-        sampler.start()
+        sampler.start()   # before the warm-up: the sampler is then already running when the timed region starts
+    device_steps_ms(model, rt, stream, torch, B, time_, 0, n_warm, reduce_loss)
+    if rank == 0:
+        sampler.mark_region()
+    barrier()
     launches0 = rt.launch_count
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)

@@ -533,6 +533,17 @@ SAM_HD NodeWords load_words(const Node<uint16_t>* N, uint32_t id) {
     n.y = (uint32_t)(w >> 32);
     return n;
 }
+// The child of a state's first word on bit b, as one byte-permute: the selector is worked out once per step
+// (CHILD_LO / CHILD_HI) and every visit of the step's walks picks with it.
+constexpr uint32_t CHILD_LO = 0x4410u, CHILD_HI = 0x4432u;   // bytes {0, 1} or {2, 3} of the word, zero above
+SAM_HD uint32_t child_selector(uint32_t bit) { return CHILD_LO + bit * (CHILD_HI - CHILD_LO); }
+SAM_HD uint32_t pick_child(uint32_t x, uint32_t selector) {
+#if defined(__CUDA_ARCH__)
+    return __byte_perm(x, 0u, selector);
+#else
+    return selector == CHILD_HI ? x >> 16 : x & 0xFFFFu;
+#endif
+}
 SAM_HD void store_words(Node<uint16_t>* N, uint32_t id, uint32_t x, uint32_t y) {
     *reinterpret_cast<unsigned long long*>(N + id) = (unsigned long long)x | ((unsigned long long)y << 32);
 }
@@ -579,7 +590,7 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
             qword = qw[i >> 5]; kword = kw[i >> 5];
             if (DEFER_CLIMB && i) { B.clone_bits[(i >> 5) - 1u] = cloned; cloned = 0; }
         }
-        const uint32_t qs = (qword & 1u) << 4, kb = kword & 1u, ks = kb << 4;
+        const uint32_t qsel = child_selector(qword & 1u), kb = kword & 1u, ks = kb << 4, ksel = child_selector(kb);
         qword >>= 1; kword >>= 1;
         const uint32_t e0 = gfail;
         // ---- query (src/rosa.rs:104-128)
@@ -588,7 +599,7 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
             uint32_t p = w, x = h, c, v = NIL;
             NodeWords n = nw;
             for (;;) {
-                c = (n.x >> qs) & 0xFFFFu;
+                c = pick_child(n.x, qsel);
                 if (c != NIL) break;
                 const uint32_t ml = n.y >> 16;
                 if (x > ml) x = ml;
@@ -634,7 +645,7 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
             uint32_t p = e0, d = NIL, jfail = 0, pml = 0;
             NodeWords n = ne;                  // e0 == NIL (first step only): the root's words, for the case below
             while (p != NIL) {
-                d = (n.x >> ks) & 0xFFFFu;
+                d = pick_child(n.x, ksel);
                 pml = n.y >> 16;
                 if (d != NIL) break;
                 half[4 * p + kb] = (uint16_t)j;
@@ -666,7 +677,7 @@ SAM_HD uint32_t euler_pass1_words(EulerBlock<uint16_t>& B, const uint32_t* qw, c
                         p = n.y & 0xFFFFu;
                         if (p == NIL) break;
                         n = load_words(N, p);
-                        if (((n.x >> ks) & 0xFFFFu) != d) break;
+                        if (pick_child(n.x, ksel) != d) break;
                     }
                 }
             } else {
