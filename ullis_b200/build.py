@@ -58,12 +58,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
         list(ex.map(run, jobs))
     if force or jobs or _stale(OUT, objs):
-        cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", OUT, *objs,
+        # linked under another name and renamed: a reader (or a copy of the tree) never sees half a library
+        tmp = OUT + ".linking"
+        cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", tmp, *objs,
                "-ldl", "-Xlinker", "--exclude-libs=ALL"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+            if os.path.exists(tmp):
+                os.remove(tmp)
             raise RuntimeError("link failed")
+        os.replace(tmp, OUT)
     return OUT
 
 
