@@ -307,8 +307,8 @@ __device__ __forceinline__ bool exact_mixed_sign(const float* __restrict__ xr, b
 }
 
 // The flagged outputs of one Q/K/V launch as a compact list, so that the exact recomputation runs over the whole
-// device instead of a few busy threads per window.  An entry is the position of the flag bit: (index of the flag
-// word among the 3 * sw words of the launch) * 32 + bit.  A warp takes one (sequence, block of 32 steps, matrix) at
+// device instead of a few busy threads per window.  An entry names the sign bit to redo: (index of its word among
+// the 3 * sw stream-major bit words of the launch) * 32 + bit.  A warp takes one (sequence, block of 32 steps, matrix) at
 // a time, reads that block's flag word of every channel and appends all the bits it found with ONE addition to the
 // list's counter (an addition per word would queue a hundred thousand of them on one address).  Entries of a
 // block lie together in the list and read the same 33 rows of x.  More flags than the list holds (never on
@@ -324,13 +324,14 @@ fix_collect_kernel(const uint32_t* __restrict__ flags, size_t sw, size_t batch, 
     const int rounds = (int)((C + 31) / 32);
     for (size_t bk = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; bk < buckets; bk += warps) {
         const size_t m = bk % 3, word = (bk / 3) % wps, b = bk / (3 * wps);
-        const size_t base = m * sw + b * C * wps + word;     // flag word of channel ch: base + ch * wps
+        const size_t base = m * sw + b * C * wps + word;     // bit word of channel ch: base + ch * wps (stream-major)
+        const uint32_t* fl = flags + m * sw + (b * wps + word) * C;   // its flag word: fl[ch] (channels side by side)
         uint32_t f[FIXQ_MAX_WORDS];
         uint32_t mine = 0;
 #pragma unroll
         for (int r = 0; r < FIXQ_MAX_WORDS; ++r) {
             const size_t ch = (size_t)r * 32 + lane;
-            f[r] = (r < rounds && ch < C) ? flags[base + ch * wps] : 0u;
+            f[r] = (r < rounds && ch < C) ? fl[ch] : 0u;
             mine += __popc(f[r]);
         }
         uint32_t incl = mine;                                  // inclusive prefix sum over the lanes
@@ -366,7 +367,7 @@ fix_collect_kernel(const uint32_t* __restrict__ flags, size_t sw, size_t batch, 
 // single thread can do; everything before it is shared: for 128 input columns at a time the whole warp loads the
 // rows of one entry after the other side by side (512 bytes per request instead of 32 requests into 32 rows),
 // forms the signed terms and leaves them in shared memory, and then lane e adds up the 128 terms of entry e.
-constexpr int FIXQ_WARPS = 2, FIXQ_COLS = 128, FIXQ_PITCH = FIXQ_COLS + 1;
+constexpr int FIXQ_WARPS = 2, FIXQ_COLS = 128, FIXQ_PITCH = FIXQ_COLS + 1, FIXQ_BATCH = 8;
 
 __global__ void __launch_bounds__(FIXQ_WARPS * 32)
 fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, const uint16_t* __restrict__ mk,
@@ -402,14 +403,14 @@ fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, c
         float sum = 0.0f;
         for (size_t i0 = 0; i0 < C; i0 += FIXQ_COLS) {
             const size_t c = i0 + 4 * lane;
-            // four entries at a time: first every load of the four (they do not depend on each other, and the
+            // FIXQ_BATCH entries at a time: first every load of the batch (they do not depend on each other, and the
             // compiler will not move a load above a store to shared memory by itself), then the arithmetic
-            for (int e0 = 0; e0 < 32; e0 += 4) {
-                float4 cur[4], prev[4];
-                uint2 mw[4];
-                uint32_t ww[4], fl[4];
+            for (int e0 = 0; e0 < 32; e0 += FIXQ_BATCH) {
+                float4 cur[FIXQ_BATCH], prev[FIXQ_BATCH];
+                uint2 mw[FIXQ_BATCH];
+                uint32_t ww[FIXQ_BATCH], fl[FIXQ_BATCH];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < FIXQ_BATCH; ++u) {
                     const int e = e0 + u;
                     fl[u] = e_flags[warp][e];
                     const float* row = e_row[warp][e];
@@ -420,7 +421,7 @@ fix_apply_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, c
                     ww[u] = e_w[warp][e][c >> 5] >> (c & 31);
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < FIXQ_BATCH; ++u) {
                     const int e = e0 + u;
                     const bool first_step = (fl[u] & 1u) != 0;
                     const float xs[4] = {cur[u].x, cur[u].y, cur[u].z, cur[u].w};
@@ -527,7 +528,7 @@ sign_fixup_kernel(const float* __restrict__ x, const uint16_t* __restrict__ mq, 
                 const uint32_t which = it / per_matrix, rem = it % per_matrix;
                 const uint32_t* flags = which == 0 ? fq : which == 1 ? fk : fv;
                 const size_t word = w0 + rem % FIX_WIN;
-                if (word < wps) f[k] = flags[(b * C + rem / FIX_WIN) * wps + word];
+                if (word < wps) f[k] = flags[(b * wps + word) * C + rem / FIX_WIN];
             }
         }
 #pragma unroll

@@ -210,8 +210,10 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
             if (m_warp < p.M && n < p.N) {
                 const uint32_t b = m_warp / p.time, word = (m_warp % p.time) >> 5;
                 const size_t o = ((size_t)b * p.N + n) * p.wps + word;
-                static_cast<uint32_t*>(pr.out)[o] = my_bits;
-                static_cast<uint32_t*>(pr.out2)[o] = my_flags;
+                static_cast<uint32_t*>(pr.out)[o] = my_bits;      // stream-major, as the automaton reads them
+                // the flag words of one block of 32 steps lie side by side over the channels: the warp writes 128
+                // consecutive bytes, and the kernel that lists the flags reads them the same way
+                static_cast<uint32_t*>(pr.out2)[((size_t)b * p.wps + word) * p.N + n] = my_flags;
             }
         } else if (EPI == EPI_CE) {
             // whole chunks (the usual case: the vocabulary is a multiple of 32) skip the per-column range test,
