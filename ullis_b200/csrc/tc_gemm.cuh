@@ -114,6 +114,22 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
             // covers eight rows.
             float* out = static_cast<float*>(pr.out);
             const uint32_t m_first = m - lane;   // first row of this warp
+            // EPI_RESIDUAL: the chunk's eight 16-byte pieces of the old rows are asked for before anything else, so
+            // that they travel while the accumulator is converted and transposed (a load placed next to its
+            // store cannot be moved up by the compiler, and each then waited for the one before it)
+            float4 old_rows[2][4];
+            if (EPI == EPI_RESIDUAL) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t gm = m_first + i * 8 + (lane >> 2), col = nc + h * 16 + (lane & 3) * 4;
+                        old_rows[h][i] = (gm < p.M && col < p.N)
+                                             ? *reinterpret_cast<const float4*>(out + (size_t)gm * p.N + col)
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -136,7 +152,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
                     if (gm < p.M && col < p.N) {            // N is a multiple of 4: the whole float4 is in range
                         float4* dst = reinterpret_cast<float4*>(out + (size_t)gm * p.N + col);
                         if (EPI == EPI_RESIDUAL) {
-                            const float4 o = *dst;
+                            const float4 o = old_rows[h][i];
                             v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
                         }
                         *dst = v;
