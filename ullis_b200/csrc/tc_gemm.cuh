@@ -102,10 +102,26 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
     if (EPI == EPI_CE && m + 1 < p.M) target = p.labels[m + 1];
 #pragma unroll 1
     for (uint32_t c = c_begin; c < c_end; ++c) {
+        const uint32_t nc = n0 + c * 32;
+        // EPI_RESIDUAL: the chunk's eight 16-byte pieces of the old rows are asked for before anything else, so
+        // that they travel while the accumulator is read, converted and transposed (a load placed next to its
+        // store cannot be moved up by the compiler, and each then waited for the one before it)
+        float4 old_rows[2][4];
+        if (EPI == EPI_RESIDUAL) {
+            const float* out = static_cast<const float*>(pr.out);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t gm = m_warp + i * 8 + (lane >> 2), col = nc + h * 16 + (lane & 3) * 4;
+                    old_rows[h][i] = (gm < p.M && col < p.N) ? *reinterpret_cast<const float4*>(out + (size_t)gm * p.N + col)
+                                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+        }
         uint32_t r[32];
         ptx::tmem_ld_32x32(taddr + c * 32, r);
         ptx::tmem_ld_wait();
-        const uint32_t nc = n0 + c * 32;
         if (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
             // A thread holds one row of the accumulator, so a direct store touches 32
             // different rows per instruction.  The chunk goes through a small
@@ -114,22 +130,6 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, const GemmProblem&
             // covers eight rows.
             float* out = static_cast<float*>(pr.out);
             const uint32_t m_first = m - lane;   // first row of this warp
-            // EPI_RESIDUAL: the chunk's eight 16-byte pieces of the old rows are asked for before anything else, so
-            // that they travel while the accumulator is converted and transposed (a load placed next to its
-            // store cannot be moved up by the compiler, and each then waited for the one before it)
-            float4 old_rows[2][4];
-            if (EPI == EPI_RESIDUAL) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t gm = m_first + i * 8 + (lane >> 2), col = nc + h * 16 + (lane & 3) * 4;
-                        old_rows[h][i] = (gm < p.M && col < p.N)
-                                             ? *reinterpret_cast<const float4*>(out + (size_t)gm * p.N + col)
-                                             : make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-                }
-            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
 #pragma unroll
