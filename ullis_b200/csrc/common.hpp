@@ -105,6 +105,7 @@ struct ullis_cuda_runtime {
                                         // (off: measured slower than the interleaved single-thread form at every stream count)
     int tc_ln_rows = 0;                 // rows per warp (1, 2, 4) in the LayerNorm + mix + operand kernel; 0 = by the number of rows
     int sam_smem_waves = 1;             // serial pass with the states in shared memory when the streams are expected to fit in this many rounds of resident CTAs; 0 = never, >= 1000 = always
+    bool rowvec_smem_ready = false;     // the staged few-row FP16 matvec has been allowed its dynamic shared memory
     bool sam_smem_ready = false;        // that kernel has been allowed its dynamic shared memory
     // Streams that reached the automaton at each call site's last call, written by the serial-pass kernels straight
     // into pinned host memory (slot 0: callers without a site); 0xFFFFFFFF = no call yet.  Children share the parent's.

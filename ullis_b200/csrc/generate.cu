@@ -67,6 +67,50 @@ __global__ void gen_shift_mix_kernel(const float* __restrict__ x, float* __restr
     prev[e] = xt;
 }
 
+// LayerNorm of one row and the time-shift mixes of that row in one launch (the two kernels above it in a step,
+// for the few rows of a step): the reference's LayerNorm arithmetic (src/model.rs:259-276: the sum, then the sum
+// of the squared deviations, each added one value after the other) is a chain one thread has to run, 2·C
+// dependent additions; it runs from shared memory, and the rest of the CTA does the affine part, the mixes and
+// the new time-shift history.  `ln_out` (nullable) receives the normalised row.
+__global__ void __launch_bounds__(128)
+gen_ln_shift_mix_kernel(const float* __restrict__ x, const uint16_t* __restrict__ lw, const uint16_t* __restrict__ lb,
+                        float* __restrict__ ln_out, float* __restrict__ prev, int has_prev,
+                        const uint16_t* __restrict__ m0, const uint16_t* __restrict__ m1,
+                        const uint16_t* __restrict__ m2, float* __restrict__ o0, float* __restrict__ o1,
+                        float* __restrict__ o2, size_t C) {
+    extern __shared__ float gen_row[];
+    __shared__ float s_mean, s_inv;
+    const size_t r = blockIdx.x;
+    for (size_t c = threadIdx.x; c < C; c += blockDim.x) gen_row[c] = x[r * C + c];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float acc = 0.0f;
+        for (size_t c = 0; c < C; ++c) acc = __fadd_rn(acc, gen_row[c]);
+        const float mean = __fdiv_rn(acc, (float)C);
+        acc = 0.0f;
+        for (size_t c = 0; c < C; ++c) {
+            const float dlt = __fsub_rn(gen_row[c], mean);
+            acc = __fadd_rn(acc, __fmul_rn(dlt, dlt));
+        }
+        s_mean = mean;
+        s_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(acc, (float)C), 1e-5f)));
+    }
+    __syncthreads();
+    const float mean = s_mean, inv = s_inv;
+    for (size_t c = threadIdx.x; c < C; c += blockDim.x) {
+        const size_t e = r * C + c;
+        const float n = __fmul_rn(__fsub_rn(gen_row[c], mean), inv);
+        const float xt = __fadd_rn(__fmul_rn(n, h2f(lw[c])), h2f(lb[c]));
+        if (ln_out) ln_out[e] = xt;
+        // time_shift_one + mixes (src/model.rs:214-228, 1331-1340, 1008-1012), as gen_shift_mix_kernel
+        const float xx = has_prev ? __fsub_rn(prev[e], xt) : -xt;
+        o0[e] = __fadd_rn(xt, __fmul_rn(xx, h2f(m0[c])));
+        if (o1) o1[e] = __fadd_rn(xt, __fmul_rn(xx, h2f(m1[c])));
+        if (o2) o2[e] = __fadd_rn(xt, __fmul_rn(xx, h2f(m2[c])));
+        prev[e] = xt;
+    }
+}
+
 // one RosaSam::push per (sequence, channel) of one layer and y = (2*idx - 1)*e (src/model.rs:1344-1351).
 // One warp per stream: lane 0 runs the query and the extend, all lanes the stamping of the suffix-link chain
 // (sam::gen_push), which is what a late position costs.
@@ -120,6 +164,7 @@ ullis_cuda_generate_state::ullis_cuda_generate_state(ullis_cuda_model* m, size_t
     streams = m->layers * per_layer;
     if (streams > SIZE_MAX / stride) fail(ULLIS_CUDA_ERR_SHAPE, "generate state shape overflow");
     m->rt->bind();
+    k::rowvec_prepare(m->rt);   // before any step is recorded into a graph
     blocks.ensure(streams * stride);
     walkers.ensure(streams * sizeof(sam::WalkerState));
     vhist.ensure(streams * wps * 4);
@@ -232,6 +277,7 @@ void ullis_cuda_generate_state::enqueue(int has_prev) {
     rt->clear_status();
     rt->h2d(IDS, h_tokens, rows * 4);
     k::embed(rt, IDS, m->embedding, X, rows, d, m->vocab);
+    const bool fused_ln = d * 4 <= 48 * 1024 && !getenv("ULLIS_CUDA_GEN_UNFUSED");   // a row in shared memory
     for (size_t l = 0; l < m->layers; ++l) {
         const LayerWeights& L = m->blocks[l];
         float* rosa_prev = static_cast<float*>(prev.get()) + (l * 2) * n;
@@ -242,13 +288,28 @@ void ullis_cuda_generate_state::enqueue(int has_prev) {
             ULLIS_CUDA_CHECK(cudaMemcpyAsync(X, A, n * 4, cudaMemcpyDeviceToDevice, rt->stream));
         }
         // ROSA (src/model.rs:1320-1352)
-        k::layer_norm(rt, X, L.ln3.weight, L.ln3.bias, A, rows, d, true);
-        gen_shift_mix_kernel<<<blocks_for(n, 256), 256, 0, rt->stream>>>(A, rosa_prev, has_prev, L.x_q, L.x_k, L.x_v, Bq, Bk,
-                                                                       Bv, n, d);
-        rt->launched("gen_shift_mix");
-        k::binary_linear_exact(rt, Bq, L.q.bits, L.q.scale, L.q.bias, W, rows, d, d, false);
-        k::binary_linear_exact(rt, Bk, L.k.bits, L.k.scale, L.k.bias, W + n, rows, d, d, false);
-        k::binary_linear_exact(rt, Bv, L.v.bits, L.v.scale, L.v.bias, W + 2 * n, rows, d, d, false);
+        if (fused_ln) {
+            gen_ln_shift_mix_kernel<<<(unsigned)rows, 128, d * 4, rt->stream>>>(X, L.ln3.weight, L.ln3.bias, nullptr, rosa_prev,
+                                                                                has_prev, L.x_q, L.x_k, L.x_v, Bq, Bk, Bv, d);
+            rt->launched("gen_ln_shift_mix");
+        } else {
+            k::layer_norm(rt, X, L.ln3.weight, L.ln3.bias, A, rows, d, true);
+            gen_shift_mix_kernel<<<blocks_for(n, 256), 256, 0, rt->stream>>>(A, rosa_prev, has_prev, L.x_q, L.x_k, L.x_v, Bq,
+                                                                           Bk, Bv, n, d);
+            rt->launched("gen_shift_mix");
+        }
+        {   // Q, K and V in one launch when the shape allows
+            const float* xs[3] = {Bq, Bk, Bv};
+            const uint32_t* bs[3] = {L.q.bits, L.k.bits, L.v.bits};
+            const uint16_t* ss[3] = {L.q.scale, L.k.scale, L.v.scale};
+            const uint16_t* bi[3] = {L.q.bias, L.k.bias, L.v.bias};
+            float* ys[3] = {W, W + n, W + 2 * n};
+            if (!fused_ln || !k::binary_rowvec_multi(rt, 3, xs, bs, ss, bi, ys, rows, d, d, false)) {
+                k::binary_linear_exact(rt, Bq, L.q.bits, L.q.scale, L.q.bias, W, rows, d, d, false);
+                k::binary_linear_exact(rt, Bk, L.k.bits, L.k.scale, L.k.bias, W + n, rows, d, d, false);
+                k::binary_linear_exact(rt, Bv, L.v.bits, L.v.scale, L.v.bias, W + 2 * n, rows, d, d, false);
+            }
+        }
         {
             auto* ws = static_cast<sam::WalkerState*>(walkers.get()) + s0;
             uint8_t* blk = static_cast<uint8_t*>(blocks.get()) + s0 * stride;
@@ -263,12 +324,28 @@ void ullis_cuda_generate_state::enqueue(int has_prev) {
         }
         k::binary_linear_exact(rt, A, L.o.bits, L.o.scale, L.o.bias, X, rows, d, d, true);  // h += rosa out
         // CMix (src/model.rs:1003-1016)
-        k::layer_norm(rt, X, L.ln2.weight, L.ln2.bias, A, rows, d, true);
-        gen_shift_mix_kernel<<<blocks_for(n, 256), 256, 0, rt->stream>>>(A, cmix_prev, has_prev, L.ffn_x_k, nullptr, nullptr, Bq,
-                                                                       nullptr, nullptr, n, d);
-        rt->launched("gen_shift_mix");
-        k::binary_linear_exact(rt, Bq, L.key.bits, L.key.scale, nullptr, W, rows, d, ffn, false);
-        k::relu2(rt, W, W, rows * ffn);
+        if (fused_ln) {
+            gen_ln_shift_mix_kernel<<<(unsigned)rows, 128, d * 4, rt->stream>>>(X, L.ln2.weight, L.ln2.bias, nullptr, cmix_prev,
+                                                                                has_prev, L.ffn_x_k, nullptr, nullptr, Bq, nullptr,
+                                                                                nullptr, d);
+            rt->launched("gen_ln_shift_mix");
+        } else {
+            k::layer_norm(rt, X, L.ln2.weight, L.ln2.bias, A, rows, d, true);
+            gen_shift_mix_kernel<<<blocks_for(n, 256), 256, 0, rt->stream>>>(A, cmix_prev, has_prev, L.ffn_x_k, nullptr, nullptr,
+                                                                           Bq, nullptr, nullptr, n, d);
+            rt->launched("gen_shift_mix");
+        }
+        {   // key and relu^2 in one launch when the shape allows
+            const float* xs[1] = {Bq};
+            const uint32_t* bs[1] = {L.key.bits};
+            const uint16_t* ss[1] = {L.key.scale};
+            const uint16_t* bi[1] = {nullptr};
+            float* ys[1] = {W};
+            if (!fused_ln || !k::binary_rowvec_multi(rt, 1, xs, bs, ss, bi, ys, rows, d, ffn, true)) {
+                k::binary_linear_exact(rt, Bq, L.key.bits, L.key.scale, nullptr, W, rows, d, ffn, false);
+                k::relu2(rt, W, W, rows * ffn);
+            }
+        }
         k::fp16_linear_exact(rt, W, L.value, X, rows, ffn, d, true);  // h += cmix out
     }
     // src/model.rs:2750-2752

@@ -40,6 +40,15 @@ void binary_linear_exact(ullis_cuda_runtime* rt, const float* x, const uint32_t*
                          bool accumulate);
 void fp16_linear_exact(ullis_cuda_runtime* rt, const float* x, const uint16_t* w, float* y, size_t rows,
                        size_t in_features, size_t out_features, bool accumulate);
+// `count` (1 to 3) packed matvecs of one shape in one launch, for few rows (a generation step): y[z] = x[z] W[z]^T
+// with W[z]'s scale and bias (bias[z] nullable), optionally followed by relu^2; the sums of binary_linear_exact.
+// Returns false (nothing launched) when the shape is not one it takes.
+bool binary_rowvec_multi(ullis_cuda_runtime* rt, int count, const float* const* x, const uint32_t* const* bits,
+                         const uint16_t* const* scale, const uint16_t* const* bias, float* const* y, size_t rows,
+                         size_t in_features, size_t out_features, bool relu2);
+// One-time set-up of the few-row kernels (shared-memory allowance); the linears do it on first use, a caller that
+// is about to record them into a CUDA graph does it beforehand.
+void rowvec_prepare(ullis_cuda_runtime* rt);
 
 // ---- sam.cu
 // idx_sw <- suffix-automaton match of each stream; uses rt->sam_scratch.  `site` names the caller's call site (a
