@@ -86,6 +86,28 @@ def test_late_context_of_the_benchmark_model(cuda_rt):
         cuda_rt.set_mode(cuda.MODE_FAST)
 
 
+def test_fused_and_unfused_steps_give_the_same_logits(cuda_rt, oracle, monkeypatch):
+    """A step runs LayerNorm + time-shift mixes as one kernel, Q / K / V as one launch and relu^2 on the key matvec;
+    with ULLIS_CUDA_GEN_UNFUSED each is a kernel of its own, as the one-shot exact path has them.  Same sums either
+    way: the logits must be identical bit for bit (and equal to the oracle's one-shot rows)."""
+    data = synth.heron_checkpoint("small", batch_size=2)
+    m_or = oracle.HeronOracle(data)
+    B, T = 2, 24
+    tokens = synth.zipf_tokens(29, B * T, m_or.vocab).reshape(B, T)
+    one_shot = m_or.logits(tokens.reshape(-1), B, T).reshape(B, T, m_or.vocab)
+    m = cuda.CudaHeron(cuda_rt, data)
+    fused = m.generate_state(B)
+    got = [m.generate_step(fused, tokens[:, t]) for t in range(T)]
+    fused.close()
+    monkeypatch.setenv("ULLIS_CUDA_GEN_UNFUSED", "1")
+    plain = m.generate_state(B)
+    for t in range(T):
+        a = m.generate_step(plain, tokens[:, t])
+        assert np.array_equal(a, got[t]) and np.array_equal(a, one_shot[:, t, :]), t
+    plain.close()
+    m.close()
+
+
 def test_generate_error_cases_leave_the_state_unchanged(cuda_rt, oracle):  # src/model.rs:2718-2723, 5044-5056
     data = synth.heron_checkpoint("tiny", batch_size=2, context_len=6)
     ref = oracle.HeronOracle(data)
