@@ -78,17 +78,42 @@ gen_ln_shift_mix_kernel(const float* __restrict__ x, const uint16_t* __restrict_
                         const uint16_t* __restrict__ m0, const uint16_t* __restrict__ m1,
                         const uint16_t* __restrict__ m2, float* __restrict__ o0, float* __restrict__ o1,
                         float* __restrict__ o2, size_t C) {
-    extern __shared__ float gen_row[];
+    extern __shared__ __align__(16) float gen_row[];
     __shared__ float s_mean, s_inv;
     const size_t r = blockIdx.x;
     for (size_t c = threadIdx.x; c < C; c += blockDim.x) gen_row[c] = x[r * C + c];
     __syncthreads();
     if (threadIdx.x == 0) {
+        // the additions are one chain; the loads are not: sixteen values are fetched (four 16-byte loads) before
+        // they are added, so that the chain waits for arithmetic only
         float acc = 0.0f;
-        for (size_t c = 0; c < C; ++c) acc = __fadd_rn(acc, gen_row[c]);
+        size_t c = 0;
+        for (; c + 16 <= C; c += 16) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const float4*>(gen_row + c + 4 * u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                acc = __fadd_rn(acc, v[u].x); acc = __fadd_rn(acc, v[u].y);
+                acc = __fadd_rn(acc, v[u].z); acc = __fadd_rn(acc, v[u].w);
+            }
+        }
+        for (; c < C; ++c) acc = __fadd_rn(acc, gen_row[c]);
         const float mean = __fdiv_rn(acc, (float)C);
         acc = 0.0f;
-        for (size_t c = 0; c < C; ++c) {
+        for (c = 0; c + 16 <= C; c += 16) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const float4*>(gen_row + c + 4 * u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float d0 = __fsub_rn(v[u].x, mean), d1 = __fsub_rn(v[u].y, mean);
+                const float d2 = __fsub_rn(v[u].z, mean), d3 = __fsub_rn(v[u].w, mean);
+                acc = __fadd_rn(acc, __fmul_rn(d0, d0)); acc = __fadd_rn(acc, __fmul_rn(d1, d1));
+                acc = __fadd_rn(acc, __fmul_rn(d2, d2)); acc = __fadd_rn(acc, __fmul_rn(d3, d3));
+            }
+        }
+        for (; c < C; ++c) {
             const float dlt = __fsub_rn(gen_row[c], mean);
             acc = __fadd_rn(acc, __fmul_rn(dlt, dlt));
         }

@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(128)
 rowvec_exact_kernel(const float* __restrict__ x, const uint32_t* __restrict__ bits,
                     const uint16_t* __restrict__ wdense, const uint16_t* __restrict__ scale,
                     const uint16_t* __restrict__ bias, float* __restrict__ y, size_t K, size_t N, int accumulate) {
-    extern __shared__ float xrow[];
+    extern __shared__ __align__(16) float xrow[];
     const size_t r = blockIdx.y, o = (size_t)blockIdx.x * 128 + threadIdx.x;
     for (size_t i = threadIdx.x; i < K; i += 128) xrow[i] = x[r * K + i];
     __syncthreads();
@@ -114,10 +114,20 @@ rowvec_exact_kernel(const float* __restrict__ x, const uint32_t* __restrict__ bi
     if (PACKED) {
         if (K % 32 == 0) {
             const uint32_t* wrow = bits + (o * K >> 5);
+            uint32_t w = wrow[0];
             for (size_t i0 = 0; i0 < K; i0 += 32) {
-                const uint32_t w = wrow[i0 >> 5];
+                const uint32_t w_next = i0 + 32 < K ? wrow[(i0 >> 5) + 1] : 0u;   // on its way while this word's terms are added
+                float4 xv[8];   // the 32 inputs of the word: eight 16-byte loads ahead of the chain of additions
 #pragma unroll
-                for (int b = 0; b < 32; ++b) sum = __fmaf_rn((w >> b) & 1u ? 1.0f : -1.0f, xrow[i0 + b], sum);
+                for (int u = 0; u < 8; ++u) xv[u] = *reinterpret_cast<const float4*>(xrow + i0 + 4 * u);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    sum = __fmaf_rn((w >> (4 * u + 0)) & 1u ? 1.0f : -1.0f, xv[u].x, sum);
+                    sum = __fmaf_rn((w >> (4 * u + 1)) & 1u ? 1.0f : -1.0f, xv[u].y, sum);
+                    sum = __fmaf_rn((w >> (4 * u + 2)) & 1u ? 1.0f : -1.0f, xv[u].z, sum);
+                    sum = __fmaf_rn((w >> (4 * u + 3)) & 1u ? 1.0f : -1.0f, xv[u].w, sum);
+                }
+                w = w_next;
             }
         } else {
             for (size_t i = 0; i < K; ++i) {
@@ -161,7 +171,7 @@ struct RowvecSet {
 };
 __global__ void __launch_bounds__(128)
 rowvec_packed_multi_kernel(RowvecSet set, size_t K, size_t N, int relu2) {
-    extern __shared__ float xrow[];
+    extern __shared__ __align__(16) float xrow[];
     const int z = blockIdx.z;
     const size_t r = blockIdx.y, o = (size_t)blockIdx.x * 128 + threadIdx.x;
     // picked with selects: indexing the parameter arrays with z would copy them to local memory
@@ -176,10 +186,20 @@ rowvec_packed_multi_kernel(RowvecSet set, size_t K, size_t N, int relu2) {
     if (o >= N) return;
     float sum = 0.0f;
     const uint32_t* wrow = bits + (o * K >> 5);
+    uint32_t w = wrow[0];
     for (size_t i0 = 0; i0 < K; i0 += 32) {
-        const uint32_t w = wrow[i0 >> 5];
+        const uint32_t w_next = i0 + 32 < K ? wrow[(i0 >> 5) + 1] : 0u;   // on its way while this word's terms are added
+        float4 xv[8];   // the 32 inputs of the word: eight 16-byte loads ahead of the chain of additions
 #pragma unroll
-        for (int b = 0; b < 32; ++b) sum = __fmaf_rn((w >> b) & 1u ? 1.0f : -1.0f, xrow[i0 + b], sum);
+        for (int u = 0; u < 8; ++u) xv[u] = *reinterpret_cast<const float4*>(xrow + i0 + 4 * u);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            sum = __fmaf_rn((w >> (4 * u + 0)) & 1u ? 1.0f : -1.0f, xv[u].x, sum);
+            sum = __fmaf_rn((w >> (4 * u + 1)) & 1u ? 1.0f : -1.0f, xv[u].y, sum);
+            sum = __fmaf_rn((w >> (4 * u + 2)) & 1u ? 1.0f : -1.0f, xv[u].z, sum);
+            sum = __fmaf_rn((w >> (4 * u + 3)) & 1u ? 1.0f : -1.0f, xv[u].w, sum);
+        }
+        w = w_next;
     }
     const float bv = bias ? h2f(bias[o]) : 0.0f;
     sum = __fadd_rn(bv, __fmul_rn(h2f(scale[o]), sum));
@@ -241,10 +261,12 @@ rowvec_fp16_staged_kernel(const float* __restrict__ x, const uint16_t* __restric
         for (int g = 0; g < RVS_KC / 8; ++g) {
             const uint4 w8 = *reinterpret_cast<const uint4*>(row + ((g ^ (t & 7)) << 4));
             const uint32_t ww[4] = {w8.x, w8.y, w8.z, w8.w};
+            const float4 xa = *reinterpret_cast<const float4*>(xs + g * 8), xb = *reinterpret_cast<const float4*>(xs + g * 8 + 4);
+            const float xe[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
 #pragma unroll
             for (int e = 0; e < 8; ++e) {   // i ascending, as the reference adds (src/model.rs:419-436)
                 const uint16_t hb = (uint16_t)(e & 1 ? ww[e >> 1] >> 16 : ww[e >> 1] & 0xFFFFu);
-                sum = __fadd_rn(sum, __fmul_rn(h2f(hb), xs[g * 8 + e]));
+                sum = __fadd_rn(sum, __fmul_rn(h2f(hb), xe[e]));
             }
         }
         __syncthreads();   // the piece's buffer is refilled RVS_STAGES - 1 rounds later at the earliest: next round
